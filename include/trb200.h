@@ -1,0 +1,265 @@
+/*
+ * trb200.h -- C ABI of the B200 (sm_100a) kernels for the Renaissance training
+ * backward hot path: Conv+BN+ReLU block backward, fused softmax-cross-entropy,
+ * and the small kernels either side of the gradient all-reduce.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless the comment says "host".
+ *   - Activations are NHWC, filters are KRSC, both compact (the reference's
+ *     DTensor strides for every shape whose channel count is a multiple of 8,
+ *     include/renaissance/tensor/distributed_tensor.h:173-207).  Half tensors
+ *     are IEEE binary16.
+ *   - `stream` / `event` arguments are a cudaStream_t / cudaEvent_t passed as
+ *     void*; NULL stream = the legacy default stream.
+ *   - Functions only enqueue work.  They never synchronise, never allocate and
+ *     never free: scratch memory is a caller-owned workspace whose size the
+ *     matching *_workspace_bytes() function returns (the reference's
+ *     DeviceContext::ensure_workspace_grow contract,
+ *     src/backend/device_context.cpp:379-428), so they can be called inside
+ *     stream capture.
+ *   - Return value: 0 on success, a negative trb200_status otherwise; the text
+ *     of the last failure on the calling thread is trb200_last_error().  The C
+ *     side never throws.  The reference's convention is exceptions
+ *     (TR_DEVICE_ERROR, include/renaissance/core/tr_exception.h:271); the
+ *     plugin adapter turns a non-zero return into one.
+ */
+#ifndef TRB200_H_
+#define TRB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum trb200_status {
+    TRB200_OK = 0,
+    TRB200_ERR_INVALID_ARGUMENT = -1,  /* null pointer, bad size, misaligned pointer */
+    TRB200_ERR_UNSUPPORTED = -2,       /* shape outside what the kernels cover */
+    TRB200_ERR_WORKSPACE = -3,         /* workspace missing or too small */
+    TRB200_ERR_CUDA = -4,              /* a CUDA runtime / driver call failed */
+    TRB200_ERR_DEVICE_TIMEOUT = -5     /* a bounded device-side wait gave up */
+} trb200_status;
+
+/* Text of the last error on this thread ("" if none).  Host pointer, valid until
+ * the next failing call on the same thread. */
+const char* trb200_last_error(void);
+
+/* Library version, major*10000 + minor*100 + patch. */
+int trb200_version(void);
+
+/* Compute capability (major*10 + minor) of the current device, or a negative
+ * trb200_status.  The tensor-core kernels need 100. */
+int trb200_device_arch(void);
+
+/* ------------------------------------------------------------------------- */
+/* Convolution geometry shared by the conv entry points.                      */
+/* ------------------------------------------------------------------------- */
+typedef struct trb200_conv_desc {
+    int32_t n, h, w, c;          /* input activation X  [n,h,w,c]            */
+    int32_t k, r, s;             /* filters W           [k,r,s,c]            */
+    int32_t pad_h, pad_w;
+    int32_t stride_h, stride_w;
+} trb200_conv_desc;              /* output Y / dY is [n,oh,ow,k], oh = (h+2*pad_h-r)/stride_h+1 */
+
+/* ------------------------------------------------------------------------- */
+/* BN + ReLU backward of the fused block.                                     */
+/* Replaces the cuDNN-FE graph MUL(dY, mask) -> batchnorm_backward built by   */
+/* build_cbr_bn_bwd_fused_graph, src/backend/ops/dtensor/cbr_op.cpp:1259-1353 */
+/* (executed at cbr_op.cpp:1371-1429).                                        */
+/*   dy_m   = dY * mask                      (mask: 1 bit / element, LSB first, */
+/*                                            flat NHWC index)                */
+/*   dbeta  = sum_m dy_m        dgamma = sum_m dy_m * (x - mean) * inv_std    */
+/*   dconv  = gamma*inv_std*(dy_m - dbeta/m - xhat*dgamma/m)   -> half        */
+/* m = n*h*w rows, c channels, c % 8 == 0.  dconv may be NULL (sums only) and */
+/* may alias neither input.  Sums are fixed-order (bitwise reproducible).     */
+/* ------------------------------------------------------------------------- */
+size_t trb200_bnrelu_bwd_workspace_bytes(int64_t m, int32_t c);
+int trb200_bnrelu_bwd(const void* dy, const void* mask_bits, const void* x,
+                      const float* gamma, const float* saved_mean, const float* saved_inv_std,
+                      void* dconv, float* dgamma, float* dbeta,
+                      int64_t m, int32_t c,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Convolution weight gradient, dW[k,r,s,c] = sum dY[n,oh,ow,k] * X[...]      */
+/* half in, float accumulate, half out, fixed-order split reduction.          */
+/* Replaces build_cbr_conv_amp_wgrad_graph + execute,                         */
+/* src/backend/ops/dtensor/cbr_op.cpp:763-840, 1431-1468.                     */
+/* ------------------------------------------------------------------------- */
+size_t trb200_conv_wgrad_workspace_bytes(const trb200_conv_desc* d);
+int trb200_conv_wgrad(const trb200_conv_desc* d, const void* dy, const void* x, void* dw,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Convolution data gradient, dX[n,ih,iw,c] = sum dY[...] * W[k,r,s,c]        */
+/* half in, float accumulate, half out.  dx must not alias dy or w (it may be */
+/* the buffer that held X: the reference writes dX in place over X).          */
+/* Replaces build_cbr_conv_amp_dgrad_graph + execute,                         */
+/* src/backend/ops/dtensor/cbr_op.cpp:842-917, 1470-1508.                     */
+/* ------------------------------------------------------------------------- */
+size_t trb200_conv_dgrad_workspace_bytes(const trb200_conv_desc* d);
+int trb200_conv_dgrad(const trb200_conv_desc* d, const void* dy, const void* w, void* dx,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* Forward convolution Y = X (*) W, half in, float accumulate, half out, on the
+ * same tensor-core kernel as dgrad (3x3, stride 1, pad 1, c % 64 == 0, k = 64,
+ * 128 or a multiple of 256; anything else returns TRB200_ERR_UNSUPPORTED).
+ * Counterpart of the conv_fprop part of the reference's forward block,
+ * src/backend/ops/dtensor/cbr_op.cpp:622-718 (statistics not included). */
+int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const void* w, void* y, void* stream);
+
+/* Diagnostics.  backend 0 = automatic (tensor cores where the shape allows),
+ * 1 = direct CUDA-core kernels only (used by tests to cross-check the two). */
+int trb200_set_conv_backend(int backend);
+
+/* Synchronous: reads the device-side status word.  TRB200_OK, or
+ * TRB200_ERR_DEVICE_TIMEOUT if a kernel's bounded wait gave up since the last
+ * call (the word is cleared).  Call it after synchronising, never in capture. */
+int trb200_device_status(void);
+
+/* Which implementation the two conv entry points would pick for this shape:
+ * 1 = tcgen05/TMEM implicit GEMM fed by TMA, 0 = direct CUDA-core kernel.
+ * `which`: 0 = wgrad, 1 = dgrad, 2 = fprop. */
+int trb200_conv_uses_tensor_cores(const trb200_conv_desc* d, int which);
+
+/* ------------------------------------------------------------------------- */
+/* Whole block backward = launch_cbr_amp_bwd_cuda / _first_layer_cuda,        */
+/* src/backend/ops/dtensor/cbr_op.cpp:1359-1522 and 1528-1651: BN+ReLU        */
+/* backward on stream_bn, then wgrad on stream_wgrad, then dgrad on           */
+/* stream_dgrad (after wgrad: dX overwrites X), then a join back onto         */
+/* stream_bn.  The three events are recorded after the respective stage (the  */
+/* caller's MultiStreamCaptureState::last_done_event of each stream); on      */
+/* return `ev_bn` has been re-recorded on stream_bn after the join.  All      */
+/* three streams may be the same stream and the events may be NULL then.      */
+/* dx == NULL selects the first-layer variant (no dgrad).                     */
+/* ------------------------------------------------------------------------- */
+typedef struct trb200_cbr_bwd_args {
+    trb200_conv_desc conv;
+    const void* dy;            /* in  [0] upstream gradient, half [n,oh,ow,k]        */
+    const void* w;             /* in  [1] filters, half KRSC                        */
+    const float* gamma;        /* in  [2] BN weight [k]                             */
+    const float* saved_mean;   /* in  [3]                                           */
+    const float* saved_inv_std;/* in  [4]                                           */
+    const void* mask_bits;     /* in  [5] ReLU mask, bit-packed                     */
+    const void* x;             /* in  [6] block input, half [n,h,w,c]               */
+    void* dx;                  /* out [0] = buffer of x (in place) or NULL          */
+    void* dw;                  /* out [1] half KRSC                                 */
+    float* dgamma;             /* out [2]                                           */
+    float* dbeta;              /* out [3]                                           */
+    const void* conv_out;      /* out [4] conv output saved by the forward (read)   */
+    void* bn_scratch;          /* out [5] activation-sized scratch: receives dconv  */
+    void* workspace;
+    size_t workspace_bytes;
+    void* stream_bn;           /* COMP_1 */
+    void* stream_wgrad;        /* COMP_3 */
+    void* stream_dgrad;        /* COMP_2 */
+    void* ev_bn;
+    void* ev_wgrad;
+    void* ev_dgrad;
+} trb200_cbr_bwd_args;
+
+size_t trb200_cbr_bwd_workspace_bytes(const trb200_conv_desc* d, int first_layer);
+int trb200_cbr_bwd(const trb200_cbr_bwd_args* a);
+
+/* ------------------------------------------------------------------------- */
+/* Softmax + cross entropy with label smoothing, AMP variant.                 */
+/* `scaling`, `label_smoothing`, `inv_scaling` are device scalars as in the   */
+/* reference (DTensor scalars).  Row strides are in elements.                 */
+/* ------------------------------------------------------------------------- */
+
+/* Forward node = softmax_ce_fwd_kernel<true> + softmax_ce_reduce_kernel,
+ * src/backend/ops/dtensor/softmax_ce_op.cu:63-177, 372-429, 504-532 (launcher
+ * softmax_ce_op.cpp:409-455): probs (fp32), loss_partial[b] (already times
+ * 1/batch), *loss = fixed-order sum of the partials (not multiplied by the loss
+ * scale), *inv_scaling = 1/batch.  probs may be NULL. */
+int trb200_softmax_ce_fwd(const void* logits, int64_t logits_stride, const int32_t* labels,
+                          const float* label_smoothing,
+                          float* probs, int64_t probs_stride,
+                          float* loss_partial, float* loss, float* inv_scaling,
+                          int32_t batch, int32_t classes, void* stream);
+
+/* Backward node = softmax_ce_bwd_kernel<true>, softmax_ce_op.cu:438-468, 613-627
+ * (launcher softmax_ce_op.cpp:591-627):
+ * d_logits = half((p - ls/C - [c==y](1-ls)) * scaling * inv_scaling). */
+int trb200_softmax_ce_bwd(const float* probs, int64_t probs_stride, const int32_t* labels,
+                          const float* scaling, const float* inv_scaling,
+                          const float* label_smoothing,
+                          void* dlogits, int64_t dlogits_stride,
+                          int32_t batch, int32_t classes, void* stream);
+
+/* Both nodes in one pass over the logits: reads each logit once, writes
+ * d_logits (and probs if not NULL), loss partials, loss and inv_scaling.  The
+ * arithmetic is that of the two nodes above. */
+int trb200_softmax_ce_fused(const void* logits, int64_t logits_stride, const int32_t* labels,
+                            const float* scaling, const float* label_smoothing,
+                            float* probs, int64_t probs_stride,
+                            void* dlogits, int64_t dlogits_stride,
+                            float* loss_partial, float* loss, float* inv_scaling,
+                            int32_t batch, int32_t classes, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Kernels either side of the gradient all-reduce (the collective itself is   */
+/* NCCL, issued by the host side).                                            */
+/* ------------------------------------------------------------------------- */
+
+/* data[i] *= factor, tr_scale_fp32_kernel, src/backend/ops/range/infra_kernels.cu:82-96
+ * (the 1/world step of launch_allreduce_cuda_impl, allreduce_op.cpp:87-95). */
+int trb200_scale_f32(float* data, int64_t n, float factor, void* stream);
+
+/* dst[i] = float(src[i]) * factor: RANGE_CAST_FP16_TO_FP32
+ * (src/backend/ops/range/cast_op.cu:18-37) with the all-reduce's mean folded in. */
+int trb200_cast_f16_to_f32(const void* src, float* dst, int64_t n, float factor, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Forward side of the block that produces the backward's inputs, and the     */
+/* steps after the all-reduce (the callers either side of the hot path).      */
+/* ------------------------------------------------------------------------- */
+
+/* Per-channel sum and sum of squares of the (half) conv output, then
+ * bn_finalize: saved_mean, saved_inv_std = 1/sqrt(biased var + eps), eq_scale =
+ * gamma*inv_std, eq_bias = beta - mean*eq_scale, running stats (unbiased var)
+ * updated in place when not NULL.  ch_sum / ch_sqsum may be NULL.  Counterparts:
+ * genstats and build_cbr_bn_finalize_graph, cbr_op.cpp:622-718 and 430-528. */
+size_t trb200_bn_stats_workspace_bytes(int64_t m, int32_t c);
+int trb200_bn_stats_finalize(const void* conv_out, const float* gamma, const float* beta, float eps,
+                             float momentum, float* ch_sum, float* ch_sqsum, float* saved_mean,
+                             float* saved_inv_std, float* eq_scale, float* eq_bias,
+                             float* running_mean, float* running_var, int64_t m, int32_t c,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/* relu_out = max(t, 0), mask bit = (t > 0) with t = half(half(x*eq_scale) + eq_bias):
+ * build_cbr_bn_relu_graph, cbr_op.cpp:534-616 (MUL, ADD with HALF intermediates,
+ * RELU_FWD, CMP_GT -> BOOLEAN).  Mask layout as in trb200_bnrelu_bwd. */
+int trb200_bn_apply_relu_mask(const void* conv_out, const float* eq_scale, const float* eq_bias,
+                              void* relu_out, void* mask_bits, int64_t m, int32_t c, void* stream);
+
+/* 2x2 stride-2 max pooling on NHWC half, argmax byte = kh*2 + kw with the first
+ * maximum winning, and its backward (gradient routed to the argmax position,
+ * zeros elsewhere): maxpool_amp_fwd_mask_kernel / maxpool_bwd_deterministic_kernel,
+ * src/backend/ops/dtensor/maxpool_op.cu:23-217.  h, w even, c % 8 == 0. */
+int trb200_maxpool2x2_fwd(const void* x, void* y, void* argmax, int32_t n, int32_t h, int32_t w,
+                          int32_t c, void* stream);
+int trb200_maxpool2x2_bwd(const void* dy, const void* argmax, void* dx, int32_t n, int32_t h, int32_t w,
+                          int32_t c, void* stream);
+
+/* *flag = 1 if any of the n floats is NaN or Inf (flag is never cleared here):
+ * check_nan_kernel, src/backend/ops/range/check_op.cu:15-79. */
+int trb200_check_nonfinite(const float* grads, int64_t n, int32_t* flag, void* stream);
+
+/* SGD with momentum over a flat float range, loss scale undone on the fly, and
+ * the half working copy refreshed in the same sweep (weights_half may be NULL):
+ *   m = beta*m + g/scaling ; w = w*(1 - lr*wd) - lr*m ; w16 = half(w)
+ * Skipped entirely when *skip_flag != 0 (the non-finite guard).  `scaling` is a
+ * device scalar (NULL = 1).  Counterparts: momentum kernel,
+ * src/backend/ops/range/optimizer_op.cu:40-60 (CPU form optimizer_op.cpp:306-313),
+ * and RANGE_CAST_FP32_TO_FP16, cast_op.cu:18-37. */
+int trb200_sgd_momentum(float* weights, const float* grads, float* momentum, void* weights_half,
+                        int64_t n, float lr, float weight_decay, float beta, const float* scaling,
+                        const int32_t* skip_flag, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRB200_H_ */

@@ -1,0 +1,326 @@
+// Forward side of the Conv+BN+ReLU block that is HBM-bound: batch statistics of
+// the conv output, bn_finalize, and BN-apply + ReLU + bit mask; plus 2x2 max
+// pooling.  These produce the inputs of the backward hot path.
+//
+// Reference counterparts (cuDNN-FE graphs in src/backend/ops/dtensor/cbr_op.cpp):
+//   genstats (sum, sum of squares per channel)            cbr_op.cpp:622-718
+//   bn_finalize -> eq_scale, eq_bias, saved stats, running stats   cbr_op.cpp:430-528
+//   y = relu(t), mask = t > 0, t = half(half(x*eq_scale) + eq_bias) cbr_op.cpp:534-616
+//   max pooling with argmax byte (kh*k + kw, first maximum wins)    maxpool_op.cu:23-217
+#include "common.cuh"
+
+namespace trb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+constexpr int kMaxBlocks = 148 * 8;
+
+struct RowPlan {
+    int tpr, bx, by, gy, gx;
+    int64_t rows_per_strip;
+};
+
+RowPlan make_row_plan(int64_t m, int c) {
+    RowPlan p;
+    p.tpr = c / 8;
+    p.bx = p.tpr < kThreads ? p.tpr : kThreads;
+    p.by = kThreads / p.bx;
+    if (p.by < 1) p.by = 1;
+    p.gy = (p.tpr + p.bx - 1) / p.bx;
+    int64_t want = (m + (int64_t)p.by * kUnroll - 1) / ((int64_t)p.by * kUnroll);
+    int64_t cap = kMaxBlocks / p.gy;
+    if (cap < 1) cap = 1;
+    p.gx = (int)(want < cap ? want : cap);
+    if (p.gx < 1) p.gx = 1;
+    int64_t rps = (m + p.gx - 1) / p.gx;
+    rps = (rps + p.by - 1) / p.by * p.by;
+    p.rows_per_strip = rps;
+    p.gx = (int)((m + rps - 1) / rps);
+    return p;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __half22float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+// per-strip partial sums of x and x*x, 8 channels per thread
+__global__ void __launch_bounds__(kThreads)
+bn_stats_partial(const uint4* __restrict__ x, float* __restrict__ partial, int64_t m, int c, int tpr, int bx,
+                 int by, int64_t rows_per_strip) {
+    __shared__ float s_red[kThreads * 16];
+    const int tx = threadIdx.x % bx, ty = threadIdx.x / bx;
+    const int vec = blockIdx.y * bx + tx;
+    const bool ok = vec < tpr && ty < by;
+    const int64_t r0 = (int64_t)blockIdx.x * rows_per_strip;
+    const int64_t r1 = (r0 + rows_per_strip < m) ? r0 + rows_per_strip : m;
+    float s1[8], s2[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { s1[j] = 0.f; s2[j] = 0.f; }
+    if (ok) {
+        for (int64_t row = r0 + ty; row < r1; row += (int64_t)by * kUnroll) {
+            uint4 v[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int64_t r = row + (int64_t)u * by;
+                v[u] = r < r1 ? x[r * tpr + vec] : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                float f[8];
+                unpack8(v[u], f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { s1[j] += f[j]; s2[j] = fmaf(f[j], f[j], s2[j]); }
+            }
+        }
+    }
+    float* mine = s_red + (size_t)threadIdx.x * 16;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { mine[j] = s1[j]; mine[8 + j] = s2[j]; }
+    __syncthreads();
+    for (int t = threadIdx.x; t < bx * 16; t += kThreads) {
+        const int otx = t / 16, j = t % 16;
+        const int ovec = blockIdx.y * bx + otx;
+        if (ovec >= tpr) continue;
+        float acc = 0.f;
+        for (int y = 0; y < by; ++y) acc += s_red[(size_t)(y * bx + otx) * 16 + j];
+        partial[((size_t)blockIdx.x * 2 + (j >> 3)) * c + ovec * 8 + (j & 7)] = acc;
+    }
+}
+
+// adds the strips in strip order (double) and finalizes the statistics
+__global__ void bn_stats_finalize(const float* __restrict__ partial, int strips, int c, int64_t m,
+                                  const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
+                                  float momentum, float* __restrict__ ch_sum, float* __restrict__ ch_sqsum,
+                                  float* __restrict__ saved_mean, float* __restrict__ saved_inv_std,
+                                  float* __restrict__ eq_scale, float* __restrict__ eq_bias,
+                                  float* __restrict__ running_mean, float* __restrict__ running_var) {
+    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+    if (ch >= c) return;
+    double s = 0.0, q = 0.0;
+    for (int i = 0; i < strips; ++i) {
+        s += (double)partial[((size_t)i * 2) * c + ch];
+        q += (double)partial[((size_t)i * 2 + 1) * c + ch];
+    }
+    if (ch_sum) ch_sum[ch] = (float)s;
+    if (ch_sqsum) ch_sqsum[ch] = (float)q;
+    const double mean_d = s / (double)m;
+    const float mean = (float)mean_d;
+    float var = (float)(q / (double)m - mean_d * mean_d);
+    if (var < 0.f) var = 0.f;
+    const float is = 1.0f / sqrtf(var + eps);
+    saved_mean[ch] = mean;
+    saved_inv_std[ch] = is;
+    const float es = gamma[ch] * is;
+    eq_scale[ch] = es;
+    eq_bias[ch] = beta[ch] - mean * es;
+    if (running_mean) running_mean[ch] = (1.0f - momentum) * running_mean[ch] + momentum * mean;
+    if (running_var) {
+        const float unb = m > 1 ? var * (float)((double)m / (double)(m - 1)) : var;
+        running_var[ch] = (1.0f - momentum) * running_var[ch] + momentum * unb;
+    }
+}
+
+// t = half(half(x*s) + b); y = max(t, 0); mask bit = t > 0
+__global__ void __launch_bounds__(kThreads)
+bn_apply_relu_mask(const uint4* __restrict__ x, const float* __restrict__ eq_scale,
+                   const float* __restrict__ eq_bias, uint4* __restrict__ y, uint8_t* __restrict__ mask,
+                   int64_t m, int tpr, int bx, int by, int64_t rows_per_strip) {
+    const int tx = threadIdx.x % bx, ty = threadIdx.x / bx;
+    const int vec = blockIdx.y * bx + tx;
+    if (vec >= tpr || ty >= by) return;
+    const int64_t r0 = (int64_t)blockIdx.x * rows_per_strip;
+    const int64_t r1 = (r0 + rows_per_strip < m) ? r0 + rows_per_strip : m;
+    float sc[8], bi[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { sc[j] = eq_scale[vec * 8 + j]; bi[j] = eq_bias[vec * 8 + j]; }
+    for (int64_t row = r0 + ty; row < r1; row += (int64_t)by * kUnroll) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t r = row + (int64_t)u * by;
+            if (r < r1) v[u] = x[r * tpr + vec];
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t r = row + (int64_t)u * by;
+            if (r >= r1) continue;
+            float f[8];
+            unpack8(v[u], f);
+            uint4 o;
+            __half* oh = reinterpret_cast<__half*>(&o);
+            uint32_t bits = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const __half a = __float2half_rn(f[j] * sc[j]);
+                const __half t = __float2half_rn(__half2float(a) + bi[j]);
+                const bool on = __half2float(t) > 0.f;
+                oh[j] = on ? t : __float2half_rn(0.f);
+                bits |= (on ? 1u : 0u) << j;
+            }
+            y[r * tpr + vec] = o;
+            mask[r * tpr + vec] = (uint8_t)bits;
+        }
+    }
+}
+
+// 2x2 / stride 2 max pooling, 8 channels per thread
+__global__ void __launch_bounds__(256)
+maxpool2x2_fwd(const uint4* __restrict__ x, uint4* __restrict__ y, uint2* __restrict__ argmax, int n, int h,
+               int w, int tpr) {
+    const int oh_n = h / 2, ow_n = w / 2;
+    const int64_t total = (int64_t)n * oh_n * ow_n * tpr;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int vec = (int)(i % tpr);
+        int64_t p = i / tpr;
+        const int ow = (int)(p % ow_n);
+        p /= ow_n;
+        const int oh = (int)(p % oh_n);
+        const int img = (int)(p / oh_n);
+        float best[8];
+        uint8_t am[8];
+        uint4 bv = make_uint4(0, 0, 0, 0);
+        __half* bh = reinterpret_cast<__half*>(&bv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { best[j] = -INFINITY; am[j] = 0; }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int ih = oh * 2 + (q >> 1), iw = ow * 2 + (q & 1);
+            const uint4 v = x[(((int64_t)img * h + ih) * w + iw) * tpr + vec];
+            const __half* vh = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float f = __half2float(vh[j]);
+                if (f > best[j]) { best[j] = f; am[j] = (uint8_t)q; bh[j] = vh[j]; }
+            }
+        }
+        y[i] = bv;
+        uint2 a;
+        a.x = am[0] | (am[1] << 8) | (am[2] << 16) | (am[3] << 24);
+        a.y = am[4] | (am[5] << 8) | (am[6] << 16) | (am[7] << 24);
+        argmax[i] = a;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+maxpool2x2_bwd(const uint4* __restrict__ dy, const uint2* __restrict__ argmax, uint4* __restrict__ dx, int n,
+               int h, int w, int tpr) {
+    const int oh_n = h / 2, ow_n = w / 2;
+    const int64_t total = (int64_t)n * oh_n * ow_n * tpr;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int vec = (int)(i % tpr);
+        int64_t p = i / tpr;
+        const int ow = (int)(p % ow_n);
+        p /= ow_n;
+        const int oh = (int)(p % oh_n);
+        const int img = (int)(p / oh_n);
+        const uint4 g = dy[i];
+        const uint2 a = argmax[i];
+        const uint16_t* gh = reinterpret_cast<const uint16_t*>(&g);
+        const uint8_t* ab = reinterpret_cast<const uint8_t*>(&a);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            uint16_t* oh16 = reinterpret_cast<uint16_t*>(&o);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) oh16[j] = ab[j] == q ? gh[j] : (uint16_t)0;
+            const int ih = oh * 2 + (q >> 1), iw = ow * 2 + (q & 1);
+            dx[(((int64_t)img * h + ih) * w + iw) * tpr + vec] = o;
+        }
+    }
+}
+
+int grid_for(int64_t items) {
+    int64_t b = (items + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (b > cap) b = cap;
+    return (int)(b < 1 ? 1 : b);
+}
+
+}  // namespace
+}  // namespace trb
+
+extern "C" size_t trb200_bn_stats_workspace_bytes(int64_t m, int32_t c) {
+    if (m <= 0 || c <= 0 || c % 8 != 0) return 0;
+    const trb::RowPlan p = trb::make_row_plan(m, c);
+    return (size_t)p.gx * 2 * (size_t)c * sizeof(float);
+}
+
+extern "C" int trb200_bn_stats_finalize(const void* conv_out, const float* gamma, const float* beta, float eps,
+                                        float momentum, float* ch_sum, float* ch_sqsum, float* saved_mean,
+                                        float* saved_inv_std, float* eq_scale, float* eq_bias,
+                                        float* running_mean, float* running_var, int64_t m, int32_t c,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+    TRB_REQUIRE(conv_out && gamma && beta && saved_mean && saved_inv_std && eq_scale && eq_bias,
+                TRB200_ERR_INVALID_ARGUMENT, "bn_stats_finalize: null pointer");
+    TRB_REQUIRE(m > 0 && c > 0 && c % 8 == 0, TRB200_ERR_UNSUPPORTED,
+                "bn_stats_finalize: need m > 0 and c a positive multiple of 8 (m=%lld c=%d)", (long long)m, c);
+    TRB_REQUIRE(trb::aligned16(conv_out), TRB200_ERR_INVALID_ARGUMENT, "bn_stats_finalize: conv_out must be 16-byte aligned");
+    const size_t need = trb200_bn_stats_workspace_bytes(m, c);
+    TRB_REQUIRE(workspace && workspace_bytes >= need, TRB200_ERR_WORKSPACE,
+                "bn_stats_finalize: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    const trb::RowPlan p = trb::make_row_plan(m, c);
+    cudaStream_t s = trb::as_stream(stream);
+    float* partial = static_cast<float*>(workspace);
+    trb::bn_stats_partial<<<dim3(p.gx, p.gy), trb::kThreads, 0, s>>>(static_cast<const uint4*>(conv_out), partial, m, c,
+                                                                     p.tpr, p.bx, p.by, p.rows_per_strip);
+    TRB_LAUNCH_CHECK("bn_stats_partial");
+    trb::bn_stats_finalize<<<(c + 127) / 128, 128, 0, s>>>(partial, p.gx, c, m, gamma, beta, eps, momentum, ch_sum,
+                                                          ch_sqsum, saved_mean, saved_inv_std, eq_scale, eq_bias,
+                                                          running_mean, running_var);
+    TRB_LAUNCH_CHECK("bn_stats_finalize");
+    return TRB200_OK;
+}
+
+extern "C" int trb200_bn_apply_relu_mask(const void* conv_out, const float* eq_scale, const float* eq_bias,
+                                         void* relu_out, void* mask_bits, int64_t m, int32_t c, void* stream) {
+    TRB_REQUIRE(conv_out && eq_scale && eq_bias && relu_out && mask_bits, TRB200_ERR_INVALID_ARGUMENT,
+                "bn_apply_relu_mask: null pointer");
+    TRB_REQUIRE(m > 0 && c > 0 && c % 8 == 0, TRB200_ERR_UNSUPPORTED,
+                "bn_apply_relu_mask: need m > 0 and c a positive multiple of 8 (m=%lld c=%d)", (long long)m, c);
+    TRB_REQUIRE(trb::aligned16(conv_out) && trb::aligned16(relu_out), TRB200_ERR_INVALID_ARGUMENT,
+                "bn_apply_relu_mask: tensors must be 16-byte aligned");
+    const trb::RowPlan p = trb::make_row_plan(m, c);
+    trb::bn_apply_relu_mask<<<dim3(p.gx, p.gy), trb::kThreads, 0, trb::as_stream(stream)>>>(
+        static_cast<const uint4*>(conv_out), eq_scale, eq_bias, static_cast<uint4*>(relu_out),
+        static_cast<uint8_t*>(mask_bits), m, p.tpr, p.bx, p.by, p.rows_per_strip);
+    TRB_LAUNCH_CHECK("bn_apply_relu_mask");
+    return TRB200_OK;
+}
+
+extern "C" int trb200_maxpool2x2_fwd(const void* x, void* y, void* argmax, int32_t n, int32_t h, int32_t w,
+                                     int32_t c, void* stream) {
+    TRB_REQUIRE(x && y && argmax, TRB200_ERR_INVALID_ARGUMENT, "maxpool2x2_fwd: null pointer");
+    TRB_REQUIRE(n > 0 && h > 0 && w > 0 && h % 2 == 0 && w % 2 == 0 && c > 0 && c % 8 == 0, TRB200_ERR_UNSUPPORTED,
+                "maxpool2x2_fwd: need even h, w and c a multiple of 8");
+    TRB_REQUIRE(trb::aligned16(x) && trb::aligned16(y) && trb::aligned16(argmax), TRB200_ERR_INVALID_ARGUMENT,
+                "maxpool2x2_fwd: tensors must be 16-byte aligned");
+    const int64_t total = (int64_t)n * (h / 2) * (w / 2) * (c / 8);
+    trb::maxpool2x2_fwd<<<trb::grid_for(total), 256, 0, trb::as_stream(stream)>>>(
+        static_cast<const uint4*>(x), static_cast<uint4*>(y), static_cast<uint2*>(argmax), n, h, w, c / 8);
+    TRB_LAUNCH_CHECK("maxpool2x2_fwd");
+    return TRB200_OK;
+}
+
+extern "C" int trb200_maxpool2x2_bwd(const void* dy, const void* argmax, void* dx, int32_t n, int32_t h, int32_t w,
+                                     int32_t c, void* stream) {
+    TRB_REQUIRE(dy && dx && argmax, TRB200_ERR_INVALID_ARGUMENT, "maxpool2x2_bwd: null pointer");
+    TRB_REQUIRE(n > 0 && h > 0 && w > 0 && h % 2 == 0 && w % 2 == 0 && c > 0 && c % 8 == 0, TRB200_ERR_UNSUPPORTED,
+                "maxpool2x2_bwd: need even h, w and c a multiple of 8");
+    TRB_REQUIRE(trb::aligned16(dy) && trb::aligned16(dx) && trb::aligned16(argmax), TRB200_ERR_INVALID_ARGUMENT,
+                "maxpool2x2_bwd: tensors must be 16-byte aligned");
+    TRB_REQUIRE(dx != dy, TRB200_ERR_INVALID_ARGUMENT, "maxpool2x2_bwd: dx must not alias dy");
+    const int64_t total = (int64_t)n * (h / 2) * (w / 2) * (c / 8);
+    trb::maxpool2x2_bwd<<<trb::grid_for(total), 256, 0, trb::as_stream(stream)>>>(
+        static_cast<const uint4*>(dy), static_cast<const uint2*>(argmax), static_cast<uint4*>(dx), n, h, w, c / 8);
+    TRB_LAUNCH_CHECK("maxpool2x2_bwd");
+    return TRB200_OK;
+}

@@ -1,0 +1,269 @@
+// BN + ReLU backward of the fused Conv+BN+ReLU block (HBM-bound, two sweeps).
+//
+// Replaces the cuDNN-FE graph MUL(dY, BOOLEAN mask) -> batchnorm_backward of the
+// reference (src/backend/ops/dtensor/cbr_op.cpp:1259-1353).
+//
+// Data layout: dy, x, dconv are [m rows][c channels] half, c % 8 == 0, so one
+// row is c/8 16-byte vectors and the mask byte that covers a vector has the same
+// index as the vector (1 bit per element, least significant bit first).
+//
+// Sweep 1 (bnrelu_bwd_reduce): every thread owns 8 adjacent channels and walks a
+//   strip of rows with 128-bit loads, keeping 2x8 float sums in registers; the
+//   block adds its threads' sums in a fixed order through shared memory and
+//   writes one partial per block.  bnrelu_bwd_finalize adds the partials of all
+//   blocks in block order in double.  No float atomics anywhere, so dgamma and
+//   dbeta are bitwise reproducible.
+// Sweep 2 (bnrelu_bwd_apply): dconv = a*(dy_m - dbeta/m - (x-mean)*k) per channel,
+//   written as 128-bit stores.  It walks the row strips in the opposite order of sweep 1 so
+//   that the rows sweep 1 read last, still resident in L2, are consumed first.
+//
+// Algorithmic HBM bytes: 2 x (2 + 2 + 1/8) read + 2 written = 10.25 B / element.
+#include "common.cuh"
+
+namespace trb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+constexpr int kMaxBlocks = 148 * 8;
+
+struct BnPlan {
+    int tpr;     // 16-byte vectors per row
+    int bx;      // threads along the row (vectors handled per block row)
+    int by;      // rows handled per block step
+    int gy;      // column chunks
+    int gx;      // row strips
+    int64_t rows_per_strip;
+};
+
+BnPlan make_plan(int64_t m, int c) {
+    BnPlan p;
+    p.tpr = c / 8;
+    p.bx = p.tpr < kThreads ? p.tpr : kThreads;
+    p.by = kThreads / p.bx;
+    if (p.by < 1) p.by = 1;
+    p.gy = (p.tpr + p.bx - 1) / p.bx;
+    int64_t want = (m + (int64_t)p.by * kUnroll - 1) / ((int64_t)p.by * kUnroll);
+    int64_t cap = kMaxBlocks / p.gy;
+    if (cap < 1) cap = 1;
+    p.gx = (int)(want < cap ? want : cap);
+    if (p.gx < 1) p.gx = 1;
+    int64_t rps = (m + p.gx - 1) / p.gx;
+    // strips are multiples of the block's row step so that every strip starts on a
+    // 16-byte boundary of the mask as well
+    rps = (rps + p.by - 1) / p.by * p.by;
+    p.rows_per_strip = rps;
+    p.gx = (int)((m + rps - 1) / rps);
+    return p;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __half22float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__global__ void __launch_bounds__(kThreads)
+bnrelu_bwd_reduce(const uint4* __restrict__ dy, const uint8_t* __restrict__ mask,
+                  const uint4* __restrict__ x, const float* __restrict__ mean,
+                  const float* __restrict__ inv_std, float* __restrict__ partial,
+                  int64_t m, int c, int tpr, int bx, int by, int64_t rows_per_strip) {
+    __shared__ float s_red[kThreads * 16];
+    const int tx = threadIdx.x % bx, ty = threadIdx.x / bx;
+    const int vec = blockIdx.y * bx + tx;           // vector (8-channel group) in the row
+    const bool col_ok = vec < tpr && ty < by;
+    const int64_t r0 = (int64_t)blockIdx.x * rows_per_strip;
+    const int64_t r1 = (r0 + rows_per_strip < m) ? r0 + rows_per_strip : m;
+
+    float sb[8], sg[8], mu[8], is[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { sb[j] = 0.f; sg[j] = 0.f; mu[j] = 0.f; is[j] = 0.f; }
+    if (col_ok) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { mu[j] = mean[vec * 8 + j]; is[j] = inv_std[vec * 8 + j]; }
+        for (int64_t row = r0 + ty; row < r1; row += (int64_t)by * kUnroll) {
+            uint4 vdy[kUnroll], vx[kUnroll];
+            uint32_t mb[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int64_t r = row + (int64_t)u * by;
+                if (r < r1) {
+                    const int64_t v = r * tpr + vec;
+                    vdy[u] = ld_stream(dy + v);
+                    vx[u] = ld_stream(x + v);
+                    mb[u] = mask[v];
+                } else {
+                    vdy[u] = make_uint4(0, 0, 0, 0);
+                    vx[u] = make_uint4(0, 0, 0, 0);
+                    mb[u] = 0;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                float g[8], xv[8];
+                unpack8(vdy[u], g);
+                unpack8(vx[u], xv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float gm = (mb[u] >> j) & 1u ? g[j] : 0.f;
+                    sb[j] += gm;
+                    sg[j] += gm * ((xv[j] - mu[j]) * is[j]);
+                }
+            }
+        }
+    }
+    // block reduction over ty in ascending order
+    float* mine = s_red + (size_t)threadIdx.x * 16;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { mine[j] = sb[j]; mine[8 + j] = sg[j]; }
+    __syncthreads();
+    // thread t < bx*16 owns value (tx = t / 16, j = t % 16)
+    for (int t = threadIdx.x; t < bx * 16; t += kThreads) {
+        const int otx = t / 16, j = t % 16;
+        const int ovec = blockIdx.y * bx + otx;
+        if (ovec >= tpr) continue;
+        float acc = 0.f;
+        for (int y = 0; y < by; ++y) acc += s_red[(size_t)(y * bx + otx) * 16 + j];
+        const int ch = ovec * 8 + (j & 7);
+        // partial[strip][stat][c], stat 0 = dbeta, 1 = dgamma
+        partial[((size_t)blockIdx.x * 2 + (j >> 3)) * c + ch] = acc;
+    }
+}
+
+__global__ void bnrelu_bwd_finalize(const float* __restrict__ partial, float* __restrict__ dgamma,
+                                    float* __restrict__ dbeta, int c, int strips) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;   // i in [0, 2c)
+    if (i >= 2 * c) return;
+    const int stat = i / c, ch = i % c;
+    double acc = 0.0;
+    for (int s = 0; s < strips; ++s) acc += (double)partial[((size_t)s * 2 + stat) * c + ch];
+    (stat == 0 ? dbeta : dgamma)[ch] = (float)acc;
+}
+
+__global__ void __launch_bounds__(kThreads)
+bnrelu_bwd_apply(const uint4* __restrict__ dy, const uint8_t* __restrict__ mask,
+                 const uint4* __restrict__ x, const float* __restrict__ gamma,
+                 const float* __restrict__ mean, const float* __restrict__ inv_std,
+                 const float* __restrict__ dgamma, const float* __restrict__ dbeta,
+                 uint4* __restrict__ out, int64_t m, int tpr, int bx, int by,
+                 int64_t rows_per_strip) {
+    const int tx = threadIdx.x % bx, ty = threadIdx.x / bx;
+    const int vec = blockIdx.y * bx + tx;
+    if (vec >= tpr || ty >= by) return;
+    // reverse strip order: see the header of this file
+    const int strip = gridDim.x - 1 - blockIdx.x;
+    const int64_t r0 = (int64_t)strip * rows_per_strip;
+    const int64_t r1 = (r0 + rows_per_strip < m) ? r0 + rows_per_strip : m;
+
+    // out = a * (g - mb - (x - mu) * k), a = gamma*inv_std, mb = dbeta/m, k = inv_std * (dgamma/m) * inv_std
+    float ca[8], cmb[8], cmu[8], ck[8];
+    const float inv_m = 1.0f / (float)m;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int ch = vec * 8 + j;
+        const float is = inv_std[ch];
+        ca[j] = gamma[ch] * is;
+        cmb[j] = dbeta[ch] * inv_m;
+        cmu[j] = mean[ch];
+        ck[j] = is * (dgamma[ch] * inv_m);
+    }
+    for (int64_t row = r0 + ty; row < r1; row += (int64_t)by * kUnroll) {
+        uint4 vdy[kUnroll], vx[kUnroll];
+        uint32_t mb[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t r = row + (int64_t)u * by;
+            if (r < r1) {
+                const int64_t v = r * tpr + vec;
+                vdy[u] = ld_stream(dy + v);
+                vx[u] = ld_stream(x + v);
+                mb[u] = mask[v];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t r = row + (int64_t)u * by;
+            if (r >= r1) continue;
+            float g[8], xv[8];
+            unpack8(vdy[u], g);
+            unpack8(vx[u], xv);
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float g0 = (mb[u] >> (2 * j)) & 1u ? g[2 * j] : 0.f;
+                const float g1 = (mb[u] >> (2 * j + 1)) & 1u ? g[2 * j + 1] : 0.f;
+                const float o0 = ca[2 * j] * (g0 - cmb[2 * j] - (xv[2 * j] - cmu[2 * j]) * ck[2 * j]);
+                const float o1 = ca[2 * j + 1] * (g1 - cmb[2 * j + 1] - (xv[2 * j + 1] - cmu[2 * j + 1]) * ck[2 * j + 1]);
+                oh[j] = __floats2half2_rn(o0, o1);
+            }
+            out[r * tpr + vec] = o;
+        }
+    }
+}
+
+}  // namespace
+
+int bnrelu_bwd_launch(const void* dy, const void* mask_bits, const void* x, const float* gamma,
+                      const float* saved_mean, const float* saved_inv_std, void* dconv,
+                      float* dgamma, float* dbeta, int64_t m, int c, void* workspace,
+                      size_t workspace_bytes, cudaStream_t s) {
+    TRB_REQUIRE(dy && mask_bits && x && gamma && saved_mean && saved_inv_std && dgamma && dbeta,
+                TRB200_ERR_INVALID_ARGUMENT, "bnrelu_bwd: null pointer");
+    TRB_REQUIRE(m > 0 && c > 0 && c % 8 == 0, TRB200_ERR_UNSUPPORTED,
+                "bnrelu_bwd: need m > 0 and c a positive multiple of 8 (m=%lld c=%d)", (long long)m, c);
+    TRB_REQUIRE(aligned16(dy) && aligned16(x) && (!dconv || aligned16(dconv)),
+                TRB200_ERR_INVALID_ARGUMENT, "bnrelu_bwd: dy, x and dconv must be 16-byte aligned");
+    TRB_REQUIRE(dconv != dy && dconv != x, TRB200_ERR_INVALID_ARGUMENT,
+                "bnrelu_bwd: dconv must not alias dy or x");
+    const size_t need = trb200_bnrelu_bwd_workspace_bytes(m, c);
+    TRB_REQUIRE(workspace && workspace_bytes >= need, TRB200_ERR_WORKSPACE,
+                "bnrelu_bwd: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    const BnPlan p = make_plan(m, c);
+    float* partial = static_cast<float*>(workspace);
+    dim3 grid(p.gx, p.gy);
+    bnrelu_bwd_reduce<<<grid, kThreads, 0, s>>>(
+        static_cast<const uint4*>(dy), static_cast<const uint8_t*>(mask_bits),
+        static_cast<const uint4*>(x), saved_mean, saved_inv_std, partial, m, c, p.tpr, p.bx, p.by,
+        p.rows_per_strip);
+    TRB_LAUNCH_CHECK("bnrelu_bwd_reduce");
+    bnrelu_bwd_finalize<<<(2 * c + 127) / 128, 128, 0, s>>>(partial, dgamma, dbeta, c, p.gx);
+    TRB_LAUNCH_CHECK("bnrelu_bwd_finalize");
+    if (dconv) {
+        bnrelu_bwd_apply<<<grid, kThreads, 0, s>>>(
+            static_cast<const uint4*>(dy), static_cast<const uint8_t*>(mask_bits),
+            static_cast<const uint4*>(x), gamma, saved_mean, saved_inv_std, dgamma, dbeta,
+            static_cast<uint4*>(dconv), m, p.tpr, p.bx, p.by, p.rows_per_strip);
+        TRB_LAUNCH_CHECK("bnrelu_bwd_apply");
+    }
+    return TRB200_OK;
+}
+
+}  // namespace trb
+
+extern "C" size_t trb200_bnrelu_bwd_workspace_bytes(int64_t m, int32_t c) {
+    if (m <= 0 || c <= 0 || c % 8 != 0) return 0;
+    const trb::BnPlan p = trb::make_plan(m, c);
+    return (size_t)p.gx * 2 * (size_t)c * sizeof(float);
+}
+
+extern "C" int trb200_bnrelu_bwd(const void* dy, const void* mask_bits, const void* x,
+                                 const float* gamma, const float* saved_mean,
+                                 const float* saved_inv_std, void* dconv, float* dgamma,
+                                 float* dbeta, int64_t m, int32_t c, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+    return trb::bnrelu_bwd_launch(dy, mask_bits, x, gamma, saved_mean, saved_inv_std, dconv, dgamma,
+                                  dbeta, m, c, workspace, workspace_bytes, trb::as_stream(stream));
+}

@@ -1,0 +1,26 @@
+// Internal interface between the convolution entry points and their kernels.
+#pragma once
+
+#include "common.cuh"
+
+namespace trb {
+
+// Direct CUDA-core kernels (conv_direct.cu): any geometry.
+size_t wgrad_direct_workspace(const trb200_conv_desc& d);
+int wgrad_direct(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* ws,
+                 size_t ws_bytes, cudaStream_t st);
+int dgrad_direct(const trb200_conv_desc& d, const void* dy, const void* w, void* dx, cudaStream_t st);
+
+// tcgen05 / TMEM implicit-GEMM kernels (conv_igemm_sm100.cu): 3x3, stride 1,
+// pad 1, channel counts that are multiples of 64.
+bool igemm_supports(const trb200_conv_desc& d, int which);   // 0 wgrad, 1 dgrad, 2 fprop
+size_t igemm_wgrad_workspace(const trb200_conv_desc& d);
+size_t igemm_dgrad_workspace(const trb200_conv_desc& d);
+int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* ws,
+                size_t ws_bytes, cudaStream_t st);
+int igemm_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* dx, void* ws,
+                size_t ws_bytes, cudaStream_t st);
+
+int validate_conv_desc(const trb200_conv_desc* d, const char* who);
+
+}  // namespace trb

@@ -1,0 +1,178 @@
+// C entry points for the convolution gradients and the whole-block backward.
+#include "common.cuh"
+#include "conv.cuh"
+
+#include <atomic>
+
+namespace trb {
+
+int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, cudaStream_t st);
+int device_status_read_and_clear(int* out);
+int bnrelu_bwd_launch(const void* dy, const void* mask_bits, const void* x, const float* gamma,
+                      const float* saved_mean, const float* saved_inv_std, void* dconv, float* dgamma,
+                      float* dbeta, int64_t m, int c, void* workspace, size_t workspace_bytes, cudaStream_t s);
+
+namespace {
+std::atomic<int> g_backend{0};   // 0 = automatic, 1 = direct kernels only
+
+bool use_igemm(const trb200_conv_desc& d, int which) { return g_backend.load() == 0 && igemm_supports(d, which); }
+}  // namespace
+
+int validate_conv_desc(const trb200_conv_desc* d, const char* who) {
+    TRB_REQUIRE(d, TRB200_ERR_INVALID_ARGUMENT, "%s: null descriptor", who);
+    TRB_REQUIRE(d->n > 0 && d->h > 0 && d->w > 0 && d->c > 0 && d->k > 0 && d->r > 0 && d->s > 0,
+                TRB200_ERR_INVALID_ARGUMENT, "%s: sizes must be positive", who);
+    TRB_REQUIRE(d->stride_h > 0 && d->stride_w > 0 && d->pad_h >= 0 && d->pad_w >= 0, TRB200_ERR_INVALID_ARGUMENT,
+                "%s: bad stride or padding", who);
+    TRB_REQUIRE(d->h + 2 * d->pad_h >= d->r && d->w + 2 * d->pad_w >= d->s, TRB200_ERR_INVALID_ARGUMENT,
+                "%s: filter larger than the padded input", who);
+    TRB_REQUIRE((int64_t)d->n * d->h * d->w * d->c < (int64_t)1 << 40, TRB200_ERR_UNSUPPORTED, "%s: tensor too large",
+                who);
+    return TRB200_OK;
+}
+
+}  // namespace trb
+
+using trb::use_igemm;
+
+extern "C" int trb200_set_conv_backend(int backend) {
+    TRB_REQUIRE(backend == 0 || backend == 1, TRB200_ERR_INVALID_ARGUMENT, "set_conv_backend: 0 or 1 expected");
+    trb::g_backend.store(backend);
+    return TRB200_OK;
+}
+
+extern "C" int trb200_conv_uses_tensor_cores(const trb200_conv_desc* d, int which) {
+    if (!d || which < 0 || which > 2) return 0;
+    return use_igemm(*d, which) ? 1 : 0;
+}
+
+extern "C" int trb200_device_status(void) {
+    int v = 0;
+    const int rc = trb::device_status_read_and_clear(&v);
+    if (rc) return rc;
+    if (v != 0)
+        return trb::fail(TRB200_ERR_DEVICE_TIMEOUT, "a device-side wait gave up (role code %d)", v);
+    return TRB200_OK;
+}
+
+extern "C" size_t trb200_conv_wgrad_workspace_bytes(const trb200_conv_desc* d) {
+    if (trb::validate_conv_desc(d, "conv_wgrad_workspace_bytes")) return 0;
+    return use_igemm(*d, 0) ? trb::igemm_wgrad_workspace(*d) : trb::wgrad_direct_workspace(*d);
+}
+
+extern "C" size_t trb200_conv_dgrad_workspace_bytes(const trb200_conv_desc* d) {
+    if (trb::validate_conv_desc(d, "conv_dgrad_workspace_bytes")) return 0;
+    return use_igemm(*d, 1) ? trb::igemm_dgrad_workspace(*d) : 0;
+}
+
+extern "C" int trb200_conv_wgrad(const trb200_conv_desc* d, const void* dy, const void* x, void* dw, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+    int rc = trb::validate_conv_desc(d, "conv_wgrad");
+    if (rc) return rc;
+    TRB_REQUIRE(dy && x && dw, TRB200_ERR_INVALID_ARGUMENT, "conv_wgrad: null pointer");
+    TRB_REQUIRE(trb::aligned16(dy) && trb::aligned16(x) && trb::aligned16(dw), TRB200_ERR_INVALID_ARGUMENT,
+                "conv_wgrad: tensors must be 16-byte aligned");
+    if (use_igemm(*d, 0)) return trb::igemm_wgrad(*d, dy, x, dw, workspace, workspace_bytes, trb::as_stream(stream));
+    return trb::wgrad_direct(*d, dy, x, dw, workspace, workspace_bytes, trb::as_stream(stream));
+}
+
+extern "C" int trb200_conv_dgrad(const trb200_conv_desc* d, const void* dy, const void* w, void* dx, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+    int rc = trb::validate_conv_desc(d, "conv_dgrad");
+    if (rc) return rc;
+    TRB_REQUIRE(dy && w && dx, TRB200_ERR_INVALID_ARGUMENT, "conv_dgrad: null pointer");
+    TRB_REQUIRE(dx != dy && dx != w, TRB200_ERR_INVALID_ARGUMENT, "conv_dgrad: dx must not alias dy or w");
+    TRB_REQUIRE(trb::aligned16(dy) && trb::aligned16(w) && trb::aligned16(dx), TRB200_ERR_INVALID_ARGUMENT,
+                "conv_dgrad: tensors must be 16-byte aligned");
+    if (use_igemm(*d, 1)) return trb::igemm_dgrad(*d, dy, w, dx, workspace, workspace_bytes, trb::as_stream(stream));
+    return trb::dgrad_direct(*d, dy, w, dx, trb::as_stream(stream));
+}
+
+extern "C" int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const void* w, void* y, void* stream) {
+    int rc = trb::validate_conv_desc(d, "conv_fprop");
+    if (rc) return rc;
+    TRB_REQUIRE(x && w && y, TRB200_ERR_INVALID_ARGUMENT, "conv_fprop: null pointer");
+    TRB_REQUIRE(y != x && y != w, TRB200_ERR_INVALID_ARGUMENT, "conv_fprop: y must not alias x or w");
+    TRB_REQUIRE(trb::igemm_supports(*d, 2), TRB200_ERR_UNSUPPORTED,
+                "conv_fprop: only 3x3 stride 1 pad 1 with c and k multiples of 64 (k = 64, 128 or a multiple of 256)");
+    return trb::igemm_fprop(*d, x, w, y, trb::as_stream(stream));
+}
+
+// ---------------------------------------------------------------------------
+// Whole block.  Workspace layout: [bnrelu partials][wgrad scratch][dgrad scratch],
+// each 256-byte aligned, so that the three stages can run on three streams.
+// ---------------------------------------------------------------------------
+namespace {
+struct BlockWs {
+    size_t bn_off, bn_bytes, wg_off, wg_bytes, dg_off, dg_bytes, total;
+};
+
+BlockWs block_ws(const trb200_conv_desc& d, bool first_layer) {
+    const int oh = trb::conv_out(d.h, d.pad_h, d.r, d.stride_h), ow = trb::conv_out(d.w, d.pad_w, d.s, d.stride_w);
+    BlockWs b;
+    b.bn_off = 0;
+    b.bn_bytes = trb200_bnrelu_bwd_workspace_bytes((int64_t)d.n * oh * ow, d.k);
+    b.wg_off = (size_t)trb::align_up((int64_t)b.bn_bytes, 256);
+    b.wg_bytes = trb200_conv_wgrad_workspace_bytes(&d);
+    b.dg_off = b.wg_off + (size_t)trb::align_up((int64_t)b.wg_bytes, 256);
+    b.dg_bytes = first_layer ? 0 : trb200_conv_dgrad_workspace_bytes(&d);
+    b.total = b.dg_off + (size_t)trb::align_up((int64_t)b.dg_bytes, 256);
+    return b;
+}
+}  // namespace
+
+extern "C" size_t trb200_cbr_bwd_workspace_bytes(const trb200_conv_desc* d, int first_layer) {
+    if (trb::validate_conv_desc(d, "cbr_bwd_workspace_bytes")) return 0;
+    return block_ws(*d, first_layer != 0).total;
+}
+
+extern "C" int trb200_cbr_bwd(const trb200_cbr_bwd_args* a) {
+    TRB_REQUIRE(a, TRB200_ERR_INVALID_ARGUMENT, "cbr_bwd: null argument block");
+    const trb200_conv_desc& d = a->conv;
+    int rc = trb::validate_conv_desc(&d, "cbr_bwd");
+    if (rc) return rc;
+    TRB_REQUIRE(a->dy && a->w && a->gamma && a->saved_mean && a->saved_inv_std && a->mask_bits && a->x && a->dw &&
+                    a->dgamma && a->dbeta && a->conv_out && a->bn_scratch,
+                TRB200_ERR_INVALID_ARGUMENT, "cbr_bwd: null pointer");
+    TRB_REQUIRE(d.k % 8 == 0, TRB200_ERR_UNSUPPORTED, "cbr_bwd: k must be a multiple of 8 (k=%d)", d.k);
+    const bool first = a->dx == nullptr;
+    const BlockWs ws = block_ws(d, first);
+    TRB_REQUIRE(ws.total == 0 || (a->workspace && a->workspace_bytes >= ws.total), TRB200_ERR_WORKSPACE,
+                "cbr_bwd: workspace of %zu bytes needed, %zu given", ws.total, a->workspace_bytes);
+    TRB_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255u) == 0, TRB200_ERR_INVALID_ARGUMENT,
+                "cbr_bwd: workspace must be 256-byte aligned");
+    cudaStream_t s_bn = trb::as_stream(a->stream_bn), s_wg = trb::as_stream(a->stream_wgrad),
+                 s_dg = trb::as_stream(a->stream_dgrad);
+    const bool multi = (s_wg != s_bn) || (s_dg != s_bn);
+    TRB_REQUIRE(!multi || (a->ev_bn && a->ev_wgrad && (first || a->ev_dgrad)), TRB200_ERR_INVALID_ARGUMENT,
+                "cbr_bwd: events are required when the streams differ");
+    unsigned char* wsp = static_cast<unsigned char*>(a->workspace);
+    const int oh = trb::conv_out(d.h, d.pad_h, d.r, d.stride_h), ow = trb::conv_out(d.w, d.pad_w, d.s, d.stride_w);
+
+    // 1) BN + ReLU backward: dconv -> bn_scratch, dgamma, dbeta
+    rc = trb::bnrelu_bwd_launch(a->dy, a->mask_bits, a->conv_out, a->gamma, a->saved_mean, a->saved_inv_std,
+                                a->bn_scratch, a->dgamma, a->dbeta, (int64_t)d.n * oh * ow, d.k, wsp + ws.bn_off,
+                                ws.bn_bytes, s_bn);
+    if (rc) return rc;
+    if (a->ev_bn) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_bn), s_bn));
+
+    // 2) wgrad(dconv, x) -> dw
+    if (s_wg != s_bn) TRB_CUDA_TRY(cudaStreamWaitEvent(s_wg, trb::as_event(a->ev_bn), 0));
+    rc = trb200_conv_wgrad(&d, a->bn_scratch, a->x, a->dw, wsp + ws.wg_off, ws.wg_bytes, s_wg);
+    if (rc) return rc;
+    if (a->ev_wgrad) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_wgrad), s_wg));
+
+    // 3) dgrad(dconv, w) -> dx, after wgrad has read x (dx is x's buffer)
+    if (!first) {
+        if (s_dg != s_wg) TRB_CUDA_TRY(cudaStreamWaitEvent(s_dg, trb::as_event(a->ev_wgrad), 0));
+        rc = trb200_conv_dgrad(&d, a->bn_scratch, a->w, a->dx, wsp + ws.dg_off, ws.dg_bytes, s_dg);
+        if (rc) return rc;
+        if (a->ev_dgrad) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_dgrad), s_dg));
+    }
+
+    // 4) join back onto the BN stream
+    if (s_wg != s_bn) TRB_CUDA_TRY(cudaStreamWaitEvent(s_bn, trb::as_event(a->ev_wgrad), 0));
+    if (!first && s_dg != s_bn) TRB_CUDA_TRY(cudaStreamWaitEvent(s_bn, trb::as_event(a->ev_dgrad), 0));
+    if (a->ev_bn) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_bn), s_bn));
+    return TRB200_OK;
+}

@@ -1,0 +1,704 @@
+// 3x3 / stride 1 / pad 1 convolution gradients as implicit GEMMs on the sm_100a
+// tensor cores: tcgen05.mma with accumulators in tensor memory, operands staged
+// in shared memory by TMA (tile mode, no cluster multicast), one output tile per
+// loop iteration of a persistent CTA.
+//
+// Reference counterparts: the cuDNN-FE conv_dgrad / conv_wgrad graphs that
+// launch_cbr_amp_bwd_cuda executes, src/backend/ops/dtensor/cbr_op.cpp:763-917,
+// 1431-1508.
+//
+// ---------------------------------------------------------------------------
+// dgrad (and forward conv: same kernel, other filter view)
+//   out[n,y,x,co] = sum_{tap=(r,s)} sum_{ci} in[n, y+r-1, x+s-1, ci] * Wv[tap][co][ci]
+//   GEMM: M = 128 output pixels (a bw x bh x bn box of the image, bw*bh*bn = 128),
+//         N = NT output channels, K loop = 9 taps x (Cin/64) slices of 64 channels.
+//   A (pixels x 64 channels) is K-major: one pixel = one 128-byte row; the TMA box
+//   of a tap is the tile's box moved by (s-1, r-1), and out-of-image pixels are
+//   zero-filled by TMA, which is the padding.  B (NT x 64) is K-major too.
+//   For dgrad, in = dconv, Wv[tap'][c][k] = W[k][2-r'][2-s'][c] (a small kernel
+//   writes that view into the workspace first).
+// wgrad
+//   dW[k][tap][c] = sum_pixels dconv[p][k] * X[p + tap offset][c]
+//   GEMM: M = 128 = two (tap, 64-channel block of c) units, N = NT channels of k,
+//   K loop = pixels, 64 per stage.  Both operands have the reduction dimension
+//   (pixels) strided and the M/N dimension contiguous: MN-major descriptors.
+//   Work = (M tile, N tile, split of the pixel range); every split writes a float
+//   partial tile and a second kernel adds the splits in split order (bitwise
+//   reproducible) and writes half KRSC.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM
+// allocation, warps 2-5 = epilogue (TMEM -> registers -> half -> shared -> TMA
+// store, or float partial -> global).  Two accumulator buffers in TMEM let the
+// epilogue of tile i overlap the main loop of tile i+1.
+#include "common.cuh"
+#include "conv.cuh"
+#include "sm100_ptx.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+
+namespace trb {
+
+__device__ int g_device_status = 0;   // first device-side failure code, 0 = none
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kATileBytes = 128 * 128;    // 128 pixels x 64 halfs
+constexpr int kStageTileBytes = 64 * 128; // wgrad: 64 pixels x 64 halfs
+constexpr int kSmemBudget = 227 * 1024;
+
+enum StatusCode {
+    kStatusProducerTimeout = 1,
+    kStatusMmaTimeout = 2,
+    kStatusEpilogueTimeout = 3,
+};
+
+struct TileShape {
+    int bw, bh, bn;       // box extents along w, h, n (product = pixels per tile)
+    int tw, th, tn;       // tiles along w, h, n
+};
+
+// Box of `pixels` image positions with the least padding; ties go to the widest box.
+TileShape pick_tile(int n, int h, int w, int pixels) {
+    TileShape best{};
+    long best_cost = -1;
+    for (int bw = pixels; bw >= 1; bw >>= 1)
+        for (int bh = pixels / bw; bh >= 1; bh >>= 1) {
+            const int bn = pixels / (bw * bh);
+            if (bw > 256 || bh > 256 || bn > 256) continue;
+            const int tw = (w + bw - 1) / bw, th = (h + bh - 1) / bh, tn = (n + bn - 1) / bn;
+            const long cost = (long)tw * bw * th * bh * tn * bn;
+            if (best_cost < 0 || cost < best_cost) {
+                best_cost = cost;
+                best = TileShape{bw, bh, bn, tw, th, tn};
+            }
+        }
+    return best;
+}
+
+// ------------------------------------------------------------------ tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// Half tensor, `rank` dims (innermost first), 128-byte swizzle, zero fill.
+int make_tmap(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+              const uint32_t* box, const char* what) {
+    EncodeTiledFn fn = encode_fn();
+    TRB_REQUIRE(fn, TRB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t gdim[5];
+    cuuint64_t gstr[4];
+    cuuint32_t bx[5], es[5];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        bx[i] = box[i];
+        es[i] = 1;
+        if (i > 0) gstr[i - 1] = strides_bytes[i];
+    }
+    const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim,
+                          gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TRB_REQUIRE(r == CUDA_SUCCESS, TRB200_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what,
+                (int)r);
+    return TRB200_OK;
+}
+
+// NHWC half activation [n,h,w,c] viewed as (c, w, h, n) with a {64, bw, bh, bn} box.
+int make_act_tmap(CUtensorMap* m, const void* base, int n, int h, int w, int c, const TileShape& t,
+                  const char* what) {
+    const uint64_t dims[4] = {(uint64_t)c, (uint64_t)w, (uint64_t)h, (uint64_t)n};
+    const uint64_t str[4] = {2, (uint64_t)c * 2, (uint64_t)w * c * 2, (uint64_t)h * w * c * 2};
+    const uint32_t box[4] = {64, (uint32_t)t.bw, (uint32_t)t.bh, (uint32_t)t.bn};
+    return make_tmap(m, base, 4, dims, str, box, what);
+}
+
+// ------------------------------------------------------------------ shared helpers
+struct PipeState {
+    int stage = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void advance(int stages) {
+        if (++stage == stages) { stage = 0; phase ^= 1u; }
+    }
+};
+
+__device__ __forceinline__ void abort_drain(volatile int* abort_flag) {
+    // after a failed wait: give copies already in flight time to land before the
+    // block gives its shared memory back
+    if (*abort_flag) {
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+}
+
+// ------------------------------------------------------------------ dgrad / fprop kernel
+struct FpropParams {
+    int cin_slices;      // Cin / 64
+    int n_tiles;         // Cout / NT
+    int m_tiles;         // tw * th * tn
+    int tw, th;          // tiles along w, h
+    int bw, bh, bn;
+    int b_tap_is_dim1;   // 1: filter view dims (ci, tap, co) [KRSC as is]; 0: (ci, co, tap)
+};
+
+template <int NT>
+struct FpropSmem {
+    static constexpr int kBTileBytes = NT * 128;
+    static constexpr int kStageBytes = kATileBytes + kBTileBytes;
+    static constexpr int kEpiBytes = 2 * kATileBytes;
+    static constexpr int kStages = (kSmemBudget - 2048 - kEpiBytes) / kStageBytes;
+    static constexpr int kTotal = kStages * kStageBytes + kEpiBytes + 2048;   // + alignment slack and barriers
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kThreads, 1)
+conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_w,
+                     const __grid_constant__ CUtensorMap tm_out, const FpropParams p, int* status) {
+    using L = FpropSmem<NT>;
+    constexpr int kStages = L::kStages;
+    constexpr uint32_t kTmemCols = 2 * NT;
+    extern __shared__ unsigned char smem_dyn[];
+    // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows
+    const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    const uint32_t a_base = base;
+    const uint32_t b_base = base + kStages * kATileBytes;
+    const uint32_t epi_base = b_base + kStages * L::kBTileBytes;
+    const uint32_t bar_base = epi_base + L::kEpiBytes;
+    // barriers: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+    auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), kEpiThreads); }
+        fence_barrier_init();
+        prefetch_tmap(&tm_in);
+        prefetch_tmap(&tm_w);
+        prefetch_tmap(&tm_out);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&s_tmem_base), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+    volatile int* abort_flag = &s_abort;
+
+    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int ksteps = 9 * p.cin_slices;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            PipeState ps;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int nt = tile % p.n_tiles, mt = tile / p.n_tiles;
+                const int w0 = (mt % p.tw) * p.bw, h0 = ((mt / p.tw) % p.th) * p.bh;
+                const int n0 = (mt / (p.tw * p.th)) * p.bn;
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    const int tap = ks / p.cin_slices, slice = ks % p.cin_slices;
+                    const int r = tap / 3, s = tap % 3;
+                    ok = mbar_wait(empty_bar(ps.stage), ps.phase ^ 1u, abort_flag, status, kStatusProducerTimeout);
+                    if (!ok) break;
+                    mbar_expect_tx(full_bar(ps.stage), L::kStageBytes);
+                    tma_load_4d(a_base + ps.stage * kATileBytes, &tm_in, full_bar(ps.stage), slice * 64,
+                                w0 + s - 1, h0 + r - 1, n0);
+                    if (p.b_tap_is_dim1)
+                        tma_load_3d(b_base + ps.stage * L::kBTileBytes, &tm_w, full_bar(ps.stage), slice * 64, tap,
+                                    nt * NT);
+                    else
+                        tma_load_3d(b_base + ps.stage * L::kBTileBytes, &tm_w, full_bar(ps.stage), slice * 64,
+                                    nt * NT, tap);
+                    ps.advance(kStages);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_f16(128, NT, false, false);
+            PipeState ps;
+            bool ok = true;
+            int iter = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
+                const int acc = iter & 1;
+                ok = mbar_wait(tempty_bar(acc), (((uint32_t)iter >> 1) & 1u) ^ 1u, abort_flag, status,
+                               kStatusMmaTimeout);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * NT);
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait(full_bar(ps.stage), ps.phase, abort_flag, status, kStatusMmaTimeout);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t adesc = smem_desc_sw128(a_base + ps.stage * kATileBytes, 16, 1024);
+                    const uint64_t bdesc = smem_desc_sw128(b_base + ps.stage * L::kBTileBytes, 16, 1024);
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4)   // 4 x (K = 16 halfs = 32 bytes inside the 128-byte row)
+                        umma_f16(d_tmem, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc,
+                                 (ks | k4) != 0 ? 1u : 0u);
+                    umma_commit(empty_bar(ps.stage));
+                    ps.advance(kStages);
+                }
+                if (ok) umma_commit(tfull_bar(acc));
+            }
+        }
+    } else {
+        // epilogue: warp (2..5) may touch TMEM lanes [32*(warp%4), +32)
+        const int q = warp & 3;
+        const int row = q * 32 + lane;             // pixel of the tile = TMEM lane
+        const bool leader = threadIdx.x == 64;     // first epilogue thread issues the TMA stores
+        bool ok = true;
+        int iter = 0;
+        int chunk_count = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
+            const int acc = iter & 1;
+            const int nt = tile % p.n_tiles, mt = tile / p.n_tiles;
+            const int w0 = (mt % p.tw) * p.bw, h0 = ((mt / p.tw) % p.th) * p.bh;
+            const int n0 = (mt / (p.tw * p.th)) * p.bn;
+            ok = mbar_wait(tfull_bar(acc), ((uint32_t)iter >> 1) & 1u, abort_flag, status, kStatusEpilogueTimeout);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int chunk = 0; chunk < NT / 64; ++chunk, ++chunk_count) {
+                const uint32_t buf = epi_base + (uint32_t)(chunk_count & 1) * kATileBytes;
+                if (leader) tma_store_wait_read<1>();     // the store that last read this buffer is done
+                named_barrier(1, kEpiThreads);
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * NT + chunk * 64);
+                uint32_t v0[32], v1[32];
+                tmem_ld_32x32(taddr, v0);
+                tmem_ld_32x32(taddr + 32, v1);
+                tmem_ld_wait();
+                // 64 floats -> 64 halfs = eight 16-byte pieces of this pixel's 128-byte row,
+                // stored with the 128-byte swizzle the output tensor map expects
+                const uint32_t row_addr = buf + (uint32_t)row * 128u;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t* src = j < 4 ? &v0[j * 8] : &v1[(j - 4) * 8];
+                    uint32_t pk[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __half2 h = __floats2half2_rn(__uint_as_float(src[2 * e]), __uint_as_float(src[2 * e + 1]));
+                        pk[e] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    const uint32_t dst = row_addr + (uint32_t)((j ^ (row & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]),
+                                 "r"(pk[2]), "r"(pk[3])
+                                 : "memory");
+                }
+                fence_proxy_async_smem();
+                named_barrier(1, kEpiThreads);
+                if (leader) {
+                    tma_store_4d(&tm_out, buf, nt * NT + chunk * 64, w0, h0, n0);
+                    tma_store_commit();
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(tempty_bar(acc));
+        }
+        if (leader) tma_store_wait_all();
+    }
+
+    abort_drain(abort_flag);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// Filter view for dgrad: out[tap'][c][k] = W[k][2 - tap'/3][2 - tap'%3][c].
+__global__ void __launch_bounds__(256)
+dgrad_filter_view_kernel(const __half* __restrict__ w, __half* __restrict__ out, int kk, int cc) {
+    const int total = 9 * kk * cc;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int k = i % kk, c = (i / kk) % cc, tap = i / (kk * cc);
+        const int r = 2 - tap / 3, s = 2 - tap % 3;
+        out[i] = w[(((int64_t)k * 3 + r) * 3 + s) * cc + c];
+    }
+}
+
+template <int NT>
+int launch_conv3x3(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensorMap& tout, const FpropParams& p,
+                   cudaStream_t st) {
+    using L = FpropSmem<NT>;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    TRB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        TRB_CUDA_TRY(cudaFuncSetAttribute(conv3x3_igemm_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          L::kTotal));
+        attr_done[dev] = true;
+    }
+    int* status = nullptr;
+    TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status));
+    const int total = p.m_tiles * p.n_tiles;
+    const int grid = total < sm_count() ? total : sm_count();
+    conv3x3_igemm_kernel<NT><<<grid, kThreads, L::kTotal, st>>>(tin, tw, tout, p, status);
+    TRB_LAUNCH_CHECK("conv3x3_igemm_kernel");
+    return TRB200_OK;
+}
+
+int pick_nt(int cout) {
+    if (cout % 256 == 0) return 256;
+    if (cout == 128) return 128;
+    if (cout == 64) return 64;
+    return 0;
+}
+
+// in: [n,h,w,cin] half; filter view described by (wv, tap_is_dim1); out: [n,h,w,cout] half.
+int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int n, int h, int w, int cin, int cout,
+                cudaStream_t st) {
+    const int nt = pick_nt(cout);
+    TRB_REQUIRE(nt != 0 && cin % 64 == 0, TRB200_ERR_UNSUPPORTED, "conv3x3 igemm: cin=%d cout=%d not covered", cin,
+                cout);
+    const TileShape t = pick_tile(n, h, w, 128);
+    CUtensorMap tin, tw, tout;
+    int rc = make_act_tmap(&tin, in, n, h, w, cin, t, "conv input");
+    if (rc) return rc;
+    rc = make_act_tmap(&tout, out, n, h, w, cout, t, "conv output");
+    if (rc) return rc;
+    if (tap_is_dim1) {
+        // KRSC as stored: (ci, tap, co)
+        const uint64_t dims[3] = {(uint64_t)cin, 9, (uint64_t)cout};
+        const uint64_t str[3] = {2, (uint64_t)cin * 2, (uint64_t)9 * cin * 2};
+        const uint32_t box[3] = {64, 1, (uint32_t)nt};
+        rc = make_tmap(&tw, wv, 3, dims, str, box, "filters (ci,tap,co)");
+    } else {
+        const uint64_t dims[3] = {(uint64_t)cin, (uint64_t)cout, 9};
+        const uint64_t str[3] = {2, (uint64_t)cin * 2, (uint64_t)cout * cin * 2};
+        const uint32_t box[3] = {64, (uint32_t)nt, 1};
+        rc = make_tmap(&tw, wv, 3, dims, str, box, "filters (ci,co,tap)");
+    }
+    if (rc) return rc;
+    FpropParams p;
+    p.cin_slices = cin / 64;
+    p.n_tiles = cout / nt;
+    p.m_tiles = t.tw * t.th * t.tn;
+    p.tw = t.tw; p.th = t.th;
+    p.bw = t.bw; p.bh = t.bh; p.bn = t.bn;
+    p.b_tap_is_dim1 = tap_is_dim1;
+    if (nt == 256) return launch_conv3x3<256>(tin, tw, tout, p, st);
+    if (nt == 128) return launch_conv3x3<128>(tin, tw, tout, p, st);
+    return launch_conv3x3<64>(tin, tw, tout, p, st);
+}
+
+// ------------------------------------------------------------------ wgrad kernel
+struct WgradParams {
+    int cblocks;        // C / 64
+    int units;          // 9 * cblocks  (unit u: tap = u / cblocks, cblock = u % cblocks)
+    int m_tiles;        // ceil(units / 2)
+    int n_tiles;        // K / NT
+    int splits;
+    int pix_tiles;      // tw * th * tn
+    int tw, th;
+    int bw, bh, bn;
+};
+
+template <int NT>
+struct WgradSmem {
+    static constexpr int kABytes = 2 * kStageTileBytes;            // two units
+    static constexpr int kBBytes = (NT / 64) * kStageTileBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStagesRaw = (kSmemBudget - 2048) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+    static constexpr int kTotal = kStages * kStageBytes + 2048;
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kThreads, 1)
+wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
+                   float* __restrict__ partial, const WgradParams p, int* status) {
+    using L = WgradSmem<NT>;
+    constexpr int kStages = L::kStages;
+    constexpr uint32_t kTmemCols = NT < 32 ? 32 : NT;
+    extern __shared__ unsigned char smem_dyn[];
+    const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    const uint32_t a_base = base;
+    const uint32_t b_base = base + kStages * L::kABytes;
+    const uint32_t bar_base = b_base + kStages * L::kBBytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    const uint32_t done_bar = bar_base + 8u * (2 * kStages);
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(done_bar, 1);
+        fence_barrier_init();
+        prefetch_tmap(&tm_x);
+        prefetch_tmap(&tm_dy);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&s_tmem_base), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+    volatile int* abort_flag = &s_abort;
+
+    // work item -> (split, m tile, n tile)
+    const int item = blockIdx.x;
+    const int nt = item % p.n_tiles;
+    const int mt = (item / p.n_tiles) % p.m_tiles;
+    const int split = item / (p.n_tiles * p.m_tiles);
+    const int pt0 = (int)((long)p.pix_tiles * split / p.splits);
+    const int pt1 = (int)((long)p.pix_tiles * (split + 1) / p.splits);
+    const int u0 = mt * 2;
+    const int u1 = (u0 + 1 < p.units) ? u0 + 1 : u0;   // odd unit count: the last tile repeats its unit
+
+    if (warp == 0) {
+        if (lane == 0) {
+            PipeState ps;
+            for (int pt = pt0; pt < pt1; ++pt) {
+                const int w0 = (pt % p.tw) * p.bw, h0 = ((pt / p.tw) % p.th) * p.bh;
+                const int n0 = (pt / (p.tw * p.th)) * p.bn;
+                if (!mbar_wait(empty_bar(ps.stage), ps.phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                mbar_expect_tx(full_bar(ps.stage), L::kStageBytes);
+                const uint32_t a_dst = a_base + ps.stage * L::kABytes;
+                const uint32_t b_dst = b_base + ps.stage * L::kBBytes;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int u = j == 0 ? u0 : u1;
+                    const int tap = u / p.cblocks, cb = u % p.cblocks;
+                    tma_load_4d(a_dst + j * kStageTileBytes, &tm_x, full_bar(ps.stage), cb * 64,
+                                w0 + tap % 3 - 1, h0 + tap / 3 - 1, n0);
+                }
+#pragma unroll
+                for (int j = 0; j < NT / 64; ++j)
+                    tma_load_4d(b_dst + j * kStageTileBytes, &tm_dy, full_bar(ps.stage), nt * NT + j * 64, w0, h0, n0);
+                ps.advance(kStages);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_f16(128, NT, true, true);
+            PipeState ps;
+            bool ok = true;
+            for (int pt = pt0; pt < pt1; ++pt) {
+                ok = mbar_wait(full_bar(ps.stage), ps.phase, abort_flag, status, kStatusMmaTimeout);
+                if (!ok) break;
+                tc_fence_after();
+                // MN-major: 64-element blocks of M/N are one 8 KB tile apart, 8 pixels are 1024 bytes apart
+                const uint64_t adesc = smem_desc_sw128(a_base + ps.stage * L::kABytes, kStageTileBytes, 1024);
+                const uint64_t bdesc = smem_desc_sw128(b_base + ps.stage * L::kBBytes, kStageTileBytes, 1024);
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4)   // 4 x (K = 16 pixels = 2048 bytes)
+                    umma_f16(tmem_base, adesc + (uint64_t)(k4 * 128), bdesc + (uint64_t)(k4 * 128), idesc,
+                             (pt > pt0 || k4 > 0) ? 1u : 0u);
+                umma_commit(empty_bar(ps.stage));
+                ps.advance(kStages);
+            }
+            if (ok) umma_commit(done_bar);
+        }
+    } else {
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        float* dst = partial + ((size_t)item * 128 + row) * NT;
+        if (pt1 > pt0) {
+            if (mbar_wait(done_bar, 0, abort_flag, status, kStatusEpilogueTimeout)) {
+                tc_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < NT; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        reinterpret_cast<float4*>(dst + c0)[j] =
+                            make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                        __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                }
+            }
+        } else {
+            for (int c0 = 0; c0 < NT; c0 += 4) *reinterpret_cast<float4*>(dst + c0) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+
+    abort_drain(abort_flag);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// dW[k][tap][c] = half(sum over splits, in split order, of partial[split][mt][nt][row][col]).
+// One block = 32 rows (c) x 32 cols (k) of one partial tile, transposed through
+// shared memory so that both the reads (along k) and the writes (along c) coalesce.
+__global__ void __launch_bounds__(256)
+wgrad_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ dw, WgradParams p, int nt_cols, int kk,
+                    int cc) {
+    __shared__ float tile[32][33];
+    const int mt = blockIdx.z / p.n_tiles, nt = blockIdx.z % p.n_tiles;
+    const int r0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const size_t tile_elems = (size_t)128 * nt_cols;
+    const size_t split_stride = (size_t)p.m_tiles * p.n_tiles * tile_elems;
+    const size_t tile_off = ((size_t)mt * p.n_tiles + nt) * tile_elems;
+    for (int rr = ty; rr < 32; rr += 8) {
+        float acc = 0.f;
+        const size_t off = tile_off + (size_t)(r0 + rr) * nt_cols + c0 + tx;
+        for (int s = 0; s < p.splits; ++s) acc += partial[(size_t)s * split_stride + off];
+        tile[rr][tx] = acc;
+    }
+    __syncthreads();
+    const int unit = mt * 2 + r0 / 64;
+    if (unit >= p.units) return;
+    const int tap = unit / p.cblocks, cb = unit % p.cblocks;
+    for (int cj = ty; cj < 32; cj += 8) {
+        const int k = nt * nt_cols + c0 + cj;
+        const int c = cb * 64 + (r0 % 64) + tx;
+        dw[((size_t)k * 9 + tap) * cc + c] = __float2half_rn(tile[tx][cj]);
+    }
+    (void)kk;
+}
+
+template <int NT>
+int launch_wgrad(const CUtensorMap& tx, const CUtensorMap& tdy, float* partial, const WgradParams& p, cudaStream_t st) {
+    using L = WgradSmem<NT>;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    TRB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        TRB_CUDA_TRY(cudaFuncSetAttribute(wgrad_igemm_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          L::kTotal));
+        attr_done[dev] = true;
+    }
+    int* status = nullptr;
+    TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status));
+    const int grid = p.m_tiles * p.n_tiles * p.splits;
+    wgrad_igemm_kernel<NT><<<grid, kThreads, L::kTotal, st>>>(tx, tdy, partial, p, status);
+    TRB_LAUNCH_CHECK("wgrad_igemm_kernel");
+    return TRB200_OK;
+}
+
+WgradParams wgrad_plan(const trb200_conv_desc& d, int nt, const TileShape& t) {
+    WgradParams p;
+    p.cblocks = d.c / 64;
+    p.units = 9 * p.cblocks;
+    p.m_tiles = (p.units + 1) / 2;
+    p.n_tiles = d.k / nt;
+    p.pix_tiles = t.tw * t.th * t.tn;
+    const int tiles = p.m_tiles * p.n_tiles;
+    int splits = sm_count() / tiles;
+    if (splits < 1) splits = 1;
+    if (splits > p.pix_tiles) splits = p.pix_tiles;
+    p.splits = splits;
+    p.tw = t.tw; p.th = t.th;
+    p.bw = t.bw; p.bh = t.bh; p.bn = t.bn;
+    return p;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ entry points of this file
+bool igemm_supports(const trb200_conv_desc& d, int which) {
+    if (d.r != 3 || d.s != 3 || d.pad_h != 1 || d.pad_w != 1 || d.stride_h != 1 || d.stride_w != 1) return false;
+    if (d.c % 64 != 0 || d.k % 64 != 0) return false;
+    if (d.n < 1 || d.h < 1 || d.w < 1) return false;
+    if (which == 0) return pick_nt(d.k) != 0;     // wgrad: N dimension = k
+    if (which == 1) return pick_nt(d.c) != 0;     // dgrad: N dimension = c
+    return pick_nt(d.k) != 0;                     // fprop: N dimension = k
+}
+
+size_t igemm_dgrad_workspace(const trb200_conv_desc& d) {
+    return (size_t)align_up((int64_t)9 * d.c * d.k * 2, 256);
+}
+
+size_t igemm_wgrad_workspace(const trb200_conv_desc& d) {
+    const int nt = pick_nt(d.k);
+    const TileShape t = pick_tile(d.n, d.h, d.w, 64);
+    const WgradParams p = wgrad_plan(d, nt, t);
+    return (size_t)p.splits * p.m_tiles * p.n_tiles * 128 * nt * sizeof(float);
+}
+
+int igemm_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes,
+                cudaStream_t st) {
+    const size_t need = igemm_dgrad_workspace(d);
+    TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, "conv_dgrad: workspace of %zu bytes needed, %zu given",
+                need, ws_bytes);
+    TRB_REQUIRE(aligned16(ws), TRB200_ERR_INVALID_ARGUMENT, "conv_dgrad: workspace must be 16-byte aligned");
+    const int total = 9 * d.k * d.c;
+    int blocks = (total + 255) / 256;
+    if (blocks > sm_count() * 4) blocks = sm_count() * 4;
+    dgrad_filter_view_kernel<<<blocks, 256, 0, st>>>(static_cast<const __half*>(w), static_cast<__half*>(ws), d.k, d.c);
+    TRB_LAUNCH_CHECK("dgrad_filter_view_kernel");
+    // in = dY [n,h,w,k], filter view (ci = k, co = c, tap), out = dX [n,h,w,c]
+    return conv3x3_run(dy, ws, 0, dx, d.n, d.h, d.w, d.k, d.c, st);
+}
+
+int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, cudaStream_t st) {
+    return conv3x3_run(x, w, 1, y, d.n, d.h, d.w, d.c, d.k, st);
+}
+
+int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* ws, size_t ws_bytes,
+                cudaStream_t st) {
+    const int nt = pick_nt(d.k);
+    TRB_REQUIRE(nt != 0, TRB200_ERR_UNSUPPORTED, "conv_wgrad igemm: k=%d not covered", d.k);
+    const size_t need = igemm_wgrad_workspace(d);
+    TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, "conv_wgrad: workspace of %zu bytes needed, %zu given",
+                need, ws_bytes);
+    TRB_REQUIRE(aligned16(ws), TRB200_ERR_INVALID_ARGUMENT, "conv_wgrad: workspace must be 16-byte aligned");
+    const TileShape t = pick_tile(d.n, d.h, d.w, 64);
+    const WgradParams p = wgrad_plan(d, nt, t);
+    CUtensorMap tx, tdy;
+    int rc = make_act_tmap(&tx, x, d.n, d.h, d.w, d.c, t, "wgrad x");
+    if (rc) return rc;
+    rc = make_act_tmap(&tdy, dy, d.n, d.h, d.w, d.k, t, "wgrad dy");
+    if (rc) return rc;
+    float* partial = static_cast<float*>(ws);
+    if (nt == 256) rc = launch_wgrad<256>(tx, tdy, partial, p, st);
+    else if (nt == 128) rc = launch_wgrad<128>(tx, tdy, partial, p, st);
+    else rc = launch_wgrad<64>(tx, tdy, partial, p, st);
+    if (rc) return rc;
+    dim3 grid(nt / 32, 4, p.m_tiles * p.n_tiles);
+    wgrad_reduce_kernel<<<grid, 256, 0, st>>>(partial, static_cast<__half*>(dw), p, nt, d.k, d.c);
+    TRB_LAUNCH_CHECK("wgrad_reduce_kernel");
+    return TRB200_OK;
+}
+
+int device_status_read_and_clear(int* out) {
+    int v = 0;
+    TRB_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)));
+    if (v != 0) {
+        const int zero = 0;
+        TRB_CUDA_TRY(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+    }
+    *out = v;
+    return TRB200_OK;
+}
+
+}  // namespace trb

@@ -1,0 +1,339 @@
+"""Host-side mirror of the reference launchers for the hot path.
+
+Each function takes torch CUDA tensors (device memory and streams are torch's;
+all arithmetic is in libtrb200.so), checks shapes the way the reference
+launcher derives them from its DTensors, and makes ONE C-ABI call.
+
+    cbr_amp_bwd            launch_cbr_amp_bwd_cuda             cbr_op.cpp:1359-1522
+    cbr_amp_bwd(dx=None)   launch_cbr_amp_bwd_first_layer_cuda cbr_op.cpp:1528-1651
+    softmax_ce_amp_fwd     launch_softmax_ce_amp_fwd_cuda      softmax_ce_op.cpp:409-455
+    softmax_ce_amp_bwd     launch_softmax_ce_amp_bwd_cuda      softmax_ce_op.cpp:591-627
+    softmax_ce_amp_fused   both nodes in one kernel
+    mean_allreduce         launch_allreduce_cuda_impl          allreduce_op.cpp:37-105
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import CbrBwdArgs, ConvDesc, check
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream(stream=None):
+    s = torch.cuda.current_stream() if stream is None else stream
+    return C.c_void_p(s.cuda_stream)
+
+
+def _need(t, dtype, name, ndim=None):
+    if not (isinstance(t, torch.Tensor) and t.is_cuda):
+        raise TypeError(f"{name}: CUDA tensor expected")
+    if t.dtype != dtype:
+        raise TypeError(f"{name}: dtype {dtype} expected, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name}: compact (contiguous) tensor expected")
+    if ndim is not None and t.dim() != ndim:
+        raise ValueError(f"{name}: {ndim} dimensions expected, got {tuple(t.shape)}")
+
+
+@dataclass
+class ConvGeometry:
+    """ConvParams of the reference (include/renaissance/graph/op_kind.h:42-52)."""
+    n: int
+    h: int
+    w: int
+    c: int
+    k: int
+    r: int = 3
+    s: int = 3
+    pad: int = 1
+    stride: int = 1
+
+    def desc(self) -> ConvDesc:
+        return ConvDesc(self.n, self.h, self.w, self.c, self.k, self.r, self.s,
+                        self.pad, self.pad, self.stride, self.stride)
+
+    @property
+    def oh(self):
+        return (self.h + 2 * self.pad - self.r) // self.stride + 1
+
+    @property
+    def ow(self):
+        return (self.w + 2 * self.pad - self.s) // self.stride + 1
+
+
+class Workspace:
+    """Grow-only device scratch, the DeviceContext::ensure_workspace_grow contract
+    (src/backend/device_context.cpp:379-428): sized in the warm-up call, reused after."""
+
+    def __init__(self, device=None):
+        self.device = device
+        self.buf = None
+
+    def ensure(self, nbytes: int) -> torch.Tensor:
+        nbytes = max(int(nbytes), 256)
+        if self.buf is None or self.buf.numel() < nbytes:
+            self.buf = torch.empty(nbytes, dtype=torch.uint8, device=self.device or "cuda")
+        return self.buf
+
+
+_default_ws: dict[int, Workspace] = {}
+
+
+def default_workspace() -> Workspace:
+    dev = torch.cuda.current_device()
+    if dev not in _default_ws:
+        _default_ws[dev] = Workspace(torch.device("cuda", dev))
+    return _default_ws[dev]
+
+
+def device_status() -> None:
+    """Synchronise, then raise if any kernel's bounded device-side wait gave up."""
+    torch.cuda.synchronize()
+    check(_lib.load().trb200_device_status())
+
+
+def set_conv_backend(direct_only: bool) -> None:
+    check(_lib.load().trb200_set_conv_backend(1 if direct_only else 0))
+
+
+def conv_uses_tensor_cores(g: ConvGeometry, which: str) -> bool:
+    idx = {"wgrad": 0, "dgrad": 1, "fprop": 2}[which]
+    d = g.desc()
+    return bool(_lib.load().trb200_conv_uses_tensor_cores(C.byref(d), idx))
+
+
+# --------------------------------------------------------------------------- BN + ReLU backward
+
+def bnrelu_bwd(dy, mask_bits, conv_out, gamma, saved_mean, saved_inv_std, dconv=None,
+               workspace: Workspace | None = None, stream=None, want_dconv=True):
+    """dconv, dgamma, dbeta of the block's BN+ReLU (cbr_op.cpp:1259-1353)."""
+    lib = _lib.load()
+    _need(dy, torch.float16, "dy")
+    _need(conv_out, torch.float16, "conv_out")
+    _need(mask_bits, torch.uint8, "mask_bits")
+    for t, nm in ((gamma, "gamma"), (saved_mean, "saved_mean"), (saved_inv_std, "saved_inv_std")):
+        _need(t, torch.float32, nm)
+    c = dy.shape[-1]
+    m = dy.numel() // c
+    if conv_out.shape != dy.shape:
+        raise ValueError("conv_out and dy must have the same shape")
+    if mask_bits.numel() * 8 < dy.numel():
+        raise ValueError("mask_bits holds fewer bits than dy has elements")
+    if dconv is None and want_dconv:
+        dconv = torch.empty_like(dy)
+    dgamma = torch.empty(c, dtype=torch.float32, device=dy.device)
+    dbeta = torch.empty(c, dtype=torch.float32, device=dy.device)
+    ws = (workspace or default_workspace()).ensure(lib.trb200_bnrelu_bwd_workspace_bytes(m, c))
+    check(lib.trb200_bnrelu_bwd(_ptr(dy), _ptr(mask_bits), _ptr(conv_out), _ptr(gamma), _ptr(saved_mean),
+                                _ptr(saved_inv_std), _ptr(dconv), _ptr(dgamma), _ptr(dbeta), m, c,
+                                _ptr(ws), ws.numel(), _stream(stream)))
+    return dconv, dgamma, dbeta
+
+
+# --------------------------------------------------------------------------- conv gradients
+
+def conv_wgrad(g: ConvGeometry, dy, x, dw=None, workspace=None, stream=None):
+    lib = _lib.load()
+    _need(dy, torch.float16, "dy", 4)
+    _need(x, torch.float16, "x", 4)
+    if tuple(x.shape) != (g.n, g.h, g.w, g.c) or tuple(dy.shape) != (g.n, g.oh, g.ow, g.k):
+        raise ValueError("conv_wgrad: tensor shapes do not match the geometry")
+    if dw is None:
+        dw = torch.empty((g.k, g.r, g.s, g.c), dtype=torch.float16, device=x.device)
+    d = g.desc()
+    ws = (workspace or default_workspace()).ensure(lib.trb200_conv_wgrad_workspace_bytes(C.byref(d)))
+    check(lib.trb200_conv_wgrad(C.byref(d), _ptr(dy), _ptr(x), _ptr(dw), _ptr(ws), ws.numel(), _stream(stream)))
+    return dw
+
+
+def conv_dgrad(g: ConvGeometry, dy, w, dx=None, workspace=None, stream=None):
+    lib = _lib.load()
+    _need(dy, torch.float16, "dy", 4)
+    _need(w, torch.float16, "w", 4)
+    if tuple(w.shape) != (g.k, g.r, g.s, g.c) or tuple(dy.shape) != (g.n, g.oh, g.ow, g.k):
+        raise ValueError("conv_dgrad: tensor shapes do not match the geometry")
+    if dx is None:
+        dx = torch.empty((g.n, g.h, g.w, g.c), dtype=torch.float16, device=dy.device)
+    d = g.desc()
+    ws = (workspace or default_workspace()).ensure(lib.trb200_conv_dgrad_workspace_bytes(C.byref(d)))
+    check(lib.trb200_conv_dgrad(C.byref(d), _ptr(dy), _ptr(w), _ptr(dx), _ptr(ws), ws.numel(), _stream(stream)))
+    return dx
+
+
+def conv_fprop(g: ConvGeometry, x, w, y=None, stream=None):
+    lib = _lib.load()
+    _need(x, torch.float16, "x", 4)
+    _need(w, torch.float16, "w", 4)
+    if tuple(x.shape) != (g.n, g.h, g.w, g.c) or tuple(w.shape) != (g.k, g.r, g.s, g.c):
+        raise ValueError("conv_fprop: tensor shapes do not match the geometry")
+    if y is None:
+        y = torch.empty((g.n, g.oh, g.ow, g.k), dtype=torch.float16, device=x.device)
+    d = g.desc()
+    check(lib.trb200_conv_fprop(C.byref(d), _ptr(x), _ptr(w), _ptr(y), _stream(stream)))
+    return y
+
+
+# --------------------------------------------------------------------------- whole block
+
+@dataclass
+class BlockStreams:
+    """The three compute streams of the reference's DeviceContext and the per-stream
+    `last_done_event`s of its MultiStreamCaptureState (capture_multi_stream.h:25-46)."""
+    bn: torch.cuda.Stream
+    wgrad: torch.cuda.Stream
+    dgrad: torch.cuda.Stream
+    ev_bn: torch.cuda.Event
+    ev_wgrad: torch.cuda.Event
+    ev_dgrad: torch.cuda.Event
+
+    @staticmethod
+    def create(device=None) -> "BlockStreams":
+        mk = lambda: torch.cuda.Stream(device=device)
+        ev = lambda: torch.cuda.Event(enable_timing=False)
+        out = BlockStreams(mk(), mk(), mk(), ev(), ev(), ev())
+        # torch creates the underlying cudaEvent lazily: record once so that the handle exists
+        for e, s in ((out.ev_bn, out.bn), (out.ev_wgrad, out.wgrad), (out.ev_dgrad, out.dgrad)):
+            e.record(s)
+        return out
+
+
+def cbr_amp_bwd(g: ConvGeometry, dy, w, gamma, saved_mean, saved_inv_std, mask_bits, x, conv_out,
+                bn_scratch=None, dw=None, first_layer=False, streams: BlockStreams | None = None,
+                workspace=None, stream=None):
+    """CBR_AMP_BWD / CBR_AMP_BWD_FIRST_LAYER.
+
+    Node ids of the reference: in [dY, W16, gamma, saved_mean, saved_inv_var, mask, X],
+    out [dX (= X's buffer), dW16, dgamma, dbeta, conv_output, bn_output]
+    (cbr_op.cpp:1365-1366).  As there, dX is written IN PLACE over ``x`` (returned as
+    ``dx``) unless ``first_layer``.  Returns dict(dx, dw, dgamma, dbeta, dconv)."""
+    lib = _lib.load()
+    _need(dy, torch.float16, "dy", 4)
+    _need(w, torch.float16, "w", 4)
+    _need(x, torch.float16, "x", 4)
+    _need(conv_out, torch.float16, "conv_out", 4)
+    _need(mask_bits, torch.uint8, "mask_bits")
+    for t, nm in ((gamma, "gamma"), (saved_mean, "saved_mean"), (saved_inv_std, "saved_inv_std")):
+        _need(t, torch.float32, nm)
+    if tuple(x.shape) != (g.n, g.h, g.w, g.c) or tuple(dy.shape) != (g.n, g.oh, g.ow, g.k) \
+            or tuple(w.shape) != (g.k, g.r, g.s, g.c) or conv_out.shape != dy.shape:
+        raise ValueError("cbr_amp_bwd: tensor shapes do not match the geometry")
+    if bn_scratch is None:
+        bn_scratch = torch.empty_like(dy)
+    if dw is None:
+        dw = torch.empty_like(w)
+    dgamma = torch.empty(g.k, dtype=torch.float32, device=x.device)
+    dbeta = torch.empty(g.k, dtype=torch.float32, device=x.device)
+    d = g.desc()
+    ws = (workspace or default_workspace()).ensure(lib.trb200_cbr_bwd_workspace_bytes(C.byref(d), int(first_layer)))
+    a = CbrBwdArgs()
+    a.conv = d
+    a.dy, a.w, a.gamma = dy.data_ptr(), w.data_ptr(), gamma.data_ptr()
+    a.saved_mean, a.saved_inv_std = saved_mean.data_ptr(), saved_inv_std.data_ptr()
+    a.mask_bits, a.x = mask_bits.data_ptr(), x.data_ptr()
+    a.dx = None if first_layer else x.data_ptr()
+    a.dw, a.dgamma, a.dbeta = dw.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr()
+    a.conv_out, a.bn_scratch = conv_out.data_ptr(), bn_scratch.data_ptr()
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    if streams is None:
+        s = (torch.cuda.current_stream() if stream is None else stream).cuda_stream
+        a.stream_bn = a.stream_wgrad = a.stream_dgrad = s
+        a.ev_bn = a.ev_wgrad = a.ev_dgrad = None
+    else:
+        a.stream_bn, a.stream_wgrad, a.stream_dgrad = (streams.bn.cuda_stream, streams.wgrad.cuda_stream,
+                                                      streams.dgrad.cuda_stream)
+        a.ev_bn, a.ev_wgrad, a.ev_dgrad = (streams.ev_bn.cuda_event, streams.ev_wgrad.cuda_event,
+                                           streams.ev_dgrad.cuda_event)
+    check(lib.trb200_cbr_bwd(C.byref(a)))
+    return dict(dx=None if first_layer else x, dw=dw, dgamma=dgamma, dbeta=dbeta, dconv=bn_scratch)
+
+
+# --------------------------------------------------------------------------- softmax + CE
+
+def softmax_ce_amp_fwd(logits, labels, label_smoothing, probs=None, want_probs=True, stream=None):
+    """SOFTMAX_CE_AMP_FWD: returns dict(loss, inv_scaling, probs, loss_partial) (device tensors)."""
+    lib = _lib.load()
+    _need(logits, torch.float16, "logits", 2)
+    _need(labels, torch.int32, "labels", 1)
+    _need(label_smoothing, torch.float32, "label_smoothing")
+    b, k = logits.shape
+    dev = logits.device
+    if probs is None and want_probs:
+        probs = torch.empty((b, k), dtype=torch.float32, device=dev)
+    part = torch.empty(b, dtype=torch.float32, device=dev)
+    loss = torch.empty(1, dtype=torch.float32, device=dev)
+    inv = torch.empty(1, dtype=torch.float32, device=dev)
+    check(lib.trb200_softmax_ce_fwd(_ptr(logits), logits.stride(0), _ptr(labels), _ptr(label_smoothing),
+                                    _ptr(probs), 0 if probs is None else probs.stride(0),
+                                    _ptr(part), _ptr(loss), _ptr(inv), b, k, _stream(stream)))
+    return dict(loss=loss, inv_scaling=inv, probs=probs, loss_partial=part)
+
+
+def softmax_ce_amp_bwd(probs, labels, scaling, inv_scaling, label_smoothing, dlogits=None, stream=None):
+    """SOFTMAX_CE_AMP_BWD: d_logits half [B, C]."""
+    lib = _lib.load()
+    _need(probs, torch.float32, "probs", 2)
+    _need(labels, torch.int32, "labels", 1)
+    b, k = probs.shape
+    if dlogits is None:
+        dlogits = torch.empty((b, k), dtype=torch.float16, device=probs.device)
+    check(lib.trb200_softmax_ce_bwd(_ptr(probs), probs.stride(0), _ptr(labels), _ptr(scaling), _ptr(inv_scaling),
+                                    _ptr(label_smoothing), _ptr(dlogits), dlogits.stride(0), b, k, _stream(stream)))
+    return dlogits
+
+
+def softmax_ce_amp_fused(logits, labels, scaling, label_smoothing, want_probs=False, dlogits=None, stream=None):
+    """FWD + BWD nodes in one pass over the logits."""
+    lib = _lib.load()
+    _need(logits, torch.float16, "logits", 2)
+    _need(labels, torch.int32, "labels", 1)
+    b, k = logits.shape
+    dev = logits.device
+    probs = torch.empty((b, k), dtype=torch.float32, device=dev) if want_probs else None
+    if dlogits is None:
+        dlogits = torch.empty((b, k), dtype=torch.float16, device=dev)
+    part = torch.empty(b, dtype=torch.float32, device=dev)
+    loss = torch.empty(1, dtype=torch.float32, device=dev)
+    inv = torch.empty(1, dtype=torch.float32, device=dev)
+    check(lib.trb200_softmax_ce_fused(_ptr(logits), logits.stride(0), _ptr(labels), _ptr(scaling),
+                                      _ptr(label_smoothing), _ptr(probs), 0 if probs is None else probs.stride(0),
+                                      _ptr(dlogits), dlogits.stride(0), _ptr(part), _ptr(loss), _ptr(inv),
+                                      b, k, _stream(stream)))
+    return dict(loss=loss, inv_scaling=inv, probs=probs, loss_partial=part, dlogits=dlogits)
+
+
+# --------------------------------------------------------------------------- all-reduce side
+
+def scale_f32(t, factor, stream=None):
+    _need(t, torch.float32, "t")
+    check(_lib.load().trb200_scale_f32(_ptr(t), t.numel(), float(factor), _stream(stream)))
+    return t
+
+
+def cast_f16_to_f32(src, dst=None, factor=1.0, stream=None):
+    _need(src, torch.float16, "src")
+    if dst is None:
+        dst = torch.empty(src.shape, dtype=torch.float32, device=src.device)
+    check(_lib.load().trb200_cast_f16_to_f32(_ptr(src), _ptr(dst), src.numel(), float(factor), _stream(stream)))
+    return dst
+
+
+def mean_allreduce(flat_f32, group=None, stream=None):
+    """RANGE_MEAN_ALLREDUCE (allreduce_op.cpp:37-105): in-place FP32 sum over the ranks
+    with NCCL, then the 1/world scale kernel.  A single rank is a no-op, as in the
+    reference when only one GPU is used."""
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return flat_f32
+    dist.all_reduce(flat_f32, op=dist.ReduceOp.SUM, group=group)
+    if flat_f32.is_cuda:
+        scale_f32(flat_f32, 1.0 / dist.get_world_size(group), stream=stream)
+    else:   # gloo ranks on CPU (tests): same arithmetic, no CUDA kernel involved
+        flat_f32.mul_(1.0 / dist.get_world_size(group))
+    return flat_f32

@@ -1,0 +1,86 @@
+"""CPU-only checks of the C-ABI library: it loads, exports every symbol that
+include/trb200.h declares, and rejects bad arguments before touching a GPU."""
+import ctypes as C
+import os
+import subprocess
+
+import pytest
+
+from renaissance_b200 import _lib
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from renaissance_b200 import build
+    build.build()
+    return _lib.load()
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = _lib.declared_symbols()
+    assert len(names) >= 20
+    out = subprocess.check_output(["nm", "-D", "--defined-only", _lib.LIB_PATH], text=True)
+    exported = {line.split()[-1] for line in out.splitlines() if " T " in line}
+    missing = [n for n in names if n not in exported]
+    assert not missing, f"declared but not exported: {missing}"
+    for n in names:
+        assert hasattr(lib, n)
+
+
+def test_version_and_error_text(lib):
+    assert lib.trb200_version() >= 100
+    assert isinstance(lib.trb200_last_error(), bytes)
+
+
+def test_null_pointers_are_rejected_without_a_gpu(lib):
+    rc = lib.trb200_bnrelu_bwd(None, None, None, None, None, None, None, None, None, 16, 64, None, 0, None)
+    assert rc == _lib.ERR_INVALID_ARGUMENT
+    assert b"null" in lib.trb200_last_error()
+    rc = lib.trb200_softmax_ce_fwd(None, 8, None, None, None, 8, None, None, None, 4, 8, None)
+    assert rc == _lib.ERR_INVALID_ARGUMENT
+    rc = lib.trb200_cbr_bwd(None)
+    assert rc == _lib.ERR_INVALID_ARGUMENT
+    with pytest.raises(_lib.Trb200Error) as e:
+        _lib.check(rc)
+    assert e.value.code == _lib.ERR_INVALID_ARGUMENT
+
+
+def test_bad_geometry_is_rejected(lib):
+    d = _lib.ConvDesc(0, 8, 8, 64, 64, 3, 3, 1, 1, 1, 1)
+    buf = C.c_void_p(256)
+    assert lib.trb200_conv_wgrad(C.byref(d), buf, buf, buf, None, 0, None) == _lib.ERR_INVALID_ARGUMENT
+    d = _lib.ConvDesc(1, 2, 2, 64, 64, 7, 7, 0, 0, 1, 1)      # filter larger than the input
+    assert lib.trb200_conv_dgrad(C.byref(d), buf, buf, C.c_void_p(512), None, 0, None) == _lib.ERR_INVALID_ARGUMENT
+    assert lib.trb200_bnrelu_bwd_workspace_bytes(100, 12) == 0     # c not a multiple of 8
+    assert lib.trb200_set_conv_backend(7) == _lib.ERR_INVALID_ARGUMENT
+
+
+def test_tensor_core_coverage_rule(lib):
+    vgg = _lib.ConvDesc(256, 56, 56, 64, 64, 3, 3, 1, 1, 1, 1)
+    first = _lib.ConvDesc(256, 224, 224, 4, 64, 3, 3, 1, 1, 1, 1)
+    strided = _lib.ConvDesc(8, 56, 56, 64, 64, 3, 3, 1, 1, 2, 2)
+    for which in (0, 1, 2):
+        assert lib.trb200_conv_uses_tensor_cores(C.byref(vgg), which) == 1
+        assert lib.trb200_conv_uses_tensor_cores(C.byref(first), which) == 0
+        assert lib.trb200_conv_uses_tensor_cores(C.byref(strided), which) == 0
+
+
+def test_workspace_sizes_are_consistent(lib):
+    d = _lib.ConvDesc(8, 28, 28, 128, 256, 3, 3, 1, 1, 1, 1)
+    wg = lib.trb200_conv_wgrad_workspace_bytes(C.byref(d))
+    dg = lib.trb200_conv_dgrad_workspace_bytes(C.byref(d))
+    bn = lib.trb200_bnrelu_bwd_workspace_bytes(8 * 28 * 28, 256)
+    total = lib.trb200_cbr_bwd_workspace_bytes(C.byref(d), 0)
+    first = lib.trb200_cbr_bwd_workspace_bytes(C.byref(d), 1)
+    assert wg > 0 and dg >= 9 * 128 * 256 * 2 and bn > 0
+    assert total >= wg + dg + bn and first >= wg + bn and first < total
+
+
+def test_product_package_never_imports_the_oracle():
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pkg = os.path.join(root, "renaissance_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.lower(), f"{f} mentions the oracle"

@@ -1,0 +1,136 @@
+"""Convolution weight / data gradients: direct kernels (any geometry) and the
+tcgen05 implicit-GEMM kernels (3x3 s1 p1, channels % 64 == 0) against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden, rel_l2
+from gpu_util import dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand_case(seed, n, h, w, c, k, r, pad, stride):
+    rng = np.random.default_rng(seed)
+    oh = (h + 2 * pad - r) // stride + 1
+    ow = (w + 2 * pad - r) // stride + 1
+    x = rng.standard_normal((n, h, w, c)).astype(np.float16)
+    wt = (rng.standard_normal((k, r, r, c)) * np.sqrt(2.0 / (r * r * c))).astype(np.float16)
+    dy = rng.standard_normal((n, oh, ow, k)).astype(np.float16)
+    return x, wt, dy
+
+
+def _oracle(orc, x, wt, dy, pad, stride):
+    dw = orc.conv_wgrad(dy.astype(np.float32), x.astype(np.float32), wt.shape, pad=pad, stride=stride)
+    dx = orc.conv_dgrad(dy.astype(np.float32), wt.astype(np.float32), x.shape, pad=pad, stride=stride)
+    return dw, dx
+
+
+DIRECT_CASES = [
+    (1, 5, 5, 3, 8, 3, 1, 1), (2, 9, 7, 4, 8, 3, 1, 2), (1, 12, 12, 3, 8, 7, 3, 2), (2, 8, 8, 16, 24, 1, 0, 1),
+    (3, 6, 10, 8, 8, 5, 2, 1), (2, 16, 16, 4, 64, 3, 1, 1),
+]
+
+
+@pytest.mark.parametrize("n,h,w,c,k,r,pad,stride", DIRECT_CASES)
+def test_direct_kernels_match_oracle(orc, n, h, w, c, k, r, pad, stride):
+    from renaissance_b200 import ops
+    x, wt, dy = _rand_case(n * 7 + h, n, h, w, c, k, r, pad, stride)
+    ref_dw, ref_dx = _oracle(orc, x, wt, dy, pad, stride)
+    g = ops.ConvGeometry(n, h, w, c, k, r, r, pad, stride)
+    assert not ops.conv_uses_tensor_cores(g, "wgrad")
+    dw = ops.conv_wgrad(g, dev(dy), dev(x))
+    dx = ops.conv_dgrad(g, dev(dy), dev(wt))
+    torch.cuda.synchronize()
+    assert rel_l2(host(dw).astype(np.float32), ref_dw) < 2e-2
+    assert rel_l2(host(dx).astype(np.float32), ref_dx) < 2e-2
+    assert rel_l2(host(dw).astype(np.float32), ref_dw) < 2e-3 and rel_l2(host(dx).astype(np.float32), ref_dx) < 2e-3
+
+
+def test_direct_kernels_match_golden():
+    from renaissance_b200 import ops
+    g = golden("conv_fp16_3x3_s1")
+    n, h, w, c, k, ker, stride, pad, _ = (int(v) for v in g["params"])
+    geo = ops.ConvGeometry(n, h, w, c, k, ker, ker, pad, stride)
+    dw = ops.conv_wgrad(geo, dev(g["dy"], torch.float16), dev(g["x"], torch.float16))
+    dx = ops.conv_dgrad(geo, dev(g["dy"], torch.float16), dev(g["w"], torch.float16))
+    # the reference's AMP threshold is MSE <= 1e-3 (tests/op/test_conv_fwd_bwd.cpp:366)
+    assert rel_l2(host(dw).astype(np.float32), g["dw"]) < 2e-3
+    assert rel_l2(host(dx).astype(np.float32), g["dx"]) < 2e-3
+
+
+IGEMM_CASES = [
+    # n, h, w, c, k        what it exercises
+    (2, 8, 8, 64, 64),      # one tile, N tile 64
+    (1, 16, 8, 64, 128),    # N tile 128
+    (3, 7, 5, 64, 64),      # odd extents: boxes hang over every edge
+    (2, 14, 14, 128, 256),  # 14x14: tile 2x2x32 images, N tile 256, two input slices
+    (5, 12, 20, 256, 64),   # four input slices, several tiles
+    (2, 28, 28, 128, 128),
+    (1, 9, 33, 64, 512),    # two N tiles
+    (4, 14, 14, 512, 512),  # deep VGG shape at a small batch
+]
+
+
+@pytest.mark.parametrize("n,h,w,c,k", IGEMM_CASES)
+def test_tensor_core_kernels_match_oracle(orc, n, h, w, c, k):
+    from renaissance_b200 import ops
+    x, wt, dy = _rand_case(n + h * 3 + c, n, h, w, c, k, 3, 1, 1)
+    ref_dw, ref_dx = _oracle(orc, x, wt, dy, 1, 1)
+    g = ops.ConvGeometry(n, h, w, c, k)
+    assert ops.conv_uses_tensor_cores(g, "wgrad") and ops.conv_uses_tensor_cores(g, "dgrad")
+    dw = ops.conv_wgrad(g, dev(dy), dev(x))
+    dx = ops.conv_dgrad(g, dev(dy), dev(wt))
+    y = ops.conv_fprop(g, dev(x), dev(wt))
+    ops.device_status()
+    ref_y = orc.conv_fwd(x.astype(np.float32), wt.astype(np.float32))
+    assert rel_l2(host(dx).astype(np.float32), ref_dx) < 2e-3
+    assert rel_l2(host(dw).astype(np.float32), ref_dw) < 2e-3
+    assert rel_l2(host(y).astype(np.float32), ref_y) < 2e-3
+
+
+def test_tensor_core_kernels_are_bitwise_reproducible_and_agree_with_direct():
+    from renaissance_b200 import ops
+    n, h, w, c, k = 8, 28, 28, 128, 256
+    x, wt, dy = _rand_case(99, n, h, w, c, k, 3, 1, 1)
+    g = ops.ConvGeometry(n, h, w, c, k)
+    xd, wd, dyd = dev(x), dev(wt), dev(dy)
+    dw1, dx1 = ops.conv_wgrad(g, dyd, xd), ops.conv_dgrad(g, dyd, wd)
+    dw2, dx2 = ops.conv_wgrad(g, dyd, xd), ops.conv_dgrad(g, dyd, wd)
+    ops.device_status()
+    assert torch.equal(dw1, dw2) and torch.equal(dx1, dx2)
+    ops.set_conv_backend(direct_only=True)
+    try:
+        dw3, dx3 = ops.conv_wgrad(g, dyd, xd), ops.conv_dgrad(g, dyd, wd)
+    finally:
+        ops.set_conv_backend(direct_only=False)
+    torch.cuda.synchronize()
+    assert rel_l2(host(dw1).astype(np.float32), host(dw3).astype(np.float32)) < 2e-3
+    assert rel_l2(host(dx1).astype(np.float32), host(dx3).astype(np.float32)) < 2e-3
+
+
+def test_full_size_config2_against_torch_fp32():
+    """BASELINE config 2 (N=256, 56x56, C=K=64): too large for the CPU oracle in a
+    test, so the check is against torch's float32 convolution gradients on the GPU
+    plus linearity in dy."""
+    from renaissance_b200 import ops
+    n, h, w, c, k = 256, 56, 56, 64, 64
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn((n, h, w, c), generator=gen, device="cuda").half()
+    wt = (torch.randn((k, 3, 3, c), generator=gen, device="cuda") * (2.0 / (9 * c)) ** 0.5).half()
+    dy = torch.randn((n, h, w, k), generator=gen, device="cuda").half()
+    g = ops.ConvGeometry(n, h, w, c, k)
+    dw = ops.conv_wgrad(g, dy, x)
+    dx = ops.conv_dgrad(g, dy, wt)
+    dx_half = ops.conv_dgrad(g, (dy.float() * 0.5).half(), wt)
+    ops.device_status()
+    assert float((dx_half.float() * 2 - dx.float()).abs().max()) <= 2e-3 * float(dx.float().abs().max())
+    torch.backends.cudnn.allow_tf32 = False
+    xn = x.float().permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    wn = wt.float().permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    out = torch.nn.functional.conv2d(xn, wn, padding=1)
+    out.backward(dy.float().permute(0, 3, 1, 2).contiguous())
+    ref_dx = xn.grad.permute(0, 2, 3, 1)
+    ref_dw = wn.grad.permute(0, 2, 3, 1)
+    assert float((dx.float() - ref_dx).norm() / ref_dx.norm()) < 2e-3
+    assert float((dw.float() - ref_dw).norm() / ref_dw.norm()) < 2e-3
