@@ -167,7 +167,7 @@ bnrelu_bwd_apply(const uint4* __restrict__ dy, const uint8_t* __restrict__ mask,
     const int64_t r0 = (int64_t)strip * rows_per_strip;
     const int64_t r1 = (r0 + rows_per_strip < m) ? r0 + rows_per_strip : m;
 
-    // out = a * (g - mb - (x - mu) * k), a = gamma*inv_std, mb = dbeta/m, k = inv_std * (dgamma/m) * inv_std
+    // out = a * (g - mb - (x - mu) * k), a = gamma*inv_std, mb = dbeta/m, k = inv_std * dgamma/m
     float ca[8], cmb[8], cmu[8], ck[8];
     const float inv_m = 1.0f / (float)m;
 #pragma unroll
