@@ -1,0 +1,309 @@
+#!/usr/bin/env python3
+"""VGG16-BN AMP training-step benchmark (BASELINE.json: "VGG16-BN fwd+bwd images/sec").
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the CPU restatement of the reference path, host cores
+
+One step = forward + backward + gradient all-reduce + SGD-momentum of VGG16-BN on a
+synthetic batch of 256 images per GPU (NHWC half, 224x224x3 padded to 4 channels,
+N(0,1); labels uniform in 0..999; random-init weights), loss scale 1024, 25 MB
+gradient buckets.  Prints ONE JSON line (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "vgg16bn_fwd_bwd_images_per_sec"
+UNIT = "images/s"
+BATCH_PER_GPU = 256
+IMAGE = 224
+CLASSES = 1000
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the roofline kernel, from the ncu
+# capture summarised in profiles/ (None until a capture of this kernel exists)
+ROOFLINE_TRAFFIC_BYTES = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], tflops=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.rows:
+            parts = [p.strip() for p in row.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def conv_flops_per_step(batch):
+    """2*N*H*W*K*9*C per pass; forward 13 layers (3 real input channels in the first), backward dgrad 12 + wgrad 13."""
+    from renaissance_b200.vgg16bn import VGG16_CFG
+    h, c, total = IMAGE, 3, 0.0
+    first = True
+    for v in VGG16_CFG:
+        if v == "M":
+            h //= 2
+            continue
+        f = 2.0 * batch * h * h * v * 9 * c
+        total += f * (2 if first else 3)
+        first = False
+        c = v
+    return total
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from renaissance_b200 import ops
+    from renaissance_b200.vgg16bn import Vgg16BnTrainer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    batch = args.batch
+    tr = Vgg16BnTrainer(batch=batch, image=IMAGE, classes=CLASSES, loss_scale=1024.0, bucket_mb=25.0, seed=1234)
+    # synthetic batches in pinned host memory (two, alternated): images ~ N(0,1), 4th channel zero
+    gen = torch.Generator().manual_seed(100 + rank)
+    host_images, host_labels = [], []
+    for _ in range(2):
+        img = torch.zeros((batch, IMAGE, IMAGE, 4), dtype=torch.float16).pin_memory()
+        img[..., :3] = torch.randn((batch, IMAGE, IMAGE, 3), generator=gen).half()
+        host_images.append(img)
+        host_labels.append(torch.randint(0, CLASSES, (batch,), generator=gen, dtype=torch.int32).pin_memory())
+    for s in range(2):
+        tr.upload(s, host_images[s], host_labels[s])
+    torch.cuda.current_stream().wait_stream(tr.copy_stream)
+    torch.cuda.synchronize()
+
+    # ---------------- device-resident timing: W warm-up steps, then exactly K timed steps
+    for _ in range(args.warmup):
+        tr.step(0)
+    ops.device_status()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    tr.timing = []
+    launches0 = ops.kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        loss = tr.step(i & 1)
+    e1.record()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    launches = ops.kernel_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    roof_events = tr.timing
+    tr.timing = None
+    ops.device_status()
+    loss_value = float(loss.item())
+    ms_per_step = ms_total / args.steps
+    value = world * batch * args.steps / (ms_total / 1e3)
+
+    # ---------------- roofline of the dominant kernel (conv3x3_igemm_kernel): its forward launches,
+    # bracketed by CUDA events inside the timed region on the launching stream
+    peaks = measured_peaks()
+    flops = sum(f for _, _, f in roof_events)
+    dur_ms = sum(a.elapsed_time(b) for a, b, _ in roof_events)
+    n_l = max(len(roof_events), 1)
+    achieved = flops / (dur_ms / 1e3) / 1e12 if dur_ms > 0 else 0.0
+    roofline = dict(kernel="conv3x3_igemm_kernel (12 forward launches per step)", bound="tensor",
+                    achieved=round(achieved, 1), peak=peaks["tflops"], unit="TFLOP/s",
+                    frac=round(achieved / peaks["tflops"], 4), peak_source=peaks["source"],
+                    flop_per_launch=flops / n_l, ms_per_launch=dur_ms / n_l, launches_timed=len(roof_events),
+                    traffic=ROOFLINE_TRAFFIC_BYTES)
+
+    # ---------------- end to end: host buffers, H2D of every step's batch and D2H of its loss inside the region
+    barrier()
+    t0 = time.perf_counter()
+    tr.upload(0, host_images[0], host_labels[0])
+    for i in range(args.steps):
+        s = i & 1
+        if i + 1 < args.steps:
+            tr.upload(s ^ 1, host_images[s ^ 1], host_labels[s ^ 1])      # prefetch the next batch (double buffer)
+        l = tr.step(s, wait_copy=True)
+        _ = float(l.item())                                                # device -> host read of the loss
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    h2d = host_images[0].numel() * 2 + host_labels[0].numel() * 4
+    e2e = dict(value=round(world * batch * args.steps / e2e_s, 1), unit=UNIT, h2d_bytes_per_step=h2d,
+               d2h_bytes_per_step=4)
+
+    # ---------------- CPU baseline beside it (rank 0, single GPU run only): the oracle's step on host cores
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(sample_batch=1)
+
+    if rank == 0:
+        line = dict(metric=METRIC, value=round(value, 1), unit=UNIT, n_gpus=world, steps=args.steps, warmup=args.warmup,
+                    ms_per_step=round(ms_per_step, 3), higher_is_better=True, scaling="weak", vs_baseline=None,
+                    dtype="fp16", data="synthetic",
+                    config=dict(workload="VGG16-BN AMP fwd+bwd+allreduce+SGD-momentum, NHWC 224x224x3(+1 pad), "
+                                         "batch 256/GPU, loss scale 1024, 25 MB buckets",
+                                global_batch=world * batch, parallelism=f"dp{world}",
+                                l2="activations (>15 GB per step) far exceed the 126 MB L2; no flush needed",
+                                conv_tflop_per_step_per_gpu=round(conv_flops_per_step(batch) / 1e12, 2),
+                                loss=round(loss_value, 4)),
+                    clocks=clocks, e2e=e2e, gpu_launches=int(launches // args.steps), roofline=roofline)
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(sample_batch=1, repeats=1):
+    """Times the CPU oracle's VGG16-BN step (all host threads) on `sample_batch` images."""
+    from oracle import oracle as orc
+    from oracle import vgg16bn_cpu as cpu
+
+    orc.lib()
+    params = cpu.init_params(seed=1234, image=IMAGE, classes=CLASSES)
+    img, labels = cpu.synthetic_batch(100, sample_batch, IMAGE, CLASSES)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        cpu.step(params, img, labels)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return dict(value=round(sample_batch / best, 4), unit=UNIT, cores=orc.num_threads(), kind="port",
+                sample=f"one full VGG16-BN step (fwd+bwd+SGD) on {sample_batch} image(s) of 224x224, "
+                       f"{best:.1f} s of wall time on {orc.num_threads()} threads")
+
+
+def run_reference(args):
+    """Reference arm: the reference's own CPU implementation of this path cannot be built here (it needs
+    mimalloc, Eigen, XNNPACK; its fused block has no CPU launcher at all), so the arm times the oracle's
+    loop-for-loop restatement of the reference CPU operators on all host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    t_all = time.perf_counter()
+    vals = []
+    sample = 1
+    for i in range(args.warmup + args.steps):
+        r = cpu_baseline(sample_batch=sample)
+        if i >= args.warmup:
+            vals.append(r["value"])
+        if time.perf_counter() - t_all > 240:      # stay within a few minutes whatever K and W say
+            if not vals:
+                vals.append(r["value"])
+            break
+    value = statistics.mean(vals)
+    r["value"] = round(value, 4)
+    line = dict(impl="reference", metric=METRIC, value=round(value, 4), unit=UNIT, n_gpus=args.gpus, steps=len(vals),
+                warmup=args.warmup, ms_per_step=round(1e3 * sample / value, 1), higher_is_better=True, scaling="weak",
+                vs_baseline=None, dtype="fp16", data="synthetic",
+                config=dict(workload="VGG16-BN AMP fwd+bwd+SGD-momentum, NHWC 224x224x3(+1 pad), CPU restatement of "
+                                     "the reference operators, bounded sample of 1 image per step",
+                            global_batch=sample, parallelism="cpu"),
+                cpu_baseline=r, e2e=dict(value=round(value, 4), unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU (the metric is quoted at 256)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

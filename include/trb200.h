@@ -49,6 +49,9 @@ const char* trb200_last_error(void);
 /* Library version, major*10000 + minor*100 + patch. */
 int trb200_version(void);
 
+/* Number of kernels this library has launched in this process so far. */
+uint64_t trb200_kernel_launch_count(void);
+
 /* Compute capability (major*10 + minor) of the current device, or a negative
  * trb200_status.  The tensor-core kernels need 100. */
 int trb200_device_arch(void);
@@ -104,11 +107,16 @@ int trb200_conv_dgrad(const trb200_conv_desc* d, const void* dy, const void* w, 
                       void* workspace, size_t workspace_bytes, void* stream);
 
 /* Forward convolution Y = X (*) W, half in, float accumulate, half out, on the
- * same tensor-core kernel as dgrad (3x3, stride 1, pad 1, c % 64 == 0, k = 64,
- * 128 or a multiple of 256; anything else returns TRB200_ERR_UNSUPPORTED).
+ * same tensor-core kernel as dgrad (3x3, stride 1, pad 1, k = 64, 128 or a multiple
+ * of 256, c % 64 == 0 or c == 4; anything else returns TRB200_ERR_UNSUPPORTED).
+ * With c == 4 (the padded first layer) the workspace receives the 3x3
+ * neighbourhoods of every pixel, n*h*w*128 bytes: any activation-sized buffer that
+ * is free at that point will do (the block's relu-output buffer, say).
  * Counterpart of the conv_fprop part of the reference's forward block,
  * src/backend/ops/dtensor/cbr_op.cpp:622-718 (statistics not included). */
-int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const void* w, void* y, void* stream);
+size_t trb200_conv_fprop_workspace_bytes(const trb200_conv_desc* d);
+int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const void* w, void* y,
+                      void* workspace, size_t workspace_bytes, void* stream);
 
 /* Diagnostics.  backend 0 = automatic (tensor cores where the shape allows),
  * 1 = direct CUDA-core kernels only (used by tests to cross-check the two). */
@@ -148,7 +156,9 @@ typedef struct trb200_cbr_bwd_args {
     void* dw;                  /* out [1] half KRSC                                 */
     float* dgamma;             /* out [2]                                           */
     float* dbeta;              /* out [3]                                           */
-    const void* conv_out;      /* out [4] conv output saved by the forward (read)   */
+    void* conv_out;            /* out [4] conv output saved by the forward: read by
+                                  the BN stage; the first-layer variant with c == 4
+                                  then overwrites it (scratch for the weight gradient) */
     void* bn_scratch;          /* out [5] activation-sized scratch: receives dconv  */
     void* workspace;
     size_t workspace_bytes;

@@ -242,7 +242,7 @@ def momentum(w, g, m, lr, wd=0.0, beta=0.9, scaling=1.0):
 # --------------------------------------------------------------------------- fused AMP block
 
 def cbr_fwd_amp(x16, w16, gamma, beta, pad=1, stride=1, eps=1e-5, momentum=0.1,
-                running_mean=None, running_var=None, round_steps=True):
+                running_mean=None, running_var=None, round_steps=True, stats_from_half=False):
     """cbr_op.cpp:430-718.  Returns dict of conv_out, sum, sqsum, saved_mean, saved_inv_std,
     eq_scale, eq_bias, relu_out, mask_bits."""
     x, w = _f16(x16), _f16(w16)
@@ -263,7 +263,7 @@ def cbr_fwd_amp(x16, w16, gamma, beta, pad=1, stride=1, eps=1e-5, momentum=0.1,
                           _p(out["saved_mean"]), _p(out["saved_inv_std"]),
                           _p(out["eq_scale"]), _p(out["eq_bias"]), _p(out["relu_out"]), _p(out["mask_bits"]),
                           n, h, ww, c, k, r, s, int(pad), int(stride), C.c_float(eps), C.c_float(momentum),
-                          1 if round_steps else 0)
+                          1 if round_steps else 0, 1 if stats_from_half else 0)
     return out
 
 

@@ -488,7 +488,9 @@ void orc_momentum_f32(float* w, const float* g, float* m, int64_t n,
  * accumulator); bn_finalize -> saved_mean, saved_inv_std, eq_scale, eq_bias;
  * y = relu(t), mask = t > 0 with t = half(half(x*eq_scale) + eq_bias) when
  * round_steps != 0 (the virtual tensors are declared HALF, cbr_op.cpp:568-577)
- * or t = x*eq_scale + eq_bias kept in float when round_steps == 0. */
+ * or t = x*eq_scale + eq_bias kept in float when round_steps == 0.
+ * stats_from_half != 0 takes the statistics from the half-rounded conv output
+ * (a separate pass over the stored tensor) instead of the float accumulator. */
 void orc_cbr_fwd_amp(const h16* X, const h16* Wt, const float* gamma, const float* beta,
                      float* running_mean, float* running_var,
                      h16* conv_out, float* ch_sum, float* ch_sqsum,
@@ -496,7 +498,7 @@ void orc_cbr_fwd_amp(const h16* X, const h16* Wt, const float* gamma, const floa
                      float* eq_scale, float* eq_bias,
                      h16* relu_out, uint8_t* mask_bits,
                      int N, int H, int W, int C, int K, int R, int S, int pad, int stride,
-                     float eps, float momentum, int round_steps) {
+                     float eps, float momentum, int round_steps, int stats_from_half) {
     const int OH = out_extent(H, pad, R, stride), OW = out_extent(W, pad, S, stride);
     const int64_t M = (int64_t)N * OH * OW;
     const int64_t ne = M * K;
@@ -510,7 +512,11 @@ void orc_cbr_fwd_amp(const h16* X, const h16* Wt, const float* gamma, const floa
     for (int64_t i = 0; i < ne; ++i) conv_out[i] = (h16)acc[i];
     for (int k = 0; k < K; ++k) {
         double s = 0.0, q = 0.0;
-        for (int64_t i = 0; i < M; ++i) { const double v = acc[i * K + k]; s += v; q += v * v; }
+        for (int64_t i = 0; i < M; ++i) {
+            /* stats_from_half: statistics of the stored half tensor instead of the float accumulator */
+            const double v = stats_from_half ? (double)(float)conv_out[i * K + k] : (double)acc[i * K + k];
+            s += v; q += v * v;
+        }
         ch_sum[k] = (float)s; ch_sqsum[k] = (float)q;
         const float mean = (float)(s / (double)M);
         float var = (float)(q / (double)M - (s / (double)M) * (s / (double)M));

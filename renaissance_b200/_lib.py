@@ -73,6 +73,7 @@ def load() -> C.CDLL:
         "trb200_last_error": (C.c_char_p, []),
         "trb200_version": (C.c_int, []),
         "trb200_device_arch": (C.c_int, []),
+        "trb200_kernel_launch_count": (C.c_uint64, []),
         "trb200_device_status": (C.c_int, []),
         "trb200_set_conv_backend": (C.c_int, [C.c_int]),
         "trb200_conv_uses_tensor_cores": (C.c_int, [pdesc, C.c_int]),
@@ -82,12 +83,21 @@ def load() -> C.CDLL:
         "trb200_conv_wgrad": (C.c_int, [pdesc, vp, vp, vp, vp, sz, vp]),
         "trb200_conv_dgrad_workspace_bytes": (sz, [pdesc]),
         "trb200_conv_dgrad": (C.c_int, [pdesc, vp, vp, vp, vp, sz, vp]),
-        "trb200_conv_fprop": (C.c_int, [pdesc, vp, vp, vp, vp]),
+        "trb200_conv_fprop_workspace_bytes": (sz, [pdesc]),
+        "trb200_conv_fprop": (C.c_int, [pdesc, vp, vp, vp, vp, sz, vp]),
         "trb200_cbr_bwd_workspace_bytes": (sz, [pdesc, C.c_int]),
         "trb200_cbr_bwd": (C.c_int, [C.POINTER(CbrBwdArgs)]),
         "trb200_softmax_ce_fwd": (C.c_int, [vp, i64, vp, vp, vp, i64, vp, vp, vp, i32, i32, vp]),
         "trb200_softmax_ce_bwd": (C.c_int, [vp, i64, vp, vp, vp, vp, vp, i64, i32, i32, vp]),
         "trb200_softmax_ce_fused": (C.c_int, [vp, i64, vp, vp, vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, vp]),
+        "trb200_bn_stats_workspace_bytes": (sz, [i64, i32]),
+        "trb200_bn_stats_finalize": (C.c_int, [vp, vp, vp, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32,
+                                               vp, sz, vp]),
+        "trb200_bn_apply_relu_mask": (C.c_int, [vp, vp, vp, vp, vp, i64, i32, vp]),
+        "trb200_maxpool2x2_fwd": (C.c_int, [vp, vp, vp, i32, i32, i32, i32, vp]),
+        "trb200_maxpool2x2_bwd": (C.c_int, [vp, vp, vp, i32, i32, i32, i32, vp]),
+        "trb200_check_nonfinite": (C.c_int, [vp, i64, vp, vp]),
+        "trb200_sgd_momentum": (C.c_int, [vp, vp, vp, vp, i64, f32, f32, f32, vp, vp, vp]),
         "trb200_scale_f32": (C.c_int, [vp, i64, f32, vp]),
         "trb200_cast_f16_to_f32": (C.c_int, [vp, vp, i64, f32, vp]),
     }

@@ -94,20 +94,29 @@ bn_stats_partial(const uint4* __restrict__ x, float* __restrict__ partial, int64
     }
 }
 
-// adds the strips in strip order (double) and finalizes the statistics
-__global__ void bn_stats_finalize(const float* __restrict__ partial, int strips, int c, int64_t m,
-                                  const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
-                                  float momentum, float* __restrict__ ch_sum, float* __restrict__ ch_sqsum,
-                                  float* __restrict__ saved_mean, float* __restrict__ saved_inv_std,
-                                  float* __restrict__ eq_scale, float* __restrict__ eq_bias,
-                                  float* __restrict__ running_mean, float* __restrict__ running_var) {
-    const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+// One warp per channel: lanes add every 32nd strip in double, a fixed butterfly adds
+// the lanes (the order of additions never changes), lane 0 finalizes the statistics.
+__global__ void __launch_bounds__(256)
+bn_stats_finalize(const float* __restrict__ partial, int strips, int c, int64_t m,
+                  const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
+                  float momentum, float* __restrict__ ch_sum, float* __restrict__ ch_sqsum,
+                  float* __restrict__ saved_mean, float* __restrict__ saved_inv_std,
+                  float* __restrict__ eq_scale, float* __restrict__ eq_bias,
+                  float* __restrict__ running_mean, float* __restrict__ running_var) {
+    const int ch = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
     if (ch >= c) return;
     double s = 0.0, q = 0.0;
-    for (int i = 0; i < strips; ++i) {
+    for (int i = lane; i < strips; i += 32) {
         s += (double)partial[((size_t)i * 2) * c + ch];
         q += (double)partial[((size_t)i * 2 + 1) * c + ch];
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        s += __shfl_xor_sync(0xffffffffu, s, o);
+        q += __shfl_xor_sync(0xffffffffu, q, o);
+    }
+    if (lane != 0) return;
     if (ch_sum) ch_sum[ch] = (float)s;
     if (ch_sqsum) ch_sqsum[ch] = (float)q;
     const double mean_d = s / (double)m;
@@ -273,7 +282,7 @@ extern "C" int trb200_bn_stats_finalize(const void* conv_out, const float* gamma
     trb::bn_stats_partial<<<dim3(p.gx, p.gy), trb::kThreads, 0, s>>>(static_cast<const uint4*>(conv_out), partial, m, c,
                                                                      p.tpr, p.bx, p.by, p.rows_per_strip);
     TRB_LAUNCH_CHECK("bn_stats_partial");
-    trb::bn_stats_finalize<<<(c + 127) / 128, 128, 0, s>>>(partial, p.gx, c, m, gamma, beta, eps, momentum, ch_sum,
+    trb::bn_stats_finalize<<<(c + 7) / 8, 256, 0, s>>>(partial, p.gx, c, m, gamma, beta, eps, momentum, ch_sum,
                                                           ch_sqsum, saved_mean, saved_inv_std, eq_scale, eq_bias,
                                                           running_mean, running_var);
     TRB_LAUNCH_CHECK("bn_stats_finalize");

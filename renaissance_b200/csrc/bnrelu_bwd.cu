@@ -142,14 +142,20 @@ bnrelu_bwd_reduce(const uint4* __restrict__ dy, const uint8_t* __restrict__ mask
     }
 }
 
-__global__ void bnrelu_bwd_finalize(const float* __restrict__ partial, float* __restrict__ dgamma,
-                                    float* __restrict__ dbeta, int c, int strips) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;   // i in [0, 2c)
+// One warp per (statistic, channel): lanes add every 32nd strip in double, then a
+// fixed butterfly adds the lanes, so the order of additions never changes.
+__global__ void __launch_bounds__(256)
+bnrelu_bwd_finalize(const float* __restrict__ partial, float* __restrict__ dgamma,
+                    float* __restrict__ dbeta, int c, int strips) {
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);   // i in [0, 2c)
+    const int lane = threadIdx.x & 31;
     if (i >= 2 * c) return;
     const int stat = i / c, ch = i % c;
     double acc = 0.0;
-    for (int s = 0; s < strips; ++s) acc += (double)partial[((size_t)s * 2 + stat) * c + ch];
-    (stat == 0 ? dbeta : dgamma)[ch] = (float)acc;
+    for (int s = lane; s < strips; s += 32) acc += (double)partial[((size_t)s * 2 + stat) * c + ch];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) (stat == 0 ? dbeta : dgamma)[ch] = (float)acc;
 }
 
 __global__ void __launch_bounds__(kThreads)
@@ -239,7 +245,7 @@ int bnrelu_bwd_launch(const void* dy, const void* mask_bits, const void* x, cons
         static_cast<const uint4*>(x), saved_mean, saved_inv_std, partial, m, c, p.tpr, p.bx, p.by,
         p.rows_per_strip);
     TRB_LAUNCH_CHECK("bnrelu_bwd_reduce");
-    bnrelu_bwd_finalize<<<(2 * c + 127) / 128, 128, 0, s>>>(partial, dgamma, dbeta, c, p.gx);
+    bnrelu_bwd_finalize<<<(2 * c + 7) / 8, 256, 0, s>>>(partial, dgamma, dbeta, c, p.gx);
     TRB_LAUNCH_CHECK("bnrelu_bwd_finalize");
     if (dconv) {
         bnrelu_bwd_apply<<<grid, kThreads, 0, s>>>(

@@ -1,6 +1,7 @@
 // Error text, version and device queries of the trb200 library.
 #include "common.cuh"
 
+#include <atomic>
 #include <cstring>
 
 namespace trb {
@@ -17,6 +18,12 @@ int fail(int code, const char* fmt, ...) {
     va_end(ap);
     return code;
 }
+
+static std::atomic<unsigned long long> g_launches{0};
+
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+unsigned long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 int sm_count() {
     static int cached[64] = {0};
@@ -35,6 +42,9 @@ int sm_count() {
 extern "C" const char* trb200_last_error(void) { return trb::last_error_buffer(); }
 
 extern "C" int trb200_version(void) { return 100; }
+
+namespace trb { unsigned long long launch_count(); }
+extern "C" uint64_t trb200_kernel_launch_count(void) { return trb::launch_count(); }
 
 extern "C" int trb200_device_arch(void) {
     int dev = 0, major = 0, minor = 0;

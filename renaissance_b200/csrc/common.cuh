@@ -26,6 +26,10 @@ inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Counts kernel launches made by this library (every launch site goes through
+// TRB_LAUNCH_CHECK); read by trb200_kernel_launch_count().
+void note_launch();
+
 #define TRB_CUDA_TRY(expr)                                                                  \
     do {                                                                                    \
         cudaError_t err__ = (expr);                                                         \
@@ -35,6 +39,7 @@ int sm_count();
 
 #define TRB_LAUNCH_CHECK(what)                                                               \
     do {                                                                                     \
+        ::trb::note_launch();                                                                \
         cudaError_t err__ = cudaGetLastError();                                              \
         if (err__ != cudaSuccess)                                                            \
             return ::trb::fail(TRB200_ERR_CUDA, "%s launch: %s", what, cudaGetErrorString(err__)); \

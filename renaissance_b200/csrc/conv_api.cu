@@ -6,7 +6,6 @@
 
 namespace trb {
 
-int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, cudaStream_t st);
 int device_status_read_and_clear(int* out);
 int bnrelu_bwd_launch(const void* dy, const void* mask_bits, const void* x, const float* gamma,
                       const float* saved_mean, const float* saved_inv_std, void* dconv, float* dgamma,
@@ -88,14 +87,22 @@ extern "C" int trb200_conv_dgrad(const trb200_conv_desc* d, const void* dy, cons
     return trb::dgrad_direct(*d, dy, w, dx, trb::as_stream(stream));
 }
 
-extern "C" int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const void* w, void* y, void* stream) {
+extern "C" size_t trb200_conv_fprop_workspace_bytes(const trb200_conv_desc* d) {
+    if (trb::validate_conv_desc(d, "conv_fprop_workspace_bytes")) return 0;
+    return trb::igemm_supports(*d, 2) ? trb::igemm_fprop_workspace(*d) : 0;
+}
+
+extern "C" int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const void* w, void* y, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
     int rc = trb::validate_conv_desc(d, "conv_fprop");
     if (rc) return rc;
     TRB_REQUIRE(x && w && y, TRB200_ERR_INVALID_ARGUMENT, "conv_fprop: null pointer");
     TRB_REQUIRE(y != x && y != w, TRB200_ERR_INVALID_ARGUMENT, "conv_fprop: y must not alias x or w");
+    TRB_REQUIRE(trb::aligned16(x) && trb::aligned16(w) && trb::aligned16(y), TRB200_ERR_INVALID_ARGUMENT,
+                "conv_fprop: tensors must be 16-byte aligned");
     TRB_REQUIRE(trb::igemm_supports(*d, 2), TRB200_ERR_UNSUPPORTED,
-                "conv_fprop: only 3x3 stride 1 pad 1 with c and k multiples of 64 (k = 64, 128 or a multiple of 256)");
-    return trb::igemm_fprop(*d, x, w, y, trb::as_stream(stream));
+                "conv_fprop: only 3x3 stride 1 pad 1 with k = 64, 128 or a multiple of 256 and c = 4 or a multiple of 64");
+    return trb::igemm_fprop(*d, x, w, y, workspace, workspace_bytes, trb::as_stream(stream));
 }
 
 // ---------------------------------------------------------------------------
@@ -113,7 +120,9 @@ BlockWs block_ws(const trb200_conv_desc& d, bool first_layer) {
     b.bn_off = 0;
     b.bn_bytes = trb200_bnrelu_bwd_workspace_bytes((int64_t)d.n * oh * ow, d.k);
     b.wg_off = (size_t)trb::align_up((int64_t)b.bn_bytes, 256);
-    b.wg_bytes = trb200_conv_wgrad_workspace_bytes(&d);
+    // first layer with 4 input channels: the conv_out buffer doubles as the im2col scratch
+    b.wg_bytes = (use_igemm(d, 0) && trb::igemm_small_c(d)) ? trb::igemm_wgrad_small_c_workspace(d)
+                                                           : trb200_conv_wgrad_workspace_bytes(&d);
     b.dg_off = b.wg_off + (size_t)trb::align_up((int64_t)b.wg_bytes, 256);
     b.dg_bytes = first_layer ? 0 : trb200_conv_dgrad_workspace_bytes(&d);
     b.total = b.dg_off + (size_t)trb::align_up((int64_t)b.dg_bytes, 256);
@@ -158,7 +167,13 @@ extern "C" int trb200_cbr_bwd(const trb200_cbr_bwd_args* a) {
 
     // 2) wgrad(dconv, x) -> dw
     if (s_wg != s_bn) TRB_CUDA_TRY(cudaStreamWaitEvent(s_wg, trb::as_event(a->ev_bn), 0));
-    rc = trb200_conv_wgrad(&d, a->bn_scratch, a->x, a->dw, wsp + ws.wg_off, ws.wg_bytes, s_wg);
+    if (use_igemm(d, 0) && trb::igemm_small_c(d)) {
+        // conv_out is dead once stage 1 has read it: it receives the 3x3 neighbourhoods of x
+        rc = trb::igemm_wgrad_small_c(d, a->bn_scratch, a->x, a->dw, a->conv_out, false, wsp + ws.wg_off, ws.wg_bytes,
+                                      s_wg);
+    } else {
+        rc = trb200_conv_wgrad(&d, a->bn_scratch, a->x, a->dw, wsp + ws.wg_off, ws.wg_bytes, s_wg);
+    }
     if (rc) return rc;
     if (a->ev_wgrad) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_wgrad), s_wg));
 

@@ -151,6 +151,8 @@ __device__ __forceinline__ void abort_drain(volatile int* abort_flag) {
 
 // ------------------------------------------------------------------ dgrad / fprop kernel
 struct FpropParams {
+    int taps;            // 9 (3x3, pad 1) or 1 (1x1, pad 0)
+    int tap_base;        // 0 for 3x3; 4 for 1x1 (the centre tap: offset (0, 0))
     int cin_slices;      // Cin / 64
     int n_tiles;         // Cout / NT
     int m_tiles;         // tw * th * tn
@@ -211,7 +213,7 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
     volatile int* abort_flag = &s_abort;
 
     const int total_tiles = p.m_tiles * p.n_tiles;
-    const int ksteps = 9 * p.cin_slices;
+    const int ksteps = p.taps * p.cin_slices;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -223,7 +225,7 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
                 const int n0 = (mt / (p.tw * p.th)) * p.bn;
                 for (int ks = 0; ks < ksteps; ++ks) {
                     const int tap = ks / p.cin_slices, slice = ks % p.cin_slices;
-                    const int r = tap / 3, s = tap % 3;
+                    const int r = (tap + p.tap_base) / 3, s = (tap + p.tap_base) % 3;
                     ok = mbar_wait(empty_bar(ps.stage), ps.phase ^ 1u, abort_flag, status, kStatusProducerTimeout);
                     if (!ok) break;
                     mbar_expect_tx(full_bar(ps.stage), L::kStageBytes);
@@ -374,7 +376,7 @@ int pick_nt(int cout) {
 
 // in: [n,h,w,cin] half; filter view described by (wv, tap_is_dim1); out: [n,h,w,cout] half.
 int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int n, int h, int w, int cin, int cout,
-                cudaStream_t st) {
+                cudaStream_t st, int taps = 9) {
     const int nt = pick_nt(cout);
     TRB_REQUIRE(nt != 0 && cin % 64 == 0, TRB200_ERR_UNSUPPORTED, "conv3x3 igemm: cin=%d cout=%d not covered", cin,
                 cout);
@@ -386,18 +388,20 @@ int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int 
     if (rc) return rc;
     if (tap_is_dim1) {
         // KRSC as stored: (ci, tap, co)
-        const uint64_t dims[3] = {(uint64_t)cin, 9, (uint64_t)cout};
-        const uint64_t str[3] = {2, (uint64_t)cin * 2, (uint64_t)9 * cin * 2};
+        const uint64_t dims[3] = {(uint64_t)cin, (uint64_t)taps, (uint64_t)cout};
+        const uint64_t str[3] = {2, (uint64_t)cin * 2, (uint64_t)taps * cin * 2};
         const uint32_t box[3] = {64, 1, (uint32_t)nt};
         rc = make_tmap(&tw, wv, 3, dims, str, box, "filters (ci,tap,co)");
     } else {
-        const uint64_t dims[3] = {(uint64_t)cin, (uint64_t)cout, 9};
+        const uint64_t dims[3] = {(uint64_t)cin, (uint64_t)cout, (uint64_t)taps};
         const uint64_t str[3] = {2, (uint64_t)cin * 2, (uint64_t)cout * cin * 2};
         const uint32_t box[3] = {64, (uint32_t)nt, 1};
         rc = make_tmap(&tw, wv, 3, dims, str, box, "filters (ci,co,tap)");
     }
     if (rc) return rc;
     FpropParams p;
+    p.taps = taps;
+    p.tap_base = taps == 1 ? 4 : 0;
     p.cin_slices = cin / 64;
     p.n_tiles = cout / nt;
     p.m_tiles = t.tw * t.th * t.tn;
@@ -411,8 +415,10 @@ int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int 
 
 // ------------------------------------------------------------------ wgrad kernel
 struct WgradParams {
+    int taps;           // 9 (3x3, pad 1) or 1 (1x1)
+    int tap_base;       // 0 for 3x3; 4 for 1x1 (centre tap)
     int cblocks;        // C / 64
-    int units;          // 9 * cblocks  (unit u: tap = u / cblocks, cblock = u % cblocks)
+    int units;          // taps * cblocks  (unit u: tap = u / cblocks, cblock = u % cblocks)
     int m_tiles;        // ceil(units / 2)
     int n_tiles;        // K / NT
     int splits;
@@ -491,7 +497,7 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                     const int u = j == 0 ? u0 : u1;
-                    const int tap = u / p.cblocks, cb = u % p.cblocks;
+                    const int tap = u / p.cblocks + p.tap_base, cb = u % p.cblocks;
                     tma_load_4d(a_dst + j * kStageTileBytes, &tm_x, full_bar(ps.stage), cb * 64,
                                 w0 + tap % 3 - 1, h0 + tap / 3 - 1, n0);
                 }
@@ -581,7 +587,7 @@ wgrad_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ dw, 
     for (int cj = ty; cj < 32; cj += 8) {
         const int k = nt * nt_cols + c0 + cj;
         const int c = cb * 64 + (r0 % 64) + tx;
-        dw[((size_t)k * 9 + tap) * cc + c] = __float2half_rn(tile[tx][cj]);
+        dw[((size_t)k * p.taps + tap) * cc + c] = __float2half_rn(tile[tx][cj]);
     }
     (void)kk;
 }
@@ -605,10 +611,12 @@ int launch_wgrad(const CUtensorMap& tx, const CUtensorMap& tdy, float* partial, 
     return TRB200_OK;
 }
 
-WgradParams wgrad_plan(const trb200_conv_desc& d, int nt, const TileShape& t) {
+WgradParams wgrad_plan(const trb200_conv_desc& d, int nt, const TileShape& t, int taps = 9) {
     WgradParams p;
+    p.taps = taps;
+    p.tap_base = taps == 1 ? 4 : 0;
     p.cblocks = d.c / 64;
-    p.units = 9 * p.cblocks;
+    p.units = taps * p.cblocks;
     p.m_tiles = (p.units + 1) / 2;
     p.n_tiles = d.k / nt;
     p.pix_tiles = t.tw * t.th * t.tn;
@@ -622,27 +630,110 @@ WgradParams wgrad_plan(const trb200_conv_desc& d, int nt, const TileShape& t) {
     return p;
 }
 
+// ------------------------------------------------------------------ first layer (C = 4)
+// A 3x3 / pad 1 convolution over 4 input channels is a 1x1 convolution over the 36
+// values of each pixel's 3x3 neighbourhood.  im2col_c4_kernel writes that
+// neighbourhood as one 128-byte row per pixel (36 halfs + 28 zeros), after which the
+// forward conv and the weight gradient are plain GEMMs on the kernels above
+// (taps = 1, 64 input channels); the zero columns contribute exact zeros.
+__global__ void __launch_bounds__(256)
+im2col_c4_kernel(const uint2* __restrict__ x, uint4* __restrict__ xp, int n, int h, int w) {
+    const int64_t total = (int64_t)n * h * w * 8;          // 8 chunks of 16 bytes per pixel
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int chunk = (int)(i & 7);
+        const int64_t pix = i >> 3;
+        const int xw = (int)(pix % w);
+        const int yh = (int)((pix / w) % h);
+        const int64_t img = pix / ((int64_t)w * h);
+        uint2 v[2] = {make_uint2(0, 0), make_uint2(0, 0)};
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int tap = chunk * 2 + j;
+            if (tap < 9) {
+                const int ih = yh + tap / 3 - 1, iw = xw + tap % 3 - 1;
+                if (ih >= 0 && ih < h && iw >= 0 && iw < w) v[j] = x[(img * h + ih) * w + iw];
+            }
+        }
+        xp[i] = make_uint4(v[0].x, v[0].y, v[1].x, v[1].y);
+    }
+}
+
+// wp[k][j] = j < 36 ? w[k][j] : 0   (KRSC with c = 4 is already [k][36])
+__global__ void pack_w_c4_kernel(const __half* __restrict__ w, __half* __restrict__ wp, int kk) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= kk * 64) return;
+    const int k = i >> 6, j = i & 63;
+    wp[i] = j < 36 ? w[k * 36 + j] : __float2half_rn(0.f);
+}
+
+__global__ void unpack_dw_c4_kernel(const __half* __restrict__ dwp, __half* __restrict__ dw, int kk) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= kk * 36) return;
+    dw[i] = dwp[(i / 36) * 64 + i % 36];
+}
+
+int im2col_c4(const void* x, void* xp, int n, int h, int w, cudaStream_t st) {
+    const int64_t total = (int64_t)n * h * w * 8;
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    im2col_c4_kernel<<<(int)blocks, 256, 0, st>>>(static_cast<const uint2*>(x), static_cast<uint4*>(xp), n, h, w);
+    TRB_LAUNCH_CHECK("im2col_c4_kernel");
+    return TRB200_OK;
+}
+
 }  // namespace
 
 // ------------------------------------------------------------------ entry points of this file
+static bool is_3x3_s1_p1(const trb200_conv_desc& d) {
+    return d.r == 3 && d.s == 3 && d.pad_h == 1 && d.pad_w == 1 && d.stride_h == 1 && d.stride_w == 1;
+}
+
+// first-layer shape: 4 input channels, handled as a 1x1 convolution over 36 (+28 zero) values
+bool igemm_small_c(const trb200_conv_desc& d) {
+    return is_3x3_s1_p1(d) && d.c == 4 && d.k % 64 == 0 && pick_nt(d.k) != 0 && d.n >= 1 && d.h >= 1 && d.w >= 1;
+}
+
 bool igemm_supports(const trb200_conv_desc& d, int which) {
-    if (d.r != 3 || d.s != 3 || d.pad_h != 1 || d.pad_w != 1 || d.stride_h != 1 || d.stride_w != 1) return false;
-    if (d.c % 64 != 0 || d.k % 64 != 0) return false;
+    if (!is_3x3_s1_p1(d)) return false;
     if (d.n < 1 || d.h < 1 || d.w < 1) return false;
+    if (igemm_small_c(d)) return which != 1;      // wgrad and fprop; a first layer has no dgrad
+    if (d.c % 64 != 0 || d.k % 64 != 0) return false;
     if (which == 0) return pick_nt(d.k) != 0;     // wgrad: N dimension = k
     if (which == 1) return pick_nt(d.c) != 0;     // dgrad: N dimension = c
     return pick_nt(d.k) != 0;                     // fprop: N dimension = k
+}
+
+size_t igemm_im2col_bytes(const trb200_conv_desc& d) {
+    return (size_t)align_up((int64_t)d.n * d.h * d.w * 64 * 2, 256);
 }
 
 size_t igemm_dgrad_workspace(const trb200_conv_desc& d) {
     return (size_t)align_up((int64_t)9 * d.c * d.k * 2, 256);
 }
 
-size_t igemm_wgrad_workspace(const trb200_conv_desc& d) {
+static size_t wgrad_partial_bytes(const trb200_conv_desc& d, int taps) {
     const int nt = pick_nt(d.k);
     const TileShape t = pick_tile(d.n, d.h, d.w, 64);
-    const WgradParams p = wgrad_plan(d, nt, t);
+    const WgradParams p = wgrad_plan(d, nt, t, taps);
     return (size_t)p.splits * p.m_tiles * p.n_tiles * 128 * nt * sizeof(float);
+}
+
+// small C without a caller-provided im2col buffer: [im2col][packed dW][partials]
+size_t igemm_wgrad_workspace(const trb200_conv_desc& d) {
+    if (igemm_small_c(d)) {
+        trb200_conv_desc e = d;
+        e.c = 64;
+        return igemm_im2col_bytes(d) + (size_t)align_up((int64_t)d.k * 64 * 2, 256) + wgrad_partial_bytes(e, 1);
+    }
+    return wgrad_partial_bytes(d, 9);
+}
+
+// [im2col][packed filters]
+size_t igemm_fprop_workspace(const trb200_conv_desc& d) {
+    if (igemm_small_c(d)) return igemm_im2col_bytes(d) + (size_t)align_up((int64_t)d.k * 64 * 2, 256);
+    return 0;
 }
 
 int igemm_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes,
@@ -660,8 +751,75 @@ int igemm_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* 
     return conv3x3_run(dy, ws, 0, dx, d.n, d.h, d.w, d.k, d.c, st);
 }
 
-int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, cudaStream_t st) {
-    return conv3x3_run(x, w, 1, y, d.n, d.h, d.w, d.c, d.k, st);
+int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, void* ws, size_t ws_bytes,
+                cudaStream_t st) {
+    if (!igemm_small_c(d)) return conv3x3_run(x, w, 1, y, d.n, d.h, d.w, d.c, d.k, st);
+    const size_t need = igemm_fprop_workspace(d);
+    TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, "conv_fprop: workspace of %zu bytes needed, %zu given",
+                need, ws_bytes);
+    TRB_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255u) == 0, TRB200_ERR_INVALID_ARGUMENT,
+                "conv_fprop: workspace must be 256-byte aligned");
+    unsigned char* base = static_cast<unsigned char*>(ws);
+    void* xp = base;
+    __half* wp = reinterpret_cast<__half*>(base + igemm_im2col_bytes(d));
+    int rc = im2col_c4(x, xp, d.n, d.h, d.w, st);
+    if (rc) return rc;
+    pack_w_c4_kernel<<<(d.k * 64 + 255) / 256, 256, 0, st>>>(static_cast<const __half*>(w), wp, d.k);
+    TRB_LAUNCH_CHECK("pack_w_c4_kernel");
+    // 1x1 convolution: filter view (ci = 64, tap = 1, co = k)
+    return conv3x3_run(xp, wp, 1, y, d.n, d.h, d.w, 64, d.k, st, 1);
+}
+
+static int wgrad_run(const trb200_conv_desc& d, int taps, const void* dy, const void* x, void* dw, float* partial,
+                     cudaStream_t st) {
+    const int nt = pick_nt(d.k);
+    const TileShape t = pick_tile(d.n, d.h, d.w, 64);
+    const WgradParams p = wgrad_plan(d, nt, t, taps);
+    CUtensorMap tx, tdy;
+    int rc = make_act_tmap(&tx, x, d.n, d.h, d.w, d.c, t, "wgrad x");
+    if (rc) return rc;
+    rc = make_act_tmap(&tdy, dy, d.n, d.h, d.w, d.k, t, "wgrad dy");
+    if (rc) return rc;
+    if (nt == 256) rc = launch_wgrad<256>(tx, tdy, partial, p, st);
+    else if (nt == 128) rc = launch_wgrad<128>(tx, tdy, partial, p, st);
+    else rc = launch_wgrad<64>(tx, tdy, partial, p, st);
+    if (rc) return rc;
+    dim3 grid(nt / 32, 4, p.m_tiles * p.n_tiles);
+    wgrad_reduce_kernel<<<grid, 256, 0, st>>>(partial, static_cast<__half*>(dw), p, nt, d.k, d.c);
+    TRB_LAUNCH_CHECK("wgrad_reduce_kernel");
+    return TRB200_OK;
+}
+
+// Small-C weight gradient.  `xp` is the im2col buffer [n,h,w,64] half: if `xp_ready`
+// it already holds the neighbourhoods of x, else they are written here first.
+// ws: [packed dW (k x 64 half)][partials].
+size_t igemm_wgrad_small_c_workspace(const trb200_conv_desc& d) {
+    trb200_conv_desc e = d;
+    e.c = 64;
+    return (size_t)align_up((int64_t)d.k * 64 * 2, 256) + wgrad_partial_bytes(e, 1);
+}
+
+int igemm_wgrad_small_c(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* xp, bool xp_ready,
+                        void* ws, size_t ws_bytes, cudaStream_t st) {
+    const size_t need = igemm_wgrad_small_c_workspace(d);
+    TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, "conv_wgrad: workspace of %zu bytes needed, %zu given",
+                need, ws_bytes);
+    TRB_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255u) == 0 && aligned16(xp), TRB200_ERR_INVALID_ARGUMENT,
+                "conv_wgrad: workspace must be 256-byte aligned");
+    if (!xp_ready) {
+        const int rc = im2col_c4(x, xp, d.n, d.h, d.w, st);
+        if (rc) return rc;
+    }
+    unsigned char* base = static_cast<unsigned char*>(ws);
+    __half* dwp = reinterpret_cast<__half*>(base);
+    float* partial = reinterpret_cast<float*>(base + align_up((int64_t)d.k * 64 * 2, 256));
+    trb200_conv_desc e = d;
+    e.c = 64;
+    const int rc = wgrad_run(e, 1, dy, xp, dwp, partial, st);
+    if (rc) return rc;
+    unpack_dw_c4_kernel<<<(d.k * 36 + 255) / 256, 256, 0, st>>>(dwp, static_cast<__half*>(dw), d.k);
+    TRB_LAUNCH_CHECK("unpack_dw_c4_kernel");
+    return TRB200_OK;
 }
 
 int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* ws, size_t ws_bytes,
@@ -671,23 +829,14 @@ int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* 
     const size_t need = igemm_wgrad_workspace(d);
     TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, "conv_wgrad: workspace of %zu bytes needed, %zu given",
                 need, ws_bytes);
-    TRB_REQUIRE(aligned16(ws), TRB200_ERR_INVALID_ARGUMENT, "conv_wgrad: workspace must be 16-byte aligned");
-    const TileShape t = pick_tile(d.n, d.h, d.w, 64);
-    const WgradParams p = wgrad_plan(d, nt, t);
-    CUtensorMap tx, tdy;
-    int rc = make_act_tmap(&tx, x, d.n, d.h, d.w, d.c, t, "wgrad x");
-    if (rc) return rc;
-    rc = make_act_tmap(&tdy, dy, d.n, d.h, d.w, d.k, t, "wgrad dy");
-    if (rc) return rc;
-    float* partial = static_cast<float*>(ws);
-    if (nt == 256) rc = launch_wgrad<256>(tx, tdy, partial, p, st);
-    else if (nt == 128) rc = launch_wgrad<128>(tx, tdy, partial, p, st);
-    else rc = launch_wgrad<64>(tx, tdy, partial, p, st);
-    if (rc) return rc;
-    dim3 grid(nt / 32, 4, p.m_tiles * p.n_tiles);
-    wgrad_reduce_kernel<<<grid, 256, 0, st>>>(partial, static_cast<__half*>(dw), p, nt, d.k, d.c);
-    TRB_LAUNCH_CHECK("wgrad_reduce_kernel");
-    return TRB200_OK;
+    TRB_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255u) == 0, TRB200_ERR_INVALID_ARGUMENT,
+                "conv_wgrad: workspace must be 256-byte aligned");
+    if (igemm_small_c(d)) {
+        unsigned char* base = static_cast<unsigned char*>(ws);
+        const size_t off = igemm_im2col_bytes(d);
+        return igemm_wgrad_small_c(d, dy, x, dw, base, false, base + off, ws_bytes - off, st);
+    }
+    return wgrad_run(d, 9, dy, x, dw, static_cast<float*>(ws), st);
 }
 
 int device_status_read_and_clear(int* out) {

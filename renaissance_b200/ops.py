@@ -93,6 +93,11 @@ def default_workspace() -> Workspace:
     return _default_ws[dev]
 
 
+def kernel_launch_count() -> int:
+    """Kernels launched by libtrb200.so in this process so far."""
+    return int(_lib.load().trb200_kernel_launch_count())
+
+
 def device_status() -> None:
     """Synchronise, then raise if any kernel's bounded device-side wait gave up."""
     torch.cuda.synchronize()
@@ -167,7 +172,7 @@ def conv_dgrad(g: ConvGeometry, dy, w, dx=None, workspace=None, stream=None):
     return dx
 
 
-def conv_fprop(g: ConvGeometry, x, w, y=None, stream=None):
+def conv_fprop(g: ConvGeometry, x, w, y=None, stream=None, workspace=None, scratch=None):
     lib = _lib.load()
     _need(x, torch.float16, "x", 4)
     _need(w, torch.float16, "w", 4)
@@ -176,7 +181,13 @@ def conv_fprop(g: ConvGeometry, x, w, y=None, stream=None):
     if y is None:
         y = torch.empty((g.n, g.oh, g.ow, g.k), dtype=torch.float16, device=x.device)
     d = g.desc()
-    check(lib.trb200_conv_fprop(C.byref(d), _ptr(x), _ptr(w), _ptr(y), _stream(stream)))
+    need = lib.trb200_conv_fprop_workspace_bytes(C.byref(d))
+    if scratch is not None and scratch.numel() * scratch.element_size() >= need:
+        ws, ws_bytes = scratch, scratch.numel() * scratch.element_size()     # caller's free activation buffer
+    else:
+        ws = (workspace or default_workspace()).ensure(need)
+        ws_bytes = ws.numel()
+    check(lib.trb200_conv_fprop(C.byref(d), _ptr(x), _ptr(w), _ptr(y), _ptr(ws), ws_bytes, _stream(stream)))
     return y
 
 
@@ -206,7 +217,7 @@ class BlockStreams:
 
 def cbr_amp_bwd(g: ConvGeometry, dy, w, gamma, saved_mean, saved_inv_std, mask_bits, x, conv_out,
                 bn_scratch=None, dw=None, first_layer=False, streams: BlockStreams | None = None,
-                workspace=None, stream=None):
+                workspace=None, stream=None, dgamma=None, dbeta=None):
     """CBR_AMP_BWD / CBR_AMP_BWD_FIRST_LAYER.
 
     Node ids of the reference: in [dY, W16, gamma, saved_mean, saved_inv_var, mask, X],
@@ -228,8 +239,10 @@ def cbr_amp_bwd(g: ConvGeometry, dy, w, gamma, saved_mean, saved_inv_std, mask_b
         bn_scratch = torch.empty_like(dy)
     if dw is None:
         dw = torch.empty_like(w)
-    dgamma = torch.empty(g.k, dtype=torch.float32, device=x.device)
-    dbeta = torch.empty(g.k, dtype=torch.float32, device=x.device)
+    if dgamma is None:
+        dgamma = torch.empty(g.k, dtype=torch.float32, device=x.device)
+    if dbeta is None:
+        dbeta = torch.empty(g.k, dtype=torch.float32, device=x.device)
     d = g.desc()
     ws = (workspace or default_workspace()).ensure(lib.trb200_cbr_bwd_workspace_bytes(C.byref(d), int(first_layer)))
     a = CbrBwdArgs()
@@ -252,6 +265,75 @@ def cbr_amp_bwd(g: ConvGeometry, dy, w, gamma, saved_mean, saved_inv_std, mask_b
                                            streams.ev_dgrad.cuda_event)
     check(lib.trb200_cbr_bwd(C.byref(a)))
     return dict(dx=None if first_layer else x, dw=dw, dgamma=dgamma, dbeta=dbeta, dconv=bn_scratch)
+
+
+# --------------------------------------------------------------------------- forward side of the block
+
+def bn_stats_finalize(conv_out, gamma, beta, eps=1e-5, momentum=0.1, running_mean=None, running_var=None,
+                      out=None, workspace=None, stream=None, want_sums=False):
+    """Batch statistics of the conv output + bn_finalize (cbr_op.cpp:430-528, 622-718).
+    Returns dict(saved_mean, saved_inv_std, eq_scale, eq_bias[, sum, sqsum])."""
+    lib = _lib.load()
+    _need(conv_out, torch.float16, "conv_out")
+    c = conv_out.shape[-1]
+    m = conv_out.numel() // c
+    dev = conv_out.device
+    if out is None:
+        out = {k: torch.empty(c, dtype=torch.float32, device=dev)
+               for k in ("saved_mean", "saved_inv_std", "eq_scale", "eq_bias")}
+    if want_sums:
+        out["sum"] = torch.empty(c, dtype=torch.float32, device=dev)
+        out["sqsum"] = torch.empty(c, dtype=torch.float32, device=dev)
+    ws = (workspace or default_workspace()).ensure(lib.trb200_bn_stats_workspace_bytes(m, c))
+    check(lib.trb200_bn_stats_finalize(_ptr(conv_out), _ptr(gamma), _ptr(beta), float(eps), float(momentum),
+                                       _ptr(out.get("sum")), _ptr(out.get("sqsum")), _ptr(out["saved_mean"]),
+                                       _ptr(out["saved_inv_std"]), _ptr(out["eq_scale"]), _ptr(out["eq_bias"]),
+                                       _ptr(running_mean), _ptr(running_var), m, c, _ptr(ws), ws.numel(),
+                                       _stream(stream)))
+    return out
+
+
+def bn_apply_relu_mask(conv_out, eq_scale, eq_bias, relu_out=None, mask_bits=None, stream=None):
+    """relu_out and the bit-packed ReLU mask (cbr_op.cpp:534-616)."""
+    lib = _lib.load()
+    _need(conv_out, torch.float16, "conv_out")
+    c = conv_out.shape[-1]
+    m = conv_out.numel() // c
+    if relu_out is None:
+        relu_out = torch.empty_like(conv_out)
+    if mask_bits is None:
+        mask_bits = torch.empty(conv_out.numel() // 8, dtype=torch.uint8, device=conv_out.device)
+    check(lib.trb200_bn_apply_relu_mask(_ptr(conv_out), _ptr(eq_scale), _ptr(eq_bias), _ptr(relu_out),
+                                        _ptr(mask_bits), m, c, _stream(stream)))
+    return relu_out, mask_bits
+
+
+def maxpool2x2_fwd(x, y=None, argmax=None, stream=None):
+    _need(x, torch.float16, "x", 4)
+    n, h, w, c = x.shape
+    if y is None:
+        y = torch.empty((n, h // 2, w // 2, c), dtype=torch.float16, device=x.device)
+    if argmax is None:
+        argmax = torch.empty((n, h // 2, w // 2, c), dtype=torch.uint8, device=x.device)
+    check(_lib.load().trb200_maxpool2x2_fwd(_ptr(x), _ptr(y), _ptr(argmax), n, h, w, c, _stream(stream)))
+    return y, argmax
+
+
+def maxpool2x2_bwd(dy, argmax, dx, stream=None):
+    _need(dy, torch.float16, "dy", 4)
+    n, h, w, c = dx.shape
+    check(_lib.load().trb200_maxpool2x2_bwd(_ptr(dy), _ptr(argmax), _ptr(dx), n, h, w, c, _stream(stream)))
+    return dx
+
+
+def check_nonfinite(flat_f32, flag, stream=None):
+    check(_lib.load().trb200_check_nonfinite(_ptr(flat_f32), flat_f32.numel(), _ptr(flag), _stream(stream)))
+
+
+def sgd_momentum(w32, g32, m32, w16, lr, weight_decay, beta, scaling=None, skip_flag=None, stream=None):
+    check(_lib.load().trb200_sgd_momentum(_ptr(w32), _ptr(g32), _ptr(m32), _ptr(w16), w32.numel(), float(lr),
+                                          float(weight_decay), float(beta), _ptr(scaling), _ptr(skip_flag),
+                                          _stream(stream)))
 
 
 # --------------------------------------------------------------------------- softmax + CE

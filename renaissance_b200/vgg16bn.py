@@ -1,0 +1,319 @@
+"""VGG16-BN AMP training step: the caller of the hot path.
+
+This is the host-side schedule of one data-parallel training step, the role the
+reference's ``DeepLearningTask::run_train_epoch_gpu`` plays
+(src/task/deep_learning_task.cpp:1162-1217), reduced to what the benchmark needs:
+
+    H2D (side stream, double buffered)                      TransferStation
+    forward : 13 x [conv -> BN stats/finalize -> BN apply + ReLU + mask], 5 max pools,
+              FC 25088-4096-4096-1000 with ReLU + dropout, softmax-CE
+    backward: softmax-CE, FC, 13 x CBR_AMP_BWD (first layer without dgrad), max pools
+    gradients: half -> float cast per ~25 MB bucket in backward order, NCCL all-reduce
+              per bucket overlapped with the rest of backward, non-finite check,
+              SGD with momentum on float master weights + half working copy
+
+Everything on the named hot path (block backward, softmax-CE) and the convolution
+forward, BN forward, pooling, casts and the optimizer run in libtrb200.so.  The
+three FC GEMMs (cuBLAS through torch.mm, as the reference uses cublasGemmEx,
+src/backend/ops/dtensor/fc_op.cpp:259-480) and dropout use library kernels through
+torch.
+
+Gradients follow the reference's in-place rule: dX of a block overwrites the block's
+input buffer (src/graph/compiler.cpp:1390-1396).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from . import ops
+from .ddp import GradientBuckets
+
+VGG16_CFG = [64, 64, "M", 128, 128, "M", 256, 256, 256, "M", 512, 512, 512, "M", 512, 512, 512, "M"]
+
+
+@dataclass
+class ParamSlot:
+    name: str
+    shape: tuple
+    offset: int          # element offset in the flat buffers
+    numel: int
+    half_grad: bool      # gradient produced in half (weights) or float (BN)
+
+
+@dataclass
+class ConvLayer:
+    idx: int
+    h: int
+    c: int
+    k: int
+    pool_after: bool
+    w: ParamSlot = None
+    gamma: ParamSlot = None
+    beta: ParamSlot = None
+    buf: dict = field(default_factory=dict)
+
+
+def _align(n, a=64):
+    return (n + a - 1) // a * a
+
+
+class Vgg16BnTrainer:
+    def __init__(self, batch=256, image=224, classes=1000, lr=0.01, momentum=0.9, weight_decay=5e-4,
+                 loss_scale=1024.0, label_smoothing=0.0, bucket_mb=25.0, seed=0, device=None,
+                 process_group=None, dropout=0.5, fc_width=4096):
+        self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+        self.batch, self.image, self.classes = batch, image, classes
+        self.lr, self.beta, self.wd = lr, momentum, weight_decay
+        self.dropout = dropout
+        self.pg = process_group
+        self.world = dist.get_world_size(process_group) if (dist.is_available() and dist.is_initialized()) else 1
+
+        # ---- layers
+        self.convs: list[ConvLayer] = []
+        h, c = image, 4                       # 3 input channels padded to 4 (arch_plan_normalize.cpp:39)
+        for i, v in enumerate(VGG16_CFG):
+            if v == "M":
+                self.convs[-1].pool_after = True
+                h //= 2
+            else:
+                self.convs.append(ConvLayer(len(self.convs), h, c, v, False))
+                c = v
+        self.feat_hw = h
+        self.fc_dims = [(h * h * c, fc_width), (fc_width, fc_width), (fc_width, classes)]
+
+        # ---- flat parameter space in BACKWARD completion order: fc3, fc2, fc1, conv13 .. conv1, then all BN vectors
+        slots, off = [], 0
+
+        def add(name, shape, half_grad):
+            nonlocal off
+            n = int(math.prod(shape))
+            s = ParamSlot(name, tuple(shape), off, n, half_grad)
+            off += _align(n)
+            slots.append(s)
+            return s
+
+        self.fc = []
+        for j in reversed(range(3)):
+            i_f, o_f = self.fc_dims[j]
+            self.fc.insert(0, dict(w=add(f"fc{j}.w", (o_f, i_f), True), b=add(f"fc{j}.b", (o_f,), True)))
+        for L in reversed(self.convs):
+            L.w = add(f"conv{L.idx}.w", (L.k, 3, 3, L.c), True)
+        self.half_numel = off                 # everything before this offset has half gradients
+        for L in reversed(self.convs):
+            L.gamma = add(f"bn{L.idx}.gamma", (L.k,), False)
+            L.beta = add(f"bn{L.idx}.beta", (L.k,), False)
+        self.total = off
+        self.slots = slots
+
+        d = self.dev
+        self.w32 = torch.zeros(self.total, dtype=torch.float32, device=d)
+        self.g32 = torch.zeros(self.total, dtype=torch.float32, device=d)
+        self.m32 = torch.zeros(self.total, dtype=torch.float32, device=d)
+        self.w16 = torch.zeros(self.total, dtype=torch.float16, device=d)
+        self.g16 = torch.zeros(self.half_numel, dtype=torch.float16, device=d)
+        self._init_params(seed)
+
+        # ---- ~25 MB buckets over the flat float gradient buffer, all-reduced as backward passes them
+        self.buckets = GradientBuckets(
+            self.g16, self.g32, self.half_numel, bucket_bytes=bucket_mb * 1024 * 1024, group=process_group,
+            cast=lambda src, dst, factor: ops.cast_f16_to_f32(src, dst, factor=factor),
+            scale=lambda t, factor: ops.scale_f32(t, factor))
+
+        # ---- scalars that the reference keeps as DTensors
+        self.scaling = torch.tensor([loss_scale], dtype=torch.float32, device=d)
+        self.label_smoothing = torch.tensor([label_smoothing], dtype=torch.float32, device=d)
+        self.nan_flag = torch.zeros(1, dtype=torch.int32, device=d)
+
+        # ---- activations
+        n = batch
+        for L in self.convs:
+            e = (n, L.h, L.h, L.k)
+            L.buf["conv_out"] = torch.empty(e, dtype=torch.float16, device=d)
+            L.buf["relu_out"] = torch.empty(e, dtype=torch.float16, device=d)
+            L.buf["mask"] = torch.empty(n * L.h * L.h * L.k // 8, dtype=torch.uint8, device=d)
+            for nm in ("saved_mean", "saved_inv_std", "eq_scale", "eq_bias"):
+                L.buf[nm] = torch.empty(L.k, dtype=torch.float32, device=d)
+            L.buf["running_mean"] = torch.zeros(L.k, dtype=torch.float32, device=d)
+            L.buf["running_var"] = torch.ones(L.k, dtype=torch.float32, device=d)
+            if L.pool_after:
+                pe = (n, L.h // 2, L.h // 2, L.k)
+                L.buf["pool_out"] = torch.empty(pe, dtype=torch.float16, device=d)
+                L.buf["argmax"] = torch.empty(pe, dtype=torch.uint8, device=d)
+        big = max(L.buf["conv_out"].numel() for L in self.convs)
+        # the blocks' bn_output scratch (+ room for the first layer's packed filters behind the im2col rows)
+        self.bn_scratch = torch.empty(big + (1 << 19), dtype=torch.float16, device=d)
+        self.images = [torch.zeros((n, image, image, 4), dtype=torch.float16, device=d) for _ in range(2)]
+        self.labels = [torch.zeros(n, dtype=torch.int32, device=d) for _ in range(2)]
+        self.logits = torch.empty((n, classes), dtype=torch.float16, device=d)
+        self.dlogits = torch.empty((n, classes), dtype=torch.float16, device=d)
+        self.loss_partial = torch.empty(n, dtype=torch.float32, device=d)
+        self.loss = torch.zeros(1, dtype=torch.float32, device=d)
+        self.inv_scaling = torch.zeros(1, dtype=torch.float32, device=d)
+        self.ws = ops.Workspace(d)
+        self.copy_stream = torch.cuda.Stream(device=d)
+        self.copy_done = [torch.cuda.Event(), torch.cuda.Event()]
+        self.slot_free = [torch.cuda.Event(), torch.cuda.Event()]
+        self.timing = None        # list of (start event, stop event, flop) per forward conv launch when enabled
+        self.debug_hook = None    # called as hook(layer, dy, x) before every block backward (tests)
+
+    # ------------------------------------------------------------------ parameters
+    def view(self, buf, slot: ParamSlot):
+        return buf[slot.offset:slot.offset + slot.numel].view(slot.shape)
+
+    def _init_params(self, seed):
+        g = torch.Generator(device=self.dev).manual_seed(seed)
+        for L in self.convs:
+            fan_in = 9 * (3 if L.idx == 0 else L.c)
+            w = torch.randn(L.w.shape, generator=g, device=self.dev) * math.sqrt(2.0 / fan_in)   # Kaiming normal
+            if L.idx == 0:
+                w[..., 3] = 0.0                 # the padded input channel carries no weight
+            self.view(self.w32, L.w).copy_(w)
+            self.view(self.w32, L.gamma).fill_(1.0)
+            self.view(self.w32, L.beta).zero_()
+        for f, (i_f, o_f) in zip(self.fc, self.fc_dims):
+            self.view(self.w32, f["w"]).copy_(torch.randn((o_f, i_f), generator=g, device=self.dev) * math.sqrt(2.0 / i_f))
+            self.view(self.w32, f["b"]).zero_()
+        self.w16.copy_(self.w32)
+
+    def load_params(self, params):
+        """Master weights from numpy arrays: dict(convs=[dict(w, gamma, beta)], fcs=[dict(w, b)])."""
+        for L, p in zip(self.convs, params["convs"]):
+            self.view(self.w32, L.w).copy_(torch.from_numpy(p["w"]))
+            self.view(self.w32, L.gamma).copy_(torch.from_numpy(p["gamma"]))
+            self.view(self.w32, L.beta).copy_(torch.from_numpy(p["beta"]))
+        for f, p in zip(self.fc, params["fcs"]):
+            self.view(self.w32, f["w"]).copy_(torch.from_numpy(p["w"]))
+            self.view(self.w32, f["b"]).copy_(torch.from_numpy(p["b"]))
+        self.w16.copy_(self.w32)
+        self.m32.zero_()
+
+    def params(self):
+        """Float master weights as numpy arrays (same structure as load_params takes)."""
+        cp = lambda slot: self.view(self.w32, slot).detach().cpu().numpy().copy()
+        return dict(convs=[dict(w=cp(L.w), gamma=cp(L.gamma), beta=cp(L.beta)) for L in self.convs],
+                    fcs=[dict(w=cp(f["w"]), b=cp(f["b"])) for f in self.fc])
+
+    # ------------------------------------------------------------------ input
+    def upload(self, slot, host_images, host_labels):
+        """Async H2D of one batch from pinned host memory into buffer `slot` on the copy stream."""
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(self.slot_free[slot])
+            self.images[slot].copy_(host_images, non_blocking=True)
+            self.labels[slot].copy_(host_labels, non_blocking=True)
+            self.copy_done[slot].record(self.copy_stream)
+
+    # ------------------------------------------------------------------ one step
+    def step(self, slot=0, wait_copy=False):
+        """Forward + backward + all-reduce + SGD on input buffer `slot`.  Returns the device loss tensor."""
+        cur = torch.cuda.current_stream()
+        if wait_copy:
+            cur.wait_event(self.copy_done[slot])
+        self._forward(self.images[slot], self.labels[slot])
+        self._backward(self.images[slot], self.labels[slot])
+        self.slot_free[slot].record(cur)
+        return self.loss
+
+    def _forward(self, images, labels):
+        n = self.batch
+        x = images
+        for L in self.convs:
+            b = L.buf
+            w16 = self.view(self.w16, L.w)
+            if L.idx == 0:
+                # 3(+1)->64 first convolution: 1x1 GEMM over the pixels' 3x3 neighbourhoods, which are
+                # written into the (still free) backward scratch buffer
+                ops.conv_fprop(ops.ConvGeometry(n, L.h, L.h, L.c, L.k), x, w16, y=b["conv_out"],
+                               scratch=self.bn_scratch)
+            else:
+                if self.timing is not None:
+                    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    t0.record()
+                ops.conv_fprop(ops.ConvGeometry(n, L.h, L.h, L.c, L.k), x, w16, y=b["conv_out"])
+                if self.timing is not None:
+                    t1.record()
+                    self.timing.append((t0, t1, 2.0 * n * L.h * L.h * L.c * L.k * 9))
+            ops.bn_stats_finalize(b["conv_out"], self.view(self.w32, L.gamma), self.view(self.w32, L.beta),
+                                  running_mean=b["running_mean"], running_var=b["running_var"], out=b,
+                                  workspace=self.ws)
+            ops.bn_apply_relu_mask(b["conv_out"], b["eq_scale"], b["eq_bias"], relu_out=b["relu_out"],
+                                   mask_bits=b["mask"])
+            x = b["relu_out"]
+            if L.pool_after:
+                ops.maxpool2x2_fwd(x, y=b["pool_out"], argmax=b["argmax"])
+                x = b["pool_out"]
+        # classifier (cuBLAS): flatten is a view of the NHWC pool output
+        a = x.reshape(n, -1)
+        self.fc_in = [a]
+        self.fc_keep = []
+        for j, f in enumerate(self.fc):
+            z = torch.addmm(self.view(self.w16, f["b"]), a, self.view(self.w16, f["w"]).t())
+            if j < 2:
+                z = torch.relu_(z)
+                if self.dropout > 0:
+                    keep = (torch.rand_like(z) >= self.dropout).to(z.dtype).mul_(1.0 / (1.0 - self.dropout))
+                    z = z * keep
+                    self.fc_keep.append(keep)
+                else:
+                    self.fc_keep.append(None)
+                self.fc_in.append(z)
+                a = z
+            else:
+                self.logits.copy_(z)
+        # loss + d_logits in one kernel (the FWD and BWD softmax-CE nodes fused)
+        ops_out = ops.softmax_ce_amp_fused(self.logits, labels, self.scaling, self.label_smoothing,
+                                           dlogits=self.dlogits)
+        self.loss, self.inv_scaling = ops_out["loss"], ops_out["inv_scaling"]
+
+    def _backward(self, images, labels):
+        n = self.batch
+        self.buckets.begin_step()
+        # ---- classifier
+        dz = self.dlogits
+        for j in reversed(range(3)):
+            f = self.fc[j]
+            a = self.fc_in[j]
+            torch.mm(dz.t(), a, out=self.view(self.g16, f["w"]))
+            torch.sum(dz, dim=0, out=self.view(self.g16, f["b"]))
+            da = torch.mm(dz, self.view(self.w16, f["w"]))
+            if j > 0:
+                if self.fc_keep[j - 1] is not None:
+                    da = da * self.fc_keep[j - 1]
+                dz = da * (self.fc_in[j] > 0).to(da.dtype)        # ReLU mask of the FC activation
+            else:
+                dz = da
+            self.buckets.mark_ready(self._end_of(f))
+        # ---- feature extractor, last block first
+        grad = dz.view(n, self.feat_hw, self.feat_hw, self.convs[-1].k)
+        for L in reversed(self.convs):
+            b = L.buf
+            if L.pool_after:
+                ops.maxpool2x2_bwd(grad, b["argmax"], b["relu_out"])      # d(relu_out) over relu_out
+                grad = b["relu_out"]
+            x = images if L.idx == 0 else (self.convs[L.idx - 1].buf["pool_out"] if self.convs[L.idx - 1].pool_after
+                                           else self.convs[L.idx - 1].buf["relu_out"])
+            geo = ops.ConvGeometry(n, L.h, L.h, L.c, L.k)
+            if self.debug_hook is not None:
+                self.debug_hook(L, grad, x)
+            out = ops.cbr_amp_bwd(geo, grad, self.view(self.w16, L.w), self.view(self.w32, L.gamma),
+                                  b["saved_mean"], b["saved_inv_std"], b["mask"], x, b["conv_out"],
+                                  bn_scratch=self.bn_scratch[:b["conv_out"].numel()].view_as(b["conv_out"]),
+                                  dw=self.view(self.g16, L.w), first_layer=(L.idx == 0), workspace=self.ws,
+                                  dgamma=self.view(self.g32, L.gamma), dbeta=self.view(self.g32, L.beta))
+            grad = out["dx"]
+            self.buckets.mark_ready(self._end_of(dict(w=L.w)))
+        # BN gradients are float already and sit after every half-gradient slot
+        self.buckets.finish()
+        # ---- guard + optimizer over the whole flat range
+        self.nan_flag.zero_()
+        ops.check_nonfinite(self.g32, self.nan_flag)
+        ops.sgd_momentum(self.w32, self.g32, self.m32, self.w16, self.lr, self.wd, self.beta,
+                         scaling=self.scaling, skip_flag=self.nan_flag)
+
+    def _end_of(self, group):
+        """End offset (exclusive) of the flat range whose half gradients are complete once `group` is done."""
+        last = group["b"] if "b" in group else group["w"]
+        return last.offset + _align(last.numel)

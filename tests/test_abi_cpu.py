@@ -59,10 +59,13 @@ def test_tensor_core_coverage_rule(lib):
     vgg = _lib.ConvDesc(256, 56, 56, 64, 64, 3, 3, 1, 1, 1, 1)
     first = _lib.ConvDesc(256, 224, 224, 4, 64, 3, 3, 1, 1, 1, 1)
     strided = _lib.ConvDesc(8, 56, 56, 64, 64, 3, 3, 1, 1, 2, 2)
+    odd = _lib.ConvDesc(8, 56, 56, 24, 64, 3, 3, 1, 1, 1, 1)
     for which in (0, 1, 2):
         assert lib.trb200_conv_uses_tensor_cores(C.byref(vgg), which) == 1
-        assert lib.trb200_conv_uses_tensor_cores(C.byref(first), which) == 0
+        # the 4-channel first layer: weight gradient and forward only (it has no data gradient)
+        assert lib.trb200_conv_uses_tensor_cores(C.byref(first), which) == (0 if which == 1 else 1)
         assert lib.trb200_conv_uses_tensor_cores(C.byref(strided), which) == 0
+        assert lib.trb200_conv_uses_tensor_cores(C.byref(odd), which) == 0
 
 
 def test_workspace_sizes_are_consistent(lib):

@@ -28,7 +28,7 @@ def _oracle(orc, x, wt, dy, pad, stride):
 
 DIRECT_CASES = [
     (1, 5, 5, 3, 8, 3, 1, 1), (2, 9, 7, 4, 8, 3, 1, 2), (1, 12, 12, 3, 8, 7, 3, 2), (2, 8, 8, 16, 24, 1, 0, 1),
-    (3, 6, 10, 8, 8, 5, 2, 1), (2, 16, 16, 4, 64, 3, 1, 1),
+    (3, 6, 10, 8, 8, 5, 2, 1), (2, 16, 16, 4, 24, 3, 1, 1),
 ]
 
 
@@ -70,6 +70,30 @@ IGEMM_CASES = [
     (1, 9, 33, 64, 512),    # two N tiles
     (4, 14, 14, 512, 512),  # deep VGG shape at a small batch
 ]
+
+
+@pytest.mark.parametrize("n,h,w,k", [(2, 16, 16, 64), (3, 9, 7, 128), (2, 20, 12, 256)])
+def test_first_layer_four_channels_on_tensor_cores(orc, n, h, w, k):
+    """c = 4 (3 image channels + 1 pad): forward and weight gradient as a 1x1 GEMM over
+    the pixels' 3x3 neighbourhoods."""
+    from renaissance_b200 import ops
+    x, wt, dy = _rand_case(n * 5 + k, n, h, w, 4, k, 3, 1, 1)
+    x[..., 3] = 0
+    ref_dw, _ = _oracle(orc, x, wt, dy, 1, 1)
+    g = ops.ConvGeometry(n, h, w, 4, k)
+    assert ops.conv_uses_tensor_cores(g, "wgrad") and ops.conv_uses_tensor_cores(g, "fprop")
+    assert not ops.conv_uses_tensor_cores(g, "dgrad")
+    dw = ops.conv_wgrad(g, dev(dy), dev(x))
+    y = ops.conv_fprop(g, dev(x), dev(wt))
+    ops.device_status()
+    assert rel_l2(host(dw).astype(np.float32), ref_dw) < 2e-3
+    assert rel_l2(host(y).astype(np.float32), orc.conv_fwd(x.astype(np.float32), wt.astype(np.float32))) < 2e-3
+    ops.set_conv_backend(direct_only=True)
+    try:
+        dw_direct = ops.conv_wgrad(g, dev(dy), dev(x))
+    finally:
+        ops.set_conv_backend(direct_only=False)
+    assert rel_l2(host(dw).astype(np.float32), host(dw_direct).astype(np.float32)) < 2e-3
 
 
 @pytest.mark.parametrize("n,h,w,c,k", IGEMM_CASES)
