@@ -65,9 +65,27 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if failed:
         raise RuntimeError("nvcc failed")
     if force or procs or _stale(LIB, objs):
-        cmd = [_nvcc(), "-shared", "-o", LIB, *objs, "-lcudart"]
+        cmd = [_nvcc(), "-Wno-deprecated-gpu-targets", "-shared", "-o", LIB, *objs, "-lcudart"]
         subprocess.check_call(cmd)
+    build_plugin(force or bool(procs))
     return LIB
+
+
+PLUGIN_DIR = os.path.join(HERE, "plugin")
+PLUGIN_LIB = os.path.join(LIB_DIR, "libtrb200_plugin.so")
+
+
+def build_plugin(force: bool = False) -> str:
+    """The operator-registry adapter and the test harness (host C++ only), linked against libtrb200.so."""
+    srcs = [os.path.join(PLUGIN_DIR, f) for f in ("b200_ops.cpp", "harness.cpp")]
+    deps = srcs + [os.path.join(PLUGIN_DIR, "tr_shim.h"), os.path.join(ROOT, "include", "trb200.h"), LIB]
+    if force or _stale(PLUGIN_LIB, deps):
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O2", "-Xcompiler", "-fPIC",
+               "-shared", "-o", PLUGIN_LIB, *srcs,
+               "-I", os.path.join(ROOT, "include"), "-I", PLUGIN_DIR, "-L", LIB_DIR, "-ltrb200",
+               "-Xlinker", "-rpath=$ORIGIN", "-lcudart"]
+        subprocess.check_call(cmd)
+    return PLUGIN_LIB
 
 
 if __name__ == "__main__":

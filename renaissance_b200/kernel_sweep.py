@@ -1,0 +1,190 @@
+"""Per-kernel roofline sweep of the hot-path kernels on one GPU.
+
+    python -m renaissance_b200.kernel_sweep                 # everything, JSON lines
+    python -m renaissance_b200.kernel_sweep --only block    # BASELINE config 2 (one block backward)
+    python -m renaissance_b200.kernel_sweep --only bnrelu --quick
+
+Covers BASELINE.json's config 2 (Conv3x3 C=K=64 + BN + ReLU backward at N=256, 56x56)
+and config 5 (BN+ReLU backward over N*H*W x C, fused softmax-CE over N x C), plus the
+13 VGG16-BN conv shapes.  Every point: 3 warm-up calls, then timed calls bracketed by
+CUDA events on the launching stream with a write over a buffer larger than L2 between
+them (not timed); the median is reported.  `frac` = achieved / measured peak
+(MEASURED_PEAKS.json beside the repository root when present: copy bandwidth and cuBLAS
+bf16 burst rate, these being kernels timed in isolation).
+
+Algorithmic work per call:
+    BN+ReLU backward   10.25 B/element  (two sweeps over dy, x, mask; one write of dconv)
+    softmax-CE fused   4 B/element + 12 B/row  (read logits, write d_logits)
+    conv dgrad / wgrad / fprop   2*N*H*W*K*9*C flop
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+
+import torch
+
+from . import ops
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def peaks():
+    p = os.path.join(_ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class Timer:
+    def __init__(self, iters):
+        self.iters = iters
+        self.flush = torch.empty(512 * 1024 * 1024, dtype=torch.uint8, device="cuda")   # 4 x L2
+
+    def __call__(self, fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(self.iters):
+            self.flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts), min(ts)
+
+
+def emit(**kw):
+    print(json.dumps(kw), flush=True)
+
+
+def bnrelu_point(t, m, c, hbm, src):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    dy = torch.randn((m, c), generator=g, device="cuda").half()
+    x = torch.randn((m, c), generator=g, device="cuda").half()
+    bits = torch.randint(0, 256, (m * c // 8,), generator=g, device="cuda", dtype=torch.int32).to(torch.uint8)
+    gamma = 1 + 0.2 * torch.randn(c, generator=g, device="cuda")
+    mean = x.float().mean(dim=0)
+    inv = 1.0 / torch.sqrt(x.float().var(dim=0, unbiased=False) + 1e-5)
+    out = torch.empty_like(dy)
+    med, best = t(lambda: ops.bnrelu_bwd(dy, bits, x, gamma, mean, inv, dconv=out))
+    byt = 10.25 * m * c + 20 * c
+    emit(kernel="bnrelu_bwd (reduce + finalize + apply)", rows=m, channels=c, ms=round(med, 4), best_ms=round(best, 4),
+         bound="hbm", achieved=round(byt / med / 1e6, 1), peak=hbm, unit="GB/s", frac=round(byt / med / 1e6 / hbm, 4),
+         peak_source=src)
+
+
+def softmax_point(t, b, c, ls, hbm, src):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    z = (torch.randn((b, c), generator=g, device="cuda") * 2).half()
+    lab = torch.randint(0, c, (b,), generator=g, device="cuda", dtype=torch.int32)
+    sc = torch.tensor([1024.0], device="cuda")
+    lsd = torch.tensor([ls], device="cuda")
+    d = torch.empty_like(z)
+    med, best = t(lambda: ops.softmax_ce_amp_fused(z, lab, sc, lsd, dlogits=d))
+    byt = 4.0 * b * c + 12 * b
+    emit(kernel="softmax_ce fused fwd+bwd", rows=b, classes=c, label_smoothing=ls, ms=round(med, 4),
+         best_ms=round(best, 4), bound="hbm", achieved=round(byt / med / 1e6, 1), peak=hbm, unit="GB/s",
+         frac=round(byt / med / 1e6 / hbm, 4), peak_source=src)
+
+
+def conv_point(t, n, h, c, k, what, tc, src):
+    geo = ops.ConvGeometry(n, h, h, c, k)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((n, h, h, c), generator=g, device="cuda").half()
+    w = (torch.randn((k, 3, 3, c), generator=g, device="cuda") * (2.0 / (9 * c)) ** 0.5).half()
+    dy = torch.randn((n, h, h, k), generator=g, device="cuda").half()
+    flop = 2.0 * n * h * h * c * k * 9
+    if what == "dgrad":
+        dx = torch.empty_like(x)
+        med, best = t(lambda: ops.conv_dgrad(geo, dy, w, dx=dx))
+    elif what == "wgrad":
+        dw = torch.empty_like(w)
+        med, best = t(lambda: ops.conv_wgrad(geo, dy, x, dw=dw))
+    else:
+        y = torch.empty_like(dy)
+        med, best = t(lambda: ops.conv_fprop(geo, x, w, y=y))
+    ops.device_status()
+    emit(kernel=f"conv {what}", shape=dict(n=n, h=h, w=h, c=c, k=k), ms=round(med, 4), best_ms=round(best, 4),
+         bound="tensor", achieved=round(flop / med / 1e9, 1), peak=tc, unit="TFLOP/s",
+         frac=round(flop / med / 1e9 / tc, 4), peak_source=src)
+
+
+def block_point(t, n, h, c, k, hbm, tc, src):
+    """BASELINE config 2: the whole block backward through trb200_cbr_bwd on three streams."""
+    geo = ops.ConvGeometry(n, h, h, c, k)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x0 = torch.randn((n, h, h, c), generator=g, device="cuda").half()
+    x = x0.clone()
+    w = (torch.randn((k, 3, 3, c), generator=g, device="cuda") * (2.0 / (9 * c)) ** 0.5).half()
+    dy = torch.randn((n, h, h, k), generator=g, device="cuda").half()
+    conv_out = torch.randn((n, h, h, k), generator=g, device="cuda").half()
+    bits = torch.randint(0, 256, (n * h * h * k // 8,), generator=g, device="cuda", dtype=torch.int32).to(torch.uint8)
+    gamma = torch.ones(k, device="cuda")
+    mean = conv_out.float().mean(dim=(0, 1, 2))
+    inv = 1.0 / torch.sqrt(conv_out.float().var(dim=(0, 1, 2), unbiased=False) + 1e-5)
+    scratch = torch.empty_like(dy)
+    dw = torch.empty_like(w)
+    st = ops.BlockStreams.create()
+    torch.cuda.synchronize()
+
+    def call():
+        with torch.cuda.stream(st.bn):
+            ops.cbr_amp_bwd(geo, dy, w, gamma, mean, inv, bits, x, conv_out, bn_scratch=scratch, dw=dw, streams=st)
+        torch.cuda.current_stream().wait_stream(st.bn)
+
+    torch.cuda.current_stream().wait_stream(st.bn)
+    med, best = t(call)
+    ops.device_status()
+    flop = 2 * 2.0 * n * h * h * c * k * 9
+    byt = 10.25 * n * h * h * k
+    emit(kernel="cbr_amp_bwd (BN+ReLU bwd, wgrad, dgrad)", shape=dict(n=n, h=h, w=h, c=c, k=k), ms=round(med, 4),
+         best_ms=round(best, 4), ideal_ms=round(flop / tc / 1e9 + byt / hbm / 1e6, 4),
+         note="ideal = conv flop at the measured tensor peak + BN bytes at the measured copy bandwidth",
+         frac=round((flop / tc / 1e9 + byt / hbm / 1e6) / med, 4), peak_source=src)
+
+
+VGG_SHAPES = [(224, 64, 64), (112, 64, 128), (112, 128, 128), (56, 128, 256), (56, 256, 256), (28, 256, 512),
+              (28, 512, 512), (14, 512, 512)]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="all", choices=["all", "block", "bnrelu", "softmax", "conv"])
+    ap.add_argument("--quick", action="store_true", help="one small point per kernel (for profiler captures)")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--batch", type=int, default=256, help="images for the conv / block points")
+    args = ap.parse_args()
+    hbm, tc, src = peaks()
+    t = Timer(1 if args.quick else args.iters)
+    n = args.batch
+    if args.only in ("all", "block"):
+        block_point(t, n, 56, 64, 64, hbm, tc, src)
+    if args.only in ("all", "bnrelu"):
+        pts = [(n * 56 * 56, 64)] if args.quick else \
+            [(1 << e, c) for c in (64, 256, 512, 2048) for e in (16, 18, 20, 22, 24) if (1 << e) * c * 2 * 3 < 150e9]
+        if not args.quick:
+            pts.insert(0, (256 * 56 * 56, 64))
+        for m, c in pts:
+            bnrelu_point(t, m, c, hbm, src)
+    if args.only in ("all", "softmax"):
+        pts = [(4096, 32000, 0.1)] if args.quick else \
+            [(b, c, ls) for b in (4096, 65536) for c in (1000, 10000, 32000) for ls in (0.0, 0.1)] + [(256, 1000, 0.0)]
+        for b, c, ls in pts:
+            softmax_point(t, b, c, ls, hbm, src)
+    if args.only in ("all", "conv"):
+        shapes = [(56, 64, 64), (28, 256, 512)] if args.quick else [(56, 64, 64)] + VGG_SHAPES
+        for h, c, k in shapes:
+            for what in ("dgrad", "wgrad", "fprop"):
+                conv_point(t, n, h, c, k, what, tc, src)
+
+
+if __name__ == "__main__":
+    main()

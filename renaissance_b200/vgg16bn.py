@@ -157,7 +157,7 @@ class Vgg16BnTrainer:
         self.copy_stream = torch.cuda.Stream(device=d)
         self.copy_done = [torch.cuda.Event(), torch.cuda.Event()]
         self.slot_free = [torch.cuda.Event(), torch.cuda.Event()]
-        self.timing = None        # list of (start event, stop event, flop) per forward conv launch when enabled
+        self.timing = None        # list of (start event, stop event, flop, bytes) per forward conv launch when enabled
         self.debug_hook = None    # called as hook(layer, dy, x) before every block backward (tests)
 
     # ------------------------------------------------------------------ parameters
@@ -235,7 +235,8 @@ class Vgg16BnTrainer:
                 ops.conv_fprop(ops.ConvGeometry(n, L.h, L.h, L.c, L.k), x, w16, y=b["conv_out"])
                 if self.timing is not None:
                     t1.record()
-                    self.timing.append((t0, t1, 2.0 * n * L.h * L.h * L.c * L.k * 9))
+                    self.timing.append((t0, t1, 2.0 * n * L.h * L.h * L.c * L.k * 9,
+                                        2.0 * (n * L.h * L.h * (L.c + L.k) + 9 * L.c * L.k)))
             ops.bn_stats_finalize(b["conv_out"], self.view(self.w32, L.gamma), self.view(self.w32, L.beta),
                                   running_mean=b["running_mean"], running_var=b["running_var"], out=b,
                                   workspace=self.ws)

@@ -79,6 +79,15 @@ def test_workspace_sizes_are_consistent(lib):
     assert total >= wg + dg + bn and first >= wg + bn and first < total
 
 
+def test_registry_adapter_library_loads_and_exports_the_hook(lib):
+    path = os.path.join(os.path.dirname(_lib.LIB_PATH), "libtrb200_plugin.so")
+    assert os.path.exists(path)
+    out = subprocess.check_output(["nm", "-D", "--defined-only", path], text=True)
+    assert " T tr_b200_register_ops" in out
+    plug = C.CDLL(path)
+    assert hasattr(plug, "tr_b200_register_ops") and hasattr(plug, "trbh_create")
+
+
 def test_product_package_never_imports_the_oracle():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     pkg = os.path.join(root, "renaissance_b200")
