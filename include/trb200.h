@@ -85,6 +85,26 @@ int trb200_bnrelu_bwd(const void* dy, const void* mask_bits, const void* x,
                       int64_t m, int32_t c,
                       void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same operator for callers that cannot allocate device memory (a runtime
+ * whose memory plan is frozen, a plugin running inside someone else's capture, a
+ * process that gave the whole GPU to its own arena).  It has no counterpart in the
+ * reference.  Instead of a workspace it uses a fixed 4 MiB array inside the library
+ * image (held by every GPU that loads the library until the process exits) and it
+ * calls no cudaMalloc, cudaFree or other allocating routine.
+ *   - Limit: c <= 4096 (and c % 8 == 0); anything larger is rejected with
+ *     TRB200_ERR_UNSUPPORTED.  m is not limited.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call before
+ *     any stream capture begins.
+ *   - All calls on a device share the array: calls whose kernels can overlap on the
+ *     GPU (different streams without ordering) race and give wrong sums.  Calls on
+ *     one stream, or ordered by events, are fine; nothing has to be cleared between
+ *     calls. */
+int trb200_bnrelu_bwd_static(const void* dy, const void* mask_bits, const void* x,
+                             const float* gamma, const float* saved_mean, const float* saved_inv_std,
+                             void* dconv, float* dgamma, float* dbeta,
+                             int64_t m, int32_t c, void* stream);
+
 /* ------------------------------------------------------------------------- */
 /* Convolution weight gradient, dW[k,r,s,c] = sum dY[n,oh,ow,k] * X[...]      */
 /* half in, float accumulate, half out, fixed-order split reduction.          */

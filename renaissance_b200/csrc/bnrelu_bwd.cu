@@ -20,6 +20,8 @@
 // Algorithmic HBM bytes: 2 x (2 + 2 + 1/8) read + 2 written = 10.25 B / element.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace trb {
 namespace {
 
@@ -272,4 +274,93 @@ extern "C" int trb200_bnrelu_bwd(const void* dy, const void* mask_bits, const vo
                                  size_t workspace_bytes, void* stream) {
     return trb::bnrelu_bwd_launch(dy, mask_bits, x, gamma, saved_mean, saved_inv_std, dconv, dgamma,
                                   dbeta, m, c, workspace, workspace_bytes, trb::as_stream(stream));
+}
+
+// ---------------------------------------------------------------------------
+// Variant for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc at the point where they need
+// the operator: a replay-only runtime whose memory plan is frozen after start-up, a
+// plugin that runs inside another framework's stream capture, or a process that has
+// handed all of the GPU's memory to its own arena.  For them the per-strip partial
+// sums live in a fixed array that is part of the library image instead of a
+// caller-provided workspace.  Every GPU that loads the library holds these 4 MiB
+// until the process exits.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticPartialFloats = 1u << 20;                  // 4 MiB
+constexpr int kStaticMaxChannels = 4096;
+static __device__ __align__(256) float g_bnrelu_static_partials[kStaticPartialFloats];
+
+// Same strip layout as make_plan(), with fewer strips when c is large so that
+// strips * 2 * c floats fit the fixed array.
+static trb::BnPlan make_static_plan(int64_t m, int c) {
+    trb::BnPlan p = trb::make_plan(m, c);
+    const int64_t cap = (int64_t)(kStaticPartialFloats / (2 * (size_t)c));
+    if (p.gx > cap) {
+        p.gx = (int)cap;
+        int64_t rps = (m + p.gx - 1) / p.gx;
+        rps = (rps + p.by - 1) / p.by * p.by;
+        p.rows_per_strip = rps;
+        p.gx = (int)((m + rps - 1) / rps);
+    }
+    return p;
+}
+
+// Device address of the fixed array on the CURRENT device, looked up once per device.
+// In host code the array's name only stands for the symbol; the address a kernel can
+// use comes from cudaGetSymbolAddress.
+static int static_partials_ptr(float** out) {
+    static std::mutex mu;
+    static float* cached[64] = {nullptr};
+    int dev = 0;
+    TRB_CUDA_TRY(cudaGetDevice(&dev));
+    TRB_REQUIRE(dev >= 0 && dev < 64, TRB200_ERR_UNSUPPORTED, "bnrelu_bwd_static: device ordinal %d not covered", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cached[dev]) {
+        float* ptr = nullptr;
+        TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_bnrelu_static_partials));
+        TRB_REQUIRE(ptr != nullptr, TRB200_ERR_CUDA, "bnrelu_bwd_static: no device address for the fixed scratch");
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return TRB200_OK;
+}
+
+extern "C" int trb200_bnrelu_bwd_static(const void* dy, const void* mask_bits, const void* x,
+                                        const float* gamma, const float* saved_mean,
+                                        const float* saved_inv_std, void* dconv, float* dgamma,
+                                        float* dbeta, int64_t m, int32_t c, void* stream) {
+    TRB_REQUIRE(dy && mask_bits && x && gamma && saved_mean && saved_inv_std && dgamma && dbeta,
+                TRB200_ERR_INVALID_ARGUMENT, "bnrelu_bwd_static: null pointer");
+    TRB_REQUIRE(m > 0 && c > 0 && c % 8 == 0, TRB200_ERR_UNSUPPORTED,
+                "bnrelu_bwd_static: need m > 0 and c a positive multiple of 8 (m=%lld c=%d)", (long long)m, c);
+    TRB_REQUIRE(c <= kStaticMaxChannels, TRB200_ERR_UNSUPPORTED,
+                "bnrelu_bwd_static: c=%d is beyond the %d channels the fixed 4 MiB scratch covers; "
+                "use trb200_bnrelu_bwd with a workspace", c, kStaticMaxChannels);
+    TRB_REQUIRE(trb::aligned16(dy) && trb::aligned16(x) && (!dconv || trb::aligned16(dconv)),
+                TRB200_ERR_INVALID_ARGUMENT, "bnrelu_bwd_static: dy, x and dconv must be 16-byte aligned");
+    TRB_REQUIRE(dconv != dy && dconv != x, TRB200_ERR_INVALID_ARGUMENT,
+                "bnrelu_bwd_static: dconv must not alias dy or x");
+    float* partial = nullptr;
+    const int rc = static_partials_ptr(&partial);
+    if (rc) return rc;
+    const trb::BnPlan p = make_static_plan(m, c);
+    cudaStream_t s = trb::as_stream(stream);
+    dim3 grid(p.gx, p.gy);
+    // every strip overwrites all of its partials before the finalize kernel reads them,
+    // so nothing left in the array by an earlier call is ever read
+    trb::bnrelu_bwd_reduce<<<grid, trb::kThreads, 0, s>>>(
+        static_cast<const uint4*>(dy), static_cast<const uint8_t*>(mask_bits), static_cast<const uint4*>(x),
+        saved_mean, saved_inv_std, partial, m, c, p.tpr, p.bx, p.by, p.rows_per_strip);
+    TRB_LAUNCH_CHECK("bnrelu_bwd_reduce (static scratch)");
+    trb::bnrelu_bwd_finalize<<<(2 * c + 7) / 8, 256, 0, s>>>(partial, dgamma, dbeta, c, p.gx);
+    TRB_LAUNCH_CHECK("bnrelu_bwd_finalize (static scratch)");
+    if (dconv) {
+        trb::bnrelu_bwd_apply<<<grid, trb::kThreads, 0, s>>>(
+            static_cast<const uint4*>(dy), static_cast<const uint8_t*>(mask_bits), static_cast<const uint4*>(x),
+            gamma, saved_mean, saved_inv_std, dgamma, dbeta, static_cast<uint4*>(dconv), m, p.tpr, p.bx, p.by,
+            p.rows_per_strip);
+        TRB_LAUNCH_CHECK("bnrelu_bwd_apply (static scratch)");
+    }
+    return TRB200_OK;
 }
