@@ -10,7 +10,7 @@ import os
 import re
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libtrb200.so")
+LIB_PATH = os.environ.get("TRB200_LIB") or os.path.join(_HERE, "lib", "libtrb200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "trb200.h")
 
 OK = 0

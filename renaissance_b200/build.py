@@ -16,14 +16,16 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
-LIB = os.path.join(LIB_DIR, "libtrb200.so")
-OBJ_DIR = os.path.join(HERE, "build")
+# development builds: TRB200_BUILD_TAG=name gives lib/libtrb200_name.so built with TRB200_EXTRA_NVCC_FLAGS
+_TAG = os.environ.get("TRB200_BUILD_TAG", "")
+LIB = os.path.join(LIB_DIR, f"libtrb200{'_' + _TAG if _TAG else ''}.so")
+OBJ_DIR = os.path.join(HERE, "build" + ("_" + _TAG if _TAG else ""))
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
     "-I", os.path.join(ROOT, "include"), "-I", CSRC,
-]
+] + os.environ.get("TRB200_EXTRA_NVCC_FLAGS", "").split()
 
 
 def _nvcc() -> str:
@@ -67,7 +69,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if force or procs or _stale(LIB, objs):
         cmd = [_nvcc(), "-Wno-deprecated-gpu-targets", "-shared", "-o", LIB, *objs, "-lcudart"]
         subprocess.check_call(cmd)
-    build_plugin(force or bool(procs))
+    if not _TAG:
+        build_plugin(force or bool(procs))
     return LIB
 
 

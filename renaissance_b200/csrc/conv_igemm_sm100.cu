@@ -26,10 +26,13 @@
 //   partial tile and a second kernel adds the splits in split order (bitwise
 //   reproducible) and writes half KRSC.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM
-// allocation, warps 2-5 = epilogue (TMEM -> registers -> half -> shared -> TMA
-// store, or float partial -> global).  Two accumulator buffers in TMEM let the
-// epilogue of tile i overlap the main loop of tile i+1.
+// Warp roles (256 threads): warp 0 = TMA producer for the A operand, warp 1 = MMA
+// issuer + TMEM allocation, warps 2 (and 3) = TMA producers for the B operand,
+// warps 4-7 = epilogue (TMEM -> registers -> half -> shared -> TMA store, or float
+// partial -> global).  Issuing a TMA box costs its thread a few hundred clocks, so
+// the loads of a stage are spread over two or three threads that all arrive on the
+// stage's "full" barrier.  Two accumulator buffers in TMEM let the epilogue of tile i
+// overlap the main loop of tile i+1.
 #include "common.cuh"
 #include "conv.cuh"
 #include "sm100_ptx.cuh"
@@ -42,11 +45,25 @@ namespace trb {
 
 __device__ int g_device_status = 0;   // first device-side failure code, 0 = none
 
+// Optional per-role cycle counters (development builds only, -DTRB200_ROLE_TIMERS):
+// [block][role 0 producer / 1 MMA / 2 epilogue][4 slots], see the RT_ADD sites.
+#ifdef TRB200_ROLE_TIMERS
+__device__ long long g_role_timers[256 * 3 * 4];
+#define RT_DECL long long rt_t0 = clock64(), rt_acc[4] = {0, 0, 0, 0}
+#define RT_ADD(i) do { const long long rt_t = clock64(); rt_acc[i] += rt_t - rt_t0; rt_t0 = rt_t; } while (0)
+#define RT_STORE(role) do { if (blockIdx.x < 256) for (int rt_i = 0; rt_i < 4; ++rt_i) \
+        g_role_timers[(blockIdx.x * 3 + (role)) * 4 + rt_i] = rt_acc[rt_i]; } while (0)
+#else
+#define RT_DECL do { } while (0)
+#define RT_ADD(i) do { } while (0)
+#define RT_STORE(role) do { } while (0)
+#endif
+
 namespace {
 
 using namespace ptx;
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 256;      // warp 0: TMA producer A, 1: MMA, 2 (and 3): TMA producer B, 4-7: epilogue
 constexpr int kEpiThreads = 128;
 constexpr int kATileBytes = 128 * 128;    // 128 pixels x 64 halfs
 constexpr int kStageTileBytes = 64 * 128; // wgrad: 64 pixels x 64 halfs
@@ -132,14 +149,6 @@ int make_act_tmap(CUtensorMap* m, const void* base, int n, int h, int w, int c, 
 }
 
 // ------------------------------------------------------------------ shared helpers
-struct PipeState {
-    int stage = 0;
-    uint32_t phase = 0;
-    __device__ __forceinline__ void advance(int stages) {
-        if (++stage == stages) { stage = 0; phase ^= 1u; }
-    }
-};
-
 __device__ __forceinline__ void abort_drain(volatile int* abort_flag) {
     // after a failed wait: give copies already in flight time to land before the
     // block gives its shared memory back
@@ -184,18 +193,19 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
     const uint32_t b_base = base + kStages * kATileBytes;
     const uint32_t epi_base = b_base + kStages * L::kBTileBytes;
     const uint32_t bar_base = epi_base + L::kEpiBytes;
-    // barriers: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    // barriers: full[kStages] (2 producers), empty[kStages], tmem_full[2], tmem_empty[2]
+    const uint32_t full0 = bar_base, empty0 = bar_base + 8u * kStages;
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
+    __shared__ int s_epi_fail;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        s_epi_fail = 0;
+        for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8u * s, 2); mbar_init(empty0 + 8u * s, 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), kEpiThreads); }
         fence_barrier_init();
         prefetch_tmap(&tm_in);
@@ -214,83 +224,141 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
 
     const int total_tiles = p.m_tiles * p.n_tiles;
     const int ksteps = p.taps * p.cin_slices;
+    // tap window: 3x3 walks r, s in [0, 3); 1x1 is the centre tap only
+    const int t_lo = p.taps == 9 ? 0 : 1, t_hi = p.taps == 9 ? 3 : 2;
 
+    // The single-thread roles below are paced by their own instruction count (a lone
+    // thread issues roughly one dependent instruction every few clocks), so their inner
+    // loops carry running addresses and counters instead of divisions and multiplies.
+    // Each of these roles is run by a whole (converged) warp with warp-uniform values, and
+    // only the instructions that must come from one thread are predicated on lane 0: the
+    // compiler can then keep addresses, coordinates and descriptors in uniform registers,
+    // which is where the TMA and MMA instructions take them from.
     if (warp == 0) {
-        if (lane == 0) {
-            PipeState ps;
+        {                                                  // producer A: one shifted activation box per K step
+            uint32_t stage = 0, phase = 0;
             bool ok = true;
+            RT_DECL;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int nt = tile % p.n_tiles, mt = tile / p.n_tiles;
+                const int mt = tile / p.n_tiles;
                 const int w0 = (mt % p.tw) * p.bw, h0 = ((mt / p.tw) % p.th) * p.bh;
                 const int n0 = (mt / (p.tw * p.th)) * p.bn;
-                for (int ks = 0; ks < ksteps; ++ks) {
-                    const int tap = ks / p.cin_slices, slice = ks % p.cin_slices;
-                    const int r = (tap + p.tap_base) / 3, s = (tap + p.tap_base) % 3;
-                    ok = mbar_wait(empty_bar(ps.stage), ps.phase ^ 1u, abort_flag, status, kStatusProducerTimeout);
-                    if (!ok) break;
-                    mbar_expect_tx(full_bar(ps.stage), L::kStageBytes);
-                    tma_load_4d(a_base + ps.stage * kATileBytes, &tm_in, full_bar(ps.stage), slice * 64,
-                                w0 + s - 1, h0 + r - 1, n0);
-                    if (p.b_tap_is_dim1)
-                        tma_load_3d(b_base + ps.stage * L::kBTileBytes, &tm_w, full_bar(ps.stage), slice * 64, tap,
-                                    nt * NT);
-                    else
-                        tma_load_3d(b_base + ps.stage * L::kBTileBytes, &tm_w, full_bar(ps.stage), slice * 64,
-                                    nt * NT, tap);
-                    ps.advance(kStages);
-                }
+                for (int r = t_lo; r < t_hi && ok; ++r)
+                    for (int s = t_lo; s < t_hi && ok; ++s)
+                        for (int slice = 0; slice < p.cin_slices; ++slice) {
+                            RT_ADD(1);
+                            ok = mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout);
+                            RT_ADD(0);
+                            if (!ok) break;
+                            const uint32_t fb = full0 + 8u * stage;
+                            if (lane == 0) {
+                                mbar_expect_tx(fb, kATileBytes);
+                                tma_load_4d(a_base + stage * kATileBytes, &tm_in, fb, slice * 64, w0 + s - 1, h0 + r - 1,
+                                            n0);
+                            }
+                            __syncwarp();
+                            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                        }
+            }
+            RT_ADD(1);
+            if (lane == 0) RT_STORE(0);
+        }
+    } else if (warp == 2) {
+        {                                                  // producer B: one filter tile per K step
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int n_off = (tile % p.n_tiles) * NT;
+                for (int tap = 0; tap < p.taps && ok; ++tap)
+                    for (int slice = 0; slice < p.cin_slices; ++slice) {
+                        ok = mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout);
+                        if (!ok) break;
+                        const uint32_t fb = full0 + 8u * stage;
+                        if (lane == 0) {
+                            mbar_expect_tx(fb, L::kBTileBytes);
+                            if (p.b_tap_is_dim1)
+                                tma_load_3d(b_base + stage * L::kBTileBytes, &tm_w, fb, slice * 64, tap, n_off);
+                            else
+                                tma_load_3d(b_base + stage * L::kBTileBytes, &tm_w, fb, slice * 64, n_off, tap);
+                        }
+                        __syncwarp();
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        {                                                  // MMA issuer
             constexpr uint32_t idesc = idesc_f16(128, NT, false, false);
-            PipeState ps;
+            constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t a_lo0 = smem_desc_lo(a_base, 16), b_lo0 = smem_desc_lo(b_base, 16);
+            uint32_t stage = 0, phase = 0;
             bool ok = true;
             int iter = 0;
+            RT_DECL;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
                 const int acc = iter & 1;
+                RT_ADD(2);
                 ok = mbar_wait(tempty_bar(acc), (((uint32_t)iter >> 1) & 1u) ^ 1u, abort_flag, status,
                                kStatusMmaTimeout);
+                RT_ADD(0);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * NT);
+                uint32_t accumulate = 0;
                 for (int ks = 0; ks < ksteps; ++ks) {
-                    ok = mbar_wait(full_bar(ps.stage), ps.phase, abort_flag, status, kStatusMmaTimeout);
+                    RT_ADD(2);
+                    ok = mbar_wait(full0 + 8u * stage, phase, abort_flag, status, kStatusMmaTimeout);
+                    RT_ADD(1);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t adesc = smem_desc_sw128(a_base + ps.stage * kATileBytes, 16, 1024);
-                    const uint64_t bdesc = smem_desc_sw128(b_base + ps.stage * L::kBTileBytes, 16, 1024);
-#pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4)   // 4 x (K = 16 halfs = 32 bytes inside the 128-byte row)
-                        umma_f16(d_tmem, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc,
-                                 (ks | k4) != 0 ? 1u : 0u);
-                    umma_commit(empty_bar(ps.stage));
-                    ps.advance(kStages);
+                    const uint32_t a_lo = a_lo0 + stage * (kATileBytes >> 4);
+                    const uint32_t b_lo = b_lo0 + stage * (L::kBTileBytes >> 4);
+                    // 4 x (K = 16 halfs = 32 bytes inside the 128-byte row: +2 in the address field)
+                    if (lane == 0) {
+                        umma_f16_lohi(d_tmem, a_lo, desc_hi, b_lo, desc_hi, idesc, accumulate);
+                        umma_f16_lohi(d_tmem, a_lo + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
+                        umma_f16_lohi(d_tmem, a_lo + 4, desc_hi, b_lo + 4, desc_hi, idesc, 1u);
+                        umma_f16_lohi(d_tmem, a_lo + 6, desc_hi, b_lo + 6, desc_hi, idesc, 1u);
+                        umma_commit(empty0 + 8u * stage);
+                    }
+                    __syncwarp();
+                    accumulate = 1u;
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) umma_commit(tfull_bar(acc));
+                if (ok && lane == 0) umma_commit(tfull_bar(acc));
+                __syncwarp();
             }
+            RT_ADD(2);
+            if (lane == 0) RT_STORE(1);
         }
-    } else {
-        // epilogue: warp (2..5) may touch TMEM lanes [32*(warp%4), +32)
+    } else if (warp >= 4) {
+        // epilogue: warp w may touch TMEM lanes [32*(w%4), +32)
         const int q = warp & 3;
         const int row = q * 32 + lane;             // pixel of the tile = TMEM lane
-        const bool leader = threadIdx.x == 64;     // first epilogue thread issues the TMA stores
-        bool ok = true;
+        const bool leader = threadIdx.x == 128;    // first epilogue thread issues the TMA stores
         int iter = 0;
         int chunk_count = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
+        RT_DECL;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
             const int acc = iter & 1;
             const int nt = tile % p.n_tiles, mt = tile / p.n_tiles;
             const int w0 = (mt % p.tw) * p.bw, h0 = ((mt / p.tw) % p.th) * p.bh;
             const int n0 = (mt / (p.tw * p.th)) * p.bn;
-            ok = mbar_wait(tfull_bar(acc), ((uint32_t)iter >> 1) & 1u, abort_flag, status, kStatusEpilogueTimeout);
-            if (!ok) break;
+            RT_ADD(2);
+            if (!mbar_wait(tfull_bar(acc), ((uint32_t)iter >> 1) & 1u, abort_flag, status, kStatusEpilogueTimeout))
+                s_epi_fail = 1;
+            // the 128 epilogue threads must take the same decision: they meet at named barriers below
+            named_barrier(2, kEpiThreads);
+            RT_ADD(0);
+            if (*(volatile int*)&s_epi_fail) break;
             tc_fence_after();
 #pragma unroll 1
             for (int chunk = 0; chunk < NT / 64; ++chunk, ++chunk_count) {
                 const uint32_t buf = epi_base + (uint32_t)(chunk_count & 1) * kATileBytes;
+                RT_ADD(2);
                 if (leader) tma_store_wait_read<1>();     // the store that last read this buffer is done
                 named_barrier(1, kEpiThreads);
+                RT_ADD(1);
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * NT + chunk * 64);
                 uint32_t v0[32], v1[32];
                 tmem_ld_32x32(taddr, v0);
@@ -324,6 +392,8 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
             mbar_arrive(tempty_bar(acc));
         }
         if (leader) tma_store_wait_all();
+        RT_ADD(2);
+        if (leader) RT_STORE(2);
     }
 
     abort_drain(abort_flag);
@@ -443,14 +513,15 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                    float* __restrict__ partial, const WgradParams p, int* status) {
     using L = WgradSmem<NT>;
     constexpr int kStages = L::kStages;
+    constexpr int kBBlocks = NT / 64;                       // 64-channel boxes of dy per stage
+    constexpr int kBProducers = kBBlocks >= 2 ? 2 : 1;
     constexpr uint32_t kTmemCols = NT < 32 ? 32 : NT;
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     const uint32_t a_base = base;
     const uint32_t b_base = base + kStages * L::kABytes;
     const uint32_t bar_base = b_base + kStages * L::kBBytes;
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    const uint32_t full0 = bar_base, empty0 = bar_base + 8u * kStages;
     const uint32_t done_bar = bar_base + 8u * (2 * kStages);
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
@@ -458,7 +529,7 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8u * s, 1 + kBProducers); mbar_init(empty0 + 8u * s, 1); }
         mbar_init(done_bar, 1);
         fence_barrier_init();
         prefetch_tmap(&tm_x);
@@ -481,54 +552,89 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const int split = item / (p.n_tiles * p.m_tiles);
     const int pt0 = (int)((long)p.pix_tiles * split / p.splits);
     const int pt1 = (int)((long)p.pix_tiles * (split + 1) / p.splits);
-    const int u0 = mt * 2;
-    const int u1 = (u0 + 1 < p.units) ? u0 + 1 : u0;   // odd unit count: the last tile repeats its unit
+    // pixel tiles are walked with running box origins (w fastest, then h, then n)
+    const int w_first = (pt0 % p.tw) * p.bw, h_first = ((pt0 / p.tw) % p.th) * p.bh;
+    const int n_first = (pt0 / (p.tw * p.th)) * p.bn;
+    const int w_end = p.tw * p.bw, h_end = p.th * p.bh;
 
     if (warp == 0) {
-        if (lane == 0) {
-            PipeState ps;
+        {                                                  // producer A: two tap-shifted boxes of x per stage
+            const int u0 = mt * 2;
+            const int u1 = (u0 + 1 < p.units) ? u0 + 1 : u0;   // odd unit count: the last tile repeats its unit
+            const int tap0 = u0 / p.cblocks + p.tap_base, c0 = (u0 % p.cblocks) * 64;
+            const int tap1 = u1 / p.cblocks + p.tap_base, c1 = (u1 % p.cblocks) * 64;
+            const int dw0 = tap0 % 3 - 1, dh0 = tap0 / 3 - 1, dw1 = tap1 % 3 - 1, dh1 = tap1 / 3 - 1;
+            uint32_t stage = 0, phase = 0;
+            int w0 = w_first, h0 = h_first, n0 = n_first;
             for (int pt = pt0; pt < pt1; ++pt) {
-                const int w0 = (pt % p.tw) * p.bw, h0 = ((pt / p.tw) % p.th) * p.bh;
-                const int n0 = (pt / (p.tw * p.th)) * p.bn;
-                if (!mbar_wait(empty_bar(ps.stage), ps.phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
-                mbar_expect_tx(full_bar(ps.stage), L::kStageBytes);
-                const uint32_t a_dst = a_base + ps.stage * L::kABytes;
-                const uint32_t b_dst = b_base + ps.stage * L::kBBytes;
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const int u = j == 0 ? u0 : u1;
-                    const int tap = u / p.cblocks + p.tap_base, cb = u % p.cblocks;
-                    tma_load_4d(a_dst + j * kStageTileBytes, &tm_x, full_bar(ps.stage), cb * 64,
-                                w0 + tap % 3 - 1, h0 + tap / 3 - 1, n0);
+                if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                const uint32_t fb = full0 + 8u * stage;
+                const uint32_t a_dst = a_base + stage * L::kABytes;
+                if (lane == 0) {
+                    mbar_expect_tx(fb, L::kABytes);
+                    tma_load_4d(a_dst, &tm_x, fb, c0, w0 + dw0, h0 + dh0, n0);
+                    tma_load_4d(a_dst + kStageTileBytes, &tm_x, fb, c1, w0 + dw1, h0 + dh1, n0);
                 }
+                __syncwarp();
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                w0 += p.bw;
+                if (w0 >= w_end) { w0 = 0; h0 += p.bh; if (h0 >= h_end) { h0 = 0; n0 += p.bn; } }
+            }
+        }
+    } else if (warp == 2 || (warp == 3 && kBProducers == 2)) {
+        {                                                  // producers B: the stage's boxes of dy, split over two warps
+            constexpr int kPer = kBBlocks / kBProducers;
+            const int j0 = (warp - 2) * kPer;
+            const int k_off = nt * NT + j0 * 64;
+            uint32_t stage = 0, phase = 0;
+            int w0 = w_first, h0 = h_first, n0 = n_first;
+            for (int pt = pt0; pt < pt1; ++pt) {
+                if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                const uint32_t fb = full0 + 8u * stage;
+                const uint32_t b_dst = b_base + stage * L::kBBytes + j0 * kStageTileBytes;
+                if (lane == 0) {
+                    mbar_expect_tx(fb, kPer * kStageTileBytes);
 #pragma unroll
-                for (int j = 0; j < NT / 64; ++j)
-                    tma_load_4d(b_dst + j * kStageTileBytes, &tm_dy, full_bar(ps.stage), nt * NT + j * 64, w0, h0, n0);
-                ps.advance(kStages);
+                    for (int j = 0; j < kPer; ++j)
+                        tma_load_4d(b_dst + j * kStageTileBytes, &tm_dy, fb, k_off + j * 64, w0, h0, n0);
+                }
+                __syncwarp();
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                w0 += p.bw;
+                if (w0 >= w_end) { w0 = 0; h0 += p.bh; if (h0 >= h_end) { h0 = 0; n0 += p.bn; } }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        {                                                  // MMA issuer
             constexpr uint32_t idesc = idesc_f16(128, NT, true, true);
-            PipeState ps;
+            // MN-major: 64-element blocks of M/N are one 8 KB tile apart, 8 pixels are 1024 bytes apart
+            constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t a_lo0 = smem_desc_lo(a_base, kStageTileBytes), b_lo0 = smem_desc_lo(b_base, kStageTileBytes);
+            uint32_t stage = 0, phase = 0;
+            uint32_t accumulate = 0;
             bool ok = true;
             for (int pt = pt0; pt < pt1; ++pt) {
-                ok = mbar_wait(full_bar(ps.stage), ps.phase, abort_flag, status, kStatusMmaTimeout);
+                ok = mbar_wait(full0 + 8u * stage, phase, abort_flag, status, kStatusMmaTimeout);
                 if (!ok) break;
                 tc_fence_after();
-                // MN-major: 64-element blocks of M/N are one 8 KB tile apart, 8 pixels are 1024 bytes apart
-                const uint64_t adesc = smem_desc_sw128(a_base + ps.stage * L::kABytes, kStageTileBytes, 1024);
-                const uint64_t bdesc = smem_desc_sw128(b_base + ps.stage * L::kBBytes, kStageTileBytes, 1024);
-#pragma unroll
-                for (int k4 = 0; k4 < 4; ++k4)   // 4 x (K = 16 pixels = 2048 bytes)
-                    umma_f16(tmem_base, adesc + (uint64_t)(k4 * 128), bdesc + (uint64_t)(k4 * 128), idesc,
-                             (pt > pt0 || k4 > 0) ? 1u : 0u);
-                umma_commit(empty_bar(ps.stage));
-                ps.advance(kStages);
+                const uint32_t a_lo = a_lo0 + stage * (L::kABytes >> 4);
+                const uint32_t b_lo = b_lo0 + stage * (L::kBBytes >> 4);
+                // 4 x (K = 16 pixels = 2048 bytes: +128 in the address field)
+                if (lane == 0) {
+                    umma_f16_lohi(tmem_base, a_lo, desc_hi, b_lo, desc_hi, idesc, accumulate);
+                    umma_f16_lohi(tmem_base, a_lo + 128, desc_hi, b_lo + 128, desc_hi, idesc, 1u);
+                    umma_f16_lohi(tmem_base, a_lo + 256, desc_hi, b_lo + 256, desc_hi, idesc, 1u);
+                    umma_f16_lohi(tmem_base, a_lo + 384, desc_hi, b_lo + 384, desc_hi, idesc, 1u);
+                    umma_commit(empty0 + 8u * stage);
+                }
+                __syncwarp();
+                accumulate = 1u;
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
-            if (ok) umma_commit(done_bar);
+            if (ok && lane == 0) umma_commit(done_bar);
+            __syncwarp();
         }
-    } else {
+    } else if (warp >= 4) {
         const int q = warp & 3;
         const int row = q * 32 + lane;
         float* dst = partial + ((size_t)item * 128 + row) * NT;
@@ -838,6 +944,13 @@ int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* 
     }
     return wgrad_run(d, 9, dy, x, dw, static_cast<float*>(ws), st);
 }
+
+#ifdef TRB200_ROLE_TIMERS
+extern "C" int trb200_debug_read_role_timers(long long* host_out, int count) {
+    TRB_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_role_timers, sizeof(long long) * (size_t)count));
+    return TRB200_OK;
+}
+#endif
 
 int device_status_read_and_clear(int* out) {
     int v = 0;
