@@ -138,6 +138,19 @@ size_t trb200_conv_fprop_workspace_bytes(const trb200_conv_desc* d);
 int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const void* w, void* y,
                       void* workspace, size_t workspace_bytes, void* stream);
 
+/* Forward convolution with the batch statistics taken in its epilogue, followed by
+ * bn_finalize: the reference's conv_fprop + genstats graph and its bn_finalize graph
+ * (cbr_op.cpp:622-718, 430-528) in two launches, without a separate pass over the
+ * conv output.  Outputs and optional pointers as in trb200_bn_stats_finalize; the
+ * statistics are those of the stored (half) output.  Same shape coverage as
+ * trb200_conv_fprop. */
+size_t trb200_conv_fprop_bn_stats_workspace_bytes(const trb200_conv_desc* d);
+int trb200_conv_fprop_bn_stats(const trb200_conv_desc* d, const void* x, const void* w, void* y,
+                               const float* gamma, const float* beta, float eps, float momentum,
+                               float* ch_sum, float* ch_sqsum, float* saved_mean, float* saved_inv_std,
+                               float* eq_scale, float* eq_bias, float* running_mean, float* running_var,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
 /* Diagnostics.  backend 0 = automatic (tensor cores where the shape allows),
  * 1 = direct CUDA-core kernels only (used by tests to cross-check the two). */
 int trb200_set_conv_backend(int backend);

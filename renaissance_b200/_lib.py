@@ -86,6 +86,9 @@ def load() -> C.CDLL:
         "trb200_conv_dgrad": (C.c_int, [pdesc, vp, vp, vp, vp, sz, vp]),
         "trb200_conv_fprop_workspace_bytes": (sz, [pdesc]),
         "trb200_conv_fprop": (C.c_int, [pdesc, vp, vp, vp, vp, sz, vp]),
+        "trb200_conv_fprop_bn_stats_workspace_bytes": (sz, [pdesc]),
+        "trb200_conv_fprop_bn_stats": (C.c_int, [pdesc, vp, vp, vp, vp, vp, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp,
+                                                 vp, sz, vp]),
         "trb200_cbr_bwd_workspace_bytes": (sz, [pdesc, C.c_int]),
         "trb200_cbr_bwd": (C.c_int, [C.POINTER(CbrBwdArgs)]),
         "trb200_softmax_ce_fwd": (C.c_int, [vp, i64, vp, vp, vp, i64, vp, vp, vp, i32, i32, vp]),

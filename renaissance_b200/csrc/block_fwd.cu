@@ -8,13 +8,14 @@
 //   y = relu(t), mask = t > 0, t = half(half(x*eq_scale) + eq_bias) cbr_op.cpp:534-616
 //   max pooling with argmax byte (kh*k + kw, first maximum wins)    maxpool_op.cu:23-217
 #include "common.cuh"
+#include "conv.cuh"
 
 namespace trb {
 namespace {
 
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
-constexpr int kMaxBlocks = 148 * 8;
+constexpr int kBlocksPerSm = 2;     // resident blocks per SM at the kernels' register use
 
 struct RowPlan {
     int tpr, bx, by, gy, gx;
@@ -28,11 +29,14 @@ RowPlan make_row_plan(int64_t m, int c) {
     p.by = kThreads / p.bx;
     if (p.by < 1) p.by = 1;
     p.gy = (p.tpr + p.bx - 1) / p.bx;
-    int64_t want = (m + (int64_t)p.by * kUnroll - 1) / ((int64_t)p.by * kUnroll);
-    int64_t cap = kMaxBlocks / p.gy;
-    if (cap < 1) cap = 1;
-    p.gx = (int)(want < cap ? want : cap);
-    if (p.gx < 1) p.gx = 1;
+    // strips of at least 8 loop trips, at most 4 waves of resident blocks, whole waves when
+    // there is more than one (equal strips: a partial last wave would idle most SMs)
+    int64_t want = (m + (int64_t)p.by * kUnroll * 8 - 1) / ((int64_t)p.by * kUnroll * 8);
+    int64_t resident = (int64_t)sm_count() * kBlocksPerSm / p.gy;
+    if (resident < 1) resident = 1;
+    int64_t g = want < resident * 4 ? want : resident * 4;
+    if (g > resident) g = g / resident * resident;
+    p.gx = (int)(g < 1 ? 1 : g);
     int64_t rps = (m + p.gx - 1) / p.gx;
     rps = (rps + p.by - 1) / p.by * p.by;
     p.rows_per_strip = rps;
@@ -255,6 +259,18 @@ int grid_for(int64_t items) {
 }
 
 }  // namespace
+
+int bn_finalize_from_partials(const float* partial, int strips, int c, int64_t m, const float* gamma,
+                              const float* beta, float eps, float momentum, float* ch_sum, float* ch_sqsum,
+                              float* saved_mean, float* saved_inv_std, float* eq_scale, float* eq_bias,
+                              float* running_mean, float* running_var, cudaStream_t st) {
+    bn_stats_finalize<<<(c + 7) / 8, 256, 0, st>>>(partial, strips, c, m, gamma, beta, eps, momentum, ch_sum, ch_sqsum,
+                                                   saved_mean, saved_inv_std, eq_scale, eq_bias, running_mean,
+                                                   running_var);
+    TRB_LAUNCH_CHECK("bn_stats_finalize");
+    return TRB200_OK;
+}
+
 }  // namespace trb
 
 extern "C" size_t trb200_bn_stats_workspace_bytes(int64_t m, int32_t c) {

@@ -27,7 +27,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
-constexpr int kMaxBlocks = 148 * 8;
+constexpr int kBlocksPerSm = 2;     // resident blocks per SM at the kernels' register use
 
 struct BnPlan {
     int tpr;     // 16-byte vectors per row
@@ -45,11 +45,14 @@ BnPlan make_plan(int64_t m, int c) {
     p.by = kThreads / p.bx;
     if (p.by < 1) p.by = 1;
     p.gy = (p.tpr + p.bx - 1) / p.bx;
-    int64_t want = (m + (int64_t)p.by * kUnroll - 1) / ((int64_t)p.by * kUnroll);
-    int64_t cap = kMaxBlocks / p.gy;
-    if (cap < 1) cap = 1;
-    p.gx = (int)(want < cap ? want : cap);
-    if (p.gx < 1) p.gx = 1;
+    // strips of at least 8 loop trips, at most 4 waves of resident blocks, whole waves when
+    // there is more than one (equal strips: a partial last wave would idle most SMs)
+    int64_t want = (m + (int64_t)p.by * kUnroll * 8 - 1) / ((int64_t)p.by * kUnroll * 8);
+    int64_t resident = (int64_t)sm_count() * kBlocksPerSm / p.gy;
+    if (resident < 1) resident = 1;
+    int64_t g = want < resident * 4 ? want : resident * 4;
+    if (g > resident) g = g / resident * resident;
+    p.gx = (int)(g < 1 ? 1 : g);
     int64_t rps = (m + p.gx - 1) / p.gx;
     // strips are multiples of the block's row step so that every strip starts on a
     // 16-byte boundary of the mask as well

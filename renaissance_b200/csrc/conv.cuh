@@ -23,8 +23,15 @@ size_t igemm_im2col_bytes(const trb200_conv_desc& d);
 size_t igemm_wgrad_small_c_workspace(const trb200_conv_desc& d);
 int igemm_wgrad_small_c(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* xp, bool xp_ready,
                         void* ws, size_t ws_bytes, cudaStream_t st);
+size_t igemm_fprop_stats_bytes(const trb200_conv_desc& d);
 int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, void* ws, size_t ws_bytes,
-                cudaStream_t st);
+                cudaStream_t st, float* stats_partial = nullptr, int* stats_strips = nullptr);
+
+// block_fwd.cu: adds [strips][2][c] partial sums in strip order and finalizes the batch statistics
+int bn_finalize_from_partials(const float* partial, int strips, int c, int64_t m, const float* gamma,
+                              const float* beta, float eps, float momentum, float* ch_sum, float* ch_sqsum,
+                              float* saved_mean, float* saved_inv_std, float* eq_scale, float* eq_bias,
+                              float* running_mean, float* running_var, cudaStream_t st);
 int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* ws,
                 size_t ws_bytes, cudaStream_t st);
 int igemm_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* dx, void* ws,

@@ -105,6 +105,46 @@ extern "C" int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const
     return trb::igemm_fprop(*d, x, w, y, workspace, workspace_bytes, trb::as_stream(stream));
 }
 
+extern "C" size_t trb200_conv_fprop_bn_stats_workspace_bytes(const trb200_conv_desc* d) {
+    if (trb::validate_conv_desc(d, "conv_fprop_bn_stats_workspace_bytes")) return 0;
+    if (!trb::igemm_supports(*d, 2)) return 0;
+    return (size_t)trb::align_up((int64_t)trb::igemm_fprop_workspace(*d), 256) + trb::igemm_fprop_stats_bytes(*d);
+}
+
+extern "C" int trb200_conv_fprop_bn_stats(const trb200_conv_desc* d, const void* x, const void* w, void* y,
+                                          const float* gamma, const float* beta, float eps, float momentum,
+                                          float* ch_sum, float* ch_sqsum, float* saved_mean, float* saved_inv_std,
+                                          float* eq_scale, float* eq_bias, float* running_mean, float* running_var,
+                                          void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = trb::validate_conv_desc(d, "conv_fprop_bn_stats");
+    if (rc) return rc;
+    TRB_REQUIRE(x && w && y && gamma && beta && saved_mean && saved_inv_std && eq_scale && eq_bias,
+                TRB200_ERR_INVALID_ARGUMENT, "conv_fprop_bn_stats: null pointer");
+    TRB_REQUIRE(y != x && y != w, TRB200_ERR_INVALID_ARGUMENT, "conv_fprop_bn_stats: y must not alias x or w");
+    TRB_REQUIRE(trb::aligned16(x) && trb::aligned16(w) && trb::aligned16(y), TRB200_ERR_INVALID_ARGUMENT,
+                "conv_fprop_bn_stats: tensors must be 16-byte aligned");
+    TRB_REQUIRE(trb::igemm_supports(*d, 2), TRB200_ERR_UNSUPPORTED,
+                "conv_fprop_bn_stats: only 3x3 stride 1 pad 1 with k = 64, 128 or a multiple of 256 and c = 4 or a "
+                "multiple of 64");
+    const size_t need = trb200_conv_fprop_bn_stats_workspace_bytes(d);
+    TRB_REQUIRE(workspace && workspace_bytes >= need, TRB200_ERR_WORKSPACE,
+                "conv_fprop_bn_stats: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    TRB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, TRB200_ERR_INVALID_ARGUMENT,
+                "conv_fprop_bn_stats: workspace must be 256-byte aligned");
+    // the statistics scratch sits at the END of the workspace so that a caller can hand over an
+    // activation-sized buffer followed by a small tail
+    unsigned char* base = static_cast<unsigned char*>(workspace);
+    const size_t stats_bytes = trb::igemm_fprop_stats_bytes(*d);
+    float* partial = reinterpret_cast<float*>(base + (workspace_bytes - stats_bytes) / 256 * 256);
+    int strips = 0;
+    rc = trb::igemm_fprop(*d, x, w, y, workspace, workspace_bytes - stats_bytes, trb::as_stream(stream), partial, &strips);
+    if (rc) return rc;
+    const int oh = trb::conv_out(d->h, d->pad_h, d->r, d->stride_h), ow = trb::conv_out(d->w, d->pad_w, d->s, d->stride_w);
+    return trb::bn_finalize_from_partials(partial, strips, d->k, (int64_t)d->n * oh * ow, gamma, beta, eps, momentum,
+                                          ch_sum, ch_sqsum, saved_mean, saved_inv_std, eq_scale, eq_bias, running_mean,
+                                          running_var, trb::as_stream(stream));
+}
+
 // ---------------------------------------------------------------------------
 // Whole block.  Workspace layout: [bnrelu partials][wgrad scratch][dgrad scratch],
 // each 256-byte aligned, so that the three stages can run on three streams.

@@ -168,6 +168,12 @@ struct FpropParams {
     int tw, th;          // tiles along w, h
     int bw, bh, bn;
     int b_tap_is_dim1;   // 1: filter view dims (ci, tap, co) [KRSC as is]; 0: (ci, co, tap)
+    // batch statistics of the output (STATS kernels only)
+    float* stats_partial;   // [strip][2][cout], strip = (block / n_tiles) * 2 + row half
+    int cout;
+    int lbw, lbh;           // log2 of bw, bh
+    int ext_w, ext_h, ext_n;   // image extents: rows of a tile beyond them are padding
+    int has_padding;        // some tile hangs over an image edge
 };
 
 template <int NT>
@@ -179,7 +185,7 @@ struct FpropSmem {
     static constexpr int kTotal = kStages * kStageBytes + kEpiBytes + 2048;   // + alignment slack and barriers
 };
 
-template <int NT>
+template <int NT, bool STATS>
 __global__ void __launch_bounds__(kThreads, 1)
 conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_w,
                      const __grid_constant__ CUtensorMap tm_out, const FpropParams p, int* status) {
@@ -200,6 +206,7 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     __shared__ int s_epi_fail;
+    __shared__ uint32_t s_valid[4];      // STATS: which of the tile's 128 rows are real pixels
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -338,6 +345,12 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
         const bool leader = threadIdx.x == 128;    // first epilogue thread issues the TMA stores
         int iter = 0;
         int chunk_count = 0;
+        // STATS: thread (column c, row half hsel) adds its column of every 64-channel chunk over
+        // 64 rows of the half-rounded tile in shared memory; sums run over all tiles of this block
+        const int st_c = (threadIdx.x - 128) & 63, st_h = (threadIdx.x - 128) >> 6;
+        float run_s[NT / 64], run_q[NT / 64];
+#pragma unroll
+        for (int i = 0; i < NT / 64; ++i) { run_s[i] = 0.f; run_q[i] = 0.f; }
         RT_DECL;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
             const int acc = iter & 1;
@@ -345,6 +358,13 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
             const int w0 = (mt % p.tw) * p.bw, h0 = ((mt / p.tw) % p.th) * p.bh;
             const int n0 = (mt / (p.tw * p.th)) * p.bn;
             RT_ADD(2);
+            if (STATS && p.has_padding) {
+                // row = ((image * bh) + y) * bw + x inside the tile's box
+                const int bx = row & (p.bw - 1), by = (row >> p.lbw) & (p.bh - 1), bi = row >> (p.lbw + p.lbh);
+                const bool real = (w0 + bx < p.ext_w) && (h0 + by < p.ext_h) && (n0 + bi < p.ext_n);
+                const uint32_t m = __ballot_sync(0xffffffffu, real);
+                if (lane == 0) s_valid[q] = m;
+            }
             if (!mbar_wait(tfull_bar(acc), ((uint32_t)iter >> 1) & 1u, abort_flag, status, kStatusEpilogueTimeout))
                 s_epi_fail = 1;
             // the 128 epilogue threads must take the same decision: they meet at named barriers below
@@ -352,7 +372,9 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
             RT_ADD(0);
             if (*(volatile int*)&s_epi_fail) break;
             tc_fence_after();
-#pragma unroll 1
+            uint32_t vm0 = 0xffffffffu, vm1 = 0xffffffffu;
+            if (STATS && p.has_padding) { vm0 = s_valid[st_h * 2]; vm1 = s_valid[st_h * 2 + 1]; }
+#pragma unroll
             for (int chunk = 0; chunk < NT / 64; ++chunk, ++chunk_count) {
                 const uint32_t buf = epi_base + (uint32_t)(chunk_count & 1) * kATileBytes;
                 RT_ADD(2);
@@ -387,9 +409,36 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
                     tma_store_4d(&tm_out, buf, nt * NT + chunk * 64, w0, h0, n0);
                     tma_store_commit();
                 }
+                if (STATS) {
+                    float s1 = 0.f, s2 = 0.f;
+                    const uint32_t col_off = (uint32_t)(st_c & 7) * 2u;
+#pragma unroll 8
+                    for (int i = 0; i < 64; ++i) {
+                        const int r = st_h * 64 + i;
+                        const uint32_t addr = buf + (uint32_t)r * 128u + (uint32_t)(((st_c >> 3) ^ (r & 7)) << 4) + col_off;
+                        unsigned short hv;
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(hv) : "r"(addr));
+                        float f = __half2float(__ushort_as_half(hv));
+                        if (!(((i < 32 ? vm0 : vm1) >> (i & 31)) & 1u)) f = 0.f;
+                        s1 += f;
+                        s2 = fmaf(f, f, s2);
+                    }
+                    run_s[chunk] += s1;
+                    run_q[chunk] += s2;
+                }
             }
             tc_fence_before();
             mbar_arrive(tempty_bar(acc));
+        }
+        if (STATS) {
+            // this block only ever sees one N tile (the grid is a multiple of n_tiles)
+            const int strip = (blockIdx.x / p.n_tiles) * 2 + st_h;
+            const int ch0 = (blockIdx.x % p.n_tiles) * NT + st_c;
+#pragma unroll
+            for (int i = 0; i < NT / 64; ++i) {
+                p.stats_partial[((size_t)strip * 2) * p.cout + ch0 + i * 64] = run_s[i];
+                p.stats_partial[((size_t)strip * 2 + 1) * p.cout + ch0 + i * 64] = run_q[i];
+            }
         }
         if (leader) tma_store_wait_all();
         RT_ADD(2);
@@ -416,7 +465,15 @@ dgrad_filter_view_kernel(const __half* __restrict__ w, __half* __restrict__ out,
     }
 }
 
-template <int NT>
+// persistent grid: one block per SM, a multiple of n_tiles so that a block keeps its N tile
+int conv3x3_grid(int m_tiles, int n_tiles) {
+    const int total = m_tiles * n_tiles;
+    int grid = total < sm_count() ? total : sm_count();
+    if (grid > n_tiles) grid = grid / n_tiles * n_tiles;
+    return grid;
+}
+
+template <int NT, bool STATS>
 int launch_conv3x3(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensorMap& tout, const FpropParams& p,
                    cudaStream_t st) {
     using L = FpropSmem<NT>;
@@ -424,15 +481,14 @@ int launch_conv3x3(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensor
     int dev = 0;
     TRB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        TRB_CUDA_TRY(cudaFuncSetAttribute(conv3x3_igemm_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TRB_CUDA_TRY(cudaFuncSetAttribute(conv3x3_igemm_kernel<NT, STATS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           L::kTotal));
         attr_done[dev] = true;
     }
     int* status = nullptr;
     TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status));
-    const int total = p.m_tiles * p.n_tiles;
-    const int grid = total < sm_count() ? total : sm_count();
-    conv3x3_igemm_kernel<NT><<<grid, kThreads, L::kTotal, st>>>(tin, tw, tout, p, status);
+    const int grid = conv3x3_grid(p.m_tiles, p.n_tiles);
+    conv3x3_igemm_kernel<NT, STATS><<<grid, kThreads, L::kTotal, st>>>(tin, tw, tout, p, status);
     TRB_LAUNCH_CHECK("conv3x3_igemm_kernel");
     return TRB200_OK;
 }
@@ -445,8 +501,10 @@ int pick_nt(int cout) {
 }
 
 // in: [n,h,w,cin] half; filter view described by (wv, tap_is_dim1); out: [n,h,w,cout] half.
+// stats_partial != nullptr: also leave per-strip sums / sums of squares of the (half) output there and report
+// the number of strips through *stats_strips.
 int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int n, int h, int w, int cin, int cout,
-                cudaStream_t st, int taps = 9) {
+                cudaStream_t st, int taps = 9, float* stats_partial = nullptr, int* stats_strips = nullptr) {
     const int nt = pick_nt(cout);
     TRB_REQUIRE(nt != 0 && cin % 64 == 0, TRB200_ERR_UNSUPPORTED, "conv3x3 igemm: cin=%d cout=%d not covered", cin,
                 cout);
@@ -478,10 +536,26 @@ int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int 
     p.tw = t.tw; p.th = t.th;
     p.bw = t.bw; p.bh = t.bh; p.bn = t.bn;
     p.b_tap_is_dim1 = tap_is_dim1;
-    if (nt == 256) return launch_conv3x3<256>(tin, tw, tout, p, st);
-    if (nt == 128) return launch_conv3x3<128>(tin, tw, tout, p, st);
-    return launch_conv3x3<64>(tin, tw, tout, p, st);
+    p.stats_partial = stats_partial;
+    p.cout = cout;
+    p.lbw = 0; p.lbh = 0;
+    while ((1 << p.lbw) < t.bw) ++p.lbw;
+    while ((1 << p.lbh) < t.bh) ++p.lbh;
+    p.ext_w = w; p.ext_h = h; p.ext_n = n;
+    p.has_padding = (t.tw * t.bw != w) || (t.th * t.bh != h) || (t.tn * t.bn != n);
+    if (stats_partial) {
+        if (stats_strips) *stats_strips = conv3x3_grid(p.m_tiles, p.n_tiles) / p.n_tiles * 2;
+        if (nt == 256) return launch_conv3x3<256, true>(tin, tw, tout, p, st);
+        if (nt == 128) return launch_conv3x3<128, true>(tin, tw, tout, p, st);
+        return launch_conv3x3<64, true>(tin, tw, tout, p, st);
+    }
+    if (nt == 256) return launch_conv3x3<256, false>(tin, tw, tout, p, st);
+    if (nt == 128) return launch_conv3x3<128, false>(tin, tw, tout, p, st);
+    return launch_conv3x3<64, false>(tin, tw, tout, p, st);
 }
+
+// upper bound of the strips the STATS kernels write for an output of `cout` channels
+int conv3x3_stats_max_strips() { return sm_count() * 2; }
 
 // ------------------------------------------------------------------ wgrad kernel
 struct WgradParams {
@@ -857,9 +931,15 @@ int igemm_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* 
     return conv3x3_run(dy, ws, 0, dx, d.n, d.h, d.w, d.k, d.c, st);
 }
 
+size_t igemm_fprop_stats_bytes(const trb200_conv_desc& d) {
+    return (size_t)align_up((int64_t)conv3x3_stats_max_strips() * 2 * d.k * (int64_t)sizeof(float), 256);
+}
+
+// stats_partial: optional float scratch of igemm_fprop_stats_bytes(); *stats_strips receives the strip count
 int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, void* ws, size_t ws_bytes,
-                cudaStream_t st) {
-    if (!igemm_small_c(d)) return conv3x3_run(x, w, 1, y, d.n, d.h, d.w, d.c, d.k, st);
+                cudaStream_t st, float* stats_partial, int* stats_strips) {
+    if (!igemm_small_c(d))
+        return conv3x3_run(x, w, 1, y, d.n, d.h, d.w, d.c, d.k, st, 9, stats_partial, stats_strips);
     const size_t need = igemm_fprop_workspace(d);
     TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, "conv_fprop: workspace of %zu bytes needed, %zu given",
                 need, ws_bytes);
@@ -873,7 +953,7 @@ int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y
     pack_w_c4_kernel<<<(d.k * 64 + 255) / 256, 256, 0, st>>>(static_cast<const __half*>(w), wp, d.k);
     TRB_LAUNCH_CHECK("pack_w_c4_kernel");
     // 1x1 convolution: filter view (ci = 64, tap = 1, co = k)
-    return conv3x3_run(xp, wp, 1, y, d.n, d.h, d.w, 64, d.k, st, 1);
+    return conv3x3_run(xp, wp, 1, y, d.n, d.h, d.w, 64, d.k, st, 1, stats_partial, stats_strips);
 }
 
 static int wgrad_run(const trb200_conv_desc& d, int taps, const void* dy, const void* x, void* dw, float* partial,

@@ -45,6 +45,18 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+__device__ __forceinline__ bool aligned16_dev(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+__device__ __forceinline__ void half8_to_float(const uint4& raw, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 t = __half22float2(h[j]);
+        f[2 * j] = t.x;
+        f[2 * j + 1] = t.y;
+    }
+}
+
 struct RowOut {
     float* probs;          // may be null
     int64_t probs_stride;
@@ -56,109 +68,139 @@ struct RowOut {
 // One warp per row, the row lives in registers: lane l holds vectors l, l+32, ...
 // of 8 halfs each.  Needs 16-byte aligned rows.
 template <int VPL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, VPL >= 8 ? 1 : 3)
 softmax_ce_rows_warp(const __half* __restrict__ logits, int64_t logits_stride,
                      const int32_t* __restrict__ labels, const float* __restrict__ scaling,
                      const float* __restrict__ label_smoothing, RowOut out, int batch, int classes) {
     const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= batch) return;
-    const __half* z = logits + (int64_t)row * logits_stride;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
     const int nvec = (classes + 7) >> 3;
-
-    float v[VPL][8];
-    float zmax = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < VPL; ++i) {
-        const int vec = i * 32 + lane;
-        uint4 raw = make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);   // -inf halfs
-        if (vec < nvec) raw = *reinterpret_cast<const uint4*>(z + vec * 8);
-        const __half2* h = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float2 t = __half22float2(h[j]);
-            v[i][2 * j] = t.x;
-            v[i][2 * j + 1] = t.y;
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            if (vec * 8 + j >= classes) v[i][j] = -INFINITY;   // padding inside the last vector
-            zmax = fmaxf(zmax, v[i][j]);
-        }
-    }
-    zmax = warp_max(zmax);
-    const float shift = -zmax * kLog2e;
-    float sum = 0.f;
-#pragma unroll
-    for (int i = 0; i < VPL; ++i)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            v[i][j] = fast_exp2(fmaf(v[i][j], kLog2e, shift));
-            sum += v[i][j];
-        }
-    sum = warp_sum(sum);
-    const float inv_sum = 1.0f / (sum + 1e-8f);
-
     const float ls = label_smoothing ? label_smoothing[0] : 0.f;
     const float keep = 1.0f - ls, spread = ls / (float)classes;
-    const int y = labels[row];
     const float inv_b = 1.0f / (float)batch;
     const float gscale = (scaling ? scaling[0] : 1.0f) * inv_b;
-    float sum_log = 0.f, py = 0.f;
+    const bool dvec = out.dlogits && (out.dlogits_stride & 7) == 0 && aligned16_dev(out.dlogits);
+    const bool pvec = out.probs && (out.probs_stride & 3) == 0 && aligned16_dev(out.probs);
+
+    const uint4 kNegInf = make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);   // -inf halfs
+    const int row_first = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    // the next row's vectors are requested before the current row is processed
+    uint4 nxt[VPL];
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
         const int vec = i * 32 + lane;
-        if (vec >= nvec) continue;
-        float p[8];
-        uint4 graw;
-        __half2* gh = reinterpret_cast<__half2*>(&graw);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int cidx = vec * 8 + j;
-            p[j] = v[i][j] * inv_sum;
-            if (cidx == y) py = p[j];
-            if (ls != 0.f && cidx < classes) sum_log += fast_log2(p[j] + 1e-8f);
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float g0 = p[2 * j] - spread, g1 = p[2 * j + 1] - spread;
-            if (vec * 8 + 2 * j == y) g0 -= keep;
-            if (vec * 8 + 2 * j + 1 == y) g1 -= keep;
-            gh[j] = __floats2half2_rn(g0 * gscale, g1 * gscale);
-        }
-        const bool full = vec * 8 + 8 <= classes;
-        if (out.dlogits) {
-            __half* d = out.dlogits + (int64_t)row * out.dlogits_stride + vec * 8;
-            if (full && (out.dlogits_stride & 7) == 0) {
-                *reinterpret_cast<uint4*>(d) = graw;
-            } else {
-                const __half* gs = reinterpret_cast<const __half*>(&graw);
-                for (int j = 0; j < 8 && vec * 8 + j < classes; ++j) d[j] = gs[j];
-            }
-        }
-        if (out.probs) {
-            float* pr = out.probs + (int64_t)row * out.probs_stride + vec * 8;
-            if (full && (out.probs_stride & 3) == 0) {
-                reinterpret_cast<float4*>(pr)[0] = make_float4(p[0], p[1], p[2], p[3]);
-                reinterpret_cast<float4*>(pr)[1] = make_float4(p[4], p[5], p[6], p[7]);
-            } else {
-                for (int j = 0; j < 8 && vec * 8 + j < classes; ++j) pr[j] = p[j];
-            }
-        }
+        nxt[i] = kNegInf;
+        if (row_first < batch && vec < nvec)
+            nxt[i] = *reinterpret_cast<const uint4*>(logits + (int64_t)row_first * logits_stride + vec * 8);
     }
-    if (out.loss_partial) {
-        py = warp_sum(py);   // exactly one lane holds a non-zero value
-        sum_log = warp_sum(sum_log) * kLn2;
-        if (lane == 0)
-            out.loss_partial[row] = (-keep * logf(py + 1e-8f) - spread * sum_log) * inv_b;
+    for (int row = row_first; row < batch; row += warps) {
+        float v[VPL][8];
+        float zmax = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) half8_to_float(nxt[i], v[i]);
+        {
+            const int row_n = row + warps;
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) {
+                const int vec = i * 32 + lane;
+                nxt[i] = kNegInf;
+                if (row_n < batch && vec < nvec)
+                    nxt[i] = *reinterpret_cast<const uint4*>(logits + (int64_t)row_n * logits_stride + vec * 8);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int vec = i * 32 + lane;
+            if (vec * 8 + 8 > classes) {                      // padding inside the row's last vector
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (vec * 8 + j >= classes) v[i][j] = -INFINITY;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) zmax = fmaxf(zmax, v[i][j]);
+        }
+        zmax = warp_max(zmax);
+        const float shift = -zmax * kLog2e;
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[i][j] = fast_exp2(fmaf(v[i][j], kLog2e, shift));
+                sum += v[i][j];
+            }
+        sum = warp_sum(sum);
+        const float inv_sum = 1.0f / (sum + 1e-8f);
+        const int y = labels[row];
+        float sum_log = 0.f, py = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int vec = i * 32 + lane;
+            if (vec >= nvec) continue;
+            const int c0 = vec * 8;
+            float p[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) p[j] = v[i][j] * inv_sum;
+            if (ls != 0.f) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (c0 + j < classes) sum_log += fast_log2(p[j] + 1e-8f);
+            }
+            const bool full = c0 + 8 <= classes;
+            if (out.probs) {
+                float* pr = out.probs + (int64_t)row * out.probs_stride + c0;
+                if (full && pvec) {
+                    reinterpret_cast<float4*>(pr)[0] = make_float4(p[0], p[1], p[2], p[3]);
+                    reinterpret_cast<float4*>(pr)[1] = make_float4(p[4], p[5], p[6], p[7]);
+                } else {
+                    for (int j = 0; j < 8 && c0 + j < classes; ++j) pr[j] = p[j];
+                }
+            }
+            const int jy = y - c0;                               // the label sits in at most one vector of the row
+            if ((unsigned)jy < 8u) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) py += (j == jy) ? p[j] : 0.f;
+            }
+            if (out.dlogits) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) p[j] -= spread;
+                if ((unsigned)jy < 8u) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) p[j] -= (j == jy) ? keep : 0.f;
+                }
+                uint4 graw;
+                __half2* gh = reinterpret_cast<__half2*>(&graw);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) gh[j] = __floats2half2_rn(p[2 * j] * gscale, p[2 * j + 1] * gscale);
+                __half* d = out.dlogits + (int64_t)row * out.dlogits_stride + c0;
+                if (full && dvec) {
+                    *reinterpret_cast<uint4*>(d) = graw;
+                } else {
+                    const __half* gs = reinterpret_cast<const __half*>(&graw);
+                    for (int j = 0; j < 8 && c0 + j < classes; ++j) d[j] = gs[j];
+                }
+            }
+        }
+        if (out.loss_partial) {
+            py = warp_sum(py);   // exactly one lane holds a non-zero value
+            sum_log = warp_sum(sum_log) * kLn2;
+            if (lane == 0)
+                out.loss_partial[row] = (-keep * logf(py + 1e-8f) - spread * sum_log) * inv_b;
+        }
     }
 }
 
-// One block per row, the row is staged once in shared memory as floats' source
-// halfs (classes * 2 bytes); used when the row does not fit a warp's registers
-// or is not 16-byte aligned.  cache == 0 re-reads global memory instead (rows
-// beyond the shared-memory size).
-template <int THREADS>
+// One block per row, the row is staged once in shared memory as halfs (classes * 2
+// bytes); used when the row does not fit a warp's registers or is not 16-byte
+// aligned.  cache == 0 re-reads global memory instead (rows beyond the
+// shared-memory size).  All three sweeps work on 16-byte vectors of 8 classes when
+// the rows are 16-byte aligned (vec_ok): the kernel is otherwise bound by its own
+// instruction count, not by memory.
+// E_HALF (only when probs are not kept and the row is staged): sweep 2 overwrites the
+// staged logits with exp(z - max) rounded to half, so that sweep 3 is one FMA per class
+// instead of a second exponential; d_logits are half anyway and the loss is taken from a
+// float recomputation of the label's class.
+template <int THREADS, bool E_HALF>
 __global__ void __launch_bounds__(THREADS)
 softmax_ce_rows_block(const __half* __restrict__ logits, int64_t logits_stride,
                       const int32_t* __restrict__ labels, const float* __restrict__ scaling,
@@ -186,31 +228,33 @@ softmax_ce_rows_block(const __half* __restrict__ logits, int64_t logits_stride,
         return s_bcast;
     };
 
-    // sweep 1: global -> shared, running max
+    const int nfull = vec_ok ? (classes >> 3) : 0;       // whole 8-class vectors
+    const int tail0 = nfull * 8;                         // first class handled one by one
+
+    // sweep 1: global -> shared, running max; four independent loads in flight per thread
     float zmax = -INFINITY;
-    if (vec_ok) {
-        const int nfull = classes >> 3;
-        for (int vec = tid; vec < nfull; vec += THREADS) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(z + vec * 8);
-            if (cache) *reinterpret_cast<uint4*>(srow + vec * 8) = raw;
-            const __half2* h = reinterpret_cast<const __half2*>(&raw);
+    for (int vec0 = tid; vec0 < nfull; vec0 += 4 * THREADS) {
+        uint4 raw[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 t = __half22float2(h[j]);
-                zmax = fmaxf(zmax, fmaxf(t.x, t.y));
-            }
+        for (int u = 0; u < 4; ++u) {
+            const int vec = vec0 + u * THREADS;
+            raw[u] = vec < nfull ? *reinterpret_cast<const uint4*>(z + vec * 8)
+                                 : make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);
         }
-        for (int cidx = nfull * 8 + tid; cidx < classes; cidx += THREADS) {
-            const __half hv = z[cidx];
-            if (cache) srow[cidx] = hv;
-            zmax = fmaxf(zmax, __half2float(hv));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int vec = vec0 + u * THREADS;
+            if (cache && vec < nfull) *reinterpret_cast<uint4*>(srow + vec * 8) = raw[u];
+            float f[8];
+            half8_to_float(raw[u], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) zmax = fmaxf(zmax, f[j]);
         }
-    } else {
-        for (int cidx = tid; cidx < classes; cidx += THREADS) {
-            const __half hv = z[cidx];
-            if (cache) srow[cidx] = hv;
-            zmax = fmaxf(zmax, __half2float(hv));
-        }
+    }
+    for (int cidx = tail0 + tid; cidx < classes; cidx += THREADS) {
+        const __half hv = z[cidx];
+        if (cache) srow[cidx] = hv;
+        zmax = fmaxf(zmax, __half2float(hv));
     }
     zmax = block_reduce(zmax, true);
     const __half* src = cache ? srow : z;
@@ -218,69 +262,123 @@ softmax_ce_rows_block(const __half* __restrict__ logits, int64_t logits_stride,
 
     // sweep 2: sum of exponentials
     float sum = 0.f;
-    for (int cidx = tid; cidx < classes; cidx += THREADS)
-        sum += fast_exp2(fmaf(__half2float(src[cidx]), kLog2e, shift));
+    const int y = labels[row];
+    const float zy = __half2float(z[y]);                  // from global: the staged row is about to be overwritten
+    for (int vec = tid; vec < nfull; vec += THREADS) {
+        float f[8];
+        half8_to_float(*reinterpret_cast<const uint4*>(src + vec * 8), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            f[j] = fast_exp2(fmaf(f[j], kLog2e, shift));
+            sum += f[j];
+        }
+        if (E_HALF) {
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+            *reinterpret_cast<uint4*>(srow + vec * 8) = o;
+        }
+    }
+    for (int cidx = tail0 + tid; cidx < classes; cidx += THREADS) {
+        const float e = fast_exp2(fmaf(__half2float(src[cidx]), kLog2e, shift));
+        sum += e;
+        if (E_HALF) srow[cidx] = __float2half_rn(e);
+    }
     sum = block_reduce(sum, false);
     const float inv_sum = 1.0f / (sum + 1e-8f);
 
     const float ls = label_smoothing ? label_smoothing[0] : 0.f;
     const float keep = 1.0f - ls, spread = ls / (float)classes;
-    const int y = labels[row];
     const float inv_b = 1.0f / (float)batch;
     const float gscale = (scaling ? scaling[0] : 1.0f) * inv_b;
+    const bool want_log = ls != 0.f;
 
-    // sweep 3: outputs (pairs of classes so that half2 stores are possible)
+    // sweep 3: outputs
     float sum_log = 0.f;
-    const bool pair_ok = out.dlogits && ((out.dlogits_stride & 1) == 0) &&
-                         ((reinterpret_cast<uintptr_t>(out.dlogits) & 3) == 0);
-    const int npairs = (classes + 1) >> 1;
-    for (int pr = tid; pr < npairs; pr += THREADS) {
-        const int c0 = pr * 2, c1 = c0 + 1;
-        const float p0 = fast_exp2(fmaf(__half2float(src[c0]), kLog2e, shift)) * inv_sum;
-        const float p1 = c1 < classes ? fast_exp2(fmaf(__half2float(src[c1]), kLog2e, shift)) * inv_sum : 0.f;
-        if (ls != 0.f) {
-            sum_log += fast_log2(p0 + 1e-8f);
-            if (c1 < classes) sum_log += fast_log2(p1 + 1e-8f);
+    __half* drow = out.dlogits ? out.dlogits + (int64_t)row * out.dlogits_stride : nullptr;
+    float* prow = out.probs ? out.probs + (int64_t)row * out.probs_stride : nullptr;
+    const bool dvec = drow && (out.dlogits_stride & 7) == 0 && aligned16_dev(out.dlogits);
+    const bool pvec = prow && (out.probs_stride & 3) == 0 && aligned16_dev(out.probs);
+    for (int vec = tid; vec < nfull; vec += THREADS) {
+        float f[8];
+        half8_to_float(*reinterpret_cast<const uint4*>(src + vec * 8), f);
+        const int c0 = vec * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            f[j] = (E_HALF ? f[j] : fast_exp2(fmaf(f[j], kLog2e, shift))) * inv_sum;
+            if (want_log) sum_log += fast_log2(f[j] + 1e-8f);
         }
-        if (out.probs) {
-            float* prow = out.probs + (int64_t)row * out.probs_stride;
-            prow[c0] = p0;
-            if (c1 < classes) prow[c1] = p1;
-        }
-        if (out.dlogits) {
-            float g0 = p0 - spread, g1 = p1 - spread;
-            if (c0 == y) g0 -= keep;
-            if (c1 == y) g1 -= keep;
-            __half* d = out.dlogits + (int64_t)row * out.dlogits_stride;
-            if (pair_ok && c1 < classes) {
-                *reinterpret_cast<__half2*>(d + c0) = __floats2half2_rn(g0 * gscale, g1 * gscale);
+        if (prow) {
+            if (pvec) {
+                reinterpret_cast<float4*>(prow + c0)[0] = make_float4(f[0], f[1], f[2], f[3]);
+                reinterpret_cast<float4*>(prow + c0)[1] = make_float4(f[4], f[5], f[6], f[7]);
             } else {
-                d[c0] = __float2half_rn(g0 * gscale);
-                if (c1 < classes) d[c1] = __float2half_rn(g1 * gscale);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) prow[c0 + j] = f[j];
             }
+        }
+        if (drow) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] -= spread;
+            const int jy = y - c0;
+            if ((unsigned)jy < 8u) {                             // at most one vector of the row holds the label
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] -= (j == jy) ? keep : 0.f;
+            }
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(f[2 * j] * gscale, f[2 * j + 1] * gscale);
+            if (dvec) {
+                *reinterpret_cast<uint4*>(drow + c0) = o;
+            } else {
+                const __half* os = reinterpret_cast<const __half*>(&o);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) drow[c0 + j] = os[j];
+            }
+        }
+    }
+    for (int cidx = tail0 + tid; cidx < classes; cidx += THREADS) {
+        const float pv = (E_HALF ? __half2float(src[cidx]) : fast_exp2(fmaf(__half2float(src[cidx]), kLog2e, shift))) * inv_sum;
+        if (want_log) sum_log += fast_log2(pv + 1e-8f);
+        if (prow) prow[cidx] = pv;
+        if (drow) {
+            float g = pv - spread;
+            if (cidx == y) g -= keep;
+            drow[cidx] = __float2half_rn(g * gscale);
         }
     }
     if (out.loss_partial) {
         sum_log = block_reduce(sum_log, false) * kLn2;
         if (tid == 0) {
-            const float py = fast_exp2(fmaf(__half2float(src[y]), kLog2e, shift)) * inv_sum;
+            const float py = fast_exp2(fmaf(zy, kLog2e, shift)) * inv_sum;
             out.loss_partial[row] = (-keep * logf(py + 1e-8f) - spread * sum_log) * inv_b;
         }
     }
 }
 
-// Fixed-order sum of the per-row partials (one block, strided adds then a
-// shared-memory tree), as softmax_ce_reduce_kernel does; also writes 1/batch.
-__global__ void __launch_bounds__(256)
+// Fixed-order sum of the per-row partials (one block: every thread adds a fixed
+// strided subset four values at a time, then a shared-memory tree), as
+// softmax_ce_reduce_kernel does; also writes 1/batch.
+__global__ void __launch_bounds__(1024)
 softmax_ce_loss_reduce(const float* __restrict__ partial, float* __restrict__ loss,
                        float* __restrict__ inv_scaling, int batch) {
-    __shared__ float s[256];
-    float acc = 0.f;
-    if (partial)
-        for (int i = threadIdx.x; i < batch; i += 256) acc += partial[i];
-    s[threadIdx.x] = acc;
+    __shared__ float s[1024];
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    if (partial) {
+        int i = threadIdx.x;
+        for (; i + 3 * 1024 < batch; i += 4 * 1024) {       // four independent loads in flight
+            a0 += partial[i];
+            a1 += partial[i + 1024];
+            a2 += partial[i + 2048];
+            a3 += partial[i + 3072];
+        }
+        for (; i < batch; i += 1024) a0 += partial[i];
+    }
+    s[threadIdx.x] = (a0 + a1) + (a2 + a3);
     __syncthreads();
-    for (int w = 128; w > 0; w >>= 1) {
+    for (int w = 512; w > 0; w >>= 1) {
         if (threadIdx.x < w) s[threadIdx.x] += s[threadIdx.x + w];
         __syncthreads();
     }
@@ -345,7 +443,9 @@ int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels
     const bool rows_aligned = aligned16(logits) && (logits_stride % 8 == 0);
     if (rows_aligned && classes <= 2048) {
         const int warps = 8;
-        dim3 grid((batch + warps - 1) / warps), block(warps * 32);
+        int blocks = (batch + warps - 1) / warps;
+        if (blocks > sm_count() * 8) blocks = sm_count() * 8;      // warps loop over rows
+        dim3 grid(blocks), block(warps * 32);
         if (classes <= 256)
             softmax_ce_rows_warp<1><<<grid, block, 0, s>>>(z, logits_stride, labels, scaling, label_smoothing, out, batch, classes);
         else if (classes <= 512)
@@ -356,7 +456,6 @@ int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels
             softmax_ce_rows_warp<8><<<grid, block, 0, s>>>(z, logits_stride, labels, scaling, label_smoothing, out, batch, classes);
         TRB_LAUNCH_CHECK("softmax_ce_rows_warp");
     } else {
-        constexpr int kT = 512;
         const size_t row_bytes = (size_t)align_up((int64_t)classes * 2, 16);
         const int cache = row_bytes <= 200 * 1024 ? 1 : 0;
         const size_t smem = cache ? row_bytes : 0;
@@ -364,16 +463,33 @@ int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels
         int dev = 0;
         TRB_CUDA_TRY(cudaGetDevice(&dev));
         if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_block<kT>,
-                                              cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            const int lim = 200 * 1024;
+            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_block<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_block<512, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_block<1024, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_block<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_block<512, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_block<1024, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
             attr_done[dev] = true;
         }
-        softmax_ce_rows_block<kT><<<batch, kT, smem, s>>>(z, logits_stride, labels, scaling, label_smoothing,
-                                                          out, batch, classes, cache, rows_aligned ? 1 : 0);
+        const int vec_ok = rows_aligned ? 1 : 0;
+        const bool e_half = cache && !out.probs && out.dlogits;
+#define TRB_SM_LAUNCH(T, E)                                                                                  \
+    softmax_ce_rows_block<T, E><<<batch, T, smem, s>>>(z, logits_stride, labels, scaling, label_smoothing, out, \
+                                                       batch, classes, cache, vec_ok)
+        // four to eight 8-class vectors per thread and sweep; rows beyond 64 K classes take 1024 threads
+        if (classes <= 8192) {
+            if (e_half) TRB_SM_LAUNCH(256, true); else TRB_SM_LAUNCH(256, false);
+        } else if (classes <= 65536) {
+            if (e_half) TRB_SM_LAUNCH(512, true); else TRB_SM_LAUNCH(512, false);
+        } else {
+            if (e_half) TRB_SM_LAUNCH(1024, true); else TRB_SM_LAUNCH(1024, false);
+        }
+#undef TRB_SM_LAUNCH
         TRB_LAUNCH_CHECK("softmax_ce_rows_block");
     }
     if (loss || inv_scaling) {
-        softmax_ce_loss_reduce<<<1, 256, 0, s>>>(out.loss_partial, loss, inv_scaling, batch);
+        softmax_ce_loss_reduce<<<1, 1024, 0, s>>>(out.loss_partial, loss, inv_scaling, batch);
         TRB_LAUNCH_CHECK("softmax_ce_loss_reduce");
     }
     return TRB200_OK;

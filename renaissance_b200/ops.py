@@ -191,6 +191,40 @@ def conv_fprop(g: ConvGeometry, x, w, y=None, stream=None, workspace=None, scrat
     return y
 
 
+def conv_fprop_bn_stats(g: ConvGeometry, x, w, gamma, beta, y=None, out=None, eps=1e-5, momentum=0.1,
+                        running_mean=None, running_var=None, workspace=None, scratch=None, stream=None,
+                        want_sums=False):
+    """Forward conv + batch statistics in its epilogue + bn_finalize (cbr_op.cpp:622-718, 430-528).
+    Returns (y, dict(saved_mean, saved_inv_std, eq_scale, eq_bias[, sum, sqsum]))."""
+    lib = _lib.load()
+    _need(x, torch.float16, "x", 4)
+    _need(w, torch.float16, "w", 4)
+    if tuple(x.shape) != (g.n, g.h, g.w, g.c) or tuple(w.shape) != (g.k, g.r, g.s, g.c):
+        raise ValueError("conv_fprop_bn_stats: tensor shapes do not match the geometry")
+    dev = x.device
+    if y is None:
+        y = torch.empty((g.n, g.oh, g.ow, g.k), dtype=torch.float16, device=dev)
+    if out is None:
+        out = {k: torch.empty(g.k, dtype=torch.float32, device=dev)
+               for k in ("saved_mean", "saved_inv_std", "eq_scale", "eq_bias")}
+    if want_sums:
+        out["sum"] = torch.empty(g.k, dtype=torch.float32, device=dev)
+        out["sqsum"] = torch.empty(g.k, dtype=torch.float32, device=dev)
+    d = g.desc()
+    need = lib.trb200_conv_fprop_bn_stats_workspace_bytes(C.byref(d))
+    if scratch is not None and scratch.numel() * scratch.element_size() >= need:
+        ws, ws_bytes = scratch, scratch.numel() * scratch.element_size()
+    else:
+        ws = (workspace or default_workspace()).ensure(need)
+        ws_bytes = ws.numel()
+    check(lib.trb200_conv_fprop_bn_stats(C.byref(d), _ptr(x), _ptr(w), _ptr(y), _ptr(gamma), _ptr(beta), float(eps),
+                                         float(momentum), _ptr(out.get("sum")), _ptr(out.get("sqsum")),
+                                         _ptr(out["saved_mean"]), _ptr(out["saved_inv_std"]), _ptr(out["eq_scale"]),
+                                         _ptr(out["eq_bias"]), _ptr(running_mean), _ptr(running_var), _ptr(ws),
+                                         ws_bytes, _stream(stream)))
+    return y, out
+
+
 # --------------------------------------------------------------------------- whole block
 
 @dataclass

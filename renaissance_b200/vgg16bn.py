@@ -223,23 +223,21 @@ class Vgg16BnTrainer:
         for L in self.convs:
             b = L.buf
             w16 = self.view(self.w16, L.w)
-            if L.idx == 0:
-                # 3(+1)->64 first convolution: 1x1 GEMM over the pixels' 3x3 neighbourhoods, which are
-                # written into the (still free) backward scratch buffer
-                ops.conv_fprop(ops.ConvGeometry(n, L.h, L.h, L.c, L.k), x, w16, y=b["conv_out"],
-                               scratch=self.bn_scratch)
-            else:
-                if self.timing is not None:
-                    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    t0.record()
-                ops.conv_fprop(ops.ConvGeometry(n, L.h, L.h, L.c, L.k), x, w16, y=b["conv_out"])
-                if self.timing is not None:
-                    t1.record()
-                    self.timing.append((t0, t1, 2.0 * n * L.h * L.h * L.c * L.k * 9,
-                                        2.0 * (n * L.h * L.h * (L.c + L.k) + 9 * L.c * L.k)))
-            ops.bn_stats_finalize(b["conv_out"], self.view(self.w32, L.gamma), self.view(self.w32, L.beta),
-                                  running_mean=b["running_mean"], running_var=b["running_var"], out=b,
-                                  workspace=self.ws)
+            geo = ops.ConvGeometry(n, L.h, L.h, L.c, L.k)
+            gamma, beta = self.view(self.w32, L.gamma), self.view(self.w32, L.beta)
+            # conv with the batch statistics taken in its epilogue, then bn_finalize.  The 3(+1)->64 first
+            # layer runs as a 1x1 GEMM over the pixels' 3x3 neighbourhoods, which go to the (still free)
+            # backward scratch buffer.
+            if self.timing is not None and L.idx > 0:
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+            ops.conv_fprop_bn_stats(geo, x, w16, gamma, beta, y=b["conv_out"], out=b,
+                                    running_mean=b["running_mean"], running_var=b["running_var"],
+                                    workspace=self.ws, scratch=self.bn_scratch if L.idx == 0 else None)
+            if self.timing is not None and L.idx > 0:
+                t1.record()
+                self.timing.append((t0, t1, 2.0 * n * L.h * L.h * L.c * L.k * 9,
+                                    2.0 * (n * L.h * L.h * (L.c + L.k) + 9 * L.c * L.k)))
             ops.bn_apply_relu_mask(b["conv_out"], b["eq_scale"], b["eq_bias"], relu_out=b["relu_out"],
                                    mask_bits=b["mask"])
             x = b["relu_out"]

@@ -41,9 +41,11 @@ def test_fused_and_split_nodes_match_oracle(orc, batch, classes, ls, scaling):
     torch.cuda.synchronize()
     _check(fused, ref, True, batch)
     assert rel_l2(host(fused["dlogits"]).astype(np.float32), ref["dlogits"].astype(np.float32)) < 2e-3
-    # fused without probs writes the same gradient
+    # fused without probs (long rows then keep exp(z - max) as half between the sweeps): same gradient to half precision
     lean = ops.softmax_ce_amp_fused(zd, ld, sc, lsd, want_probs=False)
-    assert torch.equal(lean["dlogits"], fused["dlogits"]) and lean["probs"] is None
+    assert lean["probs"] is None
+    assert rel_l2(host(lean["dlogits"]).astype(np.float32), ref["dlogits"].astype(np.float32)) < 2e-3
+    assert abs(float(lean["loss"]) - ref["loss"]) < 2e-5
     # the reference's two nodes
     fwd = ops.softmax_ce_amp_fwd(zd, ld, lsd)
     _check(fwd, ref, True, batch)

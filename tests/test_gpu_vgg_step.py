@@ -46,6 +46,38 @@ def test_bn_stats_finalize_matches_oracle(orc):
     assert np.abs(host(rm) - rm_ref).max() < 1e-5 and rel_max(host(rv), rv_ref) < 1e-4
 
 
+@pytest.mark.parametrize("n,h,w,c,k", [(2, 8, 8, 64, 64), (3, 7, 5, 64, 128), (2, 14, 14, 128, 512), (2, 12, 10, 4, 64),
+                                       (5, 9, 9, 256, 256)])
+def test_conv_with_statistics_in_its_epilogue(orc, n, h, w, c, k):
+    """conv + batch statistics + bn_finalize in two launches: the conv output must equal the plain
+    conv kernel's bit for bit, the statistics must be those of that (half) output."""
+    from renaissance_b200 import ops
+    rng = np.random.default_rng(n + h + k)
+    x = rng.standard_normal((n, h, w, c)).astype(np.float16)
+    wt = (rng.standard_normal((k, 3, 3, c)) * np.sqrt(2.0 / (9 * c))).astype(np.float16)
+    gamma = (1 + 0.2 * rng.standard_normal(k)).astype(np.float32)
+    beta = (0.2 * rng.standard_normal(k)).astype(np.float32)
+    geo = ops.ConvGeometry(n, h, w, c, k)
+    y_plain = ops.conv_fprop(geo, dev(x), dev(wt))
+    rm, rv = torch.zeros(k, device="cuda"), torch.ones(k, device="cuda")
+    y, st = ops.conv_fprop_bn_stats(geo, dev(x), dev(wt), dev(gamma), dev(beta), running_mean=rm, running_var=rv,
+                                    want_sums=True)
+    ops.device_status()
+    assert torch.equal(y, y_plain)
+    yf = host(y).astype(np.float64).reshape(-1, k)
+    m = yf.shape[0]
+    assert rel_max(host(st["sum"]), yf.sum(axis=0)) < 1e-4
+    assert rel_max(host(st["sqsum"]), (yf ** 2).sum(axis=0)) < 1e-4
+    mean = yf.mean(axis=0)
+    inv = 1.0 / np.sqrt(yf.var(axis=0) + 1e-5)
+    assert np.abs(host(st["saved_mean"]) - mean).max() < 1e-5
+    assert rel_max(host(st["saved_inv_std"]), inv) < 1e-4
+    assert rel_max(host(st["eq_scale"]), gamma * inv) < 1e-4
+    assert np.abs(host(st["eq_bias"]) - (beta - mean * gamma * inv)).max() < 1e-4
+    assert np.abs(host(rm) - 0.1 * mean).max() < 1e-5
+    assert rel_max(host(rv), 0.9 + 0.1 * yf.var(axis=0) * m / (m - 1)) < 1e-4
+
+
 def test_maxpool_matches_oracle(orc):
     from renaissance_b200 import ops
     rng = np.random.default_rng(5)
