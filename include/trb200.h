@@ -201,6 +201,10 @@ typedef struct trb200_cbr_bwd_args {
     void* ev_bn;
     void* ev_wgrad;
     void* ev_dgrad;
+    const void* pool_argmax;   /* optional: the block is followed by a 2x2 max pool and `dy` is the
+                                  gradient of the POOLED output [n,oh/2,ow/2,k]; this is the pool's
+                                  argmax tensor (trb200_maxpool2x2_fwd layout).  NULL = dy is the
+                                  gradient of the block's own output, as in the reference. */
 } trb200_cbr_bwd_args;
 
 size_t trb200_cbr_bwd_workspace_bytes(const trb200_conv_desc* d, int first_layer);
@@ -286,6 +290,22 @@ int trb200_maxpool2x2_fwd(const void* x, void* y, void* argmax, int32_t n, int32
                           int32_t c, void* stream);
 int trb200_maxpool2x2_bwd(const void* dy, const void* argmax, void* dx, int32_t n, int32_t h, int32_t w,
                           int32_t c, void* stream);
+
+/* A block followed by a 2x2 max pool, with the pool fused into the block's HBM-bound
+ * kernels so that the full-resolution ReLU output (forward) and its gradient
+ * (backward) are never written to or read from HBM.
+ *   forward : = trb200_bn_apply_relu_mask + trb200_maxpool2x2_fwd, bit for bit; relu_out
+ *             may be NULL (nothing downstream of a pooled block reads it).
+ *   backward: = trb200_maxpool2x2_bwd + trb200_bnrelu_bwd (dy_pooled is [n,h/2,w/2,c]).
+ * h, w are the block's output extents (even), c % 8 == 0. */
+int trb200_bn_apply_relu_mask_pool(const void* conv_out, const float* eq_scale, const float* eq_bias,
+                                   void* relu_out, void* mask_bits, void* pool_out, void* argmax,
+                                   int32_t n, int32_t h, int32_t w, int32_t c, void* stream);
+size_t trb200_bnrelu_pool_bwd_workspace_bytes(int32_t n, int32_t h, int32_t w, int32_t c);
+int trb200_bnrelu_pool_bwd(const void* dy_pooled, const void* argmax, const void* mask_bits, const void* x,
+                           const float* gamma, const float* saved_mean, const float* saved_inv_std,
+                           void* dconv, float* dgamma, float* dbeta, int32_t n, int32_t h, int32_t w,
+                           int32_t c, void* workspace, size_t workspace_bytes, void* stream);
 
 /* *flag = 1 if any of the n floats is NaN or Inf (flag is never cleared here):
  * check_nan_kernel, src/backend/ops/range/check_op.cu:15-79. */

@@ -45,6 +45,7 @@ class CbrBwdArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("stream_bn", C.c_void_p), ("stream_wgrad", C.c_void_p), ("stream_dgrad", C.c_void_p),
         ("ev_bn", C.c_void_p), ("ev_wgrad", C.c_void_p), ("ev_dgrad", C.c_void_p),
+        ("pool_argmax", C.c_void_p),
     ]
 
 
@@ -100,6 +101,9 @@ def load() -> C.CDLL:
         "trb200_bn_apply_relu_mask": (C.c_int, [vp, vp, vp, vp, vp, i64, i32, vp]),
         "trb200_maxpool2x2_fwd": (C.c_int, [vp, vp, vp, i32, i32, i32, i32, vp]),
         "trb200_maxpool2x2_bwd": (C.c_int, [vp, vp, vp, i32, i32, i32, i32, vp]),
+        "trb200_bn_apply_relu_mask_pool": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+        "trb200_bnrelu_pool_bwd_workspace_bytes": (sz, [i32, i32, i32, i32]),
+        "trb200_bnrelu_pool_bwd": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, sz, vp]),
         "trb200_check_nonfinite": (C.c_int, [vp, i64, vp, vp]),
         "trb200_sgd_momentum": (C.c_int, [vp, vp, vp, vp, i64, f32, f32, f32, vp, vp, vp]),
         "trb200_scale_f32": (C.c_int, [vp, i64, f32, vp]),

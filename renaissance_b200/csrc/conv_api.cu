@@ -7,6 +7,12 @@
 namespace trb {
 
 int device_status_read_and_clear(int* out);
+int softmax_status_read_and_clear(int* out);
+size_t bnrelu_pool_bwd_workspace(int n, int h, int w, int c);
+int bnrelu_pool_bwd_launch(const void* dy_pooled, const void* argmax, const void* mask_bits, const void* x,
+                           const float* gamma, const float* saved_mean, const float* saved_inv_std, void* dconv,
+                           float* dgamma, float* dbeta, int n, int h, int w, int c, void* workspace,
+                           size_t workspace_bytes, cudaStream_t s);
 int bnrelu_bwd_launch(const void* dy, const void* mask_bits, const void* x, const float* gamma,
                       const float* saved_mean, const float* saved_inv_std, void* dconv, float* dgamma,
                       float* dbeta, int64_t m, int c, void* workspace, size_t workspace_bytes, cudaStream_t s);
@@ -46,9 +52,12 @@ extern "C" int trb200_conv_uses_tensor_cores(const trb200_conv_desc* d, int whic
 }
 
 extern "C" int trb200_device_status(void) {
-    int v = 0;
-    const int rc = trb::device_status_read_and_clear(&v);
+    int v = 0, v2 = 0;
+    int rc = trb::device_status_read_and_clear(&v);
     if (rc) return rc;
+    rc = trb::softmax_status_read_and_clear(&v2);
+    if (rc) return rc;
+    if (v == 0) v = v2;
     if (v != 0)
         return trb::fail(TRB200_ERR_DEVICE_TIMEOUT, "a device-side wait gave up (role code %d)", v);
     return TRB200_OK;
@@ -159,6 +168,10 @@ BlockWs block_ws(const trb200_conv_desc& d, bool first_layer) {
     BlockWs b;
     b.bn_off = 0;
     b.bn_bytes = trb200_bnrelu_bwd_workspace_bytes((int64_t)d.n * oh * ow, d.k);
+    if (oh % 2 == 0 && ow % 2 == 0) {       // room for the pooled variant of stage 1 as well
+        const size_t pooled = trb::bnrelu_pool_bwd_workspace(d.n, oh, ow, d.k);
+        if (pooled > b.bn_bytes) b.bn_bytes = pooled;
+    }
     b.wg_off = (size_t)trb::align_up((int64_t)b.bn_bytes, 256);
     // first layer with 4 input channels: the conv_out buffer doubles as the im2col scratch
     b.wg_bytes = (use_igemm(d, 0) && trb::igemm_small_c(d)) ? trb::igemm_wgrad_small_c_workspace(d)
@@ -199,9 +212,14 @@ extern "C" int trb200_cbr_bwd(const trb200_cbr_bwd_args* a) {
     const int oh = trb::conv_out(d.h, d.pad_h, d.r, d.stride_h), ow = trb::conv_out(d.w, d.pad_w, d.s, d.stride_w);
 
     // 1) BN + ReLU backward: dconv -> bn_scratch, dgamma, dbeta
-    rc = trb::bnrelu_bwd_launch(a->dy, a->mask_bits, a->conv_out, a->gamma, a->saved_mean, a->saved_inv_std,
-                                a->bn_scratch, a->dgamma, a->dbeta, (int64_t)d.n * oh * ow, d.k, wsp + ws.bn_off,
-                                ws.bn_bytes, s_bn);
+    if (a->pool_argmax)
+        rc = trb::bnrelu_pool_bwd_launch(a->dy, a->pool_argmax, a->mask_bits, a->conv_out, a->gamma, a->saved_mean,
+                                         a->saved_inv_std, a->bn_scratch, a->dgamma, a->dbeta, d.n, oh, ow, d.k,
+                                         wsp + ws.bn_off, ws.bn_bytes, s_bn);
+    else
+        rc = trb::bnrelu_bwd_launch(a->dy, a->mask_bits, a->conv_out, a->gamma, a->saved_mean, a->saved_inv_std,
+                                    a->bn_scratch, a->dgamma, a->dbeta, (int64_t)d.n * oh * ow, d.k, wsp + ws.bn_off,
+                                    ws.bn_bytes, s_bn);
     if (rc) return rc;
     if (a->ev_bn) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_bn), s_bn));
 

@@ -1,0 +1,338 @@
+// Blocks that are followed by a 2x2 max pool: the pool fused into the block's
+// HBM-bound kernels, so that the full-resolution ReLU output (forward) and the
+// full-resolution gradient of it (backward) never travel through HBM.
+//
+//   forward : conv_out -> mask bits (full resolution), pool_out, argmax
+//             = bn_apply_relu_mask followed by maxpool2x2_fwd
+//   backward: pooled dy + argmax + mask + conv_out -> dconv, dgamma, dbeta
+//             = maxpool2x2_bwd followed by bnrelu_bwd
+// Reference counterparts: the BN-apply/ReLU/mask graph of the block
+// (src/backend/ops/dtensor/cbr_op.cpp:534-616), the max-pool kernels
+// (src/backend/ops/dtensor/maxpool_op.cu:23-217) and the BN backward graph
+// (cbr_op.cpp:1259-1353); the results are those of the unfused sequence bit for bit
+// (forward) and to the summation order of the channel sums (backward).
+//
+// One work item = one pooled pixel x 8 channels = a 2x2 window of 16-byte vectors.
+// Bytes per full-resolution element: forward 2 + 1/8 + (2 + 1)/4 = 2.875 instead of
+// 6.875; backward 2 x (2 + 1/8 + 3/4) + 2 = 7.75 instead of 14.75.
+#include "common.cuh"
+
+namespace trb {
+namespace {
+
+constexpr int kThreads = 256;
+
+struct PoolPlan {
+    int tpr, bx, by, gy, gx;
+    int64_t rows_per_strip;     // pooled pixels per strip
+};
+
+PoolPlan make_pool_plan(int64_t pooled_rows, int c) {
+    PoolPlan p;
+    p.tpr = c / 8;
+    p.bx = p.tpr < kThreads ? p.tpr : kThreads;
+    p.by = kThreads / p.bx;
+    if (p.by < 1) p.by = 1;
+    p.gy = (p.tpr + p.bx - 1) / p.bx;
+    // strips of at least 4 loop trips, at most 4 waves of 2 resident blocks per SM, whole waves
+    int64_t want = (pooled_rows + (int64_t)p.by * 4 - 1) / ((int64_t)p.by * 4);
+    int64_t resident = (int64_t)sm_count() * 2 / p.gy;
+    if (resident < 1) resident = 1;
+    int64_t g = want < resident * 4 ? want : resident * 4;
+    if (g > resident) g = g / resident * resident;
+    p.gx = (int)(g < 1 ? 1 : g);
+    int64_t rps = (pooled_rows + p.gx - 1) / p.gx;
+    rps = (rps + p.by - 1) / p.by * p.by;
+    p.rows_per_strip = rps;
+    p.gx = (int)((pooled_rows + rps - 1) / rps);
+    return p;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __half22float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+// full-resolution vector index of window position q (q = kh*2 + kw) of pooled pixel pr
+__device__ __forceinline__ int64_t window_base(int64_t pr, int oh_n, int ow_n, int w, int tpr, int vec) {
+    const int ow = (int)(pr % ow_n);
+    const int64_t t = pr / ow_n;
+    const int oh = (int)(t % oh_n);
+    const int64_t img = t / oh_n;
+    return ((img * (2 * oh_n) + 2 * oh) * (int64_t)w + 2 * ow) * tpr + vec;
+}
+
+__global__ void __launch_bounds__(kThreads)
+bn_apply_relu_mask_pool_kernel(const uint4* __restrict__ x, const float* __restrict__ eq_scale,
+                               const float* __restrict__ eq_bias, uint4* __restrict__ relu_out,
+                               uint8_t* __restrict__ mask, uint4* __restrict__ pool_out,
+                               uint2* __restrict__ argmax, int64_t pooled_rows, int oh_n, int ow_n, int w,
+                               int tpr, int bx, int by, int64_t rows_per_strip) {
+    const int tx = threadIdx.x % bx, ty = threadIdx.x / bx;
+    const int vec = blockIdx.y * bx + tx;
+    if (vec >= tpr || ty >= by) return;
+    const int64_t r0 = (int64_t)blockIdx.x * rows_per_strip;
+    const int64_t r1 = (r0 + rows_per_strip < pooled_rows) ? r0 + rows_per_strip : pooled_rows;
+    float sc[8], bi[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { sc[j] = eq_scale[vec * 8 + j]; bi[j] = eq_bias[vec * 8 + j]; }
+    const int64_t row_step = (int64_t)w * tpr;       // one image row down
+    for (int64_t pr = r0 + ty; pr < r1; pr += by) {
+        const int64_t b0 = window_base(pr, oh_n, ow_n, w, tpr, vec);
+        const int64_t idx[4] = {b0, b0 + tpr, b0 + row_step, b0 + row_step + tpr};
+        uint4 v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) v[q] = x[idx[q]];
+        float best[8];
+        uint32_t am[8];
+        uint4 bv = make_uint4(0, 0, 0, 0);
+        __half* bh = reinterpret_cast<__half*>(&bv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { best[j] = -INFINITY; am[j] = 0; }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float f[8];
+            unpack8(v[q], f);
+            uint4 o;
+            __half* oh = reinterpret_cast<__half*>(&o);
+            uint32_t bits = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const __half a = __float2half_rn(f[j] * sc[j]);
+                const __half t = __float2half_rn(__half2float(a) + bi[j]);
+                const bool on = __half2float(t) > 0.f;
+                const __half y = on ? t : __float2half_rn(0.f);
+                oh[j] = y;
+                bits |= (on ? 1u : 0u) << j;
+                const float yf = __half2float(y);
+                if (yf > best[j]) { best[j] = yf; am[j] = (uint32_t)q; bh[j] = y; }
+            }
+            mask[idx[q]] = (uint8_t)bits;
+            if (relu_out) relu_out[idx[q]] = o;
+        }
+        const int64_t po = pr * tpr + vec;
+        pool_out[po] = bv;
+        uint2 a;
+        a.x = am[0] | (am[1] << 8) | (am[2] << 16) | (am[3] << 24);
+        a.y = am[4] | (am[5] << 8) | (am[6] << 16) | (am[7] << 24);
+        argmax[po] = a;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+bnrelu_pool_bwd_reduce(const uint4* __restrict__ dy, const uint2* __restrict__ argmax,
+                       const uint8_t* __restrict__ mask, const uint4* __restrict__ x,
+                       const float* __restrict__ mean, const float* __restrict__ inv_std,
+                       float* __restrict__ partial, int64_t pooled_rows, int c, int oh_n, int ow_n, int w,
+                       int tpr, int bx, int by, int64_t rows_per_strip) {
+    __shared__ float s_red[kThreads * 16];
+    const int tx = threadIdx.x % bx, ty = threadIdx.x / bx;
+    const int vec = blockIdx.y * bx + tx;
+    const bool ok = vec < tpr && ty < by;
+    const int64_t r0 = (int64_t)blockIdx.x * rows_per_strip;
+    const int64_t r1 = (r0 + rows_per_strip < pooled_rows) ? r0 + rows_per_strip : pooled_rows;
+    float sb[8], sg[8], mu[8], is[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { sb[j] = 0.f; sg[j] = 0.f; mu[j] = 0.f; is[j] = 0.f; }
+    if (ok) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { mu[j] = mean[vec * 8 + j]; is[j] = inv_std[vec * 8 + j]; }
+        const int64_t row_step = (int64_t)w * tpr;
+        for (int64_t pr = r0 + ty; pr < r1; pr += by) {
+            const int64_t b0 = window_base(pr, oh_n, ow_n, w, tpr, vec);
+            const int64_t idx[4] = {b0, b0 + tpr, b0 + row_step, b0 + row_step + tpr};
+            const int64_t po = pr * tpr + vec;
+            const uint4 g4 = dy[po];
+            const uint2 a2 = argmax[po];
+            uint4 xv[4];
+            uint32_t mb[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { xv[q] = x[idx[q]]; mb[q] = mask[idx[q]]; }
+            float g[8];
+            unpack8(g4, g);
+            const uint8_t* ab = reinterpret_cast<const uint8_t*>(&a2);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float xf[8];
+                unpack8(xv[q], xf);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float gm = (ab[j] == q && ((mb[q] >> j) & 1u)) ? g[j] : 0.f;
+                    sb[j] += gm;
+                    sg[j] += gm * ((xf[j] - mu[j]) * is[j]);
+                }
+            }
+        }
+    }
+    float* mine = s_red + (size_t)threadIdx.x * 16;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { mine[j] = sb[j]; mine[8 + j] = sg[j]; }
+    __syncthreads();
+    for (int t = threadIdx.x; t < bx * 16; t += kThreads) {
+        const int otx = t / 16, j = t % 16;
+        const int ovec = blockIdx.y * bx + otx;
+        if (ovec >= tpr) continue;
+        float acc = 0.f;
+        for (int y = 0; y < by; ++y) acc += s_red[(size_t)(y * bx + otx) * 16 + j];
+        partial[((size_t)blockIdx.x * 2 + (j >> 3)) * c + ovec * 8 + (j & 7)] = acc;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+bnrelu_pool_bwd_finalize(const float* __restrict__ partial, float* __restrict__ dgamma,
+                         float* __restrict__ dbeta, int c, int strips) {
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (i >= 2 * c) return;
+    const int stat = i / c, ch = i % c;
+    double acc = 0.0;
+    for (int s = lane; s < strips; s += 32) acc += (double)partial[((size_t)s * 2 + stat) * c + ch];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) (stat == 0 ? dbeta : dgamma)[ch] = (float)acc;
+}
+
+__global__ void __launch_bounds__(kThreads)
+bnrelu_pool_bwd_apply(const uint4* __restrict__ dy, const uint2* __restrict__ argmax,
+                      const uint8_t* __restrict__ mask, const uint4* __restrict__ x,
+                      const float* __restrict__ gamma, const float* __restrict__ mean,
+                      const float* __restrict__ inv_std, const float* __restrict__ dgamma,
+                      const float* __restrict__ dbeta, uint4* __restrict__ out, int64_t pooled_rows,
+                      int64_t m_full, int oh_n, int ow_n, int w, int tpr, int bx, int by,
+                      int64_t rows_per_strip) {
+    const int tx = threadIdx.x % bx, ty = threadIdx.x / bx;
+    const int vec = blockIdx.y * bx + tx;
+    if (vec >= tpr || ty >= by) return;
+    const int strip = gridDim.x - 1 - blockIdx.x;     // the rows the reduce kernel read last are still in L2
+    const int64_t r0 = (int64_t)strip * rows_per_strip;
+    const int64_t r1 = (r0 + rows_per_strip < pooled_rows) ? r0 + rows_per_strip : pooled_rows;
+    float ca[8], cmb[8], cmu[8], ck[8];
+    const float inv_m = 1.0f / (float)m_full;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int ch = vec * 8 + j;
+        const float is = inv_std[ch];
+        ca[j] = gamma[ch] * is;
+        cmb[j] = dbeta[ch] * inv_m;
+        cmu[j] = mean[ch];
+        ck[j] = is * (dgamma[ch] * inv_m);
+    }
+    const int64_t row_step = (int64_t)w * tpr;
+    for (int64_t pr = r0 + ty; pr < r1; pr += by) {
+        const int64_t b0 = window_base(pr, oh_n, ow_n, w, tpr, vec);
+        const int64_t idx[4] = {b0, b0 + tpr, b0 + row_step, b0 + row_step + tpr};
+        const int64_t po = pr * tpr + vec;
+        const uint4 g4 = dy[po];
+        const uint2 a2 = argmax[po];
+        uint4 xv[4];
+        uint32_t mb[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { xv[q] = x[idx[q]]; mb[q] = mask[idx[q]]; }
+        float g[8];
+        unpack8(g4, g);
+        const uint8_t* ab = reinterpret_cast<const uint8_t*>(&a2);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float xf[8];
+            unpack8(xv[q], xf);
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int j0 = 2 * j, j1 = 2 * j + 1;
+                const float g0 = (ab[j0] == q && ((mb[q] >> j0) & 1u)) ? g[j0] : 0.f;
+                const float g1 = (ab[j1] == q && ((mb[q] >> j1) & 1u)) ? g[j1] : 0.f;
+                const float o0 = ca[j0] * (g0 - cmb[j0] - (xf[j0] - cmu[j0]) * ck[j0]);
+                const float o1 = ca[j1] * (g1 - cmb[j1] - (xf[j1] - cmu[j1]) * ck[j1]);
+                oh[j] = __floats2half2_rn(o0, o1);
+            }
+            out[idx[q]] = o;
+        }
+    }
+}
+
+int check_pool_shape(int n, int h, int w, int c, const char* who) {
+    TRB_REQUIRE(n > 0 && h > 0 && w > 0 && h % 2 == 0 && w % 2 == 0 && c > 0 && c % 8 == 0, TRB200_ERR_UNSUPPORTED,
+                "%s: need even h, w and c a positive multiple of 8 (n=%d h=%d w=%d c=%d)", who, n, h, w, c);
+    return TRB200_OK;
+}
+
+}  // namespace
+
+size_t bnrelu_pool_bwd_workspace(int n, int h, int w, int c) {
+    const PoolPlan p = make_pool_plan((int64_t)n * (h / 2) * (w / 2), c);
+    return (size_t)p.gx * 2 * (size_t)c * sizeof(float);
+}
+
+int bnrelu_pool_bwd_launch(const void* dy_pooled, const void* argmax, const void* mask_bits, const void* x,
+                           const float* gamma, const float* saved_mean, const float* saved_inv_std, void* dconv,
+                           float* dgamma, float* dbeta, int n, int h, int w, int c, void* workspace,
+                           size_t workspace_bytes, cudaStream_t s) {
+    int rc = check_pool_shape(n, h, w, c, "bnrelu_pool_bwd");
+    if (rc) return rc;
+    TRB_REQUIRE(dy_pooled && argmax && mask_bits && x && gamma && saved_mean && saved_inv_std && dconv && dgamma && dbeta,
+                TRB200_ERR_INVALID_ARGUMENT, "bnrelu_pool_bwd: null pointer");
+    TRB_REQUIRE(aligned16(dy_pooled) && aligned16(x) && aligned16(dconv) && (reinterpret_cast<uintptr_t>(argmax) & 7u) == 0,
+                TRB200_ERR_INVALID_ARGUMENT, "bnrelu_pool_bwd: tensors must be 16-byte aligned (argmax: 8)");
+    TRB_REQUIRE(dconv != x && dconv != dy_pooled, TRB200_ERR_INVALID_ARGUMENT, "bnrelu_pool_bwd: dconv must not alias an input");
+    const size_t need = bnrelu_pool_bwd_workspace(n, h, w, c);
+    TRB_REQUIRE(workspace && workspace_bytes >= need, TRB200_ERR_WORKSPACE,
+                "bnrelu_pool_bwd: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    const int64_t pooled = (int64_t)n * (h / 2) * (w / 2);
+    const PoolPlan p = make_pool_plan(pooled, c);
+    float* partial = static_cast<float*>(workspace);
+    dim3 grid(p.gx, p.gy);
+    bnrelu_pool_bwd_reduce<<<grid, kThreads, 0, s>>>(
+        static_cast<const uint4*>(dy_pooled), static_cast<const uint2*>(argmax), static_cast<const uint8_t*>(mask_bits),
+        static_cast<const uint4*>(x), saved_mean, saved_inv_std, partial, pooled, c, h / 2, w / 2, w, p.tpr, p.bx, p.by,
+        p.rows_per_strip);
+    TRB_LAUNCH_CHECK("bnrelu_pool_bwd_reduce");
+    bnrelu_pool_bwd_finalize<<<(2 * c + 7) / 8, 256, 0, s>>>(partial, dgamma, dbeta, c, p.gx);
+    TRB_LAUNCH_CHECK("bnrelu_pool_bwd_finalize");
+    bnrelu_pool_bwd_apply<<<grid, kThreads, 0, s>>>(
+        static_cast<const uint4*>(dy_pooled), static_cast<const uint2*>(argmax), static_cast<const uint8_t*>(mask_bits),
+        static_cast<const uint4*>(x), gamma, saved_mean, saved_inv_std, dgamma, dbeta, static_cast<uint4*>(dconv), pooled,
+        (int64_t)n * h * w, h / 2, w / 2, w, p.tpr, p.bx, p.by, p.rows_per_strip);
+    TRB_LAUNCH_CHECK("bnrelu_pool_bwd_apply");
+    return TRB200_OK;
+}
+
+}  // namespace trb
+
+extern "C" int trb200_bn_apply_relu_mask_pool(const void* conv_out, const float* eq_scale, const float* eq_bias,
+                                              void* relu_out, void* mask_bits, void* pool_out, void* argmax,
+                                              int32_t n, int32_t h, int32_t w, int32_t c, void* stream) {
+    int rc = trb::check_pool_shape(n, h, w, c, "bn_apply_relu_mask_pool");
+    if (rc) return rc;
+    TRB_REQUIRE(conv_out && eq_scale && eq_bias && mask_bits && pool_out && argmax, TRB200_ERR_INVALID_ARGUMENT,
+                "bn_apply_relu_mask_pool: null pointer");
+    TRB_REQUIRE(trb::aligned16(conv_out) && trb::aligned16(pool_out) && (!relu_out || trb::aligned16(relu_out)) &&
+                    (reinterpret_cast<uintptr_t>(argmax) & 7u) == 0,
+                TRB200_ERR_INVALID_ARGUMENT, "bn_apply_relu_mask_pool: tensors must be 16-byte aligned (argmax: 8)");
+    const int64_t pooled = (int64_t)n * (h / 2) * (w / 2);
+    const trb::PoolPlan p = trb::make_pool_plan(pooled, c);
+    trb::bn_apply_relu_mask_pool_kernel<<<dim3(p.gx, p.gy), trb::kThreads, 0, trb::as_stream(stream)>>>(
+        static_cast<const uint4*>(conv_out), eq_scale, eq_bias, static_cast<uint4*>(relu_out),
+        static_cast<uint8_t*>(mask_bits), static_cast<uint4*>(pool_out), static_cast<uint2*>(argmax), pooled, h / 2,
+        w / 2, w, p.tpr, p.bx, p.by, p.rows_per_strip);
+    TRB_LAUNCH_CHECK("bn_apply_relu_mask_pool_kernel");
+    return TRB200_OK;
+}
+
+extern "C" size_t trb200_bnrelu_pool_bwd_workspace_bytes(int32_t n, int32_t h, int32_t w, int32_t c) {
+    if (n <= 0 || h <= 0 || w <= 0 || c <= 0 || h % 2 || w % 2 || c % 8) return 0;
+    return trb::bnrelu_pool_bwd_workspace(n, h, w, c);
+}
+
+extern "C" int trb200_bnrelu_pool_bwd(const void* dy_pooled, const void* argmax, const void* mask_bits, const void* x,
+                                      const float* gamma, const float* saved_mean, const float* saved_inv_std,
+                                      void* dconv, float* dgamma, float* dbeta, int32_t n, int32_t h, int32_t w,
+                                      int32_t c, void* workspace, size_t workspace_bytes, void* stream) {
+    return trb::bnrelu_pool_bwd_launch(dy_pooled, argmax, mask_bits, x, gamma, saved_mean, saved_inv_std, dconv, dgamma,
+                                       dbeta, n, h, w, c, workspace, workspace_bytes, trb::as_stream(stream));
+}

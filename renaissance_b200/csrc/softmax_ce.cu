@@ -14,8 +14,12 @@
 // and writes d_logits directly; probs are written only when asked for.
 // HBM bytes per element: 2 read + 2 written (+4 when probs are kept).
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace trb {
+
+__device__ int g_softmax_status = 0;   // set when a bounded wait of the staged kernel gives up
+
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
@@ -55,6 +59,13 @@ __device__ __forceinline__ void half8_to_float(const uint4& raw, float (&f)[8]) 
         f[2 * j] = t.x;
         f[2 * j + 1] = t.y;
     }
+}
+
+// max of the 8 halfs of a 16-byte vector, taken with packed half2 instructions
+__device__ __forceinline__ float half8_max(const uint4& raw) {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+    const __half2 m = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+    return fmaxf(__low2float(m), __high2float(m));
 }
 
 struct RowOut {
@@ -245,10 +256,7 @@ softmax_ce_rows_block(const __half* __restrict__ logits, int64_t logits_stride,
         for (int u = 0; u < 4; ++u) {
             const int vec = vec0 + u * THREADS;
             if (cache && vec < nfull) *reinterpret_cast<uint4*>(srow + vec * 8) = raw[u];
-            float f[8];
-            half8_to_float(raw[u], f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) zmax = fmaxf(zmax, f[j]);
+            zmax = fmaxf(zmax, half8_max(raw[u]));
         }
     }
     for (int cidx = tail0 + tid; cidx < classes; cidx += THREADS) {
@@ -358,6 +366,183 @@ softmax_ce_rows_block(const __half* __restrict__ logits, int64_t logits_stride,
     }
 }
 
+// Persistent variant for long, 16-byte aligned rows with classes % 8 == 0: a block walks
+// rows blockIdx.x, blockIdx.x + gridDim.x, ...; each row is brought into shared memory by
+// ONE bulk (TMA) copy that completes on an mbarrier, into one of two buffers, so that the
+// copy of the next row is in flight while the three sweeps of the current row run.
+// Arithmetic and E_HALF as in softmax_ce_rows_block.
+template <int THREADS, bool E_HALF>
+__global__ void __launch_bounds__(THREADS)
+softmax_ce_rows_staged(const __half* __restrict__ logits, int64_t logits_stride,
+                       const int32_t* __restrict__ labels, const float* __restrict__ scaling,
+                       const float* __restrict__ label_smoothing, RowOut out, int batch, int classes,
+                       uint32_t buf_stride, int* status) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t s_bar[2];
+    __shared__ float s_red[THREADS / 32];
+    __shared__ float s_bcast;
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t row_bytes = (uint32_t)classes * 2u;
+    const uint32_t buf0 = ptx::smem_u32(smem_raw);
+    const uint32_t bar0 = ptx::smem_u32(&s_bar[0]);
+    if (tid == 0) {
+        s_abort = 0;
+        ptx::mbar_init(bar0, 1);
+        ptx::mbar_init(bar0 + 8, 1);
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+
+    auto block_reduce = [&](float val, bool is_max) -> float {
+        val = is_max ? warp_max(val) : warp_sum(val);
+        __syncthreads();
+        if (lane == 0) s_red[warp] = val;
+        __syncthreads();
+        if (warp == 0) {
+            float t = lane < THREADS / 32 ? s_red[lane] : (is_max ? -INFINITY : 0.f);
+            t = is_max ? warp_max(t) : warp_sum(t);
+            if (lane == 0) s_bcast = t;
+        }
+        __syncthreads();
+        return s_bcast;
+    };
+
+    const float ls = label_smoothing ? label_smoothing[0] : 0.f;
+    const float keep = 1.0f - ls, spread = ls / (float)classes;
+    const float inv_b = 1.0f / (float)batch;
+    const float gscale = (scaling ? scaling[0] : 1.0f) * inv_b;
+    const bool want_log = ls != 0.f;
+    const int nvec = classes >> 3;
+    const bool dvec = out.dlogits && (out.dlogits_stride & 7) == 0 && aligned16_dev(out.dlogits);
+    const bool pvec = out.probs && (out.probs_stride & 3) == 0 && aligned16_dev(out.probs);
+
+    int row = blockIdx.x;
+    if (tid == 0 && row < batch) {
+        ptx::mbar_expect_tx(bar0, row_bytes);
+        ptx::bulk_load_1d(buf0, logits + (int64_t)row * logits_stride, row_bytes, bar0);
+    }
+    for (int it = 0; row < batch; row += gridDim.x, ++it) {
+        const int b = it & 1;
+        const int next = row + gridDim.x;
+        if (tid == 0 && next < batch) {       // the other buffer was released by the barrier that ended the last row
+            ptx::mbar_expect_tx(bar0 + 8u * (b ^ 1), row_bytes);
+            ptx::bulk_load_1d(buf0 + (uint32_t)(b ^ 1) * buf_stride, logits + (int64_t)next * logits_stride, row_bytes,
+                              bar0 + 8u * (b ^ 1));
+        }
+        const bool ok = ptx::mbar_wait(bar0 + 8u * b, ((uint32_t)it >> 1) & 1u, &s_abort, status, 4);
+        if (__syncthreads_or(ok ? 0 : 1)) break;
+        __half* srow = reinterpret_cast<__half*>(smem_raw + (size_t)b * buf_stride);
+        const int y = labels[row];
+        const float zy = __half2float(logits[(int64_t)row * logits_stride + y]);
+
+        float zmax = -INFINITY;
+        for (int vec = tid; vec < nvec; vec += THREADS)
+            zmax = fmaxf(zmax, half8_max(*reinterpret_cast<const uint4*>(srow + vec * 8)));
+        zmax = block_reduce(zmax, true);
+        const float shift = -zmax * kLog2e;
+
+        float sum = 0.f;
+        for (int vec = tid; vec < nvec; vec += THREADS) {
+            float f[8];
+            half8_to_float(*reinterpret_cast<const uint4*>(srow + vec * 8), f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                f[j] = fast_exp2(fmaf(f[j], kLog2e, shift));
+                sum += f[j];
+            }
+            if (E_HALF) {
+                uint4 o;
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+                *reinterpret_cast<uint4*>(srow + vec * 8) = o;
+            }
+        }
+        sum = block_reduce(sum, false);
+        const float inv_sum = 1.0f / (sum + 1e-8f);
+
+        float sum_log = 0.f;
+        __half* drow = out.dlogits ? out.dlogits + (int64_t)row * out.dlogits_stride : nullptr;
+        float* prow = out.probs ? out.probs + (int64_t)row * out.probs_stride : nullptr;
+        if (E_HALF && !want_log && dvec) {
+            // gradient only: g = e * (inv_sum * gscale) - spread * gscale, one FMA per class
+            const float ga = inv_sum * gscale, gb = -spread * gscale, gk = keep * gscale;
+            for (int vec = tid; vec < nvec; vec += THREADS) {
+                float f[8];
+                half8_to_float(*reinterpret_cast<const uint4*>(srow + vec * 8), f);
+                const int c0 = vec * 8;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = fmaf(f[j], ga, gb);
+                const int jy = y - c0;
+                if ((unsigned)jy < 8u) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) f[j] -= (j == jy) ? gk : 0.f;
+                }
+                uint4 o;
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+                *reinterpret_cast<uint4*>(drow + c0) = o;
+            }
+        } else
+        for (int vec = tid; vec < nvec; vec += THREADS) {
+            float f[8];
+            half8_to_float(*reinterpret_cast<const uint4*>(srow + vec * 8), f);
+            const int c0 = vec * 8;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                f[j] = (E_HALF ? f[j] : fast_exp2(fmaf(f[j], kLog2e, shift))) * inv_sum;
+                if (want_log) sum_log += fast_log2(f[j] + 1e-8f);
+            }
+            if (prow) {
+                if (pvec) {
+                    reinterpret_cast<float4*>(prow + c0)[0] = make_float4(f[0], f[1], f[2], f[3]);
+                    reinterpret_cast<float4*>(prow + c0)[1] = make_float4(f[4], f[5], f[6], f[7]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) prow[c0 + j] = f[j];
+                }
+            }
+            if (drow) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] -= spread;
+                const int jy = y - c0;
+                if ((unsigned)jy < 8u) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) f[j] -= (j == jy) ? keep : 0.f;
+                }
+                uint4 o;
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) oh[j] = __floats2half2_rn(f[2 * j] * gscale, f[2 * j + 1] * gscale);
+                if (dvec) {
+                    *reinterpret_cast<uint4*>(drow + c0) = o;
+                } else {
+                    const __half* os = reinterpret_cast<const __half*>(&o);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) drow[c0 + j] = os[j];
+                }
+            }
+        }
+        if (out.loss_partial) {
+            sum_log = block_reduce(sum_log, false) * kLn2;
+            if (tid == 0) {
+                const float py = fast_exp2(fmaf(zy, kLog2e, shift)) * inv_sum;
+                out.loss_partial[row] = (-keep * logf(py + 1e-8f) - spread * sum_log) * inv_b;
+            }
+        }
+        // this buffer is refilled by a bulk copy two rows from now: order the generic-proxy
+        // accesses above before it
+        ptx::fence_proxy_async_smem();
+        __syncthreads();
+    }
+    if (*(volatile int*)&s_abort) {     // a wait gave up: let a copy that may still be in flight land before the block ends
+        const unsigned long long t0 = ptx::global_ns();
+        while (ptx::global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+}
+
 // Fixed-order sum of the per-row partials (one block: every thread adds a fixed
 // strided subset four values at a time, then a shared-memory tree), as
 // softmax_ce_reduce_kernel does; also writes 1/batch.
@@ -455,6 +640,39 @@ int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels
         else
             softmax_ce_rows_warp<8><<<grid, block, 0, s>>>(z, logits_stride, labels, scaling, label_smoothing, out, batch, classes);
         TRB_LAUNCH_CHECK("softmax_ce_rows_warp");
+    } else if (rows_aligned && classes % 8 == 0 && (size_t)align_up((int64_t)classes * 2, 128) <= 48 * 1024) {
+        const uint32_t buf_stride = (uint32_t)align_up((int64_t)classes * 2, 128);
+        const size_t smem = (size_t)buf_stride * 2;
+        static bool staged_attr_done[64] = {false};
+        int dev = 0;
+        TRB_CUDA_TRY(cudaGetDevice(&dev));
+        if (dev >= 0 && dev < 64 && !staged_attr_done[dev]) {
+            const int lim = 200 * 1024;
+            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_staged<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_staged<512, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_staged<1024, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_staged<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_staged<512, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_staged<1024, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+            staged_attr_done[dev] = true;
+        }
+        int* status = nullptr;
+        TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_softmax_status));
+        const int threads = classes <= 12288 ? 256 : (classes <= 24576 ? 512 : 1024);
+        int per_sm = (int)((200 * 1024) / smem);
+        if (per_sm > 2048 / threads) per_sm = 2048 / threads;
+        if (per_sm < 1) per_sm = 1;
+        int grid = sm_count() * per_sm;
+        if (grid > batch) grid = batch;
+        const bool e_half = !out.probs && out.dlogits;
+#define TRB_ST_LAUNCH(T, E)                                                                                      \
+    softmax_ce_rows_staged<T, E><<<grid, T, smem, s>>>(z, logits_stride, labels, scaling, label_smoothing, out, \
+                                                       batch, classes, buf_stride, status)
+        if (threads == 256) { if (e_half) TRB_ST_LAUNCH(256, true); else TRB_ST_LAUNCH(256, false); }
+        else if (threads == 512) { if (e_half) TRB_ST_LAUNCH(512, true); else TRB_ST_LAUNCH(512, false); }
+        else { if (e_half) TRB_ST_LAUNCH(1024, true); else TRB_ST_LAUNCH(1024, false); }
+#undef TRB_ST_LAUNCH
+        TRB_LAUNCH_CHECK("softmax_ce_rows_staged");
     } else {
         const size_t row_bytes = (size_t)align_up((int64_t)classes * 2, 16);
         const int cache = row_bytes <= 200 * 1024 ? 1 : 0;
@@ -496,6 +714,18 @@ int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels
 }
 
 }  // namespace
+
+int softmax_status_read_and_clear(int* out) {
+    int v = 0;
+    TRB_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_softmax_status, sizeof(int)));
+    if (v != 0) {
+        const int zero = 0;
+        TRB_CUDA_TRY(cudaMemcpyToSymbol(g_softmax_status, &zero, sizeof(int)));
+    }
+    *out = v;
+    return TRB200_OK;
+}
+
 }  // namespace trb
 
 extern "C" int trb200_softmax_ce_fwd(const void* logits, int64_t logits_stride, const int32_t* labels,

@@ -251,13 +251,14 @@ class BlockStreams:
 
 def cbr_amp_bwd(g: ConvGeometry, dy, w, gamma, saved_mean, saved_inv_std, mask_bits, x, conv_out,
                 bn_scratch=None, dw=None, first_layer=False, streams: BlockStreams | None = None,
-                workspace=None, stream=None, dgamma=None, dbeta=None):
+                workspace=None, stream=None, dgamma=None, dbeta=None, pool_argmax=None):
     """CBR_AMP_BWD / CBR_AMP_BWD_FIRST_LAYER.
 
     Node ids of the reference: in [dY, W16, gamma, saved_mean, saved_inv_var, mask, X],
     out [dX (= X's buffer), dW16, dgamma, dbeta, conv_output, bn_output]
     (cbr_op.cpp:1365-1366).  As there, dX is written IN PLACE over ``x`` (returned as
-    ``dx``) unless ``first_layer``.  Returns dict(dx, dw, dgamma, dbeta, dconv)."""
+    ``dx``) unless ``first_layer``.  With ``pool_argmax`` the block is followed by a 2x2 max pool and
+    ``dy`` is the gradient of the pooled output.  Returns dict(dx, dw, dgamma, dbeta, dconv)."""
     lib = _lib.load()
     _need(dy, torch.float16, "dy", 4)
     _need(w, torch.float16, "w", 4)
@@ -266,11 +267,12 @@ def cbr_amp_bwd(g: ConvGeometry, dy, w, gamma, saved_mean, saved_inv_std, mask_b
     _need(mask_bits, torch.uint8, "mask_bits")
     for t, nm in ((gamma, "gamma"), (saved_mean, "saved_mean"), (saved_inv_std, "saved_inv_std")):
         _need(t, torch.float32, nm)
-    if tuple(x.shape) != (g.n, g.h, g.w, g.c) or tuple(dy.shape) != (g.n, g.oh, g.ow, g.k) \
-            or tuple(w.shape) != (g.k, g.r, g.s, g.c) or conv_out.shape != dy.shape:
+    dy_shape = (g.n, g.oh, g.ow, g.k) if pool_argmax is None else (g.n, g.oh // 2, g.ow // 2, g.k)
+    if tuple(x.shape) != (g.n, g.h, g.w, g.c) or tuple(dy.shape) != dy_shape \
+            or tuple(w.shape) != (g.k, g.r, g.s, g.c) or tuple(conv_out.shape) != (g.n, g.oh, g.ow, g.k):
         raise ValueError("cbr_amp_bwd: tensor shapes do not match the geometry")
     if bn_scratch is None:
-        bn_scratch = torch.empty_like(dy)
+        bn_scratch = torch.empty_like(conv_out)
     if dw is None:
         dw = torch.empty_like(w)
     if dgamma is None:
@@ -288,6 +290,7 @@ def cbr_amp_bwd(g: ConvGeometry, dy, w, gamma, saved_mean, saved_inv_std, mask_b
     a.dw, a.dgamma, a.dbeta = dw.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr()
     a.conv_out, a.bn_scratch = conv_out.data_ptr(), bn_scratch.data_ptr()
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a.pool_argmax = None if pool_argmax is None else pool_argmax.data_ptr()
     if streams is None:
         s = (torch.cuda.current_stream() if stream is None else stream).cuda_stream
         a.stream_bn = a.stream_wgrad = a.stream_dgrad = s
@@ -340,6 +343,44 @@ def bn_apply_relu_mask(conv_out, eq_scale, eq_bias, relu_out=None, mask_bits=Non
     check(lib.trb200_bn_apply_relu_mask(_ptr(conv_out), _ptr(eq_scale), _ptr(eq_bias), _ptr(relu_out),
                                         _ptr(mask_bits), m, c, _stream(stream)))
     return relu_out, mask_bits
+
+
+def bn_apply_relu_mask_pool(conv_out, eq_scale, eq_bias, mask_bits=None, pool_out=None, argmax=None, relu_out=None,
+                            stream=None):
+    """BN apply + ReLU + mask + 2x2 max pool in one kernel; relu_out is written only if given."""
+    _need(conv_out, torch.float16, "conv_out", 4)
+    n, h, w, c = conv_out.shape
+    dev = conv_out.device
+    if mask_bits is None:
+        mask_bits = torch.empty(conv_out.numel() // 8, dtype=torch.uint8, device=dev)
+    if pool_out is None:
+        pool_out = torch.empty((n, h // 2, w // 2, c), dtype=torch.float16, device=dev)
+    if argmax is None:
+        argmax = torch.empty((n, h // 2, w // 2, c), dtype=torch.uint8, device=dev)
+    check(_lib.load().trb200_bn_apply_relu_mask_pool(_ptr(conv_out), _ptr(eq_scale), _ptr(eq_bias), _ptr(relu_out),
+                                                     _ptr(mask_bits), _ptr(pool_out), _ptr(argmax), n, h, w, c,
+                                                     _stream(stream)))
+    return pool_out, argmax, mask_bits
+
+
+def bnrelu_pool_bwd(dy_pooled, argmax, mask_bits, conv_out, gamma, saved_mean, saved_inv_std, dconv=None,
+                    workspace=None, stream=None):
+    """max-pool backward + BN/ReLU backward of the block in one pair of sweeps."""
+    lib = _lib.load()
+    _need(dy_pooled, torch.float16, "dy_pooled", 4)
+    _need(conv_out, torch.float16, "conv_out", 4)
+    n, h, w, c = conv_out.shape
+    if tuple(dy_pooled.shape) != (n, h // 2, w // 2, c):
+        raise ValueError("bnrelu_pool_bwd: dy_pooled must be [n, h/2, w/2, c]")
+    if dconv is None:
+        dconv = torch.empty_like(conv_out)
+    dgamma = torch.empty(c, dtype=torch.float32, device=conv_out.device)
+    dbeta = torch.empty(c, dtype=torch.float32, device=conv_out.device)
+    ws = (workspace or default_workspace()).ensure(lib.trb200_bnrelu_pool_bwd_workspace_bytes(n, h, w, c))
+    check(lib.trb200_bnrelu_pool_bwd(_ptr(dy_pooled), _ptr(argmax), _ptr(mask_bits), _ptr(conv_out), _ptr(gamma),
+                                     _ptr(saved_mean), _ptr(saved_inv_std), _ptr(dconv), _ptr(dgamma), _ptr(dbeta),
+                                     n, h, w, c, _ptr(ws), ws.numel(), _stream(stream)))
+    return dconv, dgamma, dbeta
 
 
 def maxpool2x2_fwd(x, y=None, argmax=None, stream=None):

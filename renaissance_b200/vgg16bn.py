@@ -5,9 +5,11 @@ reference's ``DeepLearningTask::run_train_epoch_gpu`` plays
 (src/task/deep_learning_task.cpp:1162-1217), reduced to what the benchmark needs:
 
     H2D (side stream, double buffered)                      TransferStation
-    forward : 13 x [conv -> BN stats/finalize -> BN apply + ReLU + mask], 5 max pools,
+    forward : 13 x [conv with BN statistics in its epilogue -> bn_finalize -> BN apply + ReLU + mask
+              (+ 2x2 max pool fused in for the 5 pooled blocks)],
               FC 25088-4096-4096-1000 with ReLU + dropout, softmax-CE
-    backward: softmax-CE, FC, 13 x CBR_AMP_BWD (first layer without dgrad), max pools
+    backward: softmax-CE, FC, 13 x CBR_AMP_BWD (first layer without dgrad; max-pool backward fused into
+              the BN stage of the pooled blocks)
     gradients: half -> float cast per ~25 MB bucket in backward order, NCCL all-reduce
               per bucket overlapped with the rest of backward, non-finite check,
               SGD with momentum on float master weights + half working copy
@@ -133,7 +135,8 @@ class Vgg16BnTrainer:
         for L in self.convs:
             e = (n, L.h, L.h, L.k)
             L.buf["conv_out"] = torch.empty(e, dtype=torch.float16, device=d)
-            L.buf["relu_out"] = torch.empty(e, dtype=torch.float16, device=d)
+            if not self._pool_after(L):
+                L.buf["relu_out"] = torch.empty(e, dtype=torch.float16, device=d)
             L.buf["mask"] = torch.empty(n * L.h * L.h * L.k // 8, dtype=torch.uint8, device=d)
             for nm in ("saved_mean", "saved_inv_std", "eq_scale", "eq_bias"):
                 L.buf[nm] = torch.empty(L.k, dtype=torch.float32, device=d)
@@ -159,6 +162,10 @@ class Vgg16BnTrainer:
         self.slot_free = [torch.cuda.Event(), torch.cuda.Event()]
         self.timing = None        # list of (start event, stop event, flop, bytes) per forward conv launch when enabled
         self.debug_hook = None    # called as hook(layer, dy, x) before every block backward (tests)
+
+    @staticmethod
+    def _pool_after(L):
+        return L.pool_after
 
     # ------------------------------------------------------------------ parameters
     def view(self, buf, slot: ParamSlot):
@@ -238,12 +245,15 @@ class Vgg16BnTrainer:
                 t1.record()
                 self.timing.append((t0, t1, 2.0 * n * L.h * L.h * L.c * L.k * 9,
                                     2.0 * (n * L.h * L.h * (L.c + L.k) + 9 * L.c * L.k)))
-            ops.bn_apply_relu_mask(b["conv_out"], b["eq_scale"], b["eq_bias"], relu_out=b["relu_out"],
-                                   mask_bits=b["mask"])
-            x = b["relu_out"]
             if L.pool_after:
-                ops.maxpool2x2_fwd(x, y=b["pool_out"], argmax=b["argmax"])
+                # the pool is fused into the BN-apply kernel: the full-resolution ReLU output is never stored
+                ops.bn_apply_relu_mask_pool(b["conv_out"], b["eq_scale"], b["eq_bias"], mask_bits=b["mask"],
+                                            pool_out=b["pool_out"], argmax=b["argmax"])
                 x = b["pool_out"]
+            else:
+                ops.bn_apply_relu_mask(b["conv_out"], b["eq_scale"], b["eq_bias"], relu_out=b["relu_out"],
+                                       mask_bits=b["mask"])
+                x = b["relu_out"]
         # classifier (cuBLAS): flatten is a view of the NHWC pool output
         a = x.reshape(n, -1)
         self.fc_in = [a]
@@ -289,9 +299,6 @@ class Vgg16BnTrainer:
         grad = dz.view(n, self.feat_hw, self.feat_hw, self.convs[-1].k)
         for L in reversed(self.convs):
             b = L.buf
-            if L.pool_after:
-                ops.maxpool2x2_bwd(grad, b["argmax"], b["relu_out"])      # d(relu_out) over relu_out
-                grad = b["relu_out"]
             x = images if L.idx == 0 else (self.convs[L.idx - 1].buf["pool_out"] if self.convs[L.idx - 1].pool_after
                                            else self.convs[L.idx - 1].buf["relu_out"])
             geo = ops.ConvGeometry(n, L.h, L.h, L.c, L.k)
@@ -301,7 +308,8 @@ class Vgg16BnTrainer:
                                   b["saved_mean"], b["saved_inv_std"], b["mask"], x, b["conv_out"],
                                   bn_scratch=self.bn_scratch[:b["conv_out"].numel()].view_as(b["conv_out"]),
                                   dw=self.view(self.g16, L.w), first_layer=(L.idx == 0), workspace=self.ws,
-                                  dgamma=self.view(self.g32, L.gamma), dbeta=self.view(self.g32, L.beta))
+                                  dgamma=self.view(self.g32, L.gamma), dbeta=self.view(self.g32, L.beta),
+                                  pool_argmax=b["argmax"] if L.pool_after else None)   # pool backward fused in
             grad = out["dx"]
             self.buckets.mark_ready(self._end_of(dict(w=L.w)))
         # BN gradients are float already and sit after every half-gradient slot

@@ -66,6 +66,29 @@ def test_block_backward_matches_golden(orc, name):
         assert rel_l2(host(out["dx"]).astype(np.float32), g["dx"]) < 2e-2
 
 
+def test_block_backward_with_fused_pool(orc):
+    """trb200_cbr_bwd with pool_argmax: dy is the gradient of the pooled output."""
+    from renaissance_b200 import ops
+    b = block_inputs(orc, 31, 2, 12, 12, 64, 64)
+    n, h, w, c = b["x"].shape
+    g = ops.ConvGeometry(n, h, w, c, 64)
+    relu = b["relu_out"]
+    _, am = orc.maxpool2x2_fwd(relu)
+    rng = np.random.default_rng(9)
+    dyp = rng.standard_normal((n, h // 2, w // 2, 64)).astype(np.float16)
+    dy_full = orc.maxpool2x2_bwd(dyp, am, relu.shape)
+    ref = orc.cbr_bwd_amp(dy_full, b["w"], b["gamma"], b["saved_mean"], b["saved_inv_std"], b["mask_bits"], b["x"],
+                          b["conv_out"])
+    xd = dev(b["x"])
+    out = ops.cbr_amp_bwd(g, dev(dyp), dev(b["w"]), dev(b["gamma"]), dev(b["saved_mean"]), dev(b["saved_inv_std"]),
+                          dev(b["mask_bits"]), xd, dev(b["conv_out"]), pool_argmax=dev(am),
+                          streams=ops.BlockStreams.create())
+    ops.device_status()
+    assert rel_max(host(out["dgamma"]), ref["dgamma"]) < 1e-4 and rel_max(host(out["dbeta"]), ref["dbeta"]) < 1e-4
+    assert rel_l2(host(out["dw"]).astype(np.float32), ref["dw"].astype(np.float32)) < 2e-3
+    assert rel_l2(host(out["dx"]).astype(np.float32), ref["dx"].astype(np.float32)) < 2e-3
+
+
 def test_block_backward_inside_cuda_graph(orc):
     """The reference replays the op from a captured CUDA graph after one warm-up call
     outside capture (src/graph/captured_graph.cpp:241-329).  Same discipline here:

@@ -91,6 +91,43 @@ def test_maxpool_matches_oracle(orc):
     assert np.array_equal(host(dx), orc.maxpool2x2_bwd(dy, am_ref, x.shape))
 
 
+@pytest.mark.parametrize("n,h,w,c", [(2, 8, 6, 16), (3, 14, 14, 64), (1, 4, 4, 520), (5, 28, 28, 256)])
+def test_pool_fused_into_block_forward_and_backward(orc, n, h, w, c):
+    """The 2x2 max pool fused into the block's BN kernels: forward equals bn_apply_relu_mask followed
+    by maxpool2x2_fwd bit for bit; backward equals maxpool2x2_bwd followed by the BN+ReLU backward
+    (oracle) to the usual tolerances."""
+    from renaissance_b200 import ops
+    rng = np.random.default_rng(n * 3 + c)
+    co = (rng.standard_normal((n, h, w, c)) * 1.2 + 0.1).astype(np.float16)
+    co[0, :2, :2, :8] = 0.5                                   # ties inside a window: first maximum must win
+    gamma = (1 + 0.2 * rng.standard_normal(c)).astype(np.float32)
+    cf = co.astype(np.float32).reshape(-1, c)
+    mean = cf.mean(axis=0).astype(np.float32)
+    inv = (1.0 / np.sqrt(cf.var(axis=0) + 1e-5)).astype(np.float32)
+    es = (gamma * inv).astype(np.float32)
+    eb = (0.1 - mean * es).astype(np.float32)
+    cod, esd, ebd = dev(co), dev(es), dev(eb)
+    relu, bits = ops.bn_apply_relu_mask(cod, esd, ebd)
+    pool_ref, am_ref = ops.maxpool2x2_fwd(relu)
+    pool, am, bits2 = ops.bn_apply_relu_mask_pool(cod, esd, ebd)
+    torch.cuda.synchronize()
+    assert torch.equal(bits, bits2) and torch.equal(pool, pool_ref) and torch.equal(am, am_ref)
+    # optional full-resolution output
+    relu2 = torch.empty_like(relu)
+    ops.bn_apply_relu_mask_pool(cod, esd, ebd, relu_out=relu2)
+    assert torch.equal(relu2, relu)
+    # backward
+    dyp = rng.standard_normal((n, h // 2, w // 2, c)).astype(np.float16)
+    dy_full = orc.maxpool2x2_bwd(dyp, host(am), co.shape)
+    ref_dx, ref_dg, ref_db = orc.bnrelu_bwd_amp(dy_full, host(bits), co, gamma, mean, inv)
+    dconv, dg, db = ops.bnrelu_pool_bwd(dev(dyp), am, bits, cod, dev(gamma), dev(mean), dev(inv))
+    torch.cuda.synchronize()
+    assert rel_max(host(dg), ref_dg) < 1e-4 and rel_max(host(db), ref_db) < 1e-4
+    assert rel_l2(host(dconv).astype(np.float32), ref_dx.astype(np.float32)) < 2e-3
+    d2, dg2, db2 = ops.bnrelu_pool_bwd(dev(dyp), am, bits, cod, dev(gamma), dev(mean), dev(inv))
+    assert torch.equal(dg, dg2) and torch.equal(db, db2) and torch.equal(dconv, d2)      # reproducible
+
+
 def test_sgd_momentum_and_nonfinite_guard(orc):
     from renaissance_b200 import ops
     rng = np.random.default_rng(6)
@@ -145,7 +182,10 @@ def test_whole_step_matches_oracle(orc):
 
     def hook(L, dy, x):
         b = L.buf
-        grabbed[L.idx] = dict(dy=host(dy).copy(), x=host(x).copy(), conv_out=host(b["conv_out"]).copy(),
+        dy_h = host(dy).copy()
+        if L.pool_after:        # the driver hands the pooled gradient + argmax to the block: unpool for the oracle
+            dy_h = orc.maxpool2x2_bwd(dy_h, host(b["argmax"]), tuple(b["conv_out"].shape))
+        grabbed[L.idx] = dict(dy=dy_h, x=host(x).copy(), conv_out=host(b["conv_out"]).copy(),
                               mask=host(b["mask"]).copy(), mean=host(b["saved_mean"]).copy(),
                               inv=host(b["saved_inv_std"]).copy())
 
