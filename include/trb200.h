@@ -190,8 +190,7 @@ typedef struct trb200_cbr_bwd_args {
     float* dgamma;             /* out [2]                                           */
     float* dbeta;              /* out [3]                                           */
     void* conv_out;            /* out [4] conv output saved by the forward: read by
-                                  the BN stage; the first-layer variant with c == 4
-                                  then overwrites it (scratch for the weight gradient) */
+                                  the BN stage                                       */
     void* bn_scratch;          /* out [5] activation-sized scratch: receives dconv  */
     void* workspace;
     size_t workspace_bytes;

@@ -13,16 +13,12 @@ int dgrad_direct(const trb200_conv_desc& d, const void* dy, const void* w, void*
 
 // tcgen05 / TMEM implicit-GEMM kernels (conv_igemm_sm100.cu): 3x3, stride 1,
 // pad 1, channel counts that are multiples of 64; plus the 4-input-channel first
-// layer (as a 1x1 convolution over an im2col buffer).
+// layer (as a 1x1 convolution over 3x3 neighbourhoods built in shared memory).
 bool igemm_supports(const trb200_conv_desc& d, int which);   // 0 wgrad, 1 dgrad, 2 fprop
 bool igemm_small_c(const trb200_conv_desc& d);
 size_t igemm_wgrad_workspace(const trb200_conv_desc& d);
 size_t igemm_dgrad_workspace(const trb200_conv_desc& d);
 size_t igemm_fprop_workspace(const trb200_conv_desc& d);
-size_t igemm_im2col_bytes(const trb200_conv_desc& d);
-size_t igemm_wgrad_small_c_workspace(const trb200_conv_desc& d);
-int igemm_wgrad_small_c(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* xp, bool xp_ready,
-                        void* ws, size_t ws_bytes, cudaStream_t st);
 size_t igemm_fprop_stats_bytes(const trb200_conv_desc& d);
 int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, void* ws, size_t ws_bytes,
                 cudaStream_t st, float* stats_partial = nullptr, int* stats_strips = nullptr);

@@ -173,9 +173,7 @@ BlockWs block_ws(const trb200_conv_desc& d, bool first_layer) {
         if (pooled > b.bn_bytes) b.bn_bytes = pooled;
     }
     b.wg_off = (size_t)trb::align_up((int64_t)b.bn_bytes, 256);
-    // first layer with 4 input channels: the conv_out buffer doubles as the im2col scratch
-    b.wg_bytes = (use_igemm(d, 0) && trb::igemm_small_c(d)) ? trb::igemm_wgrad_small_c_workspace(d)
-                                                           : trb200_conv_wgrad_workspace_bytes(&d);
+    b.wg_bytes = trb200_conv_wgrad_workspace_bytes(&d);
     b.dg_off = b.wg_off + (size_t)trb::align_up((int64_t)b.wg_bytes, 256);
     b.dg_bytes = first_layer ? 0 : trb200_conv_dgrad_workspace_bytes(&d);
     b.total = b.dg_off + (size_t)trb::align_up((int64_t)b.dg_bytes, 256);
@@ -225,13 +223,7 @@ extern "C" int trb200_cbr_bwd(const trb200_cbr_bwd_args* a) {
 
     // 2) wgrad(dconv, x) -> dw
     if (s_wg != s_bn) TRB_CUDA_TRY(cudaStreamWaitEvent(s_wg, trb::as_event(a->ev_bn), 0));
-    if (use_igemm(d, 0) && trb::igemm_small_c(d)) {
-        // conv_out is dead once stage 1 has read it: it receives the 3x3 neighbourhoods of x
-        rc = trb::igemm_wgrad_small_c(d, a->bn_scratch, a->x, a->dw, a->conv_out, false, wsp + ws.wg_off, ws.wg_bytes,
-                                      s_wg);
-    } else {
-        rc = trb200_conv_wgrad(&d, a->bn_scratch, a->x, a->dw, wsp + ws.wg_off, ws.wg_bytes, s_wg);
-    }
+    rc = trb200_conv_wgrad(&d, a->bn_scratch, a->x, a->dw, wsp + ws.wg_off, ws.wg_bytes, s_wg);
     if (rc) return rc;
     if (a->ev_wgrad) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_wgrad), s_wg));
 

@@ -63,7 +63,15 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kThreads = 256;      // warp 0: TMA producer A, 1: MMA, 2 (and 3): TMA producer B, 4-7: epilogue
+constexpr int kThreads = 256;
+// IM2COL kernels add 256 builder threads (warps 8-15).  One global-load round trip per stage is
+// longer than the MMAs of a stage, so the builders work in groups that take stages in turn.
+constexpr int kBuilderThreads = 256;
+// The builders' source is a ring of raw image tiles (the tile's pixels plus a halo, 8 bytes per
+// pixel) that a TMA producer keeps filled several tiles ahead; shapes whose halo tile does not
+// fit a ring slot, or whose width is odd, are read with plain global loads instead.
+constexpr int kRawStages = 8;
+constexpr int kRawStageBytes = 4096;      // warp 0: TMA producer A, 1: MMA, 2 (and 3): TMA producer B, 4-7: epilogue
 constexpr int kEpiThreads = 128;
 constexpr int kATileBytes = 128 * 128;    // 128 pixels x 64 halfs
 constexpr int kStageTileBytes = 64 * 128; // wgrad: 64 pixels x 64 halfs
@@ -148,6 +156,29 @@ int make_act_tmap(CUtensorMap* m, const void* base, int n, int h, int w, int c, 
     return make_tmap(m, base, 4, dims, str, box, what);
 }
 
+// 4-channel half image [n,h,w] of 8-byte pixels viewed as (w, h, n) with a {bw + 4, bh + 2, bn} box,
+// no swizzle.  The box starts two pixels left of the tile so that its first byte is 16-byte aligned.
+int make_raw_x4_tmap(CUtensorMap* m, const void* base, int n, int h, int w, const TileShape& t) {
+    EncodeTiledFn fn = encode_fn();
+    TRB_REQUIRE(fn, TRB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t gdim[3] = {(cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
+    const cuuint64_t gstr[2] = {(cuuint64_t)w * 8, (cuuint64_t)h * w * 8};
+    const cuuint32_t bx[3] = {(cuuint32_t)t.bw + 4, (cuuint32_t)t.bh + 2, (cuuint32_t)t.bn};
+    const cuuint32_t es[3] = {1, 1, 1};
+    const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void*>(base), gdim, gstr, bx, es,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TRB_REQUIRE(r == CUDA_SUCCESS, TRB200_ERR_CUDA, "cuTensorMapEncodeTiled(4-channel image) failed with CUresult %d",
+                (int)r);
+    return TRB200_OK;
+}
+
+// whether the halo tile of shape t can go through the raw ring
+bool raw_ring_fits(const TileShape& t, int w, const void* x4) {
+    return (w % 2 == 0) && t.bw >= 2 && (t.bw + 4) * (t.bh + 2) * t.bn * 8 <= kRawStageBytes &&
+           (reinterpret_cast<uintptr_t>(x4) & 15u) == 0;
+}
+
 // ------------------------------------------------------------------ shared helpers
 __device__ __forceinline__ void abort_drain(volatile int* abort_flag) {
     // after a failed wait: give copies already in flight time to land before the
@@ -156,6 +187,61 @@ __device__ __forceinline__ void abort_drain(volatile int* abort_flag) {
         const unsigned long long t0 = global_ns();
         while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
+}
+
+// First layer (4 input channels): the 3x3 neighbourhood of a pixel is 36 halfs, written as one
+// 128-byte operand row (9 taps x 8 bytes + zeros) straight into the swizzled shared-memory
+// tile, so that the im2col matrix never exists in HBM.  `row` is the row's index in the tile
+// (it decides the swizzle phase), (y, x, img) the pixel; a pixel outside the image gives zeros.
+__device__ __forceinline__ void store_im2col_row_c4(const uint2 (&t)[10], uint32_t tile, int row) {
+    const uint32_t row_addr = tile + (uint32_t)row * 128u;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint2 a = j < 5 ? t[2 * j] : make_uint2(0u, 0u);
+        const uint2 b = j < 5 ? t[2 * j + 1] : make_uint2(0u, 0u);
+        const uint32_t dst = row_addr + (uint32_t)((j ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(a.x), "r"(a.y), "r"(b.x), "r"(b.y)
+                     : "memory");
+    }
+}
+
+__device__ __forceinline__ void load_neighbourhood_global(uint2 (&t)[10], const uint2* __restrict__ x4, int img, int y,
+                                                          int x, int ext_n, int ext_h, int ext_w) {
+#pragma unroll
+    for (int k = 0; k < 10; ++k) t[k] = make_uint2(0u, 0u);
+    if (img < ext_n && y < ext_h && x < ext_w) {
+        const uint2* base = x4 + ((int64_t)img * ext_h) * ext_w;
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            const int yy = y + r - 1;
+            if (yy < 0 || yy >= ext_h) continue;
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                const int xx = x + c - 1;
+                if (xx >= 0 && xx < ext_w) t[r * 3 + c] = __ldg(base + (int64_t)yy * ext_w + xx);
+            }
+        }
+    }
+}
+
+// `centre` = shared-memory address of the pixel in a raw halo tile whose rows are `pitch` pixels long;
+// pixels outside the image were zero-filled by the copy
+__device__ __forceinline__ void load_neighbourhood_raw(uint2 (&t)[10], uint32_t centre, int pitch) {
+    t[9] = make_uint2(0u, 0u);
+#pragma unroll
+    for (int r = 0; r < 3; ++r)
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+            const uint32_t a = centre + (uint32_t)(((r - 1) * pitch + (c - 1)) * 8);
+            asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(t[r * 3 + c].x), "=r"(t[r * 3 + c].y) : "r"(a));
+        }
+}
+
+__device__ __forceinline__ void build_im2col_row_c4(const uint2* __restrict__ x4, uint32_t tile, int row, int img,
+                                                    int y, int x, int ext_n, int ext_h, int ext_w) {
+    uint2 t[10];
+    load_neighbourhood_global(t, x4, img, y, x, ext_n, ext_h, ext_w);
+    store_im2col_row_c4(t, tile, row);
 }
 
 // ------------------------------------------------------------------ dgrad / fprop kernel
@@ -169,27 +255,31 @@ struct FpropParams {
     int bw, bh, bn;
     int b_tap_is_dim1;   // 1: filter view dims (ci, tap, co) [KRSC as is]; 0: (ci, co, tap)
     // batch statistics of the output (STATS kernels only)
-    float* stats_partial;   // [strip][2][cout], strip = (block / n_tiles) * 2 + row half
+    const uint2* x4;        // IM2COL kernels: the 4-channel input image [n,h,w] of 8-byte pixels
+    int raw_ring;           // IM2COL kernels: tm_in describes x4 and halo tiles go through the raw ring
+    float* stats_partial;   // [strip][2][cout], strip = block / n_tiles
     int cout;
     int lbw, lbh;           // log2 of bw, bh
     int ext_w, ext_h, ext_n;   // image extents: rows of a tile beyond them are padding
     int has_padding;        // some tile hangs over an image edge
 };
 
-template <int NT>
+template <int NT, bool IM2COL = false>
 struct FpropSmem {
     static constexpr int kBTileBytes = NT * 128;
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     static constexpr int kEpiBytes = 2 * kATileBytes;
-    static constexpr int kStages = (kSmemBudget - 2048 - kEpiBytes) / kStageBytes;
-    static constexpr int kTotal = kStages * kStageBytes + kEpiBytes + 2048;   // + alignment slack and barriers
+    static constexpr int kRawBytes = IM2COL ? kRawStages * kRawStageBytes : 0;
+    static constexpr int kStages = (kSmemBudget - 2048 - kEpiBytes - kRawBytes) / kStageBytes;
+    static constexpr int kTotal = kStages * kStageBytes + kEpiBytes + kRawBytes + 2048;   // + alignment slack and barriers
 };
 
-template <int NT, bool STATS>
-__global__ void __launch_bounds__(kThreads, 1)
+// IM2COL: 8 more warps (two groups of 128 threads) build the A tiles from the 4-channel image instead of TMA.
+template <int NT, bool STATS, bool IM2COL>
+__global__ void __launch_bounds__(IM2COL ? kThreads + kBuilderThreads : kThreads, 1)
 conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_w,
                      const __grid_constant__ CUtensorMap tm_out, const FpropParams p, int* status) {
-    using L = FpropSmem<NT>;
+    using L = FpropSmem<NT, IM2COL>;
     constexpr int kStages = L::kStages;
     constexpr uint32_t kTmemCols = 2 * NT;
     extern __shared__ unsigned char smem_dyn[];
@@ -198,11 +288,14 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
     const uint32_t a_base = base;
     const uint32_t b_base = base + kStages * kATileBytes;
     const uint32_t epi_base = b_base + kStages * L::kBTileBytes;
-    const uint32_t bar_base = epi_base + L::kEpiBytes;
-    // barriers: full[kStages] (2 producers), empty[kStages], tmem_full[2], tmem_empty[2]
+    const uint32_t raw_base = epi_base + L::kEpiBytes;
+    const uint32_t bar_base = raw_base + L::kRawBytes;
+    // barriers: full[kStages] (2 producers), empty[kStages], tmem_full[2], tmem_empty[2],
+    // raw_full[kRawStages], raw_empty[kRawStages]
     const uint32_t full0 = bar_base, empty0 = bar_base + 8u * kStages;
     auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
     auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+    const uint32_t rfull0 = bar_base + 8u * (2 * kStages + 4), rempty0 = rfull0 + 8u * kRawStages;
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     __shared__ int s_epi_fail;
@@ -212,10 +305,13 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
     if (threadIdx.x == 0) {
         s_abort = 0;
         s_epi_fail = 0;
-        for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8u * s, 2); mbar_init(empty0 + 8u * s, 1); }
+        // a stage is full once its B tile has landed and its A tile has (one TMA box, or 128 built rows)
+        for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8u * s, IM2COL ? 129 : 2); mbar_init(empty0 + 8u * s, 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), kEpiThreads); }
+        if (IM2COL)
+            for (int s = 0; s < kRawStages; ++s) { mbar_init(rfull0 + 8u * s, 1); mbar_init(rempty0 + 8u * s, 128); }
         fence_barrier_init();
-        prefetch_tmap(&tm_in);
+        if (!IM2COL || p.raw_ring) prefetch_tmap(&tm_in);
         prefetch_tmap(&tm_w);
         prefetch_tmap(&tm_out);
     }
@@ -241,7 +337,55 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
     // only the instructions that must come from one thread are predicated on lane 0: the
     // compiler can then keep addresses, coordinates and descriptors in uniform registers,
     // which is where the TMA and MMA instructions take them from.
-    if (warp == 0) {
+    if (IM2COL && warp >= 8) {
+        // A-tile builders: thread = one pixel row of the tile, one K step (= one stage) per tile;
+        // group g takes the block's tiles g, g + 2, ...
+        constexpr int kGroups = kBuilderThreads / 128;
+        const int row = (threadIdx.x - kThreads) & 127, group = (threadIdx.x - kThreads) >> 7;
+        const int bx = row & (p.bw - 1), by = (row >> p.lbw) & (p.bh - 1), bi = row >> (p.lbw + p.lbh);
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+            if (it % kGroups != group) continue;
+            const uint32_t stage = (uint32_t)(it % kStages), phase = (uint32_t)((it / kStages) & 1);
+            uint2 t[10];
+            if (p.raw_ring) {
+                const uint32_t rs = (uint32_t)(it % kRawStages), rphase = (uint32_t)((it / kRawStages) & 1);
+                const int pitch = p.bw + 4;
+                if (!mbar_wait(rfull0 + 8u * rs, rphase, abort_flag, status, kStatusProducerTimeout)) break;
+                load_neighbourhood_raw(t, raw_base + rs * kRawStageBytes +
+                                              (uint32_t)((((bi * (p.bh + 2)) + by + 1) * pitch + bx + 2) * 8), pitch);
+                if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                store_im2col_row_c4(t, a_base + stage * kATileBytes, row);
+                mbar_arrive(rempty0 + 8u * rs);   // after the stores: the loads above have all returned
+            } else {
+                const int mt = tile / p.n_tiles;
+                const int w0 = (mt % p.tw) * p.bw, h0 = ((mt / p.tw) % p.th) * p.bh;
+                const int n0 = (mt / (p.tw * p.th)) * p.bn;
+                load_neighbourhood_global(t, p.x4, n0 + bi, h0 + by, w0 + bx, p.ext_n, p.ext_h, p.ext_w);
+                if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                store_im2col_row_c4(t, a_base + stage * kATileBytes, row);
+            }
+            fence_proxy_async_smem();             // generic-proxy stores -> visible to the MMA's async proxy
+            mbar_arrive(full0 + 8u * stage);
+        }
+    } else if (IM2COL && warp == 0) {
+        if (p.raw_ring) {                                  // raw producer: the tile's pixels plus halo, one box per tile
+            const uint32_t raw_bytes = (uint32_t)((p.bw + 4) * (p.bh + 2) * p.bn * 8);
+            uint32_t rs = 0, rphase = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                const int mt = tile / p.n_tiles;
+                const int w0 = (mt % p.tw) * p.bw, h0 = ((mt / p.tw) % p.th) * p.bh;
+                const int n0 = (mt / (p.tw * p.th)) * p.bn;
+                if (!mbar_wait(rempty0 + 8u * rs, rphase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                if (lane == 0) {
+                    mbar_expect_tx(rfull0 + 8u * rs, raw_bytes);
+                    tma_load_3d(raw_base + rs * kRawStageBytes, &tm_in, rfull0 + 8u * rs, w0 - 2, h0 - 1, n0);
+                }
+                __syncwarp();
+                if (++rs == kRawStages) { rs = 0; rphase ^= 1u; }
+            }
+        }
+    } else if (warp == 0 && !IM2COL) {
         {                                                  // producer A: one shifted activation box per K step
             uint32_t stage = 0, phase = 0;
             bool ok = true;
@@ -338,19 +482,22 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
             RT_ADD(2);
             if (lane == 0) RT_STORE(1);
         }
-    } else if (warp >= 4) {
+    } else if (warp >= 4 && warp < 8) {
         // epilogue: warp w may touch TMEM lanes [32*(w%4), +32)
         const int q = warp & 3;
         const int row = q * 32 + lane;             // pixel of the tile = TMEM lane
         const bool leader = threadIdx.x == 128;    // first epilogue thread issues the TMA stores
         int iter = 0;
         int chunk_count = 0;
-        // STATS: thread (column c, row half hsel) adds its column of every 64-channel chunk over
-        // 64 rows of the half-rounded tile in shared memory; sums run over all tiles of this block
-        const int st_c = (threadIdx.x - 128) & 63, st_h = (threadIdx.x - 128) >> 6;
-        float run_s[NT / 64], run_q[NT / 64];
+        // STATS: thread (16-byte column st_cc, row group st_rg) adds its 8 channels of every 64-channel
+        // chunk over 8 rows of the half-rounded tile in shared memory; the sums run over all tiles of
+        // this block and meet once, in row-group order, when the block is done
+        const int st_cc = (threadIdx.x - 128) & 7, st_rg = (threadIdx.x - 128) >> 3;
+        float run_s[NT / 64][8], run_q[NT / 64][8];
 #pragma unroll
-        for (int i = 0; i < NT / 64; ++i) { run_s[i] = 0.f; run_q[i] = 0.f; }
+        for (int i = 0; i < NT / 64; ++i)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { run_s[i][e] = 0.f; run_q[i][e] = 0.f; }
         RT_DECL;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
             const int acc = iter & 1;
@@ -372,8 +519,8 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
             RT_ADD(0);
             if (*(volatile int*)&s_epi_fail) break;
             tc_fence_after();
-            uint32_t vm0 = 0xffffffffu, vm1 = 0xffffffffu;
-            if (STATS && p.has_padding) { vm0 = s_valid[st_h * 2]; vm1 = s_valid[st_h * 2 + 1]; }
+            uint32_t vm = 0xffu;      // which of this thread's 8 rows are real pixels
+            if (STATS && p.has_padding) vm = (s_valid[st_rg >> 2] >> ((st_rg & 3) * 8)) & 0xffu;
 #pragma unroll
             for (int chunk = 0; chunk < NT / 64; ++chunk, ++chunk_count) {
                 const uint32_t buf = epi_base + (uint32_t)(chunk_count & 1) * kATileBytes;
@@ -410,37 +557,62 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
                     tma_store_commit();
                 }
                 if (STATS) {
-                    float s1 = 0.f, s2 = 0.f;
-                    const uint32_t col_off = (uint32_t)(st_c & 7) * 2u;
-#pragma unroll 8
-                    for (int i = 0; i < 64; ++i) {
-                        const int r = st_h * 64 + i;
-                        const uint32_t addr = buf + (uint32_t)r * 128u + (uint32_t)(((st_c >> 3) ^ (r & 7)) << 4) + col_off;
-                        unsigned short hv;
-                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(hv) : "r"(addr));
-                        float f = __half2float(__ushort_as_half(hv));
-                        if (!(((i < 32 ? vm0 : vm1) >> (i & 31)) & 1u)) f = 0.f;
-                        s1 += f;
-                        s2 = fmaf(f, f, s2);
+                    RT_ADD(2);
+                    const uint32_t rows0 = buf + (uint32_t)(st_rg * 8) * 128u;
+                    uint32_t hw[8][4];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)          // row st_rg * 8 + i: its swizzle phase is i
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(hw[i][0]), "=r"(hw[i][1]), "=r"(hw[i][2]), "=r"(hw[i][3])
+                                     : "r"(rows0 + (uint32_t)i * 128u + (uint32_t)((st_cc ^ i) << 4)));
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const bool real = (vm >> i) & 1u;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[i][e]));
+                            if (!real) f = make_float2(0.f, 0.f);
+                            run_s[chunk][2 * e] += f.x;
+                            run_s[chunk][2 * e + 1] += f.y;
+                            run_q[chunk][2 * e] = fmaf(f.x, f.x, run_q[chunk][2 * e]);
+                            run_q[chunk][2 * e + 1] = fmaf(f.y, f.y, run_q[chunk][2 * e + 1]);
+                        }
                     }
-                    run_s[chunk] += s1;
-                    run_q[chunk] += s2;
+                    RT_ADD(3);
                 }
             }
             tc_fence_before();
             mbar_arrive(tempty_bar(acc));
         }
-        if (STATS) {
-            // this block only ever sees one N tile (the grid is a multiple of n_tiles)
-            const int strip = (blockIdx.x / p.n_tiles) * 2 + st_h;
-            const int ch0 = (blockIdx.x % p.n_tiles) * NT + st_c;
+        if (leader) tma_store_wait_all();
+        if (STATS && !*(volatile int*)&s_epi_fail) {
+            // the 16 row groups meet through the (now idle) output staging buffers: red[rg][sum | sumsq][NT]
+            named_barrier(1, kEpiThreads);
+            float* red = reinterpret_cast<float*>(smem_dyn + (epi_base - smem_u32(smem_dyn)));
 #pragma unroll
             for (int i = 0; i < NT / 64; ++i) {
-                p.stats_partial[((size_t)strip * 2) * p.cout + ch0 + i * 64] = run_s[i];
-                p.stats_partial[((size_t)strip * 2 + 1) * p.cout + ch0 + i * 64] = run_q[i];
+                float4* ds = reinterpret_cast<float4*>(red + (st_rg * 2) * NT + i * 64 + st_cc * 8);
+                float4* dq = reinterpret_cast<float4*>(red + (st_rg * 2 + 1) * NT + i * 64 + st_cc * 8);
+                ds[0] = make_float4(run_s[i][0], run_s[i][1], run_s[i][2], run_s[i][3]);
+                ds[1] = make_float4(run_s[i][4], run_s[i][5], run_s[i][6], run_s[i][7]);
+                dq[0] = make_float4(run_q[i][0], run_q[i][1], run_q[i][2], run_q[i][3]);
+                dq[1] = make_float4(run_q[i][4], run_q[i][5], run_q[i][6], run_q[i][7]);
+            }
+            named_barrier(1, kEpiThreads);
+            // this block only ever sees one N tile (the grid is a multiple of n_tiles)
+            const int strip = blockIdx.x / p.n_tiles;
+            const int ch0 = (blockIdx.x % p.n_tiles) * NT;
+            for (int ch = threadIdx.x - 128; ch < NT; ch += kEpiThreads) {
+                float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+                for (int g = 0; g < 16; ++g) {
+                    s1 += red[(g * 2) * NT + ch];
+                    s2 += red[(g * 2 + 1) * NT + ch];
+                }
+                p.stats_partial[((size_t)strip * 2) * p.cout + ch0 + ch] = s1;
+                p.stats_partial[((size_t)strip * 2 + 1) * p.cout + ch0 + ch] = s2;
             }
         }
-        if (leader) tma_store_wait_all();
         RT_ADD(2);
         if (leader) RT_STORE(2);
     }
@@ -473,24 +645,35 @@ int conv3x3_grid(int m_tiles, int n_tiles) {
     return grid;
 }
 
-template <int NT, bool STATS>
+template <int NT, bool STATS, bool IM2COL>
 int launch_conv3x3(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensorMap& tout, const FpropParams& p,
                    cudaStream_t st) {
-    using L = FpropSmem<NT>;
+    using L = FpropSmem<NT, IM2COL>;
     static bool attr_done[64] = {false};
     int dev = 0;
     TRB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        TRB_CUDA_TRY(cudaFuncSetAttribute(conv3x3_igemm_kernel<NT, STATS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          L::kTotal));
+        TRB_CUDA_TRY(cudaFuncSetAttribute(conv3x3_igemm_kernel<NT, STATS, IM2COL>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
         attr_done[dev] = true;
     }
     int* status = nullptr;
     TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status));
     const int grid = conv3x3_grid(p.m_tiles, p.n_tiles);
-    conv3x3_igemm_kernel<NT, STATS><<<grid, kThreads, L::kTotal, st>>>(tin, tw, tout, p, status);
+    conv3x3_igemm_kernel<NT, STATS, IM2COL><<<grid, IM2COL ? kThreads + kBuilderThreads : kThreads, L::kTotal, st>>>(tin, tw, tout,
+                                                                                                       p, status);
     TRB_LAUNCH_CHECK("conv3x3_igemm_kernel");
     return TRB200_OK;
+}
+
+template <int NT>
+int launch_conv3x3_any(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensorMap& tout, const FpropParams& p,
+                       cudaStream_t st) {
+    const bool stats = p.stats_partial != nullptr, im2col = p.x4 != nullptr;
+    if (stats && im2col) return launch_conv3x3<NT, true, true>(tin, tw, tout, p, st);
+    if (stats) return launch_conv3x3<NT, true, false>(tin, tw, tout, p, st);
+    if (im2col) return launch_conv3x3<NT, false, true>(tin, tw, tout, p, st);
+    return launch_conv3x3<NT, false, false>(tin, tw, tout, p, st);
 }
 
 int pick_nt(int cout) {
@@ -503,16 +686,22 @@ int pick_nt(int cout) {
 // in: [n,h,w,cin] half; filter view described by (wv, tap_is_dim1); out: [n,h,w,cout] half.
 // stats_partial != nullptr: also leave per-strip sums / sums of squares of the (half) output there and report
 // the number of strips through *stats_strips.
+// x4 != nullptr: `in` is ignored, the A tiles are built in the kernel from the 4-channel image x4 (taps must be 1,
+// cin 64: the 36 neighbourhood values + 28 zeros).
 int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int n, int h, int w, int cin, int cout,
-                cudaStream_t st, int taps = 9, float* stats_partial = nullptr, int* stats_strips = nullptr) {
+                cudaStream_t st, int taps = 9, float* stats_partial = nullptr, int* stats_strips = nullptr,
+                const void* x4 = nullptr) {
     const int nt = pick_nt(cout);
     TRB_REQUIRE(nt != 0 && cin % 64 == 0, TRB200_ERR_UNSUPPORTED, "conv3x3 igemm: cin=%d cout=%d not covered", cin,
                 cout);
     const TileShape t = pick_tile(n, h, w, 128);
     CUtensorMap tin, tw, tout;
-    int rc = make_act_tmap(&tin, in, n, h, w, cin, t, "conv input");
+    int rc = make_act_tmap(&tout, out, n, h, w, cout, t, "conv output");
     if (rc) return rc;
-    rc = make_act_tmap(&tout, out, n, h, w, cout, t, "conv output");
+    const bool raw_ring = x4 && raw_ring_fits(t, w, x4);
+    if (raw_ring) rc = make_raw_x4_tmap(&tin, x4, n, h, w, t);
+    else if (x4) tin = tout;      // not used by the kernel
+    else rc = make_act_tmap(&tin, in, n, h, w, cin, t, "conv input");
     if (rc) return rc;
     if (tap_is_dim1) {
         // KRSC as stored: (ci, tap, co)
@@ -537,25 +726,22 @@ int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int 
     p.bw = t.bw; p.bh = t.bh; p.bn = t.bn;
     p.b_tap_is_dim1 = tap_is_dim1;
     p.stats_partial = stats_partial;
+    p.x4 = static_cast<const uint2*>(x4);
+    p.raw_ring = raw_ring ? 1 : 0;
     p.cout = cout;
     p.lbw = 0; p.lbh = 0;
     while ((1 << p.lbw) < t.bw) ++p.lbw;
     while ((1 << p.lbh) < t.bh) ++p.lbh;
     p.ext_w = w; p.ext_h = h; p.ext_n = n;
     p.has_padding = (t.tw * t.bw != w) || (t.th * t.bh != h) || (t.tn * t.bn != n);
-    if (stats_partial) {
-        if (stats_strips) *stats_strips = conv3x3_grid(p.m_tiles, p.n_tiles) / p.n_tiles * 2;
-        if (nt == 256) return launch_conv3x3<256, true>(tin, tw, tout, p, st);
-        if (nt == 128) return launch_conv3x3<128, true>(tin, tw, tout, p, st);
-        return launch_conv3x3<64, true>(tin, tw, tout, p, st);
-    }
-    if (nt == 256) return launch_conv3x3<256, false>(tin, tw, tout, p, st);
-    if (nt == 128) return launch_conv3x3<128, false>(tin, tw, tout, p, st);
-    return launch_conv3x3<64, false>(tin, tw, tout, p, st);
+    if (stats_partial && stats_strips) *stats_strips = conv3x3_grid(p.m_tiles, p.n_tiles) / p.n_tiles;
+    if (nt == 256) return launch_conv3x3_any<256>(tin, tw, tout, p, st);
+    if (nt == 128) return launch_conv3x3_any<128>(tin, tw, tout, p, st);
+    return launch_conv3x3_any<64>(tin, tw, tout, p, st);
 }
 
 // upper bound of the strips the STATS kernels write for an output of `cout` channels
-int conv3x3_stats_max_strips() { return sm_count() * 2; }
+int conv3x3_stats_max_strips() { return sm_count(); }
 
 // ------------------------------------------------------------------ wgrad kernel
 struct WgradParams {
@@ -569,23 +755,29 @@ struct WgradParams {
     int pix_tiles;      // tw * th * tn
     int tw, th;
     int bw, bh, bn;
+    const uint2* x4;    // IM2COL kernels: the 4-channel input image; A tiles are built in the kernel
+    int raw_ring;       // IM2COL kernels: tm_x describes x4 and halo tiles go through the raw ring
+    int lbw, lbh;       // log2 of bw, bh
+    int ext_w, ext_h, ext_n;
 };
 
-template <int NT>
+template <int NT, bool IM2COL = false>
 struct WgradSmem {
     static constexpr int kABytes = 2 * kStageTileBytes;            // two units
     static constexpr int kBBytes = (NT / 64) * kStageTileBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStagesRaw = (kSmemBudget - 2048) / kStageBytes;
+    static constexpr int kRawBytes = IM2COL ? kRawStages * kRawStageBytes : 0;
+    static constexpr int kStagesRaw = (kSmemBudget - 2048 - kRawBytes) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-    static constexpr int kTotal = kStages * kStageBytes + 2048;
+    static constexpr int kTotal = kStages * kStageBytes + kRawBytes + 2048;
 };
 
-template <int NT>
-__global__ void __launch_bounds__(kThreads, 1)
+// IM2COL: 8 more warps (four groups of 64 threads) build the A tiles (one unit, written twice) from the 4-channel image.
+template <int NT, bool IM2COL>
+__global__ void __launch_bounds__(IM2COL ? kThreads + kBuilderThreads : kThreads, 1)
 wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
                    float* __restrict__ partial, const WgradParams p, int* status) {
-    using L = WgradSmem<NT>;
+    using L = WgradSmem<NT, IM2COL>;
     constexpr int kStages = L::kStages;
     constexpr int kBBlocks = NT / 64;                       // 64-channel boxes of dy per stage
     constexpr int kBProducers = kBBlocks >= 2 ? 2 : 1;
@@ -594,19 +786,26 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     const uint32_t a_base = base;
     const uint32_t b_base = base + kStages * L::kABytes;
-    const uint32_t bar_base = b_base + kStages * L::kBBytes;
+    const uint32_t raw_base = b_base + kStages * L::kBBytes;
+    const uint32_t bar_base = raw_base + L::kRawBytes;
     const uint32_t full0 = bar_base, empty0 = bar_base + 8u * kStages;
     const uint32_t done_bar = bar_base + 8u * (2 * kStages);
+    const uint32_t rfull0 = done_bar + 8u, rempty0 = rfull0 + 8u * kRawStages;
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8u * s, 1 + kBProducers); mbar_init(empty0 + 8u * s, 1); }
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full0 + 8u * s, (IM2COL ? 64 : 1) + kBProducers);
+            mbar_init(empty0 + 8u * s, 1);
+        }
         mbar_init(done_bar, 1);
+        if (IM2COL)
+            for (int s = 0; s < kRawStages; ++s) { mbar_init(rfull0 + 8u * s, 1); mbar_init(rempty0 + 8u * s, 64); }
         fence_barrier_init();
-        prefetch_tmap(&tm_x);
+        if (!IM2COL || p.raw_ring) prefetch_tmap(&tm_x);
         prefetch_tmap(&tm_dy);
     }
     if (warp == 1) {
@@ -631,7 +830,57 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const int n_first = (pt0 / (p.tw * p.th)) * p.bn;
     const int w_end = p.tw * p.bw, h_end = p.th * p.bh;
 
-    if (warp == 0) {
+    if (IM2COL && warp >= 8) {
+        // A-tile builders: thread = one of the stage's 64 pixels; both 64-row halves of the M = 128
+        // operand get the same rows (there is a single (tap, channel) unit)
+        // group g takes the block's stages g, g + 4, ...
+        constexpr int kGroups = kBuilderThreads / 64;
+        const int row = (threadIdx.x - kThreads) & 63, group = (threadIdx.x - kThreads) >> 6;
+        const int bx = row & (p.bw - 1), by = (row >> p.lbw) & (p.bh - 1), bi = row >> (p.lbw + p.lbh);
+        int w0 = w_first, h0 = h_first, n0 = n_first;
+        for (int pt = pt0; pt < pt1; ++pt) {
+            const int it = pt - pt0;
+            if (it % kGroups == group) {
+                const uint32_t stage = (uint32_t)(it % kStages), phase = (uint32_t)((it / kStages) & 1);
+                const uint32_t a_dst = a_base + stage * L::kABytes;
+                uint2 t[10];
+                if (p.raw_ring) {
+                    const uint32_t rs = (uint32_t)(it % kRawStages), rphase = (uint32_t)((it / kRawStages) & 1);
+                    const int pitch = p.bw + 4;
+                    if (!mbar_wait(rfull0 + 8u * rs, rphase, abort_flag, status, kStatusProducerTimeout)) break;
+                    load_neighbourhood_raw(t, raw_base + rs * kRawStageBytes +
+                                                  (uint32_t)((((bi * (p.bh + 2)) + by + 1) * pitch + bx + 2) * 8), pitch);
+                } else {
+                    load_neighbourhood_global(t, p.x4, n0 + bi, h0 + by, w0 + bx, p.ext_n, p.ext_h, p.ext_w);
+                }
+                if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                store_im2col_row_c4(t, a_dst, row);
+                store_im2col_row_c4(t, a_dst + kStageTileBytes, row);
+                if (p.raw_ring) mbar_arrive(rempty0 + 8u * (uint32_t)(it % kRawStages));
+                fence_proxy_async_smem();
+                mbar_arrive(full0 + 8u * stage);
+            }
+            w0 += p.bw;
+            if (w0 >= w_end) { w0 = 0; h0 += p.bh; if (h0 >= h_end) { h0 = 0; n0 += p.bn; } }
+        }
+    } else if (IM2COL && warp == 0) {
+        if (p.raw_ring) {                                  // raw producer: the stage's pixels plus halo, one box per stage
+            const uint32_t raw_bytes = (uint32_t)((p.bw + 4) * (p.bh + 2) * p.bn * 8);
+            uint32_t rs = 0, rphase = 0;
+            int w0 = w_first, h0 = h_first, n0 = n_first;
+            for (int pt = pt0; pt < pt1; ++pt) {
+                if (!mbar_wait(rempty0 + 8u * rs, rphase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                if (lane == 0) {
+                    mbar_expect_tx(rfull0 + 8u * rs, raw_bytes);
+                    tma_load_3d(raw_base + rs * kRawStageBytes, &tm_x, rfull0 + 8u * rs, w0 - 2, h0 - 1, n0);
+                }
+                __syncwarp();
+                if (++rs == kRawStages) { rs = 0; rphase ^= 1u; }
+                w0 += p.bw;
+                if (w0 >= w_end) { w0 = 0; h0 += p.bh; if (h0 >= h_end) { h0 = 0; n0 += p.bn; } }
+            }
+        }
+    } else if (warp == 0 && !IM2COL) {
         {                                                  // producer A: two tap-shifted boxes of x per stage
             const int u0 = mt * 2;
             const int u1 = (u0 + 1 < p.units) ? u0 + 1 : u0;   // odd unit count: the last tile repeats its unit
@@ -708,7 +957,7 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             if (ok && lane == 0) umma_commit(done_bar);
             __syncwarp();
         }
-    } else if (warp >= 4) {
+    } else if (warp >= 4 && warp < 8) {
         const int q = warp & 3;
         const int row = q * 32 + lane;
         float* dst = partial + ((size_t)item * 128 + row) * NT;
@@ -772,23 +1021,28 @@ wgrad_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ dw, 
     (void)kk;
 }
 
-template <int NT>
-int launch_wgrad(const CUtensorMap& tx, const CUtensorMap& tdy, float* partial, const WgradParams& p, cudaStream_t st) {
-    using L = WgradSmem<NT>;
+template <int NT, bool IM2COL>
+int launch_wgrad_t(const CUtensorMap& tx, const CUtensorMap& tdy, float* partial, const WgradParams& p, cudaStream_t st) {
+    using L = WgradSmem<NT, IM2COL>;
     static bool attr_done[64] = {false};
     int dev = 0;
     TRB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        TRB_CUDA_TRY(cudaFuncSetAttribute(wgrad_igemm_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TRB_CUDA_TRY(cudaFuncSetAttribute(wgrad_igemm_kernel<NT, IM2COL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           L::kTotal));
         attr_done[dev] = true;
     }
     int* status = nullptr;
     TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status));
     const int grid = p.m_tiles * p.n_tiles * p.splits;
-    wgrad_igemm_kernel<NT><<<grid, kThreads, L::kTotal, st>>>(tx, tdy, partial, p, status);
+    wgrad_igemm_kernel<NT, IM2COL><<<grid, IM2COL ? kThreads + kBuilderThreads : kThreads, L::kTotal, st>>>(tx, tdy, partial, p, status);
     TRB_LAUNCH_CHECK("wgrad_igemm_kernel");
     return TRB200_OK;
+}
+
+template <int NT>
+int launch_wgrad(const CUtensorMap& tx, const CUtensorMap& tdy, float* partial, const WgradParams& p, cudaStream_t st) {
+    return p.x4 ? launch_wgrad_t<NT, true>(tx, tdy, partial, p, st) : launch_wgrad_t<NT, false>(tx, tdy, partial, p, st);
 }
 
 WgradParams wgrad_plan(const trb200_conv_desc& d, int nt, const TileShape& t, int taps = 9) {
@@ -807,38 +1061,22 @@ WgradParams wgrad_plan(const trb200_conv_desc& d, int nt, const TileShape& t, in
     p.splits = splits;
     p.tw = t.tw; p.th = t.th;
     p.bw = t.bw; p.bh = t.bh; p.bn = t.bn;
+    p.x4 = nullptr;
+    p.raw_ring = 0;
+    p.lbw = 0; p.lbh = 0;
+    while ((1 << p.lbw) < t.bw) ++p.lbw;
+    while ((1 << p.lbh) < t.bh) ++p.lbh;
+    p.ext_w = d.w; p.ext_h = d.h; p.ext_n = d.n;
     return p;
 }
 
 // ------------------------------------------------------------------ first layer (C = 4)
 // A 3x3 / pad 1 convolution over 4 input channels is a 1x1 convolution over the 36
-// values of each pixel's 3x3 neighbourhood.  im2col_c4_kernel writes that
-// neighbourhood as one 128-byte row per pixel (36 halfs + 28 zeros), after which the
-// forward conv and the weight gradient are plain GEMMs on the kernels above
-// (taps = 1, 64 input channels); the zero columns contribute exact zeros.
-__global__ void __launch_bounds__(256)
-im2col_c4_kernel(const uint2* __restrict__ x, uint4* __restrict__ xp, int n, int h, int w) {
-    const int64_t total = (int64_t)n * h * w * 8;          // 8 chunks of 16 bytes per pixel
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x) {
-        const int chunk = (int)(i & 7);
-        const int64_t pix = i >> 3;
-        const int xw = (int)(pix % w);
-        const int yh = (int)((pix / w) % h);
-        const int64_t img = pix / ((int64_t)w * h);
-        uint2 v[2] = {make_uint2(0, 0), make_uint2(0, 0)};
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int tap = chunk * 2 + j;
-            if (tap < 9) {
-                const int ih = yh + tap / 3 - 1, iw = xw + tap % 3 - 1;
-                if (ih >= 0 && ih < h && iw >= 0 && iw < w) v[j] = x[(img * h + ih) * w + iw];
-            }
-        }
-        xp[i] = make_uint4(v[0].x, v[0].y, v[1].x, v[1].y);
-    }
-}
-
+// values of each pixel's 3x3 neighbourhood.  The IM2COL variants of the kernels above
+// build that neighbourhood as one 128-byte operand row per pixel (36 halfs + 28 zeros)
+// in shared memory, after which the forward conv and the weight gradient are plain GEMMs
+// (taps = 1, 64 input channels) against filters packed to 64 columns; the zero columns
+// contribute exact zeros.
 // wp[k][j] = j < 36 ? w[k][j] : 0   (KRSC with c = 4 is already [k][36])
 __global__ void pack_w_c4_kernel(const __half* __restrict__ w, __half* __restrict__ wp, int kk) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -851,16 +1089,6 @@ __global__ void unpack_dw_c4_kernel(const __half* __restrict__ dwp, __half* __re
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= kk * 36) return;
     dw[i] = dwp[(i / 36) * 64 + i % 36];
-}
-
-int im2col_c4(const void* x, void* xp, int n, int h, int w, cudaStream_t st) {
-    const int64_t total = (int64_t)n * h * w * 8;
-    int64_t blocks = (total + 255) / 256;
-    const int64_t cap = (int64_t)sm_count() * 16;
-    if (blocks > cap) blocks = cap;
-    im2col_c4_kernel<<<(int)blocks, 256, 0, st>>>(static_cast<const uint2*>(x), static_cast<uint4*>(xp), n, h, w);
-    TRB_LAUNCH_CHECK("im2col_c4_kernel");
-    return TRB200_OK;
 }
 
 }  // namespace
@@ -885,10 +1113,6 @@ bool igemm_supports(const trb200_conv_desc& d, int which) {
     return pick_nt(d.k) != 0;                     // fprop: N dimension = k
 }
 
-size_t igemm_im2col_bytes(const trb200_conv_desc& d) {
-    return (size_t)align_up((int64_t)d.n * d.h * d.w * 64 * 2, 256);
-}
-
 size_t igemm_dgrad_workspace(const trb200_conv_desc& d) {
     return (size_t)align_up((int64_t)9 * d.c * d.k * 2, 256);
 }
@@ -900,19 +1124,19 @@ static size_t wgrad_partial_bytes(const trb200_conv_desc& d, int taps) {
     return (size_t)p.splits * p.m_tiles * p.n_tiles * 128 * nt * sizeof(float);
 }
 
-// small C without a caller-provided im2col buffer: [im2col][packed dW][partials]
+// small C: [packed dW (k x 64 half)][partials]
 size_t igemm_wgrad_workspace(const trb200_conv_desc& d) {
     if (igemm_small_c(d)) {
         trb200_conv_desc e = d;
         e.c = 64;
-        return igemm_im2col_bytes(d) + (size_t)align_up((int64_t)d.k * 64 * 2, 256) + wgrad_partial_bytes(e, 1);
+        return (size_t)align_up((int64_t)d.k * 64 * 2, 256) + wgrad_partial_bytes(e, 1);
     }
     return wgrad_partial_bytes(d, 9);
 }
 
-// [im2col][packed filters]
+// small C: the filters packed to 64 columns
 size_t igemm_fprop_workspace(const trb200_conv_desc& d) {
-    if (igemm_small_c(d)) return igemm_im2col_bytes(d) + (size_t)align_up((int64_t)d.k * 64 * 2, 256);
+    if (igemm_small_c(d)) return (size_t)align_up((int64_t)d.k * 64 * 2, 256);
     return 0;
 }
 
@@ -945,26 +1169,29 @@ int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y
                 need, ws_bytes);
     TRB_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255u) == 0, TRB200_ERR_INVALID_ARGUMENT,
                 "conv_fprop: workspace must be 256-byte aligned");
-    unsigned char* base = static_cast<unsigned char*>(ws);
-    void* xp = base;
-    __half* wp = reinterpret_cast<__half*>(base + igemm_im2col_bytes(d));
-    int rc = im2col_c4(x, xp, d.n, d.h, d.w, st);
-    if (rc) return rc;
+    TRB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 7u) == 0, TRB200_ERR_INVALID_ARGUMENT,
+                "conv_fprop: a 4-channel input must be 8-byte aligned");
+    __half* wp = static_cast<__half*>(ws);
     pack_w_c4_kernel<<<(d.k * 64 + 255) / 256, 256, 0, st>>>(static_cast<const __half*>(w), wp, d.k);
     TRB_LAUNCH_CHECK("pack_w_c4_kernel");
-    // 1x1 convolution: filter view (ci = 64, tap = 1, co = k)
-    return conv3x3_run(xp, wp, 1, y, d.n, d.h, d.w, 64, d.k, st, 1, stats_partial, stats_strips);
+    // 1x1 convolution: filter view (ci = 64, tap = 1, co = k), operand rows built from x in the kernel
+    return conv3x3_run(nullptr, wp, 1, y, d.n, d.h, d.w, 64, d.k, st, 1, stats_partial, stats_strips, x);
 }
 
+// x4 != nullptr: `x` is ignored and the operand rows are built in the kernel from the 4-channel image x4
 static int wgrad_run(const trb200_conv_desc& d, int taps, const void* dy, const void* x, void* dw, float* partial,
-                     cudaStream_t st) {
+                     cudaStream_t st, const void* x4 = nullptr) {
     const int nt = pick_nt(d.k);
     const TileShape t = pick_tile(d.n, d.h, d.w, 64);
-    const WgradParams p = wgrad_plan(d, nt, t, taps);
+    WgradParams p = wgrad_plan(d, nt, t, taps);
+    p.x4 = static_cast<const uint2*>(x4);
+    p.raw_ring = (x4 && raw_ring_fits(t, d.w, x4)) ? 1 : 0;
     CUtensorMap tx, tdy;
-    int rc = make_act_tmap(&tx, x, d.n, d.h, d.w, d.c, t, "wgrad x");
+    int rc = make_act_tmap(&tdy, dy, d.n, d.h, d.w, d.k, t, "wgrad dy");
     if (rc) return rc;
-    rc = make_act_tmap(&tdy, dy, d.n, d.h, d.w, d.k, t, "wgrad dy");
+    if (p.raw_ring) rc = make_raw_x4_tmap(&tx, x4, d.n, d.h, d.w, t);
+    else if (x4) tx = tdy;      // not used by the kernel
+    else rc = make_act_tmap(&tx, x, d.n, d.h, d.w, d.c, t, "wgrad x");
     if (rc) return rc;
     if (nt == 256) rc = launch_wgrad<256>(tx, tdy, partial, p, st);
     else if (nt == 128) rc = launch_wgrad<128>(tx, tdy, partial, p, st);
@@ -976,32 +1203,17 @@ static int wgrad_run(const trb200_conv_desc& d, int taps, const void* dy, const 
     return TRB200_OK;
 }
 
-// Small-C weight gradient.  `xp` is the im2col buffer [n,h,w,64] half: if `xp_ready`
-// it already holds the neighbourhoods of x, else they are written here first.
-// ws: [packed dW (k x 64 half)][partials].
-size_t igemm_wgrad_small_c_workspace(const trb200_conv_desc& d) {
-    trb200_conv_desc e = d;
-    e.c = 64;
-    return (size_t)align_up((int64_t)d.k * 64 * 2, 256) + wgrad_partial_bytes(e, 1);
-}
-
-int igemm_wgrad_small_c(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* xp, bool xp_ready,
-                        void* ws, size_t ws_bytes, cudaStream_t st) {
-    const size_t need = igemm_wgrad_small_c_workspace(d);
-    TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, "conv_wgrad: workspace of %zu bytes needed, %zu given",
-                need, ws_bytes);
-    TRB_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255u) == 0 && aligned16(xp), TRB200_ERR_INVALID_ARGUMENT,
-                "conv_wgrad: workspace must be 256-byte aligned");
-    if (!xp_ready) {
-        const int rc = im2col_c4(x, xp, d.n, d.h, d.w, st);
-        if (rc) return rc;
-    }
+// Small-C weight gradient.  ws: [packed dW (k x 64 half)][partials].
+static int igemm_wgrad_small_c(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* ws,
+                               cudaStream_t st) {
+    TRB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 7u) == 0, TRB200_ERR_INVALID_ARGUMENT,
+                "conv_wgrad: a 4-channel input must be 8-byte aligned");
     unsigned char* base = static_cast<unsigned char*>(ws);
     __half* dwp = reinterpret_cast<__half*>(base);
     float* partial = reinterpret_cast<float*>(base + align_up((int64_t)d.k * 64 * 2, 256));
     trb200_conv_desc e = d;
     e.c = 64;
-    const int rc = wgrad_run(e, 1, dy, xp, dwp, partial, st);
+    const int rc = wgrad_run(e, 1, dy, nullptr, dwp, partial, st, x);
     if (rc) return rc;
     unpack_dw_c4_kernel<<<(d.k * 36 + 255) / 256, 256, 0, st>>>(dwp, static_cast<__half*>(dw), d.k);
     TRB_LAUNCH_CHECK("unpack_dw_c4_kernel");
@@ -1017,11 +1229,7 @@ int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* 
                 need, ws_bytes);
     TRB_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255u) == 0, TRB200_ERR_INVALID_ARGUMENT,
                 "conv_wgrad: workspace must be 256-byte aligned");
-    if (igemm_small_c(d)) {
-        unsigned char* base = static_cast<unsigned char*>(ws);
-        const size_t off = igemm_im2col_bytes(d);
-        return igemm_wgrad_small_c(d, dy, x, dw, base, false, base + off, ws_bytes - off, st);
-    }
+    if (igemm_small_c(d)) return igemm_wgrad_small_c(d, dy, x, dw, ws, st);
     return wgrad_run(d, 9, dy, x, dw, static_cast<float*>(ws), st);
 }
 

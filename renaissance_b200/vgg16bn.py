@@ -147,8 +147,8 @@ class Vgg16BnTrainer:
                 L.buf["pool_out"] = torch.empty(pe, dtype=torch.float16, device=d)
                 L.buf["argmax"] = torch.empty(pe, dtype=torch.uint8, device=d)
         big = max(L.buf["conv_out"].numel() for L in self.convs)
-        # the blocks' bn_output scratch (+ room for the first layer's packed filters behind the im2col rows)
-        self.bn_scratch = torch.empty(big + (1 << 19), dtype=torch.float16, device=d)
+        # the blocks' bn_output scratch
+        self.bn_scratch = torch.empty(big, dtype=torch.float16, device=d)
         self.images = [torch.zeros((n, image, image, 4), dtype=torch.float16, device=d) for _ in range(2)]
         self.labels = [torch.zeros(n, dtype=torch.int32, device=d) for _ in range(2)]
         self.logits = torch.empty((n, classes), dtype=torch.float16, device=d)
@@ -233,14 +233,13 @@ class Vgg16BnTrainer:
             geo = ops.ConvGeometry(n, L.h, L.h, L.c, L.k)
             gamma, beta = self.view(self.w32, L.gamma), self.view(self.w32, L.beta)
             # conv with the batch statistics taken in its epilogue, then bn_finalize.  The 3(+1)->64 first
-            # layer runs as a 1x1 GEMM over the pixels' 3x3 neighbourhoods, which go to the (still free)
-            # backward scratch buffer.
+            # layer runs as a 1x1 GEMM over the pixels' 3x3 neighbourhoods, built in shared memory.
             if self.timing is not None and L.idx > 0:
                 t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 t0.record()
             ops.conv_fprop_bn_stats(geo, x, w16, gamma, beta, y=b["conv_out"], out=b,
                                     running_mean=b["running_mean"], running_var=b["running_var"],
-                                    workspace=self.ws, scratch=self.bn_scratch if L.idx == 0 else None)
+                                    workspace=self.ws)
             if self.timing is not None and L.idx > 0:
                 t1.record()
                 self.timing.append((t0, t1, 2.0 * n * L.h * L.h * L.c * L.k * 9,

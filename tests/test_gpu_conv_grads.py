@@ -72,10 +72,12 @@ IGEMM_CASES = [
 ]
 
 
-@pytest.mark.parametrize("n,h,w,k", [(2, 16, 16, 64), (3, 9, 7, 128), (2, 20, 12, 256)])
+@pytest.mark.parametrize("n,h,w,k", [(2, 16, 16, 64), (3, 9, 7, 128), (2, 20, 12, 256), (2, 32, 64, 64),
+                                     (5, 6, 2, 64), (1, 40, 130, 64), (70, 1, 2, 64)])
 def test_first_layer_four_channels_on_tensor_cores(orc, n, h, w, k):
     """c = 4 (3 image channels + 1 pad): forward and weight gradient as a 1x1 GEMM over
-    the pixels' 3x3 neighbourhoods."""
+    the pixels' 3x3 neighbourhoods, which the kernels build in shared memory (from halo tiles
+    fetched by TMA, or with plain loads when the width is odd or the halo tile is too large)."""
     from renaissance_b200 import ops
     x, wt, dy = _rand_case(n * 5 + k, n, h, w, 4, k, 3, 1, 1)
     x[..., 3] = 0
