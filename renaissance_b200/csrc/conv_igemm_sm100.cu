@@ -743,6 +743,18 @@ int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int 
 // upper bound of the strips the STATS kernels write for an output of `cout` channels
 int conv3x3_stats_max_strips() { return sm_count(); }
 
+#include "conv_pixn_sm100.cuh"
+
+// 64 / 128 output channels go to the kernel with the pixels on N (development builds can switch it off)
+int conv3x3_any_run(const void* in, const void* wv, int tap_is_dim1, void* out, int n, int h, int w, int cin, int cout,
+                    cudaStream_t st, float* stats_partial = nullptr, int* stats_strips = nullptr) {
+#ifndef TRB200_NO_PIXN
+    if (pixn_preferred(cin, cout))
+        return conv3x3_pixn_run(in, wv, tap_is_dim1, out, n, h, w, cin, cout, st, stats_partial, stats_strips);
+#endif
+    return conv3x3_run(in, wv, tap_is_dim1, out, n, h, w, cin, cout, st, 9, stats_partial, stats_strips);
+}
+
 // ------------------------------------------------------------------ wgrad kernel
 struct WgradParams {
     int taps;           // 9 (3x3, pad 1) or 1 (1x1)
@@ -1152,7 +1164,7 @@ int igemm_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* 
     dgrad_filter_view_kernel<<<blocks, 256, 0, st>>>(static_cast<const __half*>(w), static_cast<__half*>(ws), d.k, d.c);
     TRB_LAUNCH_CHECK("dgrad_filter_view_kernel");
     // in = dY [n,h,w,k], filter view (ci = k, co = c, tap), out = dX [n,h,w,c]
-    return conv3x3_run(dy, ws, 0, dx, d.n, d.h, d.w, d.k, d.c, st);
+    return conv3x3_any_run(dy, ws, 0, dx, d.n, d.h, d.w, d.k, d.c, st);
 }
 
 size_t igemm_fprop_stats_bytes(const trb200_conv_desc& d) {
@@ -1163,7 +1175,7 @@ size_t igemm_fprop_stats_bytes(const trb200_conv_desc& d) {
 int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, void* ws, size_t ws_bytes,
                 cudaStream_t st, float* stats_partial, int* stats_strips) {
     if (!igemm_small_c(d))
-        return conv3x3_run(x, w, 1, y, d.n, d.h, d.w, d.c, d.k, st, 9, stats_partial, stats_strips);
+        return conv3x3_any_run(x, w, 1, y, d.n, d.h, d.w, d.c, d.k, st, stats_partial, stats_strips);
     const size_t need = igemm_fprop_workspace(d);
     TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, "conv_fprop: workspace of %zu bytes needed, %zu given",
                 need, ws_bytes);
