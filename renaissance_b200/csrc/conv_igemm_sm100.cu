@@ -1082,6 +1082,17 @@ WgradParams wgrad_plan(const trb200_conv_desc& d, int nt, const TileShape& t, in
     return p;
 }
 
+#include "wgrad_unitn_sm100.cuh"
+
+// which weight-gradient kernel a layer gets: up to 128 filters the one with the units on N
+// (development builds can move the limit)
+#ifndef TRB200_UNITN_MAX_K
+#define TRB200_UNITN_MAX_K 128
+#endif
+inline bool wgrad_use_unitn(const trb200_conv_desc& d) {
+    return wgrad_unitn_supports(d) && d.k <= TRB200_UNITN_MAX_K;
+}
+
 // ------------------------------------------------------------------ first layer (C = 4)
 // A 3x3 / pad 1 convolution over 4 input channels is a 1x1 convolution over the 36
 // values of each pixel's 3x3 neighbourhood.  The IM2COL variants of the kernels above
@@ -1143,6 +1154,7 @@ size_t igemm_wgrad_workspace(const trb200_conv_desc& d) {
         e.c = 64;
         return (size_t)align_up((int64_t)d.k * 64 * 2, 256) + wgrad_partial_bytes(e, 1);
     }
+    if (wgrad_use_unitn(d)) return wgrad_unitn_partial_bytes(d);
     return wgrad_partial_bytes(d, 9);
 }
 
@@ -1242,6 +1254,7 @@ int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* 
     TRB_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255u) == 0, TRB200_ERR_INVALID_ARGUMENT,
                 "conv_wgrad: workspace must be 256-byte aligned");
     if (igemm_small_c(d)) return igemm_wgrad_small_c(d, dy, x, dw, ws, st);
+    if (wgrad_use_unitn(d)) return wgrad_unitn_run(d, dy, x, dw, static_cast<float*>(ws), st);
     return wgrad_run(d, 9, dy, x, dw, static_cast<float*>(ws), st);
 }
 
