@@ -33,11 +33,11 @@ IMAGE = 224
 CLASSES = 1000
 
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) over algorithmic bytes of
-# conv3x3_igemm_kernel, from the two ncu captures in profiles/conv3x3_igemm_kernel_n256.md
-# (166.0 / 205.6 MB and 259.8 / 310.7 MB).  Full-size launches are too large to capture under
-# --set full, and the traffic grows in proportion to the tensors, so the per-launch traffic
-# reported below is the launches' average algorithmic byte count times this ratio.
-ROOFLINE_TRAFFIC_RATIO = 0.83
+# conv3x3_igemm_kernel<256>, from the ncu capture in
+# profiles/conv3x3_igemm_kernel_n256_fprop_stats_64x56x56x256.md (163.8 / 206.7 MB).  Full-size launches
+# are too large to capture under --set full, and the traffic grows in proportion to the tensors, so the
+# per-launch traffic reported below is the launches' average algorithmic byte count times this ratio.
+ROOFLINE_TRAFFIC_RATIO = 0.79
 
 
 def measured_peaks():
@@ -190,20 +190,21 @@ def run_ours(args):
     ms_per_step = ms_total / args.steps
     value = world * batch * args.steps / (ms_total / 1e3)
 
-    # ---------------- roofline of the dominant kernel (conv3x3_igemm_kernel): its forward launches,
-    # bracketed by CUDA events inside the timed region on the launching stream
+    # ---------------- roofline of the dominant kernel (conv3x3_igemm_kernel<256>): its forward launches
+    # (the nine layers with 256 or 512 filters), bracketed by CUDA events inside the timed region on the
+    # launching stream; each bracket also holds the few-microsecond bn_stats_finalize launch that follows
     peaks = measured_peaks()
     flops = sum(e[2] for e in roof_events)
     dur_ms = sum(e[0].elapsed_time(e[1]) for e in roof_events)
     alg_bytes = sum(e[3] for e in roof_events)
     n_l = max(len(roof_events), 1)
     achieved = flops / (dur_ms / 1e3) / 1e12 if dur_ms > 0 else 0.0
-    roofline = dict(kernel="conv3x3_igemm_kernel (12 forward launches per step)", bound="tensor",
+    roofline = dict(kernel="conv3x3_igemm_kernel<256> (9 forward launches per step)", bound="tensor",
                     achieved=round(achieved, 1), peak=peaks["tflops"], unit="TFLOP/s",
                     frac=round(achieved / peaks["tflops"], 4), peak_source=peaks["source"],
                     flop_per_launch=flops / n_l, ms_per_launch=dur_ms / n_l, launches_timed=len(roof_events),
                     traffic=round(ROOFLINE_TRAFFIC_RATIO * alg_bytes / n_l),
-                    traffic_note="average algorithmic bytes per launch x 0.83 (ncu DRAM/algorithmic ratio)")
+                    traffic_note="average algorithmic bytes per launch x 0.79 (ncu DRAM/algorithmic ratio)")
 
     # ---------------- end to end: host buffers, H2D of every step's batch and D2H of its loss inside the region
     barrier()

@@ -3,6 +3,7 @@
     python -m renaissance_b200.kernel_sweep                 # everything, JSON lines
     python -m renaissance_b200.kernel_sweep --only block    # BASELINE config 2 (one block backward)
     python -m renaissance_b200.kernel_sweep --only bnrelu --quick
+    python -m renaissance_b200.kernel_sweep --only conv --quick --batch 64 --shape 56,256,256 --what fprop_stats
 
 Covers BASELINE.json's config 2 (Conv3x3 C=K=64 + BN + ReLU backward at N=256, 56x56)
 and config 5 (BN+ReLU backward over N*H*W x C, fused softmax-CE over N x C), plus the
@@ -108,6 +109,11 @@ def conv_point(t, n, h, c, k, what, tc, src):
     elif what == "wgrad":
         dw = torch.empty_like(w)
         med, best = t(lambda: ops.conv_wgrad(geo, dy, x, dw=dw))
+    elif what == "fprop_stats":
+        y = torch.empty_like(dy)
+        gamma, beta = torch.ones(k, device="cuda"), torch.zeros(k, device="cuda")
+        ws = ops.Workspace(torch.device("cuda"))
+        med, best = t(lambda: ops.conv_fprop_bn_stats(geo, x, w, gamma, beta, y=y, workspace=ws))
     else:
         y = torch.empty_like(dy)
         med, best = t(lambda: ops.conv_fprop(geo, x, w, y=y))
@@ -161,6 +167,8 @@ def main():
     ap.add_argument("--quick", action="store_true", help="one small point per kernel (for profiler captures)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--batch", type=int, default=256, help="images for the conv / block points")
+    ap.add_argument("--shape", default="", help="H,C,K: only this conv shape (with --only conv)")
+    ap.add_argument("--what", default="", help="comma list out of dgrad,wgrad,fprop,fprop_stats (with --only conv)")
     args = ap.parse_args()
     hbm, tc, src = peaks()
     t = Timer(1 if args.quick else args.iters)
@@ -181,8 +189,11 @@ def main():
             softmax_point(t, b, c, ls, hbm, src)
     if args.only in ("all", "conv"):
         shapes = [(56, 64, 64), (28, 256, 512)] if args.quick else [(56, 64, 64)] + VGG_SHAPES
+        if args.shape:
+            shapes = [tuple(int(v) for v in args.shape.split(","))]
+        kinds = tuple(args.what.split(",")) if args.what else ("dgrad", "wgrad", "fprop", "fprop_stats")
         for h, c, k in shapes:
-            for what in ("dgrad", "wgrad", "fprop"):
+            for what in kinds:
                 conv_point(t, n, h, c, k, what, tc, src)
 
 
