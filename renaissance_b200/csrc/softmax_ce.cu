@@ -16,6 +16,8 @@
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
+#include <atomic>
+
 namespace trb {
 
 __device__ int g_softmax_status = 0;   // set when a bounded wait of the staged kernel gives up
@@ -199,6 +201,159 @@ softmax_ce_rows_warp(const __half* __restrict__ logits, int64_t logits_stride,
                 out.loss_partial[row] = (-keep * logf(py + 1e-8f) - spread * sum_log) * inv_b;
         }
     }
+}
+
+// The same for the common training call: gradient and loss only (no probabilities kept), rows
+// of whole 16-byte vectors.  Per class: one conversion, one FMA and one exponential for the
+// sum, one FMA and half a pack for the gradient; the maximum is taken on packed halfs; the
+// label's class is patched by one lane after the row's vectors are stored, from a float
+// recomputation that also gives the loss.  Label smoothing adds a logarithm per class for the
+// loss and nothing to the gradient's cost.
+// Completion counters for the loss: every block of a row kernel leaves the sum of its rows'
+// losses (added in a fixed order) in a slot of a small library-owned array, and the last block to
+// finish adds the slots in block order and writes the loss; the result does not depend on which
+// block that is, and the separate one-block reduction launch is saved.  A launch takes the next
+// counter (and slot array) of the pool, so fewer calls than the pool holds may be in flight at a time.
+constexpr int kLossTickets = 64;
+constexpr int kLossTailBlocks = 2048;          // largest grid that finishes its loss this way
+__device__ unsigned int g_loss_tickets[kLossTickets];
+__device__ float g_loss_block_sums[kLossTickets][kLossTailBlocks];
+
+struct LossTail {
+    float* loss;              // may be null
+    float* inv_scaling;       // may be null
+    unsigned int* ticket;     // null: the caller launches softmax_ce_loss_reduce instead
+    float* block_sums;        // this launch's slots, one per block
+};
+
+// called by every thread of every block once its rows are done; `mine` = the losses this thread wrote
+__device__ __forceinline__ void loss_tail(const LossTail& t, float mine, int batch) {
+    if (!t.ticket) return;
+    __shared__ int s_last;
+    __shared__ float s_part[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float v = warp_sum(mine);
+    if (lane == 0) s_part[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float b = 0.f;
+        for (int w = 0; w < nw; ++w) b += s_part[w];
+        t.block_sums[blockIdx.x] = b;
+        __threadfence();                   // the slot is visible device-wide before the ticket is
+        s_last = atomicAdd(t.ticket, 1u) == gridDim.x - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float a = 0.f;
+    for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) a += __ldcg(t.block_sums + i);
+    v = warp_sum(a);
+    __syncthreads();
+    if (lane == 0) s_part[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.f;
+        for (int w = 0; w < nw; ++w) total += s_part[w];
+        if (t.loss) *t.loss = total;
+        if (t.inv_scaling) *t.inv_scaling = 1.0f / (float)batch;
+        *t.ticket = 0u;                    // ready for the next launch that draws this counter
+    }
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(256, VPL >= 8 ? 2 : 3)
+softmax_ce_rows_warp_lean(const __half* __restrict__ logits, int64_t logits_stride,
+                          const int32_t* __restrict__ labels, const float* __restrict__ scaling,
+                          const float* __restrict__ label_smoothing, __half* __restrict__ dlogits,
+                          int64_t dlogits_stride, float* __restrict__ loss_partial, int batch, int classes,
+                          LossTail tail) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int nvec = classes >> 3;
+    const float ls = label_smoothing ? label_smoothing[0] : 0.f;
+    const float keep = 1.0f - ls, spread = ls / (float)classes;
+    const float inv_b = 1.0f / (float)batch;
+    const float gscale = scaling[0] * inv_b;
+    const uint4 kNegInf = make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);   // -inf halfs
+    const int row_first = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    // the next row's vectors are requested before the current row is processed
+    uint4 nxt[VPL];
+    float my_loss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int vec = i * 32 + lane;
+        nxt[i] = kNegInf;
+        if (row_first < batch && vec < nvec)
+            nxt[i] = *reinterpret_cast<const uint4*>(logits + (int64_t)row_first * logits_stride + vec * 8);
+    }
+    for (int row = row_first; row < batch; row += warps) {
+        uint4 cur[VPL];
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) cur[i] = nxt[i];
+        const int y = labels[row];
+        const float zy = __half2float(logits[(int64_t)row * logits_stride + y]);
+        {
+            const int row_n = row + warps;
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) {
+                const int vec = i * 32 + lane;
+                nxt[i] = kNegInf;
+                if (row_n < batch && vec < nvec)
+                    nxt[i] = *reinterpret_cast<const uint4*>(logits + (int64_t)row_n * logits_stride + vec * 8);
+            }
+        }
+        float zmax = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) zmax = fmaxf(zmax, half8_max(cur[i]));
+        zmax = warp_max(zmax);
+        const float shift = -zmax * kLog2e;
+        float e[VPL][8];
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            half8_to_float(cur[i], e[i]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                e[i][j] = fast_exp2(fmaf(e[i][j], kLog2e, shift));
+                sum += e[i][j];
+            }
+        }
+        sum = warp_sum(sum);
+        const float inv_sum = 1.0f / (sum + 1e-8f);
+        const float ga = inv_sum * gscale, gb = -spread * gscale;
+        __half* drow = dlogits + (int64_t)row * dlogits_stride;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int vec = i * 32 + lane;
+            if (vec < nvec) {
+                uint4 o;
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    oh[j] = __floats2half2_rn(fmaf(e[i][2 * j], ga, gb), fmaf(e[i][2 * j + 1], ga, gb));
+                *reinterpret_cast<uint4*>(drow + vec * 8) = o;
+            }
+        }
+        float sum_log = 0.f;
+        if (ls != 0.f && loss_partial) {
+#pragma unroll
+            for (int i = 0; i < VPL; ++i)
+                if (i * 32 + lane < nvec) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) sum_log += fast_log2(fmaf(e[i][j], inv_sum, 1e-8f));
+                }
+            sum_log = warp_sum(sum_log) * kLn2;
+        }
+        // the label's class, by the lane that stored its vector
+        if (((y >> 3) & 31) == lane) {
+            const float py = fast_exp2(fmaf(zy, kLog2e, shift)) * inv_sum;
+            drow[y] = __float2half_rn((py - spread - keep) * gscale);
+            const float row_loss = (-keep * logf(py + 1e-8f) - spread * sum_log) * inv_b;
+            if (loss_partial) loss_partial[row] = row_loss;
+            my_loss += row_loss;
+        }
+    }
+    loss_tail(tail, my_loss, batch);
 }
 
 // One block per row, the row is staged once in shared memory as halfs (classes * 2
@@ -543,6 +698,160 @@ softmax_ce_rows_staged(const __half* __restrict__ logits, int64_t logits_stride,
     }
 }
 
+// One block per row with the row in the block's registers: gradient and loss only (no
+// probabilities kept), rows of whole 16-byte vectors, THREADS x VPT vectors at most.  A persistent
+// block walks rows blockIdx.x, + gridDim.x, ...; thread 0 keeps the next row on its way into the
+// other half of a two-row shared-memory buffer with a bulk copy, the block picks its vectors up
+// from there once and never writes them back.  Maximum and sum meet in ONE block-wide step: every
+// thread takes exponentials against its own maximum, (max, sum) pairs are merged by rescaling
+// (warp shuffles, then one exchange through shared memory that every warp reads back), and the
+// thread's factor exp(own max - row max) / sum goes into the single FMA that makes the gradient.
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS, THREADS == 256 ? 3 : (THREADS == 512 ? 2 : 1))
+softmax_ce_rows_regs(const __half* __restrict__ logits, int64_t logits_stride, const int32_t* __restrict__ labels,
+                     const float* __restrict__ scaling, const float* __restrict__ label_smoothing,
+                     __half* __restrict__ dlogits, int64_t dlogits_stride, float* __restrict__ loss_partial, int batch,
+                     int classes, uint32_t buf_stride, int* status, LossTail tail) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t s_bar[2];
+    __shared__ float s_m[32], s_s[32], s_l[32];
+    __shared__ int s_abort;
+    constexpr int kWarps = THREADS / 32;
+    constexpr float kFloor = -1.0e30f;             // stands in for -inf so that differences of maxima stay finite
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t row_bytes = (uint32_t)classes * 2u;
+    const uint32_t buf0 = ptx::smem_u32(smem_raw);
+    const uint32_t bar0 = ptx::smem_u32(&s_bar[0]);
+    if (tid == 0) {
+        s_abort = 0;
+        ptx::mbar_init(bar0, 1);
+        ptx::mbar_init(bar0 + 8, 1);
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+
+    const float ls = label_smoothing ? label_smoothing[0] : 0.f;
+    const float keep = 1.0f - ls, spread = ls / (float)classes;
+    const float inv_b = 1.0f / (float)batch;
+    const float gscale = scaling[0] * inv_b;
+    const float gb = -spread * gscale;
+    const int nvec = classes >> 3;
+    const uint4 kNegInf = make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);
+
+    // merges (m, s) of the other lane / warp into this one: s counts exponentials taken against m
+    auto merge = [](float& m, float& s, float m2, float s2) {
+        const float mn = fmaxf(m, m2);
+        s = s * fast_exp2((m - mn) * kLog2e) + s2 * fast_exp2((m2 - mn) * kLog2e);
+        m = mn;
+    };
+
+    float my_loss = 0.f;
+    int row = blockIdx.x;
+    if (tid == 0 && row < batch) {
+        ptx::mbar_expect_tx(bar0, row_bytes);
+        ptx::bulk_load_1d(buf0, logits + (int64_t)row * logits_stride, row_bytes, bar0);
+    }
+    for (int it = 0; row < batch; row += gridDim.x, ++it) {
+        const int b = it & 1;
+        const int next = row + gridDim.x;
+        if (tid == 0 && next < batch) {       // the other buffer was released by the barrier that ended the last row
+            ptx::mbar_expect_tx(bar0 + 8u * (b ^ 1), row_bytes);
+            ptx::bulk_load_1d(buf0 + (uint32_t)(b ^ 1) * buf_stride, logits + (int64_t)next * logits_stride, row_bytes,
+                              bar0 + 8u * (b ^ 1));
+        }
+        const bool ok = ptx::mbar_wait(bar0 + 8u * b, ((uint32_t)it >> 1) & 1u, &s_abort, status, 4);
+        if (__syncthreads_or(ok ? 0 : 1)) break;
+        const __half* srow = reinterpret_cast<const __half*>(smem_raw + (size_t)b * buf_stride);
+        const int y = labels[row];
+        const float zy = __half2float(srow[y]);
+
+        uint4 raw[VPT];
+        float m_t = kFloor;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vec = i * THREADS + tid;
+            raw[i] = vec < nvec ? *reinterpret_cast<const uint4*>(srow + vec * 8) : kNegInf;
+            m_t = fmaxf(m_t, half8_max(raw[i]));
+        }
+        const float sh_t = -m_t * kLog2e;
+        float e[VPT][8];
+        float s_t = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            half8_to_float(raw[i], e[i]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                e[i][j] = fast_exp2(fmaf(e[i][j], kLog2e, sh_t));
+                s_t += e[i][j];
+            }
+        }
+        float m = m_t, ssum = s_t;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, ssum, o);
+            merge(m, ssum, m2, s2);
+        }
+        if (lane == 0) { s_m[warp] = m; s_s[warp] = ssum; }
+        __syncthreads();
+        m = lane < kWarps ? s_m[lane] : kFloor;
+        ssum = lane < kWarps ? s_s[lane] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, ssum, o);
+            merge(m, ssum, m2, s2);
+        }
+        // m = row maximum, ssum = sum of exponentials against it (the same in every thread)
+        const float inv_sum = 1.0f / (ssum + 1e-8f);
+        const float pf = fast_exp2((m_t - m) * kLog2e) * inv_sum;      // e * pf = probability
+        const float ga = pf * gscale;
+        __half* drow = dlogits + (int64_t)row * dlogits_stride;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vec = i * THREADS + tid;
+            if (vec < nvec) {
+                uint4 o;
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    oh[j] = __floats2half2_rn(fmaf(e[i][2 * j], ga, gb), fmaf(e[i][2 * j + 1], ga, gb));
+                *reinterpret_cast<uint4*>(drow + vec * 8) = o;
+            }
+        }
+        float sum_log = 0.f;
+        if (ls != 0.f && loss_partial) {          // the same branch in every thread of the block
+            float t = 0.f;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i)
+                if (i * THREADS + tid < nvec) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) t += fast_log2(fmaf(e[i][j], pf, 1e-8f));
+                }
+            t = warp_sum(t);
+            if (lane == 0) s_l[warp] = t;
+            __syncthreads();
+            t = lane < kWarps ? s_l[lane] : 0.f;
+            sum_log = warp_sum(t) * kLn2;
+        }
+        // the label's class, by the thread that stored its vector
+        if (((y >> 3) % THREADS) == tid) {
+            const float py = fast_exp2((zy - m) * kLog2e) * inv_sum;
+            drow[y] = __float2half_rn((py - spread - keep) * gscale);
+            const float row_loss = (-keep * logf(py + 1e-8f) - spread * sum_log) * inv_b;
+            if (loss_partial) loss_partial[row] = row_loss;
+            my_loss += row_loss;
+        }
+        // this buffer is refilled by a bulk copy two rows from now: order the generic-proxy
+        // reads above before it (the barrier also frees s_m / s_s / s_l for the next row)
+        ptx::fence_proxy_async_smem();
+        __syncthreads();
+    }
+    if (*(volatile int*)&s_abort) {     // a wait gave up: let a copy that may still be in flight land before the block ends
+        const unsigned long long t0 = ptx::global_ns();
+        while (ptx::global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    loss_tail(tail, my_loss, batch);
+}
+
 // Fixed-order sum of the per-row partials (one block: every thread adds a fixed
 // strided subset four values at a time, then a shared-memory tree), as
 // softmax_ce_reduce_kernel does; also writes 1/batch.
@@ -626,7 +935,40 @@ int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels
                 float* inv_scaling, int batch, int classes, cudaStream_t s) {
     const __half* z = static_cast<const __half*>(logits);
     const bool rows_aligned = aligned16(logits) && (logits_stride % 8 == 0);
-    if (rows_aligned && classes <= 2048) {
+    // kernels that finish the loss themselves draw a completion counter; `fused_tail` says one did
+    LossTail tail{loss, inv_scaling, nullptr, nullptr};
+    bool fused_tail = false;
+#ifndef TRB200_NO_LOSS_TAIL
+    if (loss || inv_scaling) {
+        static std::atomic<unsigned int> next_ticket{0};
+        unsigned int* pool = nullptr;
+        float* sums = nullptr;
+        TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&pool), g_loss_tickets));
+        TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&sums), g_loss_block_sums));
+        const unsigned int slot = next_ticket.fetch_add(1u) % kLossTickets;
+        tail.ticket = pool + slot;
+        tail.block_sums = sums + (size_t)slot * kLossTailBlocks;
+    }
+#endif
+    if (rows_aligned && classes <= 2048 && classes % 8 == 0 && !out.probs && out.dlogits && scaling &&
+        out.dlogits_stride % 8 == 0 && aligned16(out.dlogits)) {
+        const int warps = 8;
+        int blocks = (batch + warps - 1) / warps;
+        if (blocks > sm_count() * 8) blocks = sm_count() * 8;      // warps loop over rows
+        if (blocks > kLossTailBlocks) blocks = kLossTailBlocks;
+        dim3 grid(blocks), block(warps * 32);
+#define TRB_LEAN_LAUNCH(V)                                                                                       \
+    softmax_ce_rows_warp_lean<V><<<grid, block, 0, s>>>(z, logits_stride, labels, scaling, label_smoothing,      \
+                                                        out.dlogits, out.dlogits_stride, out.loss_partial, batch, \
+                                                        classes, tail)
+        if (classes <= 256) TRB_LEAN_LAUNCH(1);
+        else if (classes <= 512) TRB_LEAN_LAUNCH(2);
+        else if (classes <= 1024) TRB_LEAN_LAUNCH(4);
+        else TRB_LEAN_LAUNCH(8);
+#undef TRB_LEAN_LAUNCH
+        TRB_LAUNCH_CHECK("softmax_ce_rows_warp_lean");
+        fused_tail = tail.ticket != nullptr;
+    } else if (rows_aligned && classes <= 2048) {
         const int warps = 8;
         int blocks = (batch + warps - 1) / warps;
         if (blocks > sm_count() * 8) blocks = sm_count() * 8;      // warps loop over rows
@@ -640,6 +982,52 @@ int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels
         else
             softmax_ce_rows_warp<8><<<grid, block, 0, s>>>(z, logits_stride, labels, scaling, label_smoothing, out, batch, classes);
         TRB_LAUNCH_CHECK("softmax_ce_rows_warp");
+    } else if (rows_aligned && classes % 8 == 0 && classes <= 32768 && !out.probs && out.dlogits && scaling &&
+               out.dlogits_stride % 8 == 0 && aligned16(out.dlogits)) {
+        // row in the block's registers: 256 threads x 2-5 vectors, 512 x 3-4 or 1024 x 3-4
+        const uint32_t buf_stride = (uint32_t)align_up((int64_t)classes * 2, 128);
+        const size_t smem = (size_t)buf_stride * 2;
+        const int nvec = classes / 8;
+        const int threads = nvec <= 1280 ? 256 : (nvec <= 2048 ? 512 : 1024);
+        const int vpt = (nvec + threads - 1) / threads;
+        int* status = nullptr;
+        TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_softmax_status));
+        int per_sm = (int)((200 * 1024) / smem);
+        const int reg_limit = threads == 256 ? 3 : (threads == 512 ? 2 : 1);
+        if (per_sm > reg_limit) per_sm = reg_limit;
+        if (per_sm < 1) per_sm = 1;
+        int grid = sm_count() * per_sm;
+        if (grid > batch) grid = batch;
+        if (grid > kLossTailBlocks) grid = kLossTailBlocks;
+        int dev = 0;
+        TRB_CUDA_TRY(cudaGetDevice(&dev));
+#define TRB_RG_LAUNCH(T, V)                                                                                          \
+    do {                                                                                                             \
+        static bool done[64] = {false};                                                                              \
+        if (dev >= 0 && dev < 64 && !done[dev]) {                                                                    \
+            TRB_CUDA_TRY(cudaFuncSetAttribute(softmax_ce_rows_regs<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                              200 * 1024));                                                          \
+            done[dev] = true;                                                                                        \
+        }                                                                                                            \
+        softmax_ce_rows_regs<T, V><<<grid, T, smem, s>>>(z, logits_stride, labels, scaling, label_smoothing,         \
+                                                         out.dlogits, out.dlogits_stride, out.loss_partial, batch,   \
+                                                         classes, buf_stride, status, tail);                         \
+    } while (0)
+        if (threads == 256) {
+            if (vpt <= 2) TRB_RG_LAUNCH(256, 2);
+            else if (vpt == 3) TRB_RG_LAUNCH(256, 3);
+            else if (vpt == 4) TRB_RG_LAUNCH(256, 4);
+            else TRB_RG_LAUNCH(256, 5);
+        } else if (threads == 512) {
+            if (vpt <= 3) TRB_RG_LAUNCH(512, 3);
+            else TRB_RG_LAUNCH(512, 4);
+        } else {
+            if (vpt <= 3) TRB_RG_LAUNCH(1024, 3);
+            else TRB_RG_LAUNCH(1024, 4);
+        }
+#undef TRB_RG_LAUNCH
+        TRB_LAUNCH_CHECK("softmax_ce_rows_regs");
+        fused_tail = tail.ticket != nullptr;
     } else if (rows_aligned && classes % 8 == 0 && (size_t)align_up((int64_t)classes * 2, 128) <= 48 * 1024) {
         const uint32_t buf_stride = (uint32_t)align_up((int64_t)classes * 2, 128);
         const size_t smem = (size_t)buf_stride * 2;
@@ -706,7 +1094,7 @@ int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels
 #undef TRB_SM_LAUNCH
         TRB_LAUNCH_CHECK("softmax_ce_rows_block");
     }
-    if (loss || inv_scaling) {
+    if ((loss || inv_scaling) && !fused_tail) {
         softmax_ce_loss_reduce<<<1, 1024, 0, s>>>(out.loss_partial, loss, inv_scaling, batch);
         TRB_LAUNCH_CHECK("softmax_ce_loss_reduce");
     }

@@ -167,7 +167,7 @@ def main():
     ap.add_argument("--quick", action="store_true", help="one small point per kernel (for profiler captures)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--batch", type=int, default=256, help="images for the conv / block points")
-    ap.add_argument("--shape", default="", help="H,C,K: only this conv shape (with --only conv)")
+    ap.add_argument("--shape", default="", help="H,C,K: only this conv shape (with --only conv); ROWS,CLASSES with --only softmax")
     ap.add_argument("--what", default="", help="comma list out of dgrad,wgrad,fprop,fprop_stats (with --only conv)")
     args = ap.parse_args()
     hbm, tc, src = peaks()
@@ -185,6 +185,9 @@ def main():
     if args.only in ("all", "softmax"):
         pts = [(4096, 32000, 0.1)] if args.quick else \
             [(b, c, ls) for b in (4096, 65536) for c in (1000, 10000, 32000) for ls in (0.0, 0.1)] + [(256, 1000, 0.0)]
+        if args.shape:
+            b, c = (int(v) for v in args.shape.split(","))
+            pts = [(b, c, 0.0)]
         for b, c, ls in pts:
             softmax_point(t, b, c, ls, hbm, src)
     if args.only in ("all", "conv"):

@@ -27,7 +27,10 @@ def _check(out, ref, want_probs, batch):
 @pytest.mark.parametrize("batch,classes,ls,scaling", [
     (1, 1, 0.0, 1.0), (3, 2, 0.0, 1.0), (8, 10, 0.0, 1.0), (5, 16, 0.1, 8.0), (64, 1000, 0.0, 1024.0),
     (64, 1000, 0.1, 1024.0), (33, 257, 0.1, 2.0), (16, 2048, 0.05, 1.0), (9, 2056, 0.1, 1.0),
-    (6, 10000, 0.0, 1024.0), (4, 32000, 0.1, 1024.0), (3, 4999, 0.1, 1.0)])
+    (6, 10000, 0.0, 1024.0), (4, 32000, 0.1, 1024.0), (3, 4999, 0.1, 1.0),
+    # every (threads, vectors per thread) variant of the register-resident row kernel, plus a ragged persistent loop
+    (5, 2560, 0.1, 4.0), (4, 6000, 0.0, 1024.0), (4, 8000, 0.1, 1.0), (3, 12000, 0.0, 16.0), (3, 16000, 0.1, 1.0),
+    (3, 24000, 0.0, 1024.0), (2, 32768, 0.1, 1.0), (700, 4096, 0.0, 1024.0), (3000, 1000, 0.1, 1024.0)])
 def test_fused_and_split_nodes_match_oracle(orc, batch, classes, ls, scaling):
     from renaissance_b200 import ops
     rng = np.random.default_rng(batch * 131 + classes)
