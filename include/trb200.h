@@ -237,7 +237,12 @@ int trb200_softmax_ce_bwd(const float* probs, int64_t probs_stride, const int32_
 
 /* Both nodes in one pass over the logits: reads each logit once, writes
  * d_logits (and probs if not NULL), loss partials, loss and inv_scaling.  The
- * arithmetic is that of the two nodes above. */
+ * arithmetic is that of the two nodes above.
+ * When probs is NULL and the rows are whole 16-byte vectors of at most 32768
+ * classes, the row kernel also finishes the loss (last block to end adds
+ * per-block sums in block order; bitwise reproducible on a given GPU) using one
+ * of 64 completion counters kept in the library: at most 64 such calls may be
+ * in flight on a GPU at a time. */
 int trb200_softmax_ce_fused(const void* logits, int64_t logits_stride, const int32_t* labels,
                             const float* scaling, const float* label_smoothing,
                             float* probs, int64_t probs_stride,
