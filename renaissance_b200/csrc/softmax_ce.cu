@@ -706,14 +706,16 @@ softmax_ce_rows_staged(const __half* __restrict__ logits, int64_t logits_stride,
 // thread takes exponentials against its own maximum, (max, sum) pairs are merged by rescaling
 // (warp shuffles, then one exchange through shared memory that every warp reads back), and the
 // thread's factor exp(own max - row max) / sum goes into the single FMA that makes the gradient.
+constexpr int kRegsMaxBuf = 4;
+
 template <int THREADS, int VPT>
 __global__ void __launch_bounds__(THREADS, THREADS == 256 ? 3 : (THREADS == 512 ? 2 : 1))
 softmax_ce_rows_regs(const __half* __restrict__ logits, int64_t logits_stride, const int32_t* __restrict__ labels,
                      const float* __restrict__ scaling, const float* __restrict__ label_smoothing,
                      __half* __restrict__ dlogits, int64_t dlogits_stride, float* __restrict__ loss_partial, int batch,
-                     int classes, uint32_t buf_stride, int* status, LossTail tail) {
+                     int classes, uint32_t buf_stride, int nbuf, int* status, LossTail tail) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t s_bar[2];
+    __shared__ __align__(8) uint64_t s_bar[kRegsMaxBuf];
     __shared__ float s_m[32], s_s[32], s_l[32];
     __shared__ int s_abort;
     constexpr int kWarps = THREADS / 32;
@@ -724,8 +726,7 @@ softmax_ce_rows_regs(const __half* __restrict__ logits, int64_t logits_stride, c
     const uint32_t bar0 = ptx::smem_u32(&s_bar[0]);
     if (tid == 0) {
         s_abort = 0;
-        ptx::mbar_init(bar0, 1);
-        ptx::mbar_init(bar0 + 8, 1);
+        for (int i = 0; i < nbuf; ++i) ptx::mbar_init(bar0 + 8u * i, 1);
         ptx::fence_barrier_init();
     }
     __syncthreads();
@@ -746,20 +747,31 @@ softmax_ce_rows_regs(const __half* __restrict__ logits, int64_t logits_stride, c
     };
 
     float my_loss = 0.f;
+    // rows blockIdx.x + k * gridDim.x; row k lives in buffer k % nbuf, and the rows up to nbuf - 1 ahead are on their way
     int row = blockIdx.x;
-    if (tid == 0 && row < batch) {
-        ptx::mbar_expect_tx(bar0, row_bytes);
-        ptx::bulk_load_1d(buf0, logits + (int64_t)row * logits_stride, row_bytes, bar0);
-    }
-    for (int it = 0; row < batch; row += gridDim.x, ++it) {
-        const int b = it & 1;
-        const int next = row + gridDim.x;
-        if (tid == 0 && next < batch) {       // the other buffer was released by the barrier that ended the last row
-            ptx::mbar_expect_tx(bar0 + 8u * (b ^ 1), row_bytes);
-            ptx::bulk_load_1d(buf0 + (uint32_t)(b ^ 1) * buf_stride, logits + (int64_t)next * logits_stride, row_bytes,
-                              bar0 + 8u * (b ^ 1));
+    if (tid == 0) {
+        for (int k = 0; k < nbuf - 1; ++k) {
+            const int64_t r = (int64_t)row + (int64_t)k * gridDim.x;
+            if (r < batch) {
+                ptx::mbar_expect_tx(bar0 + 8u * k, row_bytes);
+                ptx::bulk_load_1d(buf0 + (uint32_t)k * buf_stride, logits + r * logits_stride, row_bytes, bar0 + 8u * k);
+            }
         }
-        const bool ok = ptx::mbar_wait(bar0 + 8u * b, ((uint32_t)it >> 1) & 1u, &s_abort, status, 4);
+    }
+    int b = 0;
+    uint32_t phase = 0;
+    for (; row < batch; row += gridDim.x) {
+        {
+            // the buffer of the row before this one was released by the barrier that ended it: refill it
+            const int64_t r = (int64_t)row + (int64_t)(nbuf - 1) * gridDim.x;
+            const int bn = b == 0 ? nbuf - 1 : b - 1;
+            if (tid == 0 && r < batch) {
+                ptx::mbar_expect_tx(bar0 + 8u * bn, row_bytes);
+                ptx::bulk_load_1d(buf0 + (uint32_t)bn * buf_stride, logits + r * logits_stride, row_bytes,
+                                  bar0 + 8u * bn);
+            }
+        }
+        const bool ok = ptx::mbar_wait(bar0 + 8u * b, phase, &s_abort, status, 4);
         if (__syncthreads_or(ok ? 0 : 1)) break;
         const __half* srow = reinterpret_cast<const __half*>(smem_raw + (size_t)b * buf_stride);
         const int y = labels[row];
@@ -840,10 +852,11 @@ softmax_ce_rows_regs(const __half* __restrict__ logits, int64_t logits_stride, c
             if (loss_partial) loss_partial[row] = row_loss;
             my_loss += row_loss;
         }
-        // this buffer is refilled by a bulk copy two rows from now: order the generic-proxy
+        // this buffer is refilled by a bulk copy at the top of the next row: order the generic-proxy
         // reads above before it (the barrier also frees s_m / s_s / s_l for the next row)
         ptx::fence_proxy_async_smem();
         __syncthreads();
+        if (++b == nbuf) { b = 0; phase ^= 1u; }
     }
     if (*(volatile int*)&s_abort) {     // a wait gave up: let a copy that may still be in flight land before the block ends
         const unsigned long long t0 = ptx::global_ns();
@@ -986,16 +999,18 @@ int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels
                out.dlogits_stride % 8 == 0 && aligned16(out.dlogits)) {
         // row in the block's registers: 256 threads x 2-5 vectors, 512 x 3-4 or 1024 x 3-4
         const uint32_t buf_stride = (uint32_t)align_up((int64_t)classes * 2, 128);
-        const size_t smem = (size_t)buf_stride * 2;
         const int nvec = classes / 8;
         const int threads = nvec <= 1280 ? 256 : (nvec <= 2048 ? 512 : 1024);
         const int vpt = (nvec + threads - 1) / threads;
         int* status = nullptr;
         TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_softmax_status));
-        int per_sm = (int)((200 * 1024) / smem);
-        const int reg_limit = threads == 256 ? 3 : (threads == 512 ? 2 : 1);
-        if (per_sm > reg_limit) per_sm = reg_limit;
-        if (per_sm < 1) per_sm = 1;
+        // as many blocks per SM as the registers allow, then as deep a ring as shared memory allows
+        int per_sm = threads == 256 ? 3 : (threads == 512 ? 2 : 1);
+        while (per_sm > 1 && (size_t)per_sm * 2 * buf_stride > 200 * 1024) --per_sm;
+        int nbuf = (int)((200 * 1024) / ((size_t)per_sm * buf_stride));
+        if (nbuf > kRegsMaxBuf) nbuf = kRegsMaxBuf;
+        if (nbuf < 2) nbuf = 2;
+        const size_t smem = (size_t)buf_stride * nbuf;
         int grid = sm_count() * per_sm;
         if (grid > batch) grid = batch;
         if (grid > kLossTailBlocks) grid = kLossTailBlocks;
@@ -1011,7 +1026,7 @@ int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels
         }                                                                                                            \
         softmax_ce_rows_regs<T, V><<<grid, T, smem, s>>>(z, logits_stride, labels, scaling, label_smoothing,         \
                                                          out.dlogits, out.dlogits_stride, out.loss_partial, batch,   \
-                                                         classes, buf_stride, status, tail);                         \
+                                                         classes, buf_stride, nbuf, status, tail);                   \
     } while (0)
         if (threads == 256) {
             if (vpt <= 2) TRB_RG_LAUNCH(256, 2);

@@ -30,7 +30,9 @@ def _check(out, ref, want_probs, batch):
     (6, 10000, 0.0, 1024.0), (4, 32000, 0.1, 1024.0), (3, 4999, 0.1, 1.0),
     # every (threads, vectors per thread) variant of the register-resident row kernel, plus a ragged persistent loop
     (5, 2560, 0.1, 4.0), (4, 6000, 0.0, 1024.0), (4, 8000, 0.1, 1.0), (3, 12000, 0.0, 16.0), (3, 16000, 0.1, 1.0),
-    (3, 24000, 0.0, 1024.0), (2, 32768, 0.1, 1.0), (700, 4096, 0.0, 1024.0), (3000, 1000, 0.1, 1024.0)])
+    (3, 24000, 0.0, 1024.0), (2, 32768, 0.1, 1.0), (700, 4096, 0.0, 1024.0), (3000, 1000, 0.1, 1024.0),
+    # more rows than persistent blocks: the ring of row buffers wraps several times
+    (2000, 10000, 0.0, 1024.0), (700, 16000, 0.1, 1024.0), (400, 32000, 0.0, 1024.0)])
 def test_fused_and_split_nodes_match_oracle(orc, batch, classes, ls, scaling):
     from renaissance_b200 import ops
     rng = np.random.default_rng(batch * 131 + classes)
