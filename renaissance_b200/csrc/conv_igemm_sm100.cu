@@ -274,9 +274,17 @@ struct FpropSmem {
     static constexpr int kTotal = kStages * kStageBytes + kEpiBytes + kRawBytes + 2048;   // + alignment slack and barriers
 };
 
+// Issuing one TMA box costs its thread a few hundred clocks, which is more than the MMAs of a K step take when
+// the tile is narrow: the activation boxes of consecutive K steps are then issued by several warps in turn
+// (warps 0 and 3, and for NT = 64 two more warps behind the epilogue).
+template <int NT> __host__ __device__ constexpr int conv3x3_a_producers() { return NT == 64 ? 4 : (NT == 128 ? 2 : 1); }
+template <int NT, bool IM2COL> __host__ __device__ constexpr int conv3x3_threads() {
+    return IM2COL ? kThreads + kBuilderThreads : (NT == 64 ? kThreads + 64 : kThreads);
+}
+
 // IM2COL: 8 more warps (two groups of 128 threads) build the A tiles from the 4-channel image instead of TMA.
 template <int NT, bool STATS, bool IM2COL>
-__global__ void __launch_bounds__(IM2COL ? kThreads + kBuilderThreads : kThreads, 1)
+__global__ void __launch_bounds__(conv3x3_threads<NT, IM2COL>(), 1)
 conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_w,
                      const __grid_constant__ CUtensorMap tm_out, const FpropParams p, int* status) {
     using L = FpropSmem<NT, IM2COL>;
@@ -351,10 +359,10 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
             if (p.raw_ring) {
                 const uint32_t rs = (uint32_t)(it % kRawStages), rphase = (uint32_t)((it / kRawStages) & 1);
                 const int pitch = p.bw + 4;
-                if (!mbar_wait(rfull0 + 8u * rs, rphase, abort_flag, status, kStatusProducerTimeout)) break;
+                if (!mbar_wait_relaxed(rfull0 + 8u * rs, rphase, abort_flag, status, kStatusProducerTimeout)) break;
                 load_neighbourhood_raw(t, raw_base + rs * kRawStageBytes +
                                               (uint32_t)((((bi * (p.bh + 2)) + by + 1) * pitch + bx + 2) * 8), pitch);
-                if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                if (!mbar_wait_relaxed(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
                 store_im2col_row_c4(t, a_base + stage * kATileBytes, row);
                 mbar_arrive(rempty0 + 8u * rs);   // after the stores: the loads above have all returned
             } else {
@@ -362,7 +370,7 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
                 const int w0 = (mt % p.tw) * p.bw, h0 = ((mt / p.tw) % p.th) * p.bh;
                 const int n0 = (mt / (p.tw * p.th)) * p.bn;
                 load_neighbourhood_global(t, p.x4, n0 + bi, h0 + by, w0 + bx, p.ext_n, p.ext_h, p.ext_w);
-                if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                if (!mbar_wait_relaxed(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
                 store_im2col_row_c4(t, a_base + stage * kATileBytes, row);
             }
             fence_proxy_async_smem();             // generic-proxy stores -> visible to the MMA's async proxy
@@ -376,7 +384,7 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
                 const int mt = tile / p.n_tiles;
                 const int w0 = (mt % p.tw) * p.bw, h0 = ((mt / p.tw) % p.th) * p.bh;
                 const int n0 = (mt / (p.tw * p.th)) * p.bn;
-                if (!mbar_wait(rempty0 + 8u * rs, rphase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                if (!mbar_wait_relaxed(rempty0 + 8u * rs, rphase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
                 if (lane == 0) {
                     mbar_expect_tx(rfull0 + 8u * rs, raw_bytes);
                     tma_load_3d(raw_base + rs * kRawStageBytes, &tm_in, rfull0 + 8u * rs, w0 - 2, h0 - 1, n0);
@@ -385,9 +393,13 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
                 if (++rs == kRawStages) { rs = 0; rphase ^= 1u; }
             }
         }
-    } else if (warp == 0 && !IM2COL) {
-        {                                                  // producer A: one shifted activation box per K step
+    } else if (!IM2COL && (warp == 0 || (warp == 3 && conv3x3_a_producers<NT>() >= 2) ||
+                           (warp >= 8 && conv3x3_a_producers<NT>() >= 4))) {
+        {                                                  // producers A: one shifted activation box per K step,
+            constexpr int kAProd = conv3x3_a_producers<NT>();      // K steps dealt out to the producer warps in turn
+            const int pidx = warp == 0 ? 0 : (warp == 3 ? 1 : warp - 6);
             uint32_t stage = 0, phase = 0;
+            int turn = 0;                                  // index of the producer whose K step this is
             bool ok = true;
             RT_DECL;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -397,22 +409,30 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
                 for (int r = t_lo; r < t_hi && ok; ++r)
                     for (int s = t_lo; s < t_hi && ok; ++s)
                         for (int slice = 0; slice < p.cin_slices; ++slice) {
-                            RT_ADD(1);
-                            ok = mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout);
-                            RT_ADD(0);
-                            if (!ok) break;
-                            const uint32_t fb = full0 + 8u * stage;
-                            if (lane == 0) {
-                                mbar_expect_tx(fb, kATileBytes);
-                                tma_load_4d(a_base + stage * kATileBytes, &tm_in, fb, slice * 64, w0 + s - 1, h0 + r - 1,
-                                            n0);
+                            if (kAProd == 1 || turn == pidx) {
+                                RT_ADD(1);
+                                ok = mbar_wait_relaxed(empty0 + 8u * stage, phase ^ 1u, abort_flag, status,
+                                               kStatusProducerTimeout);
+                                RT_ADD(0);
+                                if (!ok) break;
+                                const uint32_t fb = full0 + 8u * stage;
+                                if (lane == 0) {
+#ifdef TRB200_EXP_NO_TMA
+                                    mbar_arrive(fb);
+#else
+                                    mbar_expect_tx(fb, kATileBytes);
+                                    tma_load_4d(a_base + stage * kATileBytes, &tm_in, fb, slice * 64, w0 + s - 1,
+                                                h0 + r - 1, n0);
+#endif
+                                }
+                                __syncwarp();
                             }
-                            __syncwarp();
+                            if (kAProd > 1 && ++turn == kAProd) turn = 0;
                             if (++stage == kStages) { stage = 0; phase ^= 1u; }
                         }
             }
             RT_ADD(1);
-            if (lane == 0) RT_STORE(0);
+            if (lane == 0 && warp == 0) RT_STORE(0);
         }
     } else if (warp == 2) {
         {                                                  // producer B: one filter tile per K step
@@ -422,15 +442,19 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
                 const int n_off = (tile % p.n_tiles) * NT;
                 for (int tap = 0; tap < p.taps && ok; ++tap)
                     for (int slice = 0; slice < p.cin_slices; ++slice) {
-                        ok = mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout);
+                        ok = mbar_wait_relaxed(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout);
                         if (!ok) break;
                         const uint32_t fb = full0 + 8u * stage;
                         if (lane == 0) {
+#ifdef TRB200_EXP_NO_TMA
+                            mbar_arrive(fb);
+#else
                             mbar_expect_tx(fb, L::kBTileBytes);
                             if (p.b_tap_is_dim1)
                                 tma_load_3d(b_base + stage * L::kBTileBytes, &tm_w, fb, slice * 64, tap, n_off);
                             else
                                 tma_load_3d(b_base + stage * L::kBTileBytes, &tm_w, fb, slice * 64, n_off, tap);
+#endif
                         }
                         __syncwarp();
                         if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -440,47 +464,51 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
     } else if (warp == 1) {
         {                                                  // MMA issuer
             constexpr uint32_t idesc = idesc_f16(128, NT, false, false);
-            constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
-            const uint32_t a_lo0 = smem_desc_lo(a_base, 16), b_lo0 = smem_desc_lo(b_base, 16);
-            uint32_t stage = 0, phase = 0;
-            bool ok = true;
-            int iter = 0;
-            RT_DECL;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
-                const int acc = iter & 1;
-                RT_ADD(2);
-                ok = mbar_wait(tempty_bar(acc), (((uint32_t)iter >> 1) & 1u) ^ 1u, abort_flag, status,
-                               kStatusMmaTimeout);
-                RT_ADD(0);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * NT);
-                uint32_t accumulate = 0;
-                for (int ks = 0; ks < ksteps; ++ks) {
+            // one thread runs the whole loop; per K step: wait, fence, two descriptor adds, four MMAs, commit
+            if (lane == 0) {
+                const uint64_t a_desc0 = smem_desc_sw128(a_base, 16, 1024), b_desc0 = smem_desc_sw128(b_base, 16, 1024);
+                uint32_t stage = 0, phase = 0;
+                uint64_t a_desc = a_desc0, b_desc = b_desc0;           // descriptors of the current stage
+                bool ok = true;
+                int iter = 0;
+                // the barrier of the next K step is probed before the MMAs of the current one are issued
+                bool ready = false;
+                RT_DECL;
+                for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
+                    const int acc = iter & 1;
                     RT_ADD(2);
-                    ok = mbar_wait(full0 + 8u * stage, phase, abort_flag, status, kStatusMmaTimeout);
-                    RT_ADD(1);
+                    ok = mbar_wait(tempty_bar(acc), (((uint32_t)iter >> 1) & 1u) ^ 1u, abort_flag, status,
+                                   kStatusMmaTimeout);
+                    RT_ADD(0);
                     if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t a_lo = a_lo0 + stage * (kATileBytes >> 4);
-                    const uint32_t b_lo = b_lo0 + stage * (L::kBTileBytes >> 4);
-                    // 4 x (K = 16 halfs = 32 bytes inside the 128-byte row: +2 in the address field)
-                    if (lane == 0) {
-                        umma_f16_lohi(d_tmem, a_lo, desc_hi, b_lo, desc_hi, idesc, accumulate);
-                        umma_f16_lohi(d_tmem, a_lo + 2, desc_hi, b_lo + 2, desc_hi, idesc, 1u);
-                        umma_f16_lohi(d_tmem, a_lo + 4, desc_hi, b_lo + 4, desc_hi, idesc, 1u);
-                        umma_f16_lohi(d_tmem, a_lo + 6, desc_hi, b_lo + 6, desc_hi, idesc, 1u);
-                        umma_commit(empty0 + 8u * stage);
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(acc * NT);
+                    uint32_t accumulate = 0;
+                    for (int ks = 0; ks < ksteps; ++ks) {
+                        RT_ADD(2);
+                        if (!ready) {
+                            ok = mbar_wait(full0 + 8u * stage, phase, abort_flag, status, kStatusMmaTimeout);
+                            if (!ok) break;
+                        }
+                        RT_ADD(1);
+                        const uint32_t cur = stage;
+                        const uint64_t a_cur = a_desc, b_cur = b_desc;
+                        if (++stage == kStages) {
+                            stage = 0; phase ^= 1u; a_desc = a_desc0; b_desc = b_desc0;
+                        } else {
+                            a_desc += (uint64_t)(kATileBytes >> 4); b_desc += (uint64_t)(L::kBTileBytes >> 4);
+                        }
+                        ready = mbar_test_wait(full0 + 8u * stage, phase);
+                        tc_fence_after();
+                        umma_f16_x4<2>(d_tmem, a_cur, b_cur, idesc, accumulate);
+                        umma_commit(empty0 + 8u * cur);
+                        accumulate = 1u;
                     }
-                    __syncwarp();
-                    accumulate = 1u;
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    if (ok) umma_commit(tfull_bar(acc));
                 }
-                if (ok && lane == 0) umma_commit(tfull_bar(acc));
-                __syncwarp();
+                RT_ADD(2);
+                RT_STORE(1);
             }
-            RT_ADD(2);
-            if (lane == 0) RT_STORE(1);
+            __syncwarp();
         }
     } else if (warp >= 4 && warp < 8) {
         // epilogue: warp w may touch TMEM lanes [32*(w%4), +32)
@@ -512,7 +540,7 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
                 const uint32_t m = __ballot_sync(0xffffffffu, real);
                 if (lane == 0) s_valid[q] = m;
             }
-            if (!mbar_wait(tfull_bar(acc), ((uint32_t)iter >> 1) & 1u, abort_flag, status, kStatusEpilogueTimeout))
+            if (!mbar_wait_relaxed(tfull_bar(acc), ((uint32_t)iter >> 1) & 1u, abort_flag, status, kStatusEpilogueTimeout))
                 s_epi_fail = 1;
             // the 128 epilogue threads must take the same decision: they meet at named barriers below
             named_barrier(2, kEpiThreads);
@@ -522,7 +550,11 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
             uint32_t vm = 0xffu;      // which of this thread's 8 rows are real pixels
             if (STATS && p.has_padding) vm = (s_valid[st_rg >> 2] >> ((st_rg & 3) * 8)) & 0xffu;
 #pragma unroll
+#ifdef TRB200_EXP_NO_EPI
+            for (int chunk = 0; chunk < 0; ++chunk, ++chunk_count) {
+#else
             for (int chunk = 0; chunk < NT / 64; ++chunk, ++chunk_count) {
+#endif
                 const uint32_t buf = epi_base + (uint32_t)(chunk_count & 1) * kATileBytes;
                 RT_ADD(2);
                 if (leader) tma_store_wait_read<1>();     // the store that last read this buffer is done
@@ -660,7 +692,7 @@ int launch_conv3x3(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensor
     int* status = nullptr;
     TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status));
     const int grid = conv3x3_grid(p.m_tiles, p.n_tiles);
-    conv3x3_igemm_kernel<NT, STATS, IM2COL><<<grid, IM2COL ? kThreads + kBuilderThreads : kThreads, L::kTotal, st>>>(tin, tw, tout,
+    conv3x3_igemm_kernel<NT, STATS, IM2COL><<<grid, conv3x3_threads<NT, IM2COL>(), L::kTotal, st>>>(tin, tw, tout,
                                                                                                        p, status);
     TRB_LAUNCH_CHECK("conv3x3_igemm_kernel");
     return TRB200_OK;
@@ -859,13 +891,13 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 if (p.raw_ring) {
                     const uint32_t rs = (uint32_t)(it % kRawStages), rphase = (uint32_t)((it / kRawStages) & 1);
                     const int pitch = p.bw + 4;
-                    if (!mbar_wait(rfull0 + 8u * rs, rphase, abort_flag, status, kStatusProducerTimeout)) break;
+                    if (!mbar_wait_relaxed(rfull0 + 8u * rs, rphase, abort_flag, status, kStatusProducerTimeout)) break;
                     load_neighbourhood_raw(t, raw_base + rs * kRawStageBytes +
                                                   (uint32_t)((((bi * (p.bh + 2)) + by + 1) * pitch + bx + 2) * 8), pitch);
                 } else {
                     load_neighbourhood_global(t, p.x4, n0 + bi, h0 + by, w0 + bx, p.ext_n, p.ext_h, p.ext_w);
                 }
-                if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                if (!mbar_wait_relaxed(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
                 store_im2col_row_c4(t, a_dst, row);
                 store_im2col_row_c4(t, a_dst + kStageTileBytes, row);
                 if (p.raw_ring) mbar_arrive(rempty0 + 8u * (uint32_t)(it % kRawStages));
@@ -881,7 +913,7 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             uint32_t rs = 0, rphase = 0;
             int w0 = w_first, h0 = h_first, n0 = n_first;
             for (int pt = pt0; pt < pt1; ++pt) {
-                if (!mbar_wait(rempty0 + 8u * rs, rphase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                if (!mbar_wait_relaxed(rempty0 + 8u * rs, rphase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
                 if (lane == 0) {
                     mbar_expect_tx(rfull0 + 8u * rs, raw_bytes);
                     tma_load_3d(raw_base + rs * kRawStageBytes, &tm_x, rfull0 + 8u * rs, w0 - 2, h0 - 1, n0);
@@ -902,7 +934,7 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             uint32_t stage = 0, phase = 0;
             int w0 = w_first, h0 = h_first, n0 = n_first;
             for (int pt = pt0; pt < pt1; ++pt) {
-                if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                if (!mbar_wait_relaxed(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
                 const uint32_t fb = full0 + 8u * stage;
                 const uint32_t a_dst = a_base + stage * L::kABytes;
                 if (lane == 0) {
@@ -924,7 +956,7 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             uint32_t stage = 0, phase = 0;
             int w0 = w_first, h0 = h_first, n0 = n_first;
             for (int pt = pt0; pt < pt1; ++pt) {
-                if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+                if (!mbar_wait_relaxed(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
                 const uint32_t fb = full0 + 8u * stage;
                 const uint32_t b_dst = b_base + stage * L::kBBytes + j0 * kStageTileBytes;
                 if (lane == 0) {
@@ -974,7 +1006,7 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const int row = q * 32 + lane;
         float* dst = partial + ((size_t)item * 128 + row) * NT;
         if (pt1 > pt0) {
-            if (mbar_wait(done_bar, 0, abort_flag, status, kStatusEpilogueTimeout)) {
+            if (mbar_wait_relaxed(done_bar, 0, abort_flag, status, kStatusEpilogueTimeout)) {
                 tc_fence_after();
 #pragma unroll 1
                 for (int c0 = 0; c0 < NT; c0 += 32) {

@@ -152,7 +152,7 @@ conv3x3_pixn_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
             const int c_off = (tile % p.c_tiles) * MT;
             for (int tap = 0; tap < p.taps && ok; ++tap)
                 for (int slice = 0; slice < p.cin_slices; ++slice) {
-                    ok = mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout);
+                    ok = mbar_wait_relaxed(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout);
                     if (!ok) break;
                     const uint32_t fb = full0 + 8u * stage;
                     if (lane == 0) {
@@ -182,7 +182,7 @@ conv3x3_pixn_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
                 for (int s = t_lo; s < t_hi && ok; ++s)
                     for (int slice = 0; slice < p.cin_slices; ++slice) {
                         RT_ADD(1);
-                        ok = mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout);
+                        ok = mbar_wait_relaxed(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout);
                         RT_ADD(0);
                         if (!ok) break;
                         const uint32_t fb = full0 + 8u * stage;
@@ -262,7 +262,7 @@ conv3x3_pixn_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
             const bool live = (MT == 64 ? q * 16 : q * 32) < halves * 64;   // warp-uniform
             const bool keep = MT == 128 || lane < 16;
             RT_ADD(2);
-            if (!mbar_wait(tfull_bar(acc), ((uint32_t)iter >> 1) & 1u, abort_flag, status, kStatusEpilogueTimeout))
+            if (!mbar_wait_relaxed(tfull_bar(acc), ((uint32_t)iter >> 1) & 1u, abort_flag, status, kStatusEpilogueTimeout))
                 s_epi_fail = 1;
             named_barrier(2, kEpiThreads);
             RT_ADD(0);

@@ -56,6 +56,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking probe of a phase: returns at once.  Issued ahead of the work of the current stage, its
+// shared-memory round trip (about a hundred clocks for the one thread that runs a role) overlaps that work.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait.  `abort_flag` is a shared-memory word of the block; once any role
 // sets it every other wait of the block returns false at its next poll.
 // `status` is a global word: the first failure stores `code` there.
@@ -66,6 +80,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 255u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+
+// The same for roles that are far ahead of (or behind) their partner most of the time: producers waiting for a
+// free stage, the epilogue waiting for a tile.  Every failed probe is followed by a short sleep: a warp that spins on
+// mbarrier.try_wait keeps the SM's asynchronous-operation path busy and was measured to double the issue time of
+// another warp's tcgen05.mma instructions (107 against 56 clocks per 128x64x16 MMA).
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  int* status, int code) {
+    if (mbar_test_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t it = 1;; ++it) {
+        __nanosleep(it < 8 ? 64 : 256);
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((it & 63u) == 0u) {
             if (*abort_flag) return false;
             if (global_ns() - t0 > kWaitLimitNs) {
                 *abort_flag = 1;
@@ -174,6 +210,28 @@ __device__ __forceinline__ void umma_f16_lohi(uint32_t d_tmem, uint32_t a_lo, ui
         "setp.ne.b32 p, %6, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
         ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Four MMAs over one 64-element K slice of both operands (K = 16 each) in one instruction block: 64-bit
+// descriptors, the start-address field advanced by KADV per step (2 = 32 bytes of a K-major row, 128 = 16 rows of
+// an MN-major tile); only the first one takes the accumulate flag, the others always accumulate.  Keeps the
+// issuing thread at one predicate set-up and six adds per four MMAs.
+template <int KADV>
+__device__ __forceinline__ void umma_f16_x4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 q, 0, 0;\n\t"
+        "add.u64 a1, %1, %5;\n\tadd.u64 b1, %2, %5;\n\t"
+        "add.u64 a2, a1, %5;\n\tadd.u64 b2, b1, %5;\n\t"
+        "add.u64 a3, a2, %5;\n\tadd.u64 b3, b2, %5;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, q;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "n"(KADV)
         : "memory");
 }
 

@@ -96,7 +96,7 @@ wgrad_unitn_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         uint32_t stage = 0, phase = 0;
         int w0 = w_first, h0 = h_first, n0 = n_first;
         for (int pt = pt0; pt < pt1; ++pt) {
-            if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+            if (!mbar_wait_relaxed(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
             const uint32_t fb = full0 + 8u * stage;
             const uint32_t a_dst = a_base + stage * kUnABytes;
             if (lane == 0) {
@@ -126,7 +126,7 @@ wgrad_unitn_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         RT_DECL;
         for (int pt = pt0; pt < pt1; ++pt) {
             RT_ADD(1);
-            if (!mbar_wait(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
+            if (!mbar_wait_relaxed(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
             RT_ADD(0);
             const uint32_t fb = full0 + 8u * stage;
             const uint32_t b_dst = b_base + stage * kUnBBytes + j0 * kStageTileBytes;
@@ -184,7 +184,7 @@ wgrad_unitn_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const bool live = q * 32 < p.k_halves * 64;          // warp-uniform
         float* dst = partial + ((size_t)item * 128 + row) * 256;
         if (pt1 > pt0) {
-            if (mbar_wait(done_bar, 0, abort_flag, status, kStatusEpilogueTimeout) && live) {
+            if (mbar_wait_relaxed(done_bar, 0, abort_flag, status, kStatusEpilogueTimeout) && live) {
                 tc_fence_after();
 #pragma unroll 1
                 for (int c0 = 0; c0 < nu * 64; c0 += 32) {

@@ -66,6 +66,27 @@ def emit(**kw):
     print(json.dumps(kw), flush=True)
 
 
+def _library(t, build):
+    """Times a cuDNN graph of the reference's path (renaissance_b200.cudnn_reference); {} when not asked for."""
+    if not WITH_CUDNN:
+        return {}
+    try:
+        run = build()
+        med, _ = t(run)
+        return {"cudnn_ms": round(med, 4)}
+    except Exception as e:          # an unsupported graph is a result, not a failure of the sweep
+        return {"cudnn_ms": None, "cudnn_note": str(e).splitlines()[0][:160]}
+
+
+def _nhw(m):
+    if m == 256 * 56 * 56:
+        return (256, 56, 56)
+    return (m >> 12, 64, 64) if m % 4096 == 0 else (m, 1, 1)
+
+
+WITH_CUDNN = False
+
+
 def bnrelu_point(t, m, c, hbm, src):
     g = torch.Generator(device="cuda").manual_seed(0)
     dy = torch.randn((m, c), generator=g, device="cuda").half()
@@ -77,9 +98,16 @@ def bnrelu_point(t, m, c, hbm, src):
     out = torch.empty_like(dy)
     med, best = t(lambda: ops.bnrelu_bwd(dy, bits, x, gamma, mean, inv, dconv=out))
     byt = 10.25 * m * c + 20 * c
+
+    def build():
+        from . import cudnn_reference as cr
+        dg, db = torch.empty(c, device="cuda"), torch.empty(c, device="cuda")
+        return cr.bnrelu_bwd(dy, bits, x, gamma, mean, inv, torch.empty_like(dy), dg, db, nhw=_nhw(m))
+
+    lib = _library(t, build)
     emit(kernel="bnrelu_bwd (reduce + finalize + apply)", rows=m, channels=c, ms=round(med, 4), best_ms=round(best, 4),
          bound="hbm", achieved=round(byt / med / 1e6, 1), peak=hbm, unit="GB/s", frac=round(byt / med / 1e6 / hbm, 4),
-         peak_source=src)
+         peak_source=src, **lib)
 
 
 def softmax_point(t, b, c, ls, hbm, src):
@@ -118,9 +146,24 @@ def conv_point(t, n, h, c, k, what, tc, src):
         y = torch.empty_like(dy)
         med, best = t(lambda: ops.conv_fprop(geo, x, w, y=y))
     ops.device_status()
+
+    def build():
+        from . import cudnn_reference as cr
+        if c < 8:
+            raise RuntimeError("the reference pads the first layer to 4 channels; cuDNN tensor-core graphs need C % 8 == 0")
+        if what == "dgrad":
+            return cr.conv_dgrad(dy, w, torch.empty_like(x))
+        if what == "wgrad":
+            return cr.conv_wgrad(x, dy, torch.empty_like(w))
+        if what == "fprop_stats":
+            st = (torch.empty(k, device="cuda"), torch.empty(k, device="cuda"))
+            return cr.conv_fprop(x, w, torch.empty_like(dy), genstats=st)
+        return cr.conv_fprop(x, w, torch.empty_like(dy))
+
+    lib = _library(t, build)
     emit(kernel=f"conv {what}", shape=dict(n=n, h=h, w=h, c=c, k=k), ms=round(med, 4), best_ms=round(best, 4),
          bound="tensor", achieved=round(flop / med / 1e9, 1), peak=tc, unit="TFLOP/s",
-         frac=round(flop / med / 1e9 / tc, 4), peak_source=src)
+         frac=round(flop / med / 1e9 / tc, 4), peak_source=src, **lib)
 
 
 def block_point(t, n, h, c, k, hbm, tc, src):
@@ -167,9 +210,13 @@ def main():
     ap.add_argument("--quick", action="store_true", help="one small point per kernel (for profiler captures)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--batch", type=int, default=256, help="images for the conv / block points")
+    ap.add_argument("--cudnn", action="store_true",
+                    help="also time the reference's cuDNN-frontend graphs for the conv and BN+ReLU points (cudnn_ms)")
     ap.add_argument("--shape", default="", help="H,C,K: only this conv shape (with --only conv); ROWS,CLASSES with --only softmax")
     ap.add_argument("--what", default="", help="comma list out of dgrad,wgrad,fprop,fprop_stats (with --only conv)")
     args = ap.parse_args()
+    global WITH_CUDNN
+    WITH_CUDNN = args.cudnn
     hbm, tc, src = peaks()
     t = Timer(1 if args.quick else args.iters)
     n = args.batch
