@@ -270,14 +270,18 @@ struct FpropSmem {
     static constexpr int kStageBytes = kATileBytes + kBTileBytes;
     static constexpr int kEpiBytes = 2 * kATileBytes;
     static constexpr int kRawBytes = IM2COL ? kRawStages * kRawStageBytes : 0;
-    static constexpr int kStages = (kSmemBudget - 2048 - kEpiBytes - kRawBytes) / kStageBytes;
+    // parties that take stages in turn (builder groups, producers dealt K steps) need a ring they divide, so that a
+    // stage always has the same owner: a parity wait is only safe for a party that has seen the previous use of the
+    // same stage complete.  The ring is 8 stages, or the largest even count that fits.
+    static constexpr int kStagesFit = (kSmemBudget - 2048 - kEpiBytes - kRawBytes) / kStageBytes;
+    static constexpr int kStages = kStagesFit >= 8 ? 8 : (kStagesFit >= 2 ? kStagesFit / 2 * 2 : kStagesFit);
     static constexpr int kTotal = kStages * kStageBytes + kEpiBytes + kRawBytes + 2048;   // + alignment slack and barriers
 };
 
 // Issuing one TMA box costs its thread a few hundred clocks, which is more than the MMAs of a K step take when
 // the tile is narrow: the activation boxes of consecutive K steps are then issued by several warps in turn
 // (warps 0 and 3, and for NT = 64 two more warps behind the epilogue).
-template <int NT> __host__ __device__ constexpr int conv3x3_a_producers() { return NT == 64 ? 4 : (NT == 128 ? 2 : 1); }
+template <int NT> __host__ __device__ constexpr int conv3x3_a_producers() { return NT == 64 ? 4 : 2; }
 template <int NT, bool IM2COL> __host__ __device__ constexpr int conv3x3_threads() {
     return IM2COL ? kThreads + kBuilderThreads : (NT == 64 ? kThreads + 64 : kThreads);
 }
@@ -333,6 +337,8 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
     const uint32_t tmem_base = s_tmem_base;
     volatile int* abort_flag = &s_abort;
 
+    static_assert(IM2COL || kStages % conv3x3_a_producers<NT>() == 0, "a stage keeps its A producer");
+    static_assert(!IM2COL || kStages % (kBuilderThreads / 128) == 0, "a stage keeps its builder group");
     const int total_tiles = p.m_tiles * p.n_tiles;
     const int ksteps = p.taps * p.cin_slices;
     // tap window: 3x3 walks r, s in [0, 3); 1x1 is the centre tap only
@@ -812,7 +818,8 @@ struct WgradSmem {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kRawBytes = IM2COL ? kRawStages * kRawStageBytes : 0;
     static constexpr int kStagesRaw = (kSmemBudget - 2048 - kRawBytes) / kStageBytes;
-    static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+    // the first-layer builder groups take stages in turn: a ring of 8 or 4 keeps every stage with one group
+    static constexpr int kStages = kStagesRaw >= 8 ? 8 : (IM2COL && kStagesRaw >= 4 ? 4 : kStagesRaw);
     static constexpr int kTotal = kStages * kStageBytes + kRawBytes + 2048;
 };
 
@@ -879,6 +886,7 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         // operand get the same rows (there is a single (tap, channel) unit)
         // group g takes the block's stages g, g + 4, ...
         constexpr int kGroups = kBuilderThreads / 64;
+        static_assert(!IM2COL || kStages % kGroups == 0, "a stage keeps its builder group");
         const int row = (threadIdx.x - kThreads) & 63, group = (threadIdx.x - kThreads) >> 6;
         const int bx = row & (p.bw - 1), by = (row >> p.lbw) & (p.bh - 1), bi = row >> (p.lbw + p.lbh);
         int w0 = w_first, h0 = h_first, n0 = n_first;
