@@ -967,7 +967,10 @@ int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels
         out.dlogits_stride % 8 == 0 && aligned16(out.dlogits)) {
         const int warps = 8;
         int blocks = (batch + warps - 1) / warps;
-        if (blocks > sm_count() * 8) blocks = sm_count() * 8;      // warps loop over rows
+        // exactly the blocks that are resident at once (3 per SM, 2 for the widest rows): warps loop over rows, and a
+        // grid of several partial waves would leave the last one half empty
+        const int resident = sm_count() * (classes > 1024 ? 2 : 3);
+        if (blocks > resident) blocks = resident;
         if (blocks > kLossTailBlocks) blocks = kLossTailBlocks;
         dim3 grid(blocks), block(warps * 32);
 #define TRB_LEAN_LAUNCH(V)                                                                                       \
