@@ -26,13 +26,20 @@
 //   partial tile and a second kernel adds the splits in split order (bitwise
 //   reproducible) and writes half KRSC.
 //
-// Warp roles (256 threads): warp 0 = TMA producer for the A operand, warp 1 = MMA
-// issuer + TMEM allocation, warps 2 (and 3) = TMA producers for the B operand,
-// warps 4-7 = epilogue (TMEM -> registers -> half -> shared -> TMA store, or float
-// partial -> global).  Issuing a TMA box costs its thread a few hundred clocks, so
-// the loads of a stage are spread over two or three threads that all arrive on the
-// stage's "full" barrier.  Two accumulator buffers in TMEM let the epilogue of tile i
-// overlap the main loop of tile i+1.
+// Warp roles (256 threads and up): warp 0 (and 3, 8, 9) = TMA producers for the activation operand, warp 1 = MMA
+// issuer + TMEM allocation, warp 2 (and 3 / 8) = TMA producers for the filter / dconv operand, warps 4-7 =
+// epilogue (TMEM -> registers -> half -> shared -> TMA store, or float partial -> global).  One thread pays about
+// 55 clocks for every tcgen05.mma, commit or barrier probe it issues and a few hundred for a TMA box, so the loads
+// of a stage are spread over several threads that all arrive on the stage's "full" barrier, K steps are dealt to
+// producer warps in turn, and the MMA issuer probes the barrier of its next stage before it issues the MMAs of the
+// current one.  A stage of a ring keeps the same producers and the same consumer for the whole kernel (the rings
+// have a length their parties divide): a parity wait is only safe for a party that saw the previous use of that
+// stage complete.  Two accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// A tcgen05.mma occupies the tensor pipe for max(N / 2, operand bytes / 128) clocks whatever M is, and the issuer's
+// ~460 clocks per K step of four MMAs hide behind it only at N = 256.  The kernels of this file therefore serve the
+// layers with 256 channels or more on N; conv_pixn_sm100.cuh (pixels on N) and wgrad_unitn_sm100.cuh ((tap,
+// channel-block) units on N) serve the layers with 64 or 128.
 #include "common.cuh"
 #include "conv.cuh"
 #include "sm100_ptx.cuh"
@@ -282,8 +289,10 @@ struct FpropSmem {
 // the tile is narrow: the activation boxes of consecutive K steps are then issued by several warps in turn
 // (warps 0 and 3, and for NT = 64 two more warps behind the epilogue).
 template <int NT> __host__ __device__ constexpr int conv3x3_a_producers() { return NT == 64 ? 4 : 2; }
+// the 256-row filter tile is fetched as two 128-row boxes by two warps (warp 2 and warp 8)
+template <int NT, bool IM2COL> __host__ __device__ constexpr int conv3x3_b_split() { return (NT == 256 && !IM2COL) ? 2 : 1; }
 template <int NT, bool IM2COL> __host__ __device__ constexpr int conv3x3_threads() {
-    return IM2COL ? kThreads + kBuilderThreads : (NT == 64 ? kThreads + 64 : kThreads);
+    return IM2COL ? kThreads + kBuilderThreads : (NT == 64 ? kThreads + 64 : (NT == 256 ? kThreads + 32 : kThreads));
 }
 
 // IM2COL: 8 more warps (two groups of 128 threads) build the A tiles from the 4-channel image instead of TMA.
@@ -318,7 +327,7 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
         s_abort = 0;
         s_epi_fail = 0;
         // a stage is full once its B tile has landed and its A tile has (one TMA box, or 128 built rows)
-        for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8u * s, IM2COL ? 129 : 2); mbar_init(empty0 + 8u * s, 1); }
+        for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8u * s, IM2COL ? 129 : 1 + conv3x3_b_split<NT, IM2COL>()); mbar_init(empty0 + 8u * s, 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), kEpiThreads); }
         if (IM2COL)
             for (int s = 0; s < kRawStages; ++s) { mbar_init(rfull0 + 8u * s, 1); mbar_init(rempty0 + 8u * s, 128); }
@@ -423,13 +432,9 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
                                 if (!ok) break;
                                 const uint32_t fb = full0 + 8u * stage;
                                 if (lane == 0) {
-#ifdef TRB200_EXP_NO_TMA
-                                    mbar_arrive(fb);
-#else
                                     mbar_expect_tx(fb, kATileBytes);
                                     tma_load_4d(a_base + stage * kATileBytes, &tm_in, fb, slice * 64, w0 + s - 1,
                                                 h0 + r - 1, n0);
-#endif
                                 }
                                 __syncwarp();
                             }
@@ -440,27 +445,27 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
             RT_ADD(1);
             if (lane == 0 && warp == 0) RT_STORE(0);
         }
-    } else if (warp == 2) {
-        {                                                  // producer B: one filter tile per K step
+    } else if (warp == 2 || (conv3x3_b_split<NT, IM2COL>() == 2 && warp == 8)) {
+        {                                                  // producer(s) B: one filter tile per K step; the 256-row
+            constexpr int kSplit = conv3x3_b_split<NT, IM2COL>();   // tile is fetched as two boxes by two warps
+            constexpr uint32_t kBoxBytes = L::kBTileBytes / kSplit;
+            const int half = warp == 2 ? 0 : 1;
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int n_off = (tile % p.n_tiles) * NT;
+                const int n_off = (tile % p.n_tiles) * NT + half * (NT / kSplit);
                 for (int tap = 0; tap < p.taps && ok; ++tap)
                     for (int slice = 0; slice < p.cin_slices; ++slice) {
                         ok = mbar_wait_relaxed(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout);
                         if (!ok) break;
                         const uint32_t fb = full0 + 8u * stage;
                         if (lane == 0) {
-#ifdef TRB200_EXP_NO_TMA
-                            mbar_arrive(fb);
-#else
-                            mbar_expect_tx(fb, L::kBTileBytes);
+                            mbar_expect_tx(fb, kBoxBytes);
+                            const uint32_t dst = b_base + stage * L::kBTileBytes + (uint32_t)half * kBoxBytes;
                             if (p.b_tap_is_dim1)
-                                tma_load_3d(b_base + stage * L::kBTileBytes, &tm_w, fb, slice * 64, tap, n_off);
+                                tma_load_3d(dst, &tm_w, fb, slice * 64, tap, n_off);
                             else
-                                tma_load_3d(b_base + stage * L::kBTileBytes, &tm_w, fb, slice * 64, n_off, tap);
-#endif
+                                tma_load_3d(dst, &tm_w, fb, slice * 64, n_off, tap);
                         }
                         __syncwarp();
                         if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -556,11 +561,7 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
             uint32_t vm = 0xffu;      // which of this thread's 8 rows are real pixels
             if (STATS && p.has_padding) vm = (s_valid[st_rg >> 2] >> ((st_rg & 3) * 8)) & 0xffu;
 #pragma unroll
-#ifdef TRB200_EXP_NO_EPI
-            for (int chunk = 0; chunk < 0; ++chunk, ++chunk_count) {
-#else
             for (int chunk = 0; chunk < NT / 64; ++chunk, ++chunk_count) {
-#endif
                 const uint32_t buf = epi_base + (uint32_t)(chunk_count & 1) * kATileBytes;
                 RT_ADD(2);
                 if (leader) tma_store_wait_read<1>();     // the store that last read this buffer is done
@@ -741,16 +742,17 @@ int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int 
     else if (x4) tin = tout;      // not used by the kernel
     else rc = make_act_tmap(&tin, in, n, h, w, cin, t, "conv input");
     if (rc) return rc;
+    const int b_rows = (nt == 256 && !x4) ? 128 : nt;      // rows of one filter box (the 256-row tile takes two)
     if (tap_is_dim1) {
         // KRSC as stored: (ci, tap, co)
         const uint64_t dims[3] = {(uint64_t)cin, (uint64_t)taps, (uint64_t)cout};
         const uint64_t str[3] = {2, (uint64_t)cin * 2, (uint64_t)taps * cin * 2};
-        const uint32_t box[3] = {64, 1, (uint32_t)nt};
+        const uint32_t box[3] = {64, 1, (uint32_t)b_rows};
         rc = make_tmap(&tw, wv, 3, dims, str, box, "filters (ci,tap,co)");
     } else {
         const uint64_t dims[3] = {(uint64_t)cin, (uint64_t)cout, (uint64_t)taps};
         const uint64_t str[3] = {2, (uint64_t)cin * 2, (uint64_t)cout * cin * 2};
-        const uint32_t box[3] = {64, (uint32_t)nt, 1};
+        const uint32_t box[3] = {64, (uint32_t)b_rows, 1};
         rc = make_tmap(&tw, wv, 3, dims, str, box, "filters (ci,co,tap)");
     }
     if (rc) return rc;

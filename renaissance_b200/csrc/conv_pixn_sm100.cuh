@@ -1,10 +1,11 @@
 // 3x3 / stride 1 / pad 1 convolution (forward and data gradient) with the output PIXELS on
 // the MMA's N dimension, for layers with 64 or 128 output channels.
 //
-// A tcgen05.mma of shape M x N x 16 occupies the tensor pipe for about M clocks whatever N is
-// (measured: the same ~120 clocks per instruction at M = 128 for N = 64, 128 and 256), so the
-// pipe is only full at N = 256.  The kernels in conv_igemm_sm100.cu put the output channels
-// on N and reach 28 % / 60 % of peak at 64 / 128 channels.  Here the GEMM is transposed:
+// A tcgen05.mma of shape M x N x 16 occupies the tensor pipe for max(N / 2, operand bytes / 128) clocks whatever
+// M is, and the thread that issues it pays about 55 clocks per MMA, commit or barrier probe: a K step of four MMAs
+// costs its issuer ~460 clocks inside a kernel, which only N = 256 (512 pipe clocks) hides.  The kernels in
+// conv_igemm_sm100.cu put the output channels on N and reach 28 % / 60 % of peak at 64 / 128 channels.  Here the
+// GEMM is transposed:
 //
 //   D[co][pixel] = sum_{tap} sum_{ci} Wv[tap][co][ci] * in[pixel + tap offset][ci]
 //   M = MT output channels (A operand = filters, K-major rows of 64 input channels),

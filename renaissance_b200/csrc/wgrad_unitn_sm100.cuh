@@ -8,9 +8,9 @@
 //   N = up to 4 units = 256 columns (B operand = tap-shifted boxes of X, MN-major),
 //   K loop = pixels, 64 per stage.
 //
-// A tcgen05.mma costs about the same ~120 clocks for every shape up to 128 x 256 x 16, so the
-// instruction count decides: with the filters on N (wgrad_igemm_kernel) a 64-filter layer needs
-// one instruction per two units and 16 pixels, here one per four units.
+// The thread that issues the MMAs pays about 55 clocks per tcgen05.mma, commit or barrier probe, so its ~460
+// clocks per K step of four MMAs hide behind the tensor pipe only at N = 256 (4 x 128 clocks): with the filters on N
+// (wgrad_igemm_kernel) a 64-filter layer needs one instruction per two units and 16 pixels, here one per four units.
 //
 // Work item = (split of the pixel range, block of 128 filters, group of 4 units); every item
 // leaves a float partial tile and wgrad_unitn_reduce adds the splits in split order (bitwise
