@@ -8,6 +8,8 @@
 //   y = relu(t), mask = t > 0, t = half(half(x*eq_scale) + eq_bias) cbr_op.cpp:534-616
 //   max pooling with argmax byte (kh*k + kw, first maximum wins)    maxpool_op.cu:23-217
 #include "common.cuh"
+
+#include <cuda_fp16.h>
 #include "conv.cuh"
 
 namespace trb {
@@ -164,20 +166,21 @@ bn_apply_relu_mask(const uint4* __restrict__ x, const float* __restrict__ eq_sca
         for (int u = 0; u < kUnroll; ++u) {
             const int64_t r = row + (int64_t)u * by;
             if (r >= r1) continue;
-            float f[8];
-            unpack8(v[u], f);
-            uint4 o;
-            __half* oh = reinterpret_cast<__half*>(&o);
+            // two channels per packed conversion and comparison; the roundings are those of the scalar form
+            const __half2* h = reinterpret_cast<const __half2*>(&v[u]);
+            const __half2 zero2 = __float2half2_rn(0.f);
+            uint32_t o[4];
             uint32_t bits = 0;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const __half a = __float2half_rn(f[j] * sc[j]);
-                const __half t = __float2half_rn(__half2float(a) + bi[j]);
-                const bool on = __half2float(t) > 0.f;
-                oh[j] = on ? t : __float2half_rn(0.f);
-                bits |= (on ? 1u : 0u) << j;
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]);
+                const float2 a = __half22float2(__floats2half2_rn(f.x * sc[2 * i], f.y * sc[2 * i + 1]));
+                const __half2 t = __floats2half2_rn(a.x + bi[2 * i], a.y + bi[2 * i + 1]);
+                const uint32_t on = __hgt2_mask(t, zero2);                     // 0xffff per lane with t > 0
+                o[i] = *reinterpret_cast<const uint32_t*>(&t) & on;            // ReLU: +0 where off
+                bits |= ((on & 1u) | ((on >> 15) & 2u)) << (2 * i);
             }
-            y[r * tpr + vec] = o;
+            y[r * tpr + vec] = make_uint4(o[0], o[1], o[2], o[3]);
             mask[r * tpr + vec] = (uint8_t)bits;
         }
     }

@@ -17,6 +17,8 @@
 // 6.875; backward 2 x (2 + 1/8 + 3/4) + 2 = 7.75 instead of 14.75.
 #include "common.cuh"
 
+#include <cuda_fp16.h>
+
 namespace trb {
 namespace {
 
@@ -67,6 +69,50 @@ __device__ __forceinline__ int64_t window_base(int64_t pr, int oh_n, int ow_n, i
     return ((img * (2 * oh_n) + 2 * oh) * (int64_t)w + 2 * ow) * tpr + vec;
 }
 
+// t = half(half(x * s) + b) for 8 channels, two per packed conversion (the roundings are those of the scalar form)
+__device__ __forceinline__ void bn_apply8(const uint4& v, const float (&sc)[8], const float (&bi)[8], __half2 (&t)[4]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        const float2 a = __half22float2(__floats2half2_rn(f.x * sc[2 * i], f.y * sc[2 * i + 1]));
+        t[i] = __floats2half2_rn(a.x + bi[2 * i], a.y + bi[2 * i + 1]);
+    }
+}
+
+// One pooled pixel x 8 channels: ReLU output (to relu_out if asked), mask byte of each of the four window positions,
+// window maximum and the position of its first occurrence.  Comparisons and selections run on packed halfs.
+__device__ __forceinline__ void pool_window(const uint4 (&v)[4], const int64_t (&idx)[4], const float (&sc)[8],
+                                            const float (&bi)[8], uint4* __restrict__ relu_out,
+                                            uint8_t* __restrict__ mask, uint4& best_out, uint2& am_out) {
+    const __half2 zero2 = __float2half2_rn(0.f);
+    uint32_t best[4], am[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { best[i] = 0xfc00fc00u; am[i] = 0u; }        // -inf, position 0
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        __half2 t[4];
+        bn_apply8(v[q], sc, bi, t);
+        uint32_t y[4];
+        uint32_t bits = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t on = __hgt2_mask(t[i], zero2);                      // 0xffff per lane with t > 0
+            y[i] = *reinterpret_cast<const uint32_t*>(&t[i]) & on;             // ReLU: +0 where off
+            bits |= ((on & 1u) | ((on >> 15) & 2u)) << (2 * i);
+            const uint32_t gt = __hgt2_mask(*reinterpret_cast<const __half2*>(&y[i]),
+                                            *reinterpret_cast<const __half2*>(&best[i]));   // strictly greater: first wins
+            best[i] = (y[i] & gt) | (best[i] & ~gt);
+            am[i] = ((uint32_t)(q | (q << 16)) & gt) | (am[i] & ~gt);
+        }
+        mask[idx[q]] = (uint8_t)bits;
+        if (relu_out) relu_out[idx[q]] = make_uint4(y[0], y[1], y[2], y[3]);
+    }
+    best_out = make_uint4(best[0], best[1], best[2], best[3]);
+    am_out.x = __byte_perm(am[0], am[1], 0x6420);        // one byte per channel
+    am_out.y = __byte_perm(am[2], am[3], 0x6420);
+}
+
 __global__ void __launch_bounds__(kThreads)
 bn_apply_relu_mask_pool_kernel(const uint4* __restrict__ x, const float* __restrict__ eq_scale,
                                const float* __restrict__ eq_bias, uint4* __restrict__ relu_out,
@@ -82,45 +128,29 @@ bn_apply_relu_mask_pool_kernel(const uint4* __restrict__ x, const float* __restr
 #pragma unroll
     for (int j = 0; j < 8; ++j) { sc[j] = eq_scale[vec * 8 + j]; bi[j] = eq_bias[vec * 8 + j]; }
     const int64_t row_step = (int64_t)w * tpr;       // one image row down
-    for (int64_t pr = r0 + ty; pr < r1; pr += by) {
+    // two windows (eight 16-byte loads) in flight per thread
+    for (int64_t pr = r0 + ty; pr < r1; pr += 2 * (int64_t)by) {
+        const int64_t pr2 = pr + by;
+        const bool two = pr2 < r1;
         const int64_t b0 = window_base(pr, oh_n, ow_n, w, tpr, vec);
-        const int64_t idx[4] = {b0, b0 + tpr, b0 + row_step, b0 + row_step + tpr};
-        uint4 v[4];
+        const int64_t b1 = two ? window_base(pr2, oh_n, ow_n, w, tpr, vec) : b0;
+        const int64_t idx0[4] = {b0, b0 + tpr, b0 + row_step, b0 + row_step + tpr};
+        const int64_t idx1[4] = {b1, b1 + tpr, b1 + row_step, b1 + row_step + tpr};
+        uint4 v0[4], v1[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) v[q] = x[idx[q]];
-        float best[8];
-        uint32_t am[8];
-        uint4 bv = make_uint4(0, 0, 0, 0);
-        __half* bh = reinterpret_cast<__half*>(&bv);
+        for (int q = 0; q < 4; ++q) v0[q] = x[idx0[q]];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { best[j] = -INFINITY; am[j] = 0; }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            float f[8];
-            unpack8(v[q], f);
-            uint4 o;
-            __half* oh = reinterpret_cast<__half*>(&o);
-            uint32_t bits = 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const __half a = __float2half_rn(f[j] * sc[j]);
-                const __half t = __float2half_rn(__half2float(a) + bi[j]);
-                const bool on = __half2float(t) > 0.f;
-                const __half y = on ? t : __float2half_rn(0.f);
-                oh[j] = y;
-                bits |= (on ? 1u : 0u) << j;
-                const float yf = __half2float(y);
-                if (yf > best[j]) { best[j] = yf; am[j] = (uint32_t)q; bh[j] = y; }
-            }
-            mask[idx[q]] = (uint8_t)bits;
-            if (relu_out) relu_out[idx[q]] = o;
-        }
-        const int64_t po = pr * tpr + vec;
-        pool_out[po] = bv;
+        for (int q = 0; q < 4; ++q) v1[q] = x[idx1[q]];
+        uint4 bv;
         uint2 a;
-        a.x = am[0] | (am[1] << 8) | (am[2] << 16) | (am[3] << 24);
-        a.y = am[4] | (am[5] << 8) | (am[6] << 16) | (am[7] << 24);
-        argmax[po] = a;
+        pool_window(v0, idx0, sc, bi, relu_out, mask, bv, a);
+        pool_out[pr * tpr + vec] = bv;
+        argmax[pr * tpr + vec] = a;
+        if (two) {
+            pool_window(v1, idx1, sc, bi, relu_out, mask, bv, a);
+            pool_out[pr2 * tpr + vec] = bv;
+            argmax[pr2 * tpr + vec] = a;
+        }
     }
 }
 
