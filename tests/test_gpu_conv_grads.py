@@ -69,6 +69,10 @@ IGEMM_CASES = [
     (2, 28, 28, 128, 128),
     (1, 9, 33, 64, 512),    # two N tiles
     (4, 14, 14, 512, 512),  # deep VGG shape at a small batch
+    (2, 11, 13, 128, 64),   # channels-as-M tile of 64 over two input slices, ragged last pixel tile
+    (1, 6, 6, 256, 128),    # four input slices, fewer pixels than one 256-pixel tile
+    (5, 3, 3, 64, 128),     # images smaller than the filter's reach on every side
+    (2, 17, 9, 256, 64),    # wgrad units spread over more split-K parts than pixel tiles
 ]
 
 
