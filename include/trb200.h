@@ -59,11 +59,19 @@ int trb200_device_arch(void);
 /* ------------------------------------------------------------------------- */
 /* Convolution geometry shared by the conv entry points.                      */
 /* ------------------------------------------------------------------------- */
+/* Storage type of the 16-bit tensors (activations, filters, their gradients).
+ * Arithmetic is float for both.  Half is the reference's AMP type (DType::FP16);
+ * bfloat16 is what its ResNet-50 configuration names and the reference has no
+ * backend for. */
+#define TRB200_DTYPE_F16 0
+#define TRB200_DTYPE_BF16 1
+
 typedef struct trb200_conv_desc {
     int32_t n, h, w, c;          /* input activation X  [n,h,w,c]            */
     int32_t k, r, s;             /* filters W           [k,r,s,c]            */
     int32_t pad_h, pad_w;
     int32_t stride_h, stride_w;
+    int32_t dtype;               /* TRB200_DTYPE_*; 0 (half) when zero-initialised */
 } trb200_conv_desc;              /* output Y / dY is [n,oh,ow,k], oh = (h+2*pad_h-r)/stride_h+1 */
 
 /* ------------------------------------------------------------------------- */
@@ -84,6 +92,12 @@ int trb200_bnrelu_bwd(const void* dy, const void* mask_bits, const void* x,
                       void* dconv, float* dgamma, float* dbeta,
                       int64_t m, int32_t c,
                       void* workspace, size_t workspace_bytes, void* stream);
+/* The same with the storage type of dy, x and dconv given (TRB200_DTYPE_*). */
+int trb200_bnrelu_bwd_dtype(const void* dy, const void* mask_bits, const void* x,
+                            const float* gamma, const float* saved_mean, const float* saved_inv_std,
+                            void* dconv, float* dgamma, float* dbeta,
+                            int64_t m, int32_t c, int32_t dtype,
+                            void* workspace, size_t workspace_bytes, void* stream);
 
 /* The same operator for callers that cannot allocate device memory (a runtime
  * whose memory plan is frozen, a plugin running inside someone else's capture, a

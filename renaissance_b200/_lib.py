@@ -32,7 +32,7 @@ class Trb200Error(RuntimeError):
 
 class ConvDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in
-                ("n", "h", "w", "c", "k", "r", "s", "pad_h", "pad_w", "stride_h", "stride_w")]
+                ("n", "h", "w", "c", "k", "r", "s", "pad_h", "pad_w", "stride_h", "stride_w", "dtype")]
 
 
 class CbrBwdArgs(C.Structure):
@@ -80,6 +80,7 @@ def load() -> C.CDLL:
         "trb200_conv_uses_tensor_cores": (C.c_int, [pdesc, C.c_int]),
         "trb200_bnrelu_bwd_workspace_bytes": (sz, [i64, i32]),
         "trb200_bnrelu_bwd": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, vp, sz, vp]),
+        "trb200_bnrelu_bwd_dtype": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, vp, sz, vp]),
         "trb200_bnrelu_bwd_static": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, vp]),
         "trb200_conv_wgrad_workspace_bytes": (sz, [pdesc]),
         "trb200_conv_wgrad": (C.c_int, [pdesc, vp, vp, vp, vp, sz, vp]),

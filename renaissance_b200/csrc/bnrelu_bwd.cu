@@ -62,16 +62,6 @@ BnPlan make_plan(int64_t m, int c) {
     return p;
 }
 
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-    const __half2* h = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float2 t = __half22float2(h[i]);
-        f[2 * i] = t.x;
-        f[2 * i + 1] = t.y;
-    }
-}
-
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -80,11 +70,12 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) {
     return v;
 }
 
-__global__ void __launch_bounds__(kThreads)
-bnrelu_bwd_reduce(const uint4* __restrict__ dy, const uint8_t* __restrict__ mask,
-                  const uint4* __restrict__ x, const float* __restrict__ mean,
-                  const float* __restrict__ inv_std, float* __restrict__ partial,
-                  int64_t m, int c, int tpr, int bx, int by, int64_t rows_per_strip) {
+template <bool BF16>
+__device__ __forceinline__ void
+bnrelu_bwd_reduce_body(const uint4* __restrict__ dy, const uint8_t* __restrict__ mask,
+                       const uint4* __restrict__ x, const float* __restrict__ mean,
+                       const float* __restrict__ inv_std, float* __restrict__ partial,
+                       int64_t m, int c, int tpr, int bx, int by, int64_t rows_per_strip) {
     __shared__ float s_red[kThreads * 16];
     const int tx = threadIdx.x % bx, ty = threadIdx.x / bx;
     const int vec = blockIdx.y * bx + tx;           // vector (8-channel group) in the row
@@ -118,8 +109,8 @@ bnrelu_bwd_reduce(const uint4* __restrict__ dy, const uint8_t* __restrict__ mask
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
                 float g[8], xv[8];
-                unpack8(vdy[u], g);
-                unpack8(vx[u], xv);
+                unpack8_t<BF16>(vdy[u], g);
+                unpack8_t<BF16>(vx[u], xv);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const float gm = (mb[u] >> j) & 1u ? g[j] : 0.f;
@@ -149,6 +140,19 @@ bnrelu_bwd_reduce(const uint4* __restrict__ dy, const uint8_t* __restrict__ mask
 
 // One warp per (statistic, channel): lanes add every 32nd strip in double, then a
 // fixed butterfly adds the lanes, so the order of additions never changes.
+#define TRB_BN_REDUCE_ARGS                                                                                   \
+    const uint4 *__restrict__ dy, const uint8_t *__restrict__ mask, const uint4 *__restrict__ x,                 \
+        const float *__restrict__ mean, const float *__restrict__ inv_std, float *__restrict__ partial, int64_t m, \
+        int c, int tpr, int bx, int by, int64_t rows_per_strip
+
+__global__ void __launch_bounds__(kThreads) bnrelu_bwd_reduce(TRB_BN_REDUCE_ARGS) {
+    bnrelu_bwd_reduce_body<false>(dy, mask, x, mean, inv_std, partial, m, c, tpr, bx, by, rows_per_strip);
+}
+
+__global__ void __launch_bounds__(kThreads) bnrelu_bwd_reduce_bf16(TRB_BN_REDUCE_ARGS) {
+    bnrelu_bwd_reduce_body<true>(dy, mask, x, mean, inv_std, partial, m, c, tpr, bx, by, rows_per_strip);
+}
+
 __global__ void __launch_bounds__(256)
 bnrelu_bwd_finalize(const float* __restrict__ partial, float* __restrict__ dgamma,
                     float* __restrict__ dbeta, int c, int strips) {
@@ -163,13 +167,14 @@ bnrelu_bwd_finalize(const float* __restrict__ partial, float* __restrict__ dgamm
     if (lane == 0) (stat == 0 ? dbeta : dgamma)[ch] = (float)acc;
 }
 
-__global__ void __launch_bounds__(kThreads)
-bnrelu_bwd_apply(const uint4* __restrict__ dy, const uint8_t* __restrict__ mask,
-                 const uint4* __restrict__ x, const float* __restrict__ gamma,
-                 const float* __restrict__ mean, const float* __restrict__ inv_std,
-                 const float* __restrict__ dgamma, const float* __restrict__ dbeta,
-                 uint4* __restrict__ out, int64_t m, int tpr, int bx, int by,
-                 int64_t rows_per_strip) {
+template <bool BF16>
+__device__ __forceinline__ void
+bnrelu_bwd_apply_body(const uint4* __restrict__ dy, const uint8_t* __restrict__ mask,
+                      const uint4* __restrict__ x, const float* __restrict__ gamma,
+                      const float* __restrict__ mean, const float* __restrict__ inv_std,
+                      const float* __restrict__ dgamma, const float* __restrict__ dbeta,
+                      uint4* __restrict__ out, int64_t m, int tpr, int bx, int by,
+                      int64_t rows_per_strip) {
     const int tx = threadIdx.x % bx, ty = threadIdx.x / bx;
     const int vec = blockIdx.y * bx + tx;
     if (vec >= tpr || ty >= by) return;
@@ -208,21 +213,37 @@ bnrelu_bwd_apply(const uint4* __restrict__ dy, const uint8_t* __restrict__ mask,
             const int64_t r = row + (int64_t)u * by;
             if (r >= r1) continue;
             float g[8], xv[8];
-            unpack8(vdy[u], g);
-            unpack8(vx[u], xv);
+            unpack8_t<BF16>(vdy[u], g);
+            unpack8_t<BF16>(vx[u], xv);
             uint4 o;
-            __half2* oh = reinterpret_cast<__half2*>(&o);
+            uint32_t* oh = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float g0 = (mb[u] >> (2 * j)) & 1u ? g[2 * j] : 0.f;
                 const float g1 = (mb[u] >> (2 * j + 1)) & 1u ? g[2 * j + 1] : 0.f;
                 const float o0 = ca[2 * j] * (g0 - cmb[2 * j] - (xv[2 * j] - cmu[2 * j]) * ck[2 * j]);
                 const float o1 = ca[2 * j + 1] * (g1 - cmb[2 * j + 1] - (xv[2 * j + 1] - cmu[2 * j + 1]) * ck[2 * j + 1]);
-                oh[j] = __floats2half2_rn(o0, o1);
+                oh[j] = pack2_t<BF16>(o0, o1);
             }
             out[r * tpr + vec] = o;
         }
     }
+}
+
+#define TRB_BN_APPLY_ARGS                                                                                     \
+    const uint4 *__restrict__ dy, const uint8_t *__restrict__ mask, const uint4 *__restrict__ x,                  \
+        const float *__restrict__ gamma, const float *__restrict__ mean, const float *__restrict__ inv_std,       \
+        const float *__restrict__ dgamma, const float *__restrict__ dbeta, uint4 *__restrict__ out, int64_t m,    \
+        int tpr, int bx, int by, int64_t rows_per_strip
+
+__global__ void __launch_bounds__(kThreads) bnrelu_bwd_apply(TRB_BN_APPLY_ARGS) {
+    bnrelu_bwd_apply_body<false>(dy, mask, x, gamma, mean, inv_std, dgamma, dbeta, out, m, tpr, bx, by,
+                                 rows_per_strip);
+}
+
+__global__ void __launch_bounds__(kThreads) bnrelu_bwd_apply_bf16(TRB_BN_APPLY_ARGS) {
+    bnrelu_bwd_apply_body<true>(dy, mask, x, gamma, mean, inv_std, dgamma, dbeta, out, m, tpr, bx, by,
+                                rows_per_strip);
 }
 
 }  // namespace
@@ -230,7 +251,9 @@ bnrelu_bwd_apply(const uint4* __restrict__ dy, const uint8_t* __restrict__ mask,
 int bnrelu_bwd_launch(const void* dy, const void* mask_bits, const void* x, const float* gamma,
                       const float* saved_mean, const float* saved_inv_std, void* dconv,
                       float* dgamma, float* dbeta, int64_t m, int c, void* workspace,
-                      size_t workspace_bytes, cudaStream_t s) {
+                      size_t workspace_bytes, cudaStream_t s, int dtype) {
+    TRB_REQUIRE(valid_dtype(dtype), TRB200_ERR_INVALID_ARGUMENT, "bnrelu_bwd: unknown dtype %d", dtype);
+    const bool bf16 = dtype == TRB200_DTYPE_BF16;
     TRB_REQUIRE(dy && mask_bits && x && gamma && saved_mean && saved_inv_std && dgamma && dbeta,
                 TRB200_ERR_INVALID_ARGUMENT, "bnrelu_bwd: null pointer");
     TRB_REQUIRE(m > 0 && c > 0 && c % 8 == 0, TRB200_ERR_UNSUPPORTED,
@@ -245,7 +268,7 @@ int bnrelu_bwd_launch(const void* dy, const void* mask_bits, const void* x, cons
     const BnPlan p = make_plan(m, c);
     float* partial = static_cast<float*>(workspace);
     dim3 grid(p.gx, p.gy);
-    bnrelu_bwd_reduce<<<grid, kThreads, 0, s>>>(
+    (bf16 ? bnrelu_bwd_reduce_bf16 : bnrelu_bwd_reduce)<<<grid, kThreads, 0, s>>>(
         static_cast<const uint4*>(dy), static_cast<const uint8_t*>(mask_bits),
         static_cast<const uint4*>(x), saved_mean, saved_inv_std, partial, m, c, p.tpr, p.bx, p.by,
         p.rows_per_strip);
@@ -253,7 +276,7 @@ int bnrelu_bwd_launch(const void* dy, const void* mask_bits, const void* x, cons
     bnrelu_bwd_finalize<<<(2 * c + 7) / 8, 256, 0, s>>>(partial, dgamma, dbeta, c, p.gx);
     TRB_LAUNCH_CHECK("bnrelu_bwd_finalize");
     if (dconv) {
-        bnrelu_bwd_apply<<<grid, kThreads, 0, s>>>(
+        (bf16 ? bnrelu_bwd_apply_bf16 : bnrelu_bwd_apply)<<<grid, kThreads, 0, s>>>(
             static_cast<const uint4*>(dy), static_cast<const uint8_t*>(mask_bits),
             static_cast<const uint4*>(x), gamma, saved_mean, saved_inv_std, dgamma, dbeta,
             static_cast<uint4*>(dconv), m, p.tpr, p.bx, p.by, p.rows_per_strip);
@@ -276,7 +299,16 @@ extern "C" int trb200_bnrelu_bwd(const void* dy, const void* mask_bits, const vo
                                  float* dbeta, int64_t m, int32_t c, void* workspace,
                                  size_t workspace_bytes, void* stream) {
     return trb::bnrelu_bwd_launch(dy, mask_bits, x, gamma, saved_mean, saved_inv_std, dconv, dgamma,
-                                  dbeta, m, c, workspace, workspace_bytes, trb::as_stream(stream));
+                                  dbeta, m, c, workspace, workspace_bytes, trb::as_stream(stream), TRB200_DTYPE_F16);
+}
+
+extern "C" int trb200_bnrelu_bwd_dtype(const void* dy, const void* mask_bits, const void* x,
+                                       const float* gamma, const float* saved_mean,
+                                       const float* saved_inv_std, void* dconv, float* dgamma,
+                                       float* dbeta, int64_t m, int32_t c, int32_t dtype, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+    return trb::bnrelu_bwd_launch(dy, mask_bits, x, gamma, saved_mean, saved_inv_std, dconv, dgamma,
+                                  dbeta, m, c, workspace, workspace_bytes, trb::as_stream(stream), dtype);
 }
 
 // ---------------------------------------------------------------------------

@@ -15,7 +15,8 @@ int bnrelu_pool_bwd_launch(const void* dy_pooled, const void* argmax, const void
                            size_t workspace_bytes, cudaStream_t s);
 int bnrelu_bwd_launch(const void* dy, const void* mask_bits, const void* x, const float* gamma,
                       const float* saved_mean, const float* saved_inv_std, void* dconv, float* dgamma,
-                      float* dbeta, int64_t m, int c, void* workspace, size_t workspace_bytes, cudaStream_t s);
+                      float* dbeta, int64_t m, int c, void* workspace, size_t workspace_bytes, cudaStream_t s,
+                      int dtype);
 
 namespace {
 std::atomic<int> g_backend{0};   // 0 = automatic, 1 = direct kernels only
@@ -33,6 +34,7 @@ int validate_conv_desc(const trb200_conv_desc* d, const char* who) {
                 "%s: filter larger than the padded input", who);
     TRB_REQUIRE((int64_t)d->n * d->h * d->w * d->c < (int64_t)1 << 40, TRB200_ERR_UNSUPPORTED, "%s: tensor too large",
                 who);
+    TRB_REQUIRE(valid_dtype(d->dtype), TRB200_ERR_INVALID_ARGUMENT, "%s: unknown dtype %d", who, d->dtype);
     return TRB200_OK;
 }
 
@@ -210,6 +212,8 @@ extern "C" int trb200_cbr_bwd(const trb200_cbr_bwd_args* a) {
     const int oh = trb::conv_out(d.h, d.pad_h, d.r, d.stride_h), ow = trb::conv_out(d.w, d.pad_w, d.s, d.stride_w);
 
     // 1) BN + ReLU backward: dconv -> bn_scratch, dgamma, dbeta
+    TRB_REQUIRE(!a->pool_argmax || d.dtype == TRB200_DTYPE_F16, TRB200_ERR_UNSUPPORTED,
+                "cbr_bwd: the pooled variant is built for half tensors only");
     if (a->pool_argmax)
         rc = trb::bnrelu_pool_bwd_launch(a->dy, a->pool_argmax, a->mask_bits, a->conv_out, a->gamma, a->saved_mean,
                                          a->saved_inv_std, a->bn_scratch, a->dgamma, a->dbeta, d.n, oh, ow, d.k,
@@ -217,7 +221,7 @@ extern "C" int trb200_cbr_bwd(const trb200_cbr_bwd_args* a) {
     else
         rc = trb::bnrelu_bwd_launch(a->dy, a->mask_bits, a->conv_out, a->gamma, a->saved_mean, a->saved_inv_std,
                                     a->bn_scratch, a->dgamma, a->dbeta, (int64_t)d.n * oh * ow, d.k, wsp + ws.bn_off,
-                                    ws.bn_bytes, s_bn);
+                                    ws.bn_bytes, s_bn, d.dtype);
     if (rc) return rc;
     if (a->ev_bn) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_bn), s_bn));
 

@@ -1,7 +1,7 @@
 // Direct (CUDA-core) convolution gradients for every geometry the tensor-core
 // kernels do not take: any filter size, stride and padding, any channel count.
-// Same arithmetic as the tensor-core path: half operands, float accumulation,
-// half results; the weight gradient is split over rows of the output image and
+// Same arithmetic as the tensor-core path: 16-bit operands (half or bfloat16), float
+// accumulation, 16-bit results; the weight gradient is split over rows of the output image and
 // the splits are added in split order, so results are bitwise reproducible.
 //
 // Reference counterparts: cuDNN-FE conv_dgrad / conv_wgrad graphs,
@@ -12,9 +12,10 @@
 namespace trb {
 namespace {
 
-__global__ void __launch_bounds__(256)
-dgrad_direct_kernel(const __half* __restrict__ dy, const __half* __restrict__ w,
-                    __half* __restrict__ dx, trb200_conv_desc d, int oh_n, int ow_n) {
+template <bool BF16>
+__device__ __forceinline__ void
+dgrad_direct_body(const uint16_t* __restrict__ dy, const uint16_t* __restrict__ w,
+                  uint16_t* __restrict__ dx, const trb200_conv_desc& d, int oh_n, int ow_n) {
     const int64_t total = (int64_t)d.n * d.h * d.w * d.c;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (int64_t)gridDim.x * blockDim.x) {
@@ -35,22 +36,35 @@ dgrad_direct_kernel(const __half* __restrict__ dy, const __half* __restrict__ w,
                 if (u < 0 || u % d.stride_w) continue;
                 const int ow = u / d.stride_w;
                 if (ow >= ow_n) continue;
-                const __half* g = dy + (((int64_t)n * oh_n + oh) * ow_n + ow) * d.k;
-                const __half* wp = w + ((int64_t)r * d.s + s) * d.c + c;
+                const uint16_t* g = dy + (((int64_t)n * oh_n + oh) * ow_n + ow) * d.k;
+                const uint16_t* wp = w + ((int64_t)r * d.s + s) * d.c + c;
                 const int64_t wk = (int64_t)d.r * d.s * d.c;
                 for (int k = 0; k < d.k; ++k)
-                    acc = fmaf(__half2float(g[k]), __half2float(wp[k * wk]), acc);
+                    acc = fmaf(load16_t<BF16>(g + k), load16_t<BF16>(wp + k * wk), acc);
             }
         }
-        dx[idx] = __float2half_rn(acc);
+        dx[idx] = round16_t<BF16>(acc);
     }
 }
 
-// One thread per dW element and split; split = a range of output rows (n, oh).
 __global__ void __launch_bounds__(256)
-wgrad_direct_kernel(const __half* __restrict__ dy, const __half* __restrict__ x,
-                    float* __restrict__ partial, trb200_conv_desc d, int oh_n, int ow_n,
-                    int rows_per_split) {
+dgrad_direct_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict__ w, uint16_t* __restrict__ dx,
+                    trb200_conv_desc d, int oh_n, int ow_n) {
+    dgrad_direct_body<false>(dy, w, dx, d, oh_n, ow_n);
+}
+
+__global__ void __launch_bounds__(256)
+dgrad_direct_kernel_bf16(const uint16_t* __restrict__ dy, const uint16_t* __restrict__ w, uint16_t* __restrict__ dx,
+                         trb200_conv_desc d, int oh_n, int ow_n) {
+    dgrad_direct_body<true>(dy, w, dx, d, oh_n, ow_n);
+}
+
+// One thread per dW element and split; split = a range of output rows (n, oh).
+template <bool BF16>
+__device__ __forceinline__ void
+wgrad_direct_body(const uint16_t* __restrict__ dy, const uint16_t* __restrict__ x,
+                  float* __restrict__ partial, const trb200_conv_desc& d, int oh_n, int ow_n,
+                  int rows_per_split) {
     const int n_out = d.k * d.r * d.s * d.c;
     const int o = blockIdx.x * blockDim.x + threadIdx.x;
     if (o >= n_out) return;
@@ -66,24 +80,36 @@ wgrad_direct_kernel(const __half* __restrict__ dy, const __half* __restrict__ x,
         const int n = q / oh_n, oh = q % oh_n;
         const int ih = oh * d.stride_h + r - d.pad_h;
         if (ih < 0 || ih >= d.h) continue;
-        const __half* g = dy + ((int64_t)q * ow_n) * d.k + k;
-        const __half* xr = x + (((int64_t)n * d.h + ih) * d.w) * d.c + c;
+        const uint16_t* g = dy + ((int64_t)q * ow_n) * d.k + k;
+        const uint16_t* xr = x + (((int64_t)n * d.h + ih) * d.w) * d.c + c;
         for (int ow = 0; ow < ow_n; ++ow) {
             const int iw = ow * d.stride_w + s - d.pad_w;
             if (iw < 0 || iw >= d.w) continue;
-            acc = fmaf(__half2float(g[(int64_t)ow * d.k]), __half2float(xr[(int64_t)iw * d.c]), acc);
+            acc = fmaf(load16_t<BF16>(g + (int64_t)ow * d.k), load16_t<BF16>(xr + (int64_t)iw * d.c), acc);
         }
     }
     partial[(int64_t)blockIdx.y * n_out + o] = acc;
 }
 
 __global__ void __launch_bounds__(256)
-wgrad_direct_reduce(const float* __restrict__ partial, __half* __restrict__ dw, int n_out, int splits) {
+wgrad_direct_kernel(const uint16_t* __restrict__ dy, const uint16_t* __restrict__ x, float* __restrict__ partial,
+                    trb200_conv_desc d, int oh_n, int ow_n, int rows_per_split) {
+    wgrad_direct_body<false>(dy, x, partial, d, oh_n, ow_n, rows_per_split);
+}
+
+__global__ void __launch_bounds__(256)
+wgrad_direct_kernel_bf16(const uint16_t* __restrict__ dy, const uint16_t* __restrict__ x, float* __restrict__ partial,
+                         trb200_conv_desc d, int oh_n, int ow_n, int rows_per_split) {
+    wgrad_direct_body<true>(dy, x, partial, d, oh_n, ow_n, rows_per_split);
+}
+
+__global__ void __launch_bounds__(256)
+wgrad_direct_reduce(const float* __restrict__ partial, uint16_t* __restrict__ dw, int n_out, int splits, int bf16) {
     const int o = blockIdx.x * blockDim.x + threadIdx.x;
     if (o >= n_out) return;
     float acc = 0.f;
     for (int sp = 0; sp < splits; ++sp) acc += partial[(int64_t)sp * n_out + o];
-    dw[o] = __float2half_rn(acc);
+    dw[o] = bf16 ? round16_t<true>(acc) : round16_t<false>(acc);
 }
 
 int direct_splits(const trb200_conv_desc& d) {
@@ -115,11 +141,13 @@ int wgrad_direct(const trb200_conv_desc& d, const void* dy, const void* x, void*
     const int rows = d.n * oh;
     const int rows_per_split = (rows + splits - 1) / splits;
     dim3 grid((n_out + 255) / 256, splits);
-    wgrad_direct_kernel<<<grid, 256, 0, st>>>(static_cast<const __half*>(dy), static_cast<const __half*>(x),
-                                              static_cast<float*>(ws), d, oh, ow, rows_per_split);
+    const bool bf16 = d.dtype == TRB200_DTYPE_BF16;
+    (bf16 ? wgrad_direct_kernel_bf16 : wgrad_direct_kernel)<<<grid, 256, 0, st>>>(
+        static_cast<const uint16_t*>(dy), static_cast<const uint16_t*>(x), static_cast<float*>(ws), d, oh, ow,
+        rows_per_split);
     TRB_LAUNCH_CHECK("wgrad_direct_kernel");
     wgrad_direct_reduce<<<(n_out + 255) / 256, 256, 0, st>>>(static_cast<const float*>(ws),
-                                                            static_cast<__half*>(dw), n_out, splits);
+                                                            static_cast<uint16_t*>(dw), n_out, splits, bf16 ? 1 : 0);
     TRB_LAUNCH_CHECK("wgrad_direct_reduce");
     return TRB200_OK;
 }
@@ -130,9 +158,8 @@ int dgrad_direct(const trb200_conv_desc& d, const void* dy, const void* w, void*
     int64_t blocks = (total + 255) / 256;
     const int64_t cap = (int64_t)sm_count() * 16;
     if (blocks > cap) blocks = cap;
-    dgrad_direct_kernel<<<(int)blocks, 256, 0, st>>>(static_cast<const __half*>(dy),
-                                                     static_cast<const __half*>(w),
-                                                     static_cast<__half*>(dx), d, oh, ow);
+    (d.dtype == TRB200_DTYPE_BF16 ? dgrad_direct_kernel_bf16 : dgrad_direct_kernel)<<<(int)blocks, 256, 0, st>>>(
+        static_cast<const uint16_t*>(dy), static_cast<const uint16_t*>(w), static_cast<uint16_t*>(dx), d, oh, ow);
     TRB_LAUNCH_CHECK("dgrad_direct_kernel");
     return TRB200_OK;
 }

@@ -296,10 +296,10 @@ template <int NT, bool IM2COL> __host__ __device__ constexpr int conv3x3_threads
 }
 
 // IM2COL: 8 more warps (two groups of 128 threads) build the A tiles from the 4-channel image instead of TMA.
-template <int NT, bool STATS, bool IM2COL>
-__global__ void __launch_bounds__(conv3x3_threads<NT, IM2COL>(), 1)
-conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_w,
-                     const __grid_constant__ CUtensorMap tm_out, const FpropParams p, int* status) {
+template <int NT, bool STATS, bool IM2COL, bool BF16>
+__device__ __forceinline__ void
+conv3x3_igemm_body(const CUtensorMap& tm_in, const CUtensorMap& tm_w, const CUtensorMap& tm_out, const FpropParams& p,
+                   int* status) {
     using L = FpropSmem<NT, IM2COL>;
     constexpr int kStages = L::kStages;
     constexpr uint32_t kTmemCols = 2 * NT;
@@ -474,7 +474,7 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
         }
     } else if (warp == 1) {
         {                                                  // MMA issuer
-            constexpr uint32_t idesc = idesc_f16(128, NT, false, false);
+            constexpr uint32_t idesc = idesc_f16(128, NT, false, false) | (BF16 ? idesc_ab_bf16() : 0u);
             // one thread runs the whole loop; per K step: wait, fence, two descriptor adds, four MMAs, commit
             if (lane == 0) {
                 const uint64_t a_desc0 = smem_desc_sw128(a_base, 16, 1024), b_desc0 = smem_desc_sw128(b_base, 16, 1024);
@@ -581,8 +581,7 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
                     uint32_t pk[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const __half2 h = __floats2half2_rn(__uint_as_float(src[2 * e]), __uint_as_float(src[2 * e + 1]));
-                        pk[e] = *reinterpret_cast<const uint32_t*>(&h);
+                        pk[e] = pack2_t<BF16>(__uint_as_float(src[2 * e]), __uint_as_float(src[2 * e + 1]));
                     }
                     const uint32_t dst = row_addr + (uint32_t)((j ^ (row & 7)) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]),
@@ -609,7 +608,7 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
                         const bool real = (vm >> i) & 1u;
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[i][e]));
+                            float2 f = unpack2_t<BF16>(hw[i][e]);
                             if (!real) f = make_float2(0.f, 0.f);
                             run_s[chunk][2 * e] += f.x;
                             run_s[chunk][2 * e + 1] += f.y;
@@ -665,9 +664,25 @@ conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_con
     }
 }
 
+// The kernels proper: one instantiation of the body per storage type, the half one under the plain name.  The
+// 4-channel first-layer variant (IM2COL) is built for half only.
+template <int NT, bool STATS, bool IM2COL>
+__global__ void __launch_bounds__(conv3x3_threads<NT, IM2COL>(), 1)
+conv3x3_igemm_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_w,
+                     const __grid_constant__ CUtensorMap tm_out, const FpropParams p, int* status) {
+    conv3x3_igemm_body<NT, STATS, IM2COL, false>(tm_in, tm_w, tm_out, p, status);
+}
+
+template <int NT, bool STATS>
+__global__ void __launch_bounds__(conv3x3_threads<NT, false>(), 1)
+conv3x3_igemm_kernel_bf16(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_w,
+                          const __grid_constant__ CUtensorMap tm_out, const FpropParams p, int* status) {
+    conv3x3_igemm_body<NT, STATS, false, true>(tm_in, tm_w, tm_out, p, status);
+}
+
 // Filter view for dgrad: out[tap'][c][k] = W[k][2 - tap'/3][2 - tap'%3][c].
 __global__ void __launch_bounds__(256)
-dgrad_filter_view_kernel(const __half* __restrict__ w, __half* __restrict__ out, int kk, int cc) {
+dgrad_filter_view_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__ out, int kk, int cc) {
     const int total = 9 * kk * cc;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int k = i % kk, c = (i / kk) % cc, tap = i / (kk * cc);
@@ -686,7 +701,7 @@ int conv3x3_grid(int m_tiles, int n_tiles) {
 
 template <int NT, bool STATS, bool IM2COL>
 int launch_conv3x3(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensorMap& tout, const FpropParams& p,
-                   cudaStream_t st) {
+                   cudaStream_t st, bool bf16) {
     using L = FpropSmem<NT, IM2COL>;
     static bool attr_done[64] = {false};
     int dev = 0;
@@ -694,11 +709,23 @@ int launch_conv3x3(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensor
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
         TRB_CUDA_TRY(cudaFuncSetAttribute(conv3x3_igemm_kernel<NT, STATS, IM2COL>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+        if constexpr (!IM2COL)
+            TRB_CUDA_TRY(cudaFuncSetAttribute(conv3x3_igemm_kernel_bf16<NT, STATS>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
         attr_done[dev] = true;
     }
     int* status = nullptr;
     TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status));
     const int grid = conv3x3_grid(p.m_tiles, p.n_tiles);
+    if constexpr (!IM2COL) {
+        if (bf16) {
+            conv3x3_igemm_kernel_bf16<NT, STATS><<<grid, conv3x3_threads<NT, false>(), L::kTotal, st>>>(tin, tw, tout, p,
+                                                                                                      status);
+            TRB_LAUNCH_CHECK("conv3x3_igemm_kernel_bf16");
+            return TRB200_OK;
+        }
+    }
+    TRB_REQUIRE(!bf16, TRB200_ERR_UNSUPPORTED, "conv3x3 igemm: the 4-channel variant is built for half tensors only");
     conv3x3_igemm_kernel<NT, STATS, IM2COL><<<grid, conv3x3_threads<NT, IM2COL>(), L::kTotal, st>>>(tin, tw, tout,
                                                                                                        p, status);
     TRB_LAUNCH_CHECK("conv3x3_igemm_kernel");
@@ -707,12 +734,12 @@ int launch_conv3x3(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensor
 
 template <int NT>
 int launch_conv3x3_any(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensorMap& tout, const FpropParams& p,
-                       cudaStream_t st) {
+                       cudaStream_t st, bool bf16) {
     const bool stats = p.stats_partial != nullptr, im2col = p.x4 != nullptr;
-    if (stats && im2col) return launch_conv3x3<NT, true, true>(tin, tw, tout, p, st);
-    if (stats) return launch_conv3x3<NT, true, false>(tin, tw, tout, p, st);
-    if (im2col) return launch_conv3x3<NT, false, true>(tin, tw, tout, p, st);
-    return launch_conv3x3<NT, false, false>(tin, tw, tout, p, st);
+    if (stats && im2col) return launch_conv3x3<NT, true, true>(tin, tw, tout, p, st, bf16);
+    if (stats) return launch_conv3x3<NT, true, false>(tin, tw, tout, p, st, bf16);
+    if (im2col) return launch_conv3x3<NT, false, true>(tin, tw, tout, p, st, bf16);
+    return launch_conv3x3<NT, false, false>(tin, tw, tout, p, st, bf16);
 }
 
 int pick_nt(int cout) {
@@ -729,7 +756,7 @@ int pick_nt(int cout) {
 // cin 64: the 36 neighbourhood values + 28 zeros).
 int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int n, int h, int w, int cin, int cout,
                 cudaStream_t st, int taps = 9, float* stats_partial = nullptr, int* stats_strips = nullptr,
-                const void* x4 = nullptr) {
+                const void* x4 = nullptr, bool bf16 = false) {
     const int nt = pick_nt(cout);
     TRB_REQUIRE(nt != 0 && cin % 64 == 0, TRB200_ERR_UNSUPPORTED, "conv3x3 igemm: cin=%d cout=%d not covered", cin,
                 cout);
@@ -775,9 +802,9 @@ int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int 
     p.ext_w = w; p.ext_h = h; p.ext_n = n;
     p.has_padding = (t.tw * t.bw != w) || (t.th * t.bh != h) || (t.tn * t.bn != n);
     if (stats_partial && stats_strips) *stats_strips = conv3x3_grid(p.m_tiles, p.n_tiles) / p.n_tiles;
-    if (nt == 256) return launch_conv3x3_any<256>(tin, tw, tout, p, st);
-    if (nt == 128) return launch_conv3x3_any<128>(tin, tw, tout, p, st);
-    return launch_conv3x3_any<64>(tin, tw, tout, p, st);
+    if (nt == 256) return launch_conv3x3_any<256>(tin, tw, tout, p, st, bf16);
+    if (nt == 128) return launch_conv3x3_any<128>(tin, tw, tout, p, st, bf16);
+    return launch_conv3x3_any<64>(tin, tw, tout, p, st, bf16);
 }
 
 // upper bound of the strips the STATS kernels write for an output of `cout` channels
@@ -787,12 +814,13 @@ int conv3x3_stats_max_strips() { return sm_count(); }
 
 // 64 / 128 output channels go to the kernel with the pixels on N (development builds can switch it off)
 int conv3x3_any_run(const void* in, const void* wv, int tap_is_dim1, void* out, int n, int h, int w, int cin, int cout,
-                    cudaStream_t st, float* stats_partial = nullptr, int* stats_strips = nullptr) {
+                    cudaStream_t st, float* stats_partial = nullptr, int* stats_strips = nullptr, bool bf16 = false) {
 #ifndef TRB200_NO_PIXN
     if (pixn_preferred(cin, cout))
-        return conv3x3_pixn_run(in, wv, tap_is_dim1, out, n, h, w, cin, cout, st, stats_partial, stats_strips);
+        return conv3x3_pixn_run(in, wv, tap_is_dim1, out, n, h, w, cin, cout, st, stats_partial, stats_strips, bf16);
 #endif
-    return conv3x3_run(in, wv, tap_is_dim1, out, n, h, w, cin, cout, st, 9, stats_partial, stats_strips);
+    return conv3x3_run(in, wv, tap_is_dim1, out, n, h, w, cin, cout, st, 9, stats_partial, stats_strips, nullptr,
+                       bf16);
 }
 
 // ------------------------------------------------------------------ wgrad kernel
@@ -811,6 +839,7 @@ struct WgradParams {
     int raw_ring;       // IM2COL kernels: tm_x describes x4 and halo tiles go through the raw ring
     int lbw, lbh;       // log2 of bw, bh
     int ext_w, ext_h, ext_n;
+    int bf16;           // operands and dW are bfloat16 instead of half
 };
 
 template <int NT, bool IM2COL = false>
@@ -983,7 +1012,7 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         }
     } else if (warp == 1) {
         {                                                  // MMA issuer
-            constexpr uint32_t idesc = idesc_f16(128, NT, true, true);
+            const uint32_t idesc = idesc_f16(128, NT, true, true) | (p.bf16 ? idesc_ab_bf16() : 0u);
             // MN-major: 64-element blocks of M/N are one 8 KB tile apart, 8 pixels are 1024 bytes apart
             constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
             const uint32_t a_lo0 = smem_desc_lo(a_base, kStageTileBytes), b_lo0 = smem_desc_lo(b_base, kStageTileBytes);
@@ -1048,7 +1077,7 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 // One block = 32 rows (c) x 32 cols (k) of one partial tile, transposed through
 // shared memory so that both the reads (along k) and the writes (along c) coalesce.
 __global__ void __launch_bounds__(256)
-wgrad_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ dw, WgradParams p, int nt_cols, int kk,
+wgrad_reduce_kernel(const float* __restrict__ partial, uint16_t* __restrict__ dw, WgradParams p, int nt_cols, int kk,
                     int cc) {
     __shared__ float tile[32][33];
     const int mt = blockIdx.z / p.n_tiles, nt = blockIdx.z % p.n_tiles;
@@ -1070,7 +1099,7 @@ wgrad_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ dw, 
     for (int cj = ty; cj < 32; cj += 8) {
         const int k = nt * nt_cols + c0 + cj;
         const int c = cb * 64 + (r0 % 64) + tx;
-        dw[((size_t)k * p.taps + tap) * cc + c] = __float2half_rn(tile[tx][cj]);
+        dw[((size_t)k * p.taps + tap) * cc + c] = p.bf16 ? round16_t<true>(tile[tx][cj]) : round16_t<false>(tile[tx][cj]);
     }
     (void)kk;
 }
@@ -1121,6 +1150,7 @@ WgradParams wgrad_plan(const trb200_conv_desc& d, int nt, const TileShape& t, in
     while ((1 << p.lbw) < t.bw) ++p.lbw;
     while ((1 << p.lbh) < t.bh) ++p.lbh;
     p.ext_w = d.w; p.ext_h = d.h; p.ext_n = d.n;
+    p.bf16 = d.dtype == TRB200_DTYPE_BF16 ? 1 : 0;
     return p;
 }
 
@@ -1165,7 +1195,7 @@ static bool is_3x3_s1_p1(const trb200_conv_desc& d) {
 
 // first-layer shape: 4 input channels, handled as a 1x1 convolution over 36 (+28 zero) values
 bool igemm_small_c(const trb200_conv_desc& d) {
-    return is_3x3_s1_p1(d) && d.c == 4 && d.k % 64 == 0 && pick_nt(d.k) != 0 && d.n >= 1 && d.h >= 1 && d.w >= 1;
+    return d.dtype == TRB200_DTYPE_F16 && is_3x3_s1_p1(d) && d.c == 4 && d.k % 64 == 0 && pick_nt(d.k) != 0 && d.n >= 1 && d.h >= 1 && d.w >= 1;
 }
 
 bool igemm_supports(const trb200_conv_desc& d, int which) {
@@ -1215,10 +1245,11 @@ int igemm_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* 
     const int total = 9 * d.k * d.c;
     int blocks = (total + 255) / 256;
     if (blocks > sm_count() * 4) blocks = sm_count() * 4;
-    dgrad_filter_view_kernel<<<blocks, 256, 0, st>>>(static_cast<const __half*>(w), static_cast<__half*>(ws), d.k, d.c);
+    dgrad_filter_view_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(w), static_cast<uint16_t*>(ws), d.k,
+                                                     d.c);
     TRB_LAUNCH_CHECK("dgrad_filter_view_kernel");
     // in = dY [n,h,w,k], filter view (ci = k, co = c, tap), out = dX [n,h,w,c]
-    return conv3x3_any_run(dy, ws, 0, dx, d.n, d.h, d.w, d.k, d.c, st);
+    return conv3x3_any_run(dy, ws, 0, dx, d.n, d.h, d.w, d.k, d.c, st, nullptr, nullptr, d.dtype == TRB200_DTYPE_BF16);
 }
 
 size_t igemm_fprop_stats_bytes(const trb200_conv_desc& d) {
@@ -1229,7 +1260,8 @@ size_t igemm_fprop_stats_bytes(const trb200_conv_desc& d) {
 int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, void* ws, size_t ws_bytes,
                 cudaStream_t st, float* stats_partial, int* stats_strips) {
     if (!igemm_small_c(d))
-        return conv3x3_any_run(x, w, 1, y, d.n, d.h, d.w, d.c, d.k, st, stats_partial, stats_strips);
+        return conv3x3_any_run(x, w, 1, y, d.n, d.h, d.w, d.c, d.k, st, stats_partial, stats_strips,
+                               d.dtype == TRB200_DTYPE_BF16);
     const size_t need = igemm_fprop_workspace(d);
     TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, "conv_fprop: workspace of %zu bytes needed, %zu given",
                 need, ws_bytes);
@@ -1264,7 +1296,7 @@ static int wgrad_run(const trb200_conv_desc& d, int taps, const void* dy, const 
     else rc = launch_wgrad<64>(tx, tdy, partial, p, st);
     if (rc) return rc;
     dim3 grid(nt / 32, 4, p.m_tiles * p.n_tiles);
-    wgrad_reduce_kernel<<<grid, 256, 0, st>>>(partial, static_cast<__half*>(dw), p, nt, d.k, d.c);
+    wgrad_reduce_kernel<<<grid, 256, 0, st>>>(partial, static_cast<uint16_t*>(dw), p, nt, d.k, d.c);
     TRB_LAUNCH_CHECK("wgrad_reduce_kernel");
     return TRB200_OK;
 }

@@ -58,7 +58,7 @@ __device__ __forceinline__ void pixn_sub_origin(const PixnParams& p, int r0, int
 // staging rows; MASKED applies the pixel validity bits (m0: pixels 0-31, m1: 32-63) to the sums.
 // The TMEM loads are warp-wide (every lane of the warp must run them); `keep` says whether this lane's row
 // is a channel at all (at M = 64 only lanes 0-15 of a warp hold one).
-template <bool STATS, bool MASKED>
+template <bool STATS, bool MASKED, bool BF16>
 __device__ __forceinline__ void pixn_epi_chunk(uint32_t taddr, uint32_t dst0, int sw_base, uint32_t m0, uint32_t m1,
                                                bool keep, float& sum, float& sumsq) {
     // dst0 = staging address of (pixel 0, this channel) without the swizzle term; the 16-byte piece
@@ -75,8 +75,7 @@ __device__ __forceinline__ void pixn_epi_chunk(uint32_t taddr, uint32_t dst0, in
         if (keep) {
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-            const __half2 h = __floats2half2_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-            const uint32_t hb = *reinterpret_cast<const uint32_t*>(&h);
+            const uint32_t hb = pack2_t<BF16>(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
             const int pj = half * 32 + j;
             asm volatile("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\t"
                          "st.shared.b16 [%0], lo;\n\tst.shared.b16 [%1], hi;\n\t}"
@@ -84,7 +83,7 @@ __device__ __forceinline__ void pixn_epi_chunk(uint32_t taddr, uint32_t dst0, in
                            "r"(rowbase[(pj + 1) & 7] + (uint32_t)(pj + 1) * 128u), "r"(hb)
                          : "memory");
             if (STATS) {
-                float2 f = __half22float2(h);
+                float2 f = unpack2_t<BF16>(hb);
                 if (MASKED) {
                     if (!((m >> j) & 1u)) f.x = 0.f;
                     if (!((m >> (j + 1)) & 1u)) f.y = 0.f;
@@ -99,10 +98,10 @@ __device__ __forceinline__ void pixn_epi_chunk(uint32_t taddr, uint32_t dst0, in
     }
 }
 
-template <int MT, bool STATS>
-__global__ void __launch_bounds__(kThreads, 1)
-conv3x3_pixn_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_w,
-                    const __grid_constant__ CUtensorMap tm_out, const PixnParams p, int* status) {
+template <int MT, bool STATS, bool BF16>
+__device__ __forceinline__ void
+conv3x3_pixn_body(const CUtensorMap& tm_in, const CUtensorMap& tm_w, const CUtensorMap& tm_out, const PixnParams& p,
+                  int* status) {
     constexpr int kStages = kPixStages;
     constexpr uint32_t kTmemCols = 512;                    // two accumulators of 256 pixels
     constexpr uint32_t kATxBytes = MT * 128;
@@ -200,7 +199,7 @@ conv3x3_pixn_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
         if (lane == 0 && warp == 2) RT_STORE(0);
     } else if (warp == 1) {
         // MMA issuer
-        constexpr uint32_t idesc = idesc_f16(MT, kPixN, false, false);
+        constexpr uint32_t idesc = idesc_f16(MT, kPixN, false, false) | (BF16 ? idesc_ab_bf16() : 0u);
         constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
         const uint32_t a_lo0 = smem_desc_lo(a_base, 16), b_lo0 = smem_desc_lo(b_base, 16);
         uint32_t stage = 0, phase = 0;
@@ -290,9 +289,9 @@ conv3x3_pixn_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
                     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) +
                                            (uint32_t)(acc * kPixN + chunk * kPixChunk);
                     if (STATS && p.has_padding)
-                        pixn_epi_chunk<STATS, true>(taddr, buf + ch_off, sw_base, m0, m1, keep, run_s, run_q);
+                        pixn_epi_chunk<STATS, true, BF16>(taddr, buf + ch_off, sw_base, m0, m1, keep, run_s, run_q);
                     else
-                        pixn_epi_chunk<STATS, false>(taddr, buf + ch_off, sw_base, m0, m1, keep, run_s, run_q);
+                        pixn_epi_chunk<STATS, false, BF16>(taddr, buf + ch_off, sw_base, m0, m1, keep, run_s, run_q);
                 }
                 RT_ADD(3);
                 fence_proxy_async_smem();
@@ -341,21 +340,39 @@ inline TileShape pixn_sub_box(const TileShape& t, int span) {
     return s;
 }
 
+// The kernels proper: one instantiation of the body per storage type, the half one under the plain name.
+template <int MT, bool STATS>
+__global__ void __launch_bounds__(kThreads, 1)
+conv3x3_pixn_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_w,
+                    const __grid_constant__ CUtensorMap tm_out, const PixnParams p, int* status) {
+    conv3x3_pixn_body<MT, STATS, false>(tm_in, tm_w, tm_out, p, status);
+}
+
+template <int MT, bool STATS>
+__global__ void __launch_bounds__(kThreads, 1)
+conv3x3_pixn_kernel_bf16(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_w,
+                         const __grid_constant__ CUtensorMap tm_out, const PixnParams p, int* status) {
+    conv3x3_pixn_body<MT, STATS, true>(tm_in, tm_w, tm_out, p, status);
+}
+
 template <int MT, bool STATS>
 int launch_pixn(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensorMap& tout, const PixnParams& p,
-                cudaStream_t st) {
+                cudaStream_t st, bool bf16) {
     static bool attr_done[64] = {false};
     int dev = 0;
     TRB_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
         TRB_CUDA_TRY(cudaFuncSetAttribute(conv3x3_pixn_kernel<MT, STATS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           kPixSmemTotal));
+        TRB_CUDA_TRY(cudaFuncSetAttribute(conv3x3_pixn_kernel_bf16<MT, STATS>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, kPixSmemTotal));
         attr_done[dev] = true;
     }
     int* status = nullptr;
     TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status));
     const int grid = conv3x3_grid(p.p_tiles, p.c_tiles);
-    conv3x3_pixn_kernel<MT, STATS><<<grid, kThreads, kPixSmemTotal, st>>>(tin, tw, tout, p, status);
+    if (bf16) conv3x3_pixn_kernel_bf16<MT, STATS><<<grid, kThreads, kPixSmemTotal, st>>>(tin, tw, tout, p, status);
+    else conv3x3_pixn_kernel<MT, STATS><<<grid, kThreads, kPixSmemTotal, st>>>(tin, tw, tout, p, status);
     TRB_LAUNCH_CHECK("conv3x3_pixn_kernel");
     return TRB200_OK;
 }
@@ -365,7 +382,7 @@ inline bool pixn_preferred(int cin, int cout) { return cin % 64 == 0 && (cout ==
 
 // Same contract as conv3x3_run (3x3 taps, cin a multiple of 64).
 int conv3x3_pixn_run(const void* in, const void* wv, int tap_is_dim1, void* out, int n, int h, int w, int cin,
-                     int cout, cudaStream_t st, float* stats_partial, int* stats_strips) {
+                     int cout, cudaStream_t st, float* stats_partial, int* stats_strips, bool bf16) {
     const int MT = cout == 64 ? 64 : 128;
     const TileShape t = pick_tile(n, h, w, kPixN);
     const TileShape th = pixn_sub_box(t, 128), tc = pixn_sub_box(t, kPixChunk);
@@ -404,9 +421,9 @@ int conv3x3_pixn_run(const void* in, const void* wv, int tap_is_dim1, void* out,
     p.stats_partial = stats_partial;
     if (stats_partial && stats_strips) *stats_strips = conv3x3_grid(p.p_tiles, p.c_tiles) / p.c_tiles;
     if (MT == 64) {
-        if (stats_partial) return launch_pixn<64, true>(tin, tw, tout, p, st);
-        return launch_pixn<64, false>(tin, tw, tout, p, st);
+        if (stats_partial) return launch_pixn<64, true>(tin, tw, tout, p, st, bf16);
+        return launch_pixn<64, false>(tin, tw, tout, p, st, bf16);
     }
-    if (stats_partial) return launch_pixn<128, true>(tin, tw, tout, p, st);
-    return launch_pixn<128, false>(tin, tw, tout, p, st);
+    if (stats_partial) return launch_pixn<128, true>(tin, tw, tout, p, st, bf16);
+    return launch_pixn<128, false>(tin, tw, tout, p, st, bf16);
 }

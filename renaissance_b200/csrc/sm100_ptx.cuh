@@ -287,14 +287,18 @@ __host__ __device__ constexpr uint32_t smem_desc_hi_sw128(uint32_t sbo_bytes) {
     return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
 }
 
-// Instruction descriptor of tcgen05.mma.kind::f16: half A and B, float D.
-//   bits 4-5 D format (1 = f32)   bits 7-9 A format (0 = f16)   bits 10-12 B format
+// Instruction descriptor of tcgen05.mma.kind::f16: half (or, with idesc_ab_bf16() or-ed in, bfloat16) A and B,
+// float D.
+//   bits 4-5 D format (1 = f32)   bits 7-9 A format (0 = f16, 1 = bf16)   bits 10-12 B format
 //   bit 15 A is MN-major          bit 16 B is MN-major
 //   bits 17-22 N >> 3             bits 24-28 M >> 4
 __host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool a_mn_major, bool b_mn_major) {
     return (1u << 4) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
+
+// A and B format fields for bfloat16 operands (both operands have the same type here)
+__host__ __device__ constexpr uint32_t idesc_ab_bf16() { return (1u << 7) | (1u << 10); }
 
 }  // namespace ptx
 }  // namespace trb

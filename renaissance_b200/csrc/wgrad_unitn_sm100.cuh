@@ -31,6 +31,7 @@ struct WgradUnitnParams {
     int tw, th;
     int bw, bh, bn;     // 64-pixel box
     int kk, cc;         // K, C
+    int bf16;           // operands and dW are bfloat16 instead of half
 };
 
 constexpr int kUnABytes = 2 * kStageTileBytes;     // 64 pixels x 128 filters
@@ -145,7 +146,7 @@ wgrad_unitn_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         if (lane == 0 && warp == 2) RT_STORE(0);
     } else if (warp == 1) {
         // MMA issuer: M = 128 filters, N = 64 columns per unit of the group
-        const uint32_t idesc = idesc_f16(128, nu * 64, true, true);
+        const uint32_t idesc = idesc_f16(128, nu * 64, true, true) | (p.bf16 ? idesc_ab_bf16() : 0u);
         // MN-major: 64-element blocks of M/N are one 8 KB tile apart, 8 pixels are 1024 bytes apart
         constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
         const uint32_t a_lo0 = smem_desc_lo(a_base, kStageTileBytes), b_lo0 = smem_desc_lo(b_base, kStageTileBytes);
@@ -212,10 +213,10 @@ wgrad_unitn_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
 }
 
-// dW[k][col] = half(sum over splits, in split order, of partial[split][kb][nt][k % 128][col % 256]);
+// dW[k][col] = half or bfloat16(sum over splits, in split order, of partial[split][kb][nt][k % 128][col % 256]);
 // one thread = 4 consecutive columns of one filter row.
 __global__ void __launch_bounds__(256)
-wgrad_unitn_reduce(const float* __restrict__ partial, __half* __restrict__ dw, WgradUnitnParams p) {
+wgrad_unitn_reduce(const float* __restrict__ partial, uint16_t* __restrict__ dw, WgradUnitnParams p) {
     const int cols = 9 * p.cc;                    // columns of a filter row
     const int quads = cols / 4;
     const long total = (long)p.kk * quads;
@@ -229,10 +230,9 @@ wgrad_unitn_reduce(const float* __restrict__ partial, __half* __restrict__ dw, W
             const float4 v = *reinterpret_cast<const float4*>(partial + (size_t)s * split_stride + off);
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
-        const __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
         uint2 o;
-        o.x = *reinterpret_cast<const uint32_t*>(&lo);
-        o.y = *reinterpret_cast<const uint32_t*>(&hi);
+        o.x = p.bf16 ? pack2_t<true>(acc.x, acc.y) : pack2_t<false>(acc.x, acc.y);
+        o.y = p.bf16 ? pack2_t<true>(acc.z, acc.w) : pack2_t<false>(acc.z, acc.w);
         *reinterpret_cast<uint2*>(dw + (size_t)k * cols + col) = o;
     }
 }
@@ -253,6 +253,7 @@ WgradUnitnParams wgrad_unitn_plan(const trb200_conv_desc& d, const TileShape& t)
     p.tw = t.tw; p.th = t.th;
     p.bw = t.bw; p.bh = t.bh; p.bn = t.bn;
     p.kk = d.k; p.cc = d.c;
+    p.bf16 = d.dtype == TRB200_DTYPE_BF16 ? 1 : 0;
     return p;
 }
 
@@ -292,7 +293,7 @@ int wgrad_unitn_run(const trb200_conv_desc& d, const void* dy, const void* x, vo
     const long total = (long)d.k * (9 * d.c / 4);
     long blocks = (total + 255) / 256;
     if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
-    wgrad_unitn_reduce<<<(int)blocks, 256, 0, st>>>(partial, static_cast<__half*>(dw), p);
+    wgrad_unitn_reduce<<<(int)blocks, 256, 0, st>>>(partial, static_cast<uint16_t*>(dw), p);
     TRB_LAUNCH_CHECK("wgrad_unitn_reduce");
     return TRB200_OK;
 }

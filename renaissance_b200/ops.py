@@ -31,6 +31,10 @@ def _stream(stream=None):
     return C.c_void_p(s.cuda_stream)
 
 
+# TRB200_DTYPE_* of include/trb200.h
+DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1}
+
+
 def _need(t, dtype, name, ndim=None):
     if not (isinstance(t, torch.Tensor) and t.is_cuda):
         raise TypeError(f"{name}: CUDA tensor expected")
@@ -54,10 +58,11 @@ class ConvGeometry:
     s: int = 3
     pad: int = 1
     stride: int = 1
+    dtype: torch.dtype = torch.float16     # storage type of activations, filters and their gradients
 
     def desc(self) -> ConvDesc:
         return ConvDesc(self.n, self.h, self.w, self.c, self.k, self.r, self.s,
-                        self.pad, self.pad, self.stride, self.stride)
+                        self.pad, self.pad, self.stride, self.stride, DTYPE_CODE[self.dtype])
 
     @property
     def oh(self):
@@ -120,8 +125,10 @@ def bnrelu_bwd(dy, mask_bits, conv_out, gamma, saved_mean, saved_inv_std, dconv=
                workspace: Workspace | None = None, stream=None, want_dconv=True):
     """dconv, dgamma, dbeta of the block's BN+ReLU (cbr_op.cpp:1259-1353)."""
     lib = _lib.load()
-    _need(dy, torch.float16, "dy")
-    _need(conv_out, torch.float16, "conv_out")
+    if dy.dtype not in DTYPE_CODE:
+        raise TypeError(f"dy: float16 or bfloat16 expected, got {dy.dtype}")
+    _need(dy, dy.dtype, "dy")
+    _need(conv_out, dy.dtype, "conv_out")
     _need(mask_bits, torch.uint8, "mask_bits")
     for t, nm in ((gamma, "gamma"), (saved_mean, "saved_mean"), (saved_inv_std, "saved_inv_std")):
         _need(t, torch.float32, nm)
@@ -136,9 +143,9 @@ def bnrelu_bwd(dy, mask_bits, conv_out, gamma, saved_mean, saved_inv_std, dconv=
     dgamma = torch.empty(c, dtype=torch.float32, device=dy.device)
     dbeta = torch.empty(c, dtype=torch.float32, device=dy.device)
     ws = (workspace or default_workspace()).ensure(lib.trb200_bnrelu_bwd_workspace_bytes(m, c))
-    check(lib.trb200_bnrelu_bwd(_ptr(dy), _ptr(mask_bits), _ptr(conv_out), _ptr(gamma), _ptr(saved_mean),
-                                _ptr(saved_inv_std), _ptr(dconv), _ptr(dgamma), _ptr(dbeta), m, c,
-                                _ptr(ws), ws.numel(), _stream(stream)))
+    check(lib.trb200_bnrelu_bwd_dtype(_ptr(dy), _ptr(mask_bits), _ptr(conv_out), _ptr(gamma), _ptr(saved_mean),
+                                      _ptr(saved_inv_std), _ptr(dconv), _ptr(dgamma), _ptr(dbeta), m, c,
+                                      DTYPE_CODE[dy.dtype], _ptr(ws), ws.numel(), _stream(stream)))
     return dconv, dgamma, dbeta
 
 
@@ -146,12 +153,12 @@ def bnrelu_bwd(dy, mask_bits, conv_out, gamma, saved_mean, saved_inv_std, dconv=
 
 def conv_wgrad(g: ConvGeometry, dy, x, dw=None, workspace=None, stream=None):
     lib = _lib.load()
-    _need(dy, torch.float16, "dy", 4)
-    _need(x, torch.float16, "x", 4)
+    _need(dy, g.dtype, "dy", 4)
+    _need(x, g.dtype, "x", 4)
     if tuple(x.shape) != (g.n, g.h, g.w, g.c) or tuple(dy.shape) != (g.n, g.oh, g.ow, g.k):
         raise ValueError("conv_wgrad: tensor shapes do not match the geometry")
     if dw is None:
-        dw = torch.empty((g.k, g.r, g.s, g.c), dtype=torch.float16, device=x.device)
+        dw = torch.empty((g.k, g.r, g.s, g.c), dtype=g.dtype, device=x.device)
     d = g.desc()
     ws = (workspace or default_workspace()).ensure(lib.trb200_conv_wgrad_workspace_bytes(C.byref(d)))
     check(lib.trb200_conv_wgrad(C.byref(d), _ptr(dy), _ptr(x), _ptr(dw), _ptr(ws), ws.numel(), _stream(stream)))
@@ -160,12 +167,12 @@ def conv_wgrad(g: ConvGeometry, dy, x, dw=None, workspace=None, stream=None):
 
 def conv_dgrad(g: ConvGeometry, dy, w, dx=None, workspace=None, stream=None):
     lib = _lib.load()
-    _need(dy, torch.float16, "dy", 4)
-    _need(w, torch.float16, "w", 4)
+    _need(dy, g.dtype, "dy", 4)
+    _need(w, g.dtype, "w", 4)
     if tuple(w.shape) != (g.k, g.r, g.s, g.c) or tuple(dy.shape) != (g.n, g.oh, g.ow, g.k):
         raise ValueError("conv_dgrad: tensor shapes do not match the geometry")
     if dx is None:
-        dx = torch.empty((g.n, g.h, g.w, g.c), dtype=torch.float16, device=dy.device)
+        dx = torch.empty((g.n, g.h, g.w, g.c), dtype=g.dtype, device=dy.device)
     d = g.desc()
     ws = (workspace or default_workspace()).ensure(lib.trb200_conv_dgrad_workspace_bytes(C.byref(d)))
     check(lib.trb200_conv_dgrad(C.byref(d), _ptr(dy), _ptr(w), _ptr(dx), _ptr(ws), ws.numel(), _stream(stream)))
@@ -174,12 +181,12 @@ def conv_dgrad(g: ConvGeometry, dy, w, dx=None, workspace=None, stream=None):
 
 def conv_fprop(g: ConvGeometry, x, w, y=None, stream=None, workspace=None, scratch=None):
     lib = _lib.load()
-    _need(x, torch.float16, "x", 4)
-    _need(w, torch.float16, "w", 4)
+    _need(x, g.dtype, "x", 4)
+    _need(w, g.dtype, "w", 4)
     if tuple(x.shape) != (g.n, g.h, g.w, g.c) or tuple(w.shape) != (g.k, g.r, g.s, g.c):
         raise ValueError("conv_fprop: tensor shapes do not match the geometry")
     if y is None:
-        y = torch.empty((g.n, g.oh, g.ow, g.k), dtype=torch.float16, device=x.device)
+        y = torch.empty((g.n, g.oh, g.ow, g.k), dtype=g.dtype, device=x.device)
     d = g.desc()
     need = lib.trb200_conv_fprop_workspace_bytes(C.byref(d))
     if scratch is not None and scratch.numel() * scratch.element_size() >= need:
@@ -197,13 +204,13 @@ def conv_fprop_bn_stats(g: ConvGeometry, x, w, gamma, beta, y=None, out=None, ep
     """Forward conv + batch statistics in its epilogue + bn_finalize (cbr_op.cpp:622-718, 430-528).
     Returns (y, dict(saved_mean, saved_inv_std, eq_scale, eq_bias[, sum, sqsum]))."""
     lib = _lib.load()
-    _need(x, torch.float16, "x", 4)
-    _need(w, torch.float16, "w", 4)
+    _need(x, g.dtype, "x", 4)
+    _need(w, g.dtype, "w", 4)
     if tuple(x.shape) != (g.n, g.h, g.w, g.c) or tuple(w.shape) != (g.k, g.r, g.s, g.c):
         raise ValueError("conv_fprop_bn_stats: tensor shapes do not match the geometry")
     dev = x.device
     if y is None:
-        y = torch.empty((g.n, g.oh, g.ow, g.k), dtype=torch.float16, device=dev)
+        y = torch.empty((g.n, g.oh, g.ow, g.k), dtype=g.dtype, device=dev)
     if out is None:
         out = {k: torch.empty(g.k, dtype=torch.float32, device=dev)
                for k in ("saved_mean", "saved_inv_std", "eq_scale", "eq_bias")}

@@ -34,7 +34,8 @@ void check(int rc, const char* op) {
 }
 
 trb200_conv_desc conv_desc(const DTensor& x, const DTensor& w, const ConvParams& cp) {
-    trb200_conv_desc d;
+    trb200_conv_desc d{};
+    d.dtype = TRB200_DTYPE_F16;                       // the reference's AMP tensors are DType::FP16
     d.n = x.n(); d.h = x.h(); d.w = x.w(); d.c = x.c();
     d.k = w.n(); d.r = w.h(); d.s = w.w();            // KRSC stored as (n,h,w,c) = (K,R,S,C)
     d.pad_h = cp.pad_h; d.pad_w = cp.pad_w;

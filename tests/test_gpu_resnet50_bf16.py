@@ -1,0 +1,138 @@
+"""The ResNet-50 bf16 configuration at the level the hot path reaches it: every distinct convolution of the
+network (the reference lists them in scripts/resnet50_conv.json as kernel, in/out channels, in/out extent,
+stride, padding) has its data and weight gradients checked against the CPU oracle on bfloat16 tensors, and
+the BN+ReLU backward is checked on bfloat16 activations of the network's shapes.  The reference has no
+backend for this configuration, so the oracle (float arithmetic on the bf16-rounded inputs) is the only
+reference; the batch is 2 so that it finishes in seconds."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_l2, rel_max
+from gpu_util import dev, host
+
+pytestmark = pytest.mark.gpu
+
+# kernel, in channels, out channels, input extent, output extent, stride, padding
+RESNET50_CONVS = [
+    (7, 4, 64, 224, 112, 2, 3),
+    (1, 64, 64, 56, 56, 1, 0), (3, 64, 64, 56, 56, 1, 1), (1, 64, 256, 56, 56, 1, 0), (1, 256, 64, 56, 56, 1, 0),
+    (1, 256, 128, 56, 56, 1, 0), (1, 256, 512, 56, 28, 2, 0), (3, 128, 128, 56, 28, 2, 1),
+    (1, 128, 512, 28, 28, 1, 0), (1, 512, 128, 28, 28, 1, 0), (3, 128, 128, 28, 28, 1, 1),
+    (1, 512, 256, 28, 28, 1, 0), (1, 512, 1024, 28, 14, 2, 0), (3, 256, 256, 28, 14, 2, 1),
+    (1, 256, 1024, 14, 14, 1, 0), (1, 1024, 256, 14, 14, 1, 0), (3, 256, 256, 14, 14, 1, 1),
+    (1, 1024, 512, 14, 14, 1, 0), (1, 1024, 2048, 14, 7, 2, 0), (3, 512, 512, 14, 7, 2, 1),
+    (1, 512, 2048, 7, 7, 1, 0), (1, 2048, 512, 7, 7, 1, 0), (3, 512, 512, 7, 7, 1, 1),
+]
+
+
+def bf16_round(a):
+    """float32 array with every value rounded to the nearest bfloat16."""
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).bfloat16().float().numpy()
+
+
+def dev_bf16(a):
+    return dev(a).bfloat16()
+
+
+def host_f32(t):
+    return host(t.float())
+
+
+@pytest.mark.parametrize("r,c,k,h,oh,stride,pad", RESNET50_CONVS)
+def test_conv_gradients_bf16_match_oracle(orc, r, c, k, h, oh, stride, pad):
+    from renaissance_b200 import ops
+    n = 2
+    rng = np.random.default_rng(r * 1000 + c + k + h)
+    x = bf16_round(rng.standard_normal((n, h, h, c)))
+    wt = bf16_round(rng.standard_normal((k, r, r, c)) * np.sqrt(2.0 / (r * r * c)))
+    dy = bf16_round(rng.standard_normal((n, oh, oh, k)))
+    g = ops.ConvGeometry(n, h, h, c, k, r, r, pad, stride, dtype=torch.bfloat16)
+    assert (g.oh, g.ow) == (oh, oh)
+    # the 3x3 stride-1 layers run on the tcgen05 kernels, the others on the direct kernels
+    assert ops.conv_uses_tensor_cores(g, "dgrad") == ((r, stride, pad) == (3, 1, 1))
+    assert ops.conv_uses_tensor_cores(g, "wgrad") == ((r, stride, pad) == (3, 1, 1))
+    ref_dw = orc.conv_wgrad(dy, x, wt.shape, pad=pad, stride=stride)
+    ref_dx = orc.conv_dgrad(dy, wt, x.shape, pad=pad, stride=stride)
+    dw = ops.conv_wgrad(g, dev_bf16(dy), dev_bf16(x))
+    dx = ops.conv_dgrad(g, dev_bf16(dy), dev_bf16(wt))
+    ops.device_status()
+    assert dw.dtype == torch.bfloat16 and dx.dtype == torch.bfloat16
+    # 2e-2 relative L2 is the stated bound for 16-bit gradients; rounding the result to bf16 (8 significant
+    # bits) alone gives about 2e-3
+    assert rel_l2(host_f32(dw), ref_dw) < 2e-2 and rel_l2(host_f32(dx), ref_dx) < 2e-2
+    assert rel_l2(host_f32(dw), ref_dw) < 4e-3 and rel_l2(host_f32(dx), ref_dx) < 4e-3
+
+
+@pytest.mark.parametrize("m,c", [(2 * 112 * 112, 64), (2 * 56 * 56, 256), (2 * 28 * 28, 512), (2 * 14 * 14, 1024),
+                                 (2 * 7 * 7, 2048), (33, 8)])
+def test_bnrelu_bwd_bf16_matches_oracle(orc, m, c):
+    from renaissance_b200 import ops
+    rng = np.random.default_rng(m + c)
+    dy = bf16_round(rng.standard_normal((m, c)))
+    x = bf16_round(rng.standard_normal((m, c)) * 1.5 + 0.3)
+    mask = (rng.random((m, c)) < 0.5).astype(np.int8)
+    bits = orc.mask_pack(mask)
+    gamma = (1.0 + 0.2 * rng.standard_normal(c)).astype(np.float32)
+    mean = x.mean(axis=0).astype(np.float32)
+    inv_std = (1.0 / np.sqrt(x.var(axis=0) + 1e-5)).astype(np.float32)
+    # oracle: ReLU backward through the mask, then the float BN backward (double accumulators)
+    dy_m = dy * mask.astype(np.float32)
+    ref = orc.bn_bwd(dy_m, x, gamma, mean, inv_std)
+    ref_dx, ref_dg, ref_db = ref[0], ref[1], ref[2]
+    dconv, dg, db = ops.bnrelu_bwd(dev_bf16(dy), dev(bits), dev_bf16(x), dev(gamma), dev(mean), dev(inv_std))
+    torch.cuda.synchronize()
+    assert dconv.dtype == torch.bfloat16
+    assert rel_max(host(dg), ref_dg) < 1e-4 and rel_max(host(db), ref_db) < 1e-4
+    assert rel_l2(host_f32(dconv), ref_dx) < 2e-2
+    assert rel_l2(host_f32(dconv), ref_dx) < 4e-3
+
+
+@pytest.mark.parametrize("n,h,w,c,k", [(2, 8, 8, 64, 64), (3, 7, 5, 64, 128), (2, 14, 14, 128, 256),
+                                       (1, 9, 33, 64, 512), (5, 12, 20, 256, 64), (2, 28, 28, 128, 128),
+                                       (4, 14, 14, 512, 512)])
+def test_tensor_core_kernels_bf16_match_oracle(orc, n, h, w, c, k):
+    """Every tcgen05 kernel variant (pixels on M with 256-filter tiles, pixels on N with 64 / 128 filters, both
+    weight-gradient kernels, the statistics epilogue) on bfloat16 operands."""
+    from renaissance_b200 import ops
+    rng = np.random.default_rng(n + 3 * h + c)
+    x = bf16_round(rng.standard_normal((n, h, w, c)))
+    wt = bf16_round(rng.standard_normal((k, 3, 3, c)) * np.sqrt(2.0 / (9 * c)))
+    dy = bf16_round(rng.standard_normal((n, h, w, k)))
+    g = ops.ConvGeometry(n, h, w, c, k, dtype=torch.bfloat16)
+    for which in ("wgrad", "dgrad", "fprop"):
+        assert ops.conv_uses_tensor_cores(g, which)
+    dw = ops.conv_wgrad(g, dev_bf16(dy), dev_bf16(x))
+    dx = ops.conv_dgrad(g, dev_bf16(dy), dev_bf16(wt))
+    y = ops.conv_fprop(g, dev_bf16(x), dev_bf16(wt))
+    gamma, beta = np.ones(k, np.float32), np.zeros(k, np.float32)
+    y2, st = ops.conv_fprop_bn_stats(g, dev_bf16(x), dev_bf16(wt), dev(gamma), dev(beta), want_sums=True)
+    ops.device_status()
+    ref_y = orc.conv_fwd(x, wt)
+    assert rel_l2(host_f32(dx), orc.conv_dgrad(dy, wt, x.shape)) < 4e-3
+    assert rel_l2(host_f32(dw), orc.conv_wgrad(dy, x, wt.shape)) < 4e-3
+    assert rel_l2(host_f32(y), ref_y) < 4e-3
+    assert torch.equal(y, y2)
+    # the statistics are those of the rounded (bf16) output
+    yr = host_f32(y).reshape(-1, k).astype(np.float64)
+    assert rel_max(host(st["sum"]), yr.sum(axis=0)) < 1e-4
+    assert rel_max(host(st["sqsum"]), (yr * yr).sum(axis=0)) < 1e-4
+
+
+def test_bf16_and_half_kernels_agree_on_values_both_types_hold(orc):
+    """Values that are exact in both 16-bit types (small integers / 4) must give the same gradients through
+    the bf16 and the half kernels up to the rounding of the result."""
+    from renaissance_b200 import ops
+    n, h, c, k = 2, 12, 16, 24
+    rng = np.random.default_rng(5)
+    x = rng.integers(-8, 9, (n, h, h, c)).astype(np.float32) / 4
+    wt = rng.integers(-8, 9, (k, 3, 3, c)).astype(np.float32) / 8
+    dy = rng.integers(-8, 9, (n, h, h, k)).astype(np.float32) / 4
+    out = {}
+    for dt in (torch.float16, torch.bfloat16):
+        g = ops.ConvGeometry(n, h, h, c, k, dtype=dt)
+        out[dt] = (ops.conv_wgrad(g, dev(dy).to(dt), dev(x).to(dt)).float(),
+                   ops.conv_dgrad(g, dev(dy).to(dt), dev(wt).to(dt)).float())
+    torch.cuda.synchronize()
+    for a, b in zip(out[torch.float16], out[torch.bfloat16]):
+        assert rel_l2(host(b), host(a)) < 4e-3
