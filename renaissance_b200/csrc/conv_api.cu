@@ -112,7 +112,8 @@ extern "C" int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const
     TRB_REQUIRE(trb::aligned16(x) && trb::aligned16(w) && trb::aligned16(y), TRB200_ERR_INVALID_ARGUMENT,
                 "conv_fprop: tensors must be 16-byte aligned");
     TRB_REQUIRE(trb::igemm_supports(*d, 2), TRB200_ERR_UNSUPPORTED,
-                "conv_fprop: only 3x3 stride 1 pad 1 with k = 64, 128 or a multiple of 256 and c = 4 or a multiple of 64");
+                "conv_fprop: only 3x3 stride 1 pad 1 (c = 4 or a multiple of 64) and 1x1 stride 1 (c a multiple of 64), "
+                "with k = 64, 128 or a multiple of 256");
     return trb::igemm_fprop(*d, x, w, y, workspace, workspace_bytes, trb::as_stream(stream));
 }
 
@@ -135,8 +136,8 @@ extern "C" int trb200_conv_fprop_bn_stats(const trb200_conv_desc* d, const void*
     TRB_REQUIRE(trb::aligned16(x) && trb::aligned16(w) && trb::aligned16(y), TRB200_ERR_INVALID_ARGUMENT,
                 "conv_fprop_bn_stats: tensors must be 16-byte aligned");
     TRB_REQUIRE(trb::igemm_supports(*d, 2), TRB200_ERR_UNSUPPORTED,
-                "conv_fprop_bn_stats: only 3x3 stride 1 pad 1 with k = 64, 128 or a multiple of 256 and c = 4 or a "
-                "multiple of 64");
+                "conv_fprop_bn_stats: only 3x3 stride 1 pad 1 (c = 4 or a multiple of 64) and 1x1 stride 1 (c a multiple "
+                "of 64), with k = 64, 128 or a multiple of 256");
     const size_t need = trb200_conv_fprop_bn_stats_workspace_bytes(d);
     TRB_REQUIRE(workspace && workspace_bytes >= need, TRB200_ERR_WORKSPACE,
                 "conv_fprop_bn_stats: workspace of %zu bytes needed, %zu given", need, workspace_bytes);

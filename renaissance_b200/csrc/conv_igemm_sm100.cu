@@ -680,14 +680,14 @@ conv3x3_igemm_kernel_bf16(const __grid_constant__ CUtensorMap tm_in, const __gri
     conv3x3_igemm_body<NT, STATS, false, true>(tm_in, tm_w, tm_out, p, status);
 }
 
-// Filter view for dgrad: out[tap'][c][k] = W[k][2 - tap'/3][2 - tap'%3][c].
+// Filter view for dgrad: out[tap'][c][k] = W[k][taps - 1 - tap'][c], i.e. the filter turned by 180 degrees
+// (3x3: W[k][2 - tap'/3][2 - tap'%3][c]; 1x1: the transpose).
 __global__ void __launch_bounds__(256)
-dgrad_filter_view_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__ out, int kk, int cc) {
-    const int total = 9 * kk * cc;
+dgrad_filter_view_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__ out, int kk, int cc, int taps) {
+    const int total = taps * kk * cc;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int k = i % kk, c = (i / kk) % cc, tap = i / (kk * cc);
-        const int r = 2 - tap / 3, s = 2 - tap % 3;
-        out[i] = w[(((int64_t)k * 3 + r) * 3 + s) * cc + c];
+        out[i] = w[((int64_t)k * taps + (taps - 1 - tap)) * cc + c];
     }
 }
 
@@ -814,12 +814,14 @@ int conv3x3_stats_max_strips() { return sm_count(); }
 
 // 64 / 128 output channels go to the kernel with the pixels on N (development builds can switch it off)
 int conv3x3_any_run(const void* in, const void* wv, int tap_is_dim1, void* out, int n, int h, int w, int cin, int cout,
-                    cudaStream_t st, float* stats_partial = nullptr, int* stats_strips = nullptr, bool bf16 = false) {
+                    cudaStream_t st, float* stats_partial = nullptr, int* stats_strips = nullptr, bool bf16 = false,
+                    int taps = 9) {
 #ifndef TRB200_NO_PIXN
     if (pixn_preferred(cin, cout))
-        return conv3x3_pixn_run(in, wv, tap_is_dim1, out, n, h, w, cin, cout, st, stats_partial, stats_strips, bf16);
+        return conv3x3_pixn_run(in, wv, tap_is_dim1, out, n, h, w, cin, cout, st, stats_partial, stats_strips, bf16,
+                                taps);
 #endif
-    return conv3x3_run(in, wv, tap_is_dim1, out, n, h, w, cin, cout, st, 9, stats_partial, stats_strips, nullptr,
+    return conv3x3_run(in, wv, tap_is_dim1, out, n, h, w, cin, cout, st, taps, stats_partial, stats_strips, nullptr,
                        bf16);
 }
 
@@ -1162,7 +1164,7 @@ WgradParams wgrad_plan(const trb200_conv_desc& d, int nt, const TileShape& t, in
 #define TRB200_UNITN_MAX_K 128
 #endif
 inline bool wgrad_use_unitn(const trb200_conv_desc& d) {
-    return wgrad_unitn_supports(d) && d.k <= TRB200_UNITN_MAX_K;
+    return d.r == 3 && wgrad_unitn_supports(d) && d.k <= TRB200_UNITN_MAX_K;
 }
 
 // ------------------------------------------------------------------ first layer (C = 4)
@@ -1198,8 +1200,15 @@ bool igemm_small_c(const trb200_conv_desc& d) {
     return d.dtype == TRB200_DTYPE_F16 && is_3x3_s1_p1(d) && d.c == 4 && d.k % 64 == 0 && pick_nt(d.k) != 0 && d.n >= 1 && d.h >= 1 && d.w >= 1;
 }
 
+static bool is_1x1_s1_p0(const trb200_conv_desc& d) {
+    return d.r == 1 && d.s == 1 && d.pad_h == 0 && d.pad_w == 0 && d.stride_h == 1 && d.stride_w == 1;
+}
+
+// filter taps of a geometry the tensor-core kernels take: 9 or 1
+static int igemm_taps(const trb200_conv_desc& d) { return is_1x1_s1_p0(d) ? 1 : 9; }
+
 bool igemm_supports(const trb200_conv_desc& d, int which) {
-    if (!is_3x3_s1_p1(d)) return false;
+    if (!is_3x3_s1_p1(d) && !is_1x1_s1_p0(d)) return false;
     if (d.n < 1 || d.h < 1 || d.w < 1) return false;
     if (igemm_small_c(d)) return which != 1;      // wgrad and fprop; a first layer has no dgrad
     if (d.c % 64 != 0 || d.k % 64 != 0) return false;
@@ -1209,7 +1218,7 @@ bool igemm_supports(const trb200_conv_desc& d, int which) {
 }
 
 size_t igemm_dgrad_workspace(const trb200_conv_desc& d) {
-    return (size_t)align_up((int64_t)9 * d.c * d.k * 2, 256);
+    return (size_t)align_up((int64_t)igemm_taps(d) * d.c * d.k * 2, 256);
 }
 
 static size_t wgrad_partial_bytes(const trb200_conv_desc& d, int taps) {
@@ -1227,7 +1236,7 @@ size_t igemm_wgrad_workspace(const trb200_conv_desc& d) {
         return (size_t)align_up((int64_t)d.k * 64 * 2, 256) + wgrad_partial_bytes(e, 1);
     }
     if (wgrad_use_unitn(d)) return wgrad_unitn_partial_bytes(d);
-    return wgrad_partial_bytes(d, 9);
+    return wgrad_partial_bytes(d, igemm_taps(d));
 }
 
 // small C: the filters packed to 64 columns
@@ -1242,14 +1251,16 @@ int igemm_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* 
     TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, "conv_dgrad: workspace of %zu bytes needed, %zu given",
                 need, ws_bytes);
     TRB_REQUIRE(aligned16(ws), TRB200_ERR_INVALID_ARGUMENT, "conv_dgrad: workspace must be 16-byte aligned");
-    const int total = 9 * d.k * d.c;
+    const int taps = igemm_taps(d);
+    const int total = taps * d.k * d.c;
     int blocks = (total + 255) / 256;
     if (blocks > sm_count() * 4) blocks = sm_count() * 4;
     dgrad_filter_view_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(w), static_cast<uint16_t*>(ws), d.k,
-                                                     d.c);
+                                                     d.c, taps);
     TRB_LAUNCH_CHECK("dgrad_filter_view_kernel");
     // in = dY [n,h,w,k], filter view (ci = k, co = c, tap), out = dX [n,h,w,c]
-    return conv3x3_any_run(dy, ws, 0, dx, d.n, d.h, d.w, d.k, d.c, st, nullptr, nullptr, d.dtype == TRB200_DTYPE_BF16);
+    return conv3x3_any_run(dy, ws, 0, dx, d.n, d.h, d.w, d.k, d.c, st, nullptr, nullptr, d.dtype == TRB200_DTYPE_BF16,
+                           taps);
 }
 
 size_t igemm_fprop_stats_bytes(const trb200_conv_desc& d) {
@@ -1261,7 +1272,7 @@ int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y
                 cudaStream_t st, float* stats_partial, int* stats_strips) {
     if (!igemm_small_c(d))
         return conv3x3_any_run(x, w, 1, y, d.n, d.h, d.w, d.c, d.k, st, stats_partial, stats_strips,
-                               d.dtype == TRB200_DTYPE_BF16);
+                               d.dtype == TRB200_DTYPE_BF16, igemm_taps(d));
     const size_t need = igemm_fprop_workspace(d);
     TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, "conv_fprop: workspace of %zu bytes needed, %zu given",
                 need, ws_bytes);
@@ -1329,7 +1340,7 @@ int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* 
                 "conv_wgrad: workspace must be 256-byte aligned");
     if (igemm_small_c(d)) return igemm_wgrad_small_c(d, dy, x, dw, ws, st);
     if (wgrad_use_unitn(d)) return wgrad_unitn_run(d, dy, x, dw, static_cast<float*>(ws), st);
-    return wgrad_run(d, 9, dy, x, dw, static_cast<float*>(ws), st);
+    return wgrad_run(d, igemm_taps(d), dy, x, dw, static_cast<float*>(ws), st);
 }
 
 #ifdef TRB200_ROLE_TIMERS

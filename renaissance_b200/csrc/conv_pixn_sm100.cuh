@@ -380,9 +380,9 @@ int launch_pixn(const CUtensorMap& tin, const CUtensorMap& tw, const CUtensorMap
 // whether the pixel-N kernel is the better one for `cout` output channels
 inline bool pixn_preferred(int cin, int cout) { return cin % 64 == 0 && (cout == 64 || cout == 128); }
 
-// Same contract as conv3x3_run (3x3 taps, cin a multiple of 64).
+// Same contract as conv3x3_run (taps = 9 or 1, cin a multiple of 64).
 int conv3x3_pixn_run(const void* in, const void* wv, int tap_is_dim1, void* out, int n, int h, int w, int cin,
-                     int cout, cudaStream_t st, float* stats_partial, int* stats_strips, bool bf16) {
+                     int cout, cudaStream_t st, float* stats_partial, int* stats_strips, bool bf16, int taps) {
     const int MT = cout == 64 ? 64 : 128;
     const TileShape t = pick_tile(n, h, w, kPixN);
     const TileShape th = pixn_sub_box(t, 128), tc = pixn_sub_box(t, kPixChunk);
@@ -391,7 +391,6 @@ int conv3x3_pixn_run(const void* in, const void* wv, int tap_is_dim1, void* out,
     if (rc) return rc;
     rc = make_act_tmap(&tout, out, n, h, w, cout, tc, "conv output");
     if (rc) return rc;
-    const int taps = 9;
     if (tap_is_dim1) {
         const uint64_t dims[3] = {(uint64_t)cin, (uint64_t)taps, (uint64_t)cout};
         const uint64_t str[3] = {2, (uint64_t)cin * 2, (uint64_t)taps * cin * 2};

@@ -119,6 +119,37 @@ def test_tensor_core_kernels_match_oracle(orc, n, h, w, c, k):
     assert rel_l2(host(y).astype(np.float32), ref_y) < 2e-3
 
 
+@pytest.mark.parametrize("n,h,w,c,k", [(2, 8, 8, 64, 64), (3, 7, 5, 128, 256), (2, 14, 14, 256, 64),
+                                       (1, 9, 33, 512, 128), (4, 7, 7, 1024, 512), (2, 28, 28, 64, 256)])
+def test_one_by_one_convolutions_on_tensor_cores(orc, n, h, w, c, k):
+    """1x1 stride 1: the same kernels with one filter tap (a plain GEMM over the pixels)."""
+    from renaissance_b200 import ops
+    x, wt, dy = _rand_case(n + h + c + k, n, h, w, c, k, 1, 0, 1)
+    ref_dw, ref_dx = _oracle(orc, x, wt, dy, 0, 1)
+    g = ops.ConvGeometry(n, h, w, c, k, 1, 1, 0, 1)
+    for which in ("wgrad", "dgrad", "fprop"):
+        assert ops.conv_uses_tensor_cores(g, which)
+    dw = ops.conv_wgrad(g, dev(dy), dev(x))
+    dx = ops.conv_dgrad(g, dev(dy), dev(wt))
+    y = ops.conv_fprop(g, dev(x), dev(wt))
+    gamma, beta = np.ones(k, np.float32), np.zeros(k, np.float32)
+    y2, st = ops.conv_fprop_bn_stats(g, dev(x), dev(wt), dev(gamma), dev(beta), want_sums=True)
+    ops.device_status()
+    assert rel_l2(host(dx).astype(np.float32), ref_dx) < 2e-3
+    assert rel_l2(host(dw).astype(np.float32), ref_dw) < 2e-3
+    assert rel_l2(host(y).astype(np.float32), orc.conv_fwd(x.astype(np.float32), wt.astype(np.float32), pad=0)) < 2e-3
+    assert torch.equal(y, y2)
+    yf = host(y).astype(np.float64).reshape(-1, k)
+    assert rel_l2(host(st["sum"]), yf.sum(axis=0)) < 1e-4
+    ops.set_conv_backend(direct_only=True)
+    try:
+        dw3, dx3 = ops.conv_wgrad(g, dev(dy), dev(x)), ops.conv_dgrad(g, dev(dy), dev(wt))
+    finally:
+        ops.set_conv_backend(direct_only=False)
+    assert rel_l2(host(dw).astype(np.float32), host(dw3).astype(np.float32)) < 2e-3
+    assert rel_l2(host(dx).astype(np.float32), host(dx3).astype(np.float32)) < 2e-3
+
+
 def test_tensor_core_kernels_are_bitwise_reproducible_and_agree_with_direct():
     from renaissance_b200 import ops
     n, h, w, c, k = 8, 28, 28, 128, 256
