@@ -122,9 +122,10 @@ int trb200_bnrelu_bwd_static(const void* dy, const void* mask_bits, const void* 
 /* ------------------------------------------------------------------------- */
 /* Convolution weight gradient, dW[k,r,s,c] = sum dY[n,oh,ow,k] * X[...]      */
 /* 16-bit in (d->dtype), float accumulate, 16-bit out, fixed-order split      */
-/* reduction.  3x3 stride 1 pad 1 and 1x1 stride 1 with c and k multiples of  */
-/* 64 (k = 64, 128 or a multiple of 256), and half 3x3 with c = 4, run on the */
-/* tcgen05 kernels; every other geometry on the direct kernels.               */
+/* reduction.  3x3 pad 1 and 1x1 pad 0 at stride 1 or 2 with c and k          */
+/* multiples of 64 (k = 64, 128 or a multiple of 256), and half 3x3 stride 1  */
+/* with c = 4, run on the tcgen05 kernels (stride 2 through the stride-1      */
+/* kernel and a resampling pass); every other geometry on the direct kernels. */
 /* Replaces build_cbr_conv_amp_wgrad_graph + execute,                         */
 /* src/backend/ops/dtensor/cbr_op.cpp:763-840, 1431-1468.                     */
 /* ------------------------------------------------------------------------- */
@@ -146,9 +147,9 @@ int trb200_conv_dgrad(const trb200_conv_desc* d, const void* dy, const void* w, 
                       void* workspace, size_t workspace_bytes, void* stream);
 
 /* Forward convolution Y = X (*) W, 16-bit in (d->dtype), float accumulate, 16-bit
- * out, on the same tensor-core kernel as dgrad (3x3 stride 1 pad 1 or 1x1 stride 1,
- * k = 64, 128 or a multiple of 256, c % 64 == 0, or half 3x3 with c == 4; anything
- * else returns TRB200_ERR_UNSUPPORTED).
+ * out, on the same tensor-core kernel as dgrad (3x3 pad 1 or 1x1 pad 0 at stride 1
+ * or 2, k = 64, 128 or a multiple of 256, c % 64 == 0, or half 3x3 stride 1 with
+ * c == 4; anything else returns TRB200_ERR_UNSUPPORTED).
  * With c == 4 (the padded first layer) the workspace receives the 3x3
  * neighbourhoods of every pixel, n*h*w*128 bytes: any activation-sized buffer that
  * is free at that point will do (the block's relu-output buffer, say).

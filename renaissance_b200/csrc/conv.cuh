@@ -33,6 +33,17 @@ int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* 
 int igemm_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* dx, void* ws,
                 size_t ws_bytes, cudaStream_t st);
 
+// conv_strided.cu: 3x3 pad 1 and 1x1 pad 0 with stride 2, through the stride-1 tensor-core kernels and one
+// resampling pass (workspace: the resampled tensor, then the inner kernel's workspace).
+bool strided_supports(const trb200_conv_desc& d, int which);   // 0 wgrad, 1 dgrad, 2 fprop
+size_t strided_workspace(const trb200_conv_desc& d, int which);
+int strided_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* ws, size_t ws_bytes,
+                  cudaStream_t st);
+int strided_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes,
+                  cudaStream_t st);
+int strided_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, void* ws, size_t ws_bytes,
+                  cudaStream_t st);
+
 int validate_conv_desc(const trb200_conv_desc* d, const char* who);
 
 }  // namespace trb

@@ -22,6 +22,7 @@ namespace {
 std::atomic<int> g_backend{0};   // 0 = automatic, 1 = direct kernels only
 
 bool use_igemm(const trb200_conv_desc& d, int which) { return g_backend.load() == 0 && igemm_supports(d, which); }
+bool use_strided(const trb200_conv_desc& d, int which) { return g_backend.load() == 0 && strided_supports(d, which); }
 }  // namespace
 
 int validate_conv_desc(const trb200_conv_desc* d, const char* who) {
@@ -41,6 +42,7 @@ int validate_conv_desc(const trb200_conv_desc* d, const char* who) {
 }  // namespace trb
 
 using trb::use_igemm;
+using trb::use_strided;
 
 extern "C" int trb200_set_conv_backend(int backend) {
     TRB_REQUIRE(backend == 0 || backend == 1, TRB200_ERR_INVALID_ARGUMENT, "set_conv_backend: 0 or 1 expected");
@@ -50,7 +52,7 @@ extern "C" int trb200_set_conv_backend(int backend) {
 
 extern "C" int trb200_conv_uses_tensor_cores(const trb200_conv_desc* d, int which) {
     if (!d || which < 0 || which > 2) return 0;
-    return use_igemm(*d, which) ? 1 : 0;
+    return (use_igemm(*d, which) || use_strided(*d, which)) ? 1 : 0;
 }
 
 extern "C" int trb200_device_status(void) {
@@ -67,12 +69,15 @@ extern "C" int trb200_device_status(void) {
 
 extern "C" size_t trb200_conv_wgrad_workspace_bytes(const trb200_conv_desc* d) {
     if (trb::validate_conv_desc(d, "conv_wgrad_workspace_bytes")) return 0;
-    return use_igemm(*d, 0) ? trb::igemm_wgrad_workspace(*d) : trb::wgrad_direct_workspace(*d);
+    if (use_igemm(*d, 0)) return trb::igemm_wgrad_workspace(*d);
+    if (use_strided(*d, 0)) return trb::strided_workspace(*d, 0);
+    return trb::wgrad_direct_workspace(*d);
 }
 
 extern "C" size_t trb200_conv_dgrad_workspace_bytes(const trb200_conv_desc* d) {
     if (trb::validate_conv_desc(d, "conv_dgrad_workspace_bytes")) return 0;
-    return use_igemm(*d, 1) ? trb::igemm_dgrad_workspace(*d) : 0;
+    if (use_igemm(*d, 1)) return trb::igemm_dgrad_workspace(*d);
+    return use_strided(*d, 1) ? trb::strided_workspace(*d, 1) : 0;
 }
 
 extern "C" int trb200_conv_wgrad(const trb200_conv_desc* d, const void* dy, const void* x, void* dw, void* workspace,
@@ -83,6 +88,7 @@ extern "C" int trb200_conv_wgrad(const trb200_conv_desc* d, const void* dy, cons
     TRB_REQUIRE(trb::aligned16(dy) && trb::aligned16(x) && trb::aligned16(dw), TRB200_ERR_INVALID_ARGUMENT,
                 "conv_wgrad: tensors must be 16-byte aligned");
     if (use_igemm(*d, 0)) return trb::igemm_wgrad(*d, dy, x, dw, workspace, workspace_bytes, trb::as_stream(stream));
+    if (use_strided(*d, 0)) return trb::strided_wgrad(*d, dy, x, dw, workspace, workspace_bytes, trb::as_stream(stream));
     return trb::wgrad_direct(*d, dy, x, dw, workspace, workspace_bytes, trb::as_stream(stream));
 }
 
@@ -95,12 +101,14 @@ extern "C" int trb200_conv_dgrad(const trb200_conv_desc* d, const void* dy, cons
     TRB_REQUIRE(trb::aligned16(dy) && trb::aligned16(w) && trb::aligned16(dx), TRB200_ERR_INVALID_ARGUMENT,
                 "conv_dgrad: tensors must be 16-byte aligned");
     if (use_igemm(*d, 1)) return trb::igemm_dgrad(*d, dy, w, dx, workspace, workspace_bytes, trb::as_stream(stream));
+    if (use_strided(*d, 1)) return trb::strided_dgrad(*d, dy, w, dx, workspace, workspace_bytes, trb::as_stream(stream));
     return trb::dgrad_direct(*d, dy, w, dx, trb::as_stream(stream));
 }
 
 extern "C" size_t trb200_conv_fprop_workspace_bytes(const trb200_conv_desc* d) {
     if (trb::validate_conv_desc(d, "conv_fprop_workspace_bytes")) return 0;
-    return trb::igemm_supports(*d, 2) ? trb::igemm_fprop_workspace(*d) : 0;
+    if (trb::igemm_supports(*d, 2)) return trb::igemm_fprop_workspace(*d);
+    return trb::strided_supports(*d, 2) ? trb::strided_workspace(*d, 2) : 0;
 }
 
 extern "C" int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const void* w, void* y, void* workspace,
@@ -111,9 +119,11 @@ extern "C" int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const
     TRB_REQUIRE(y != x && y != w, TRB200_ERR_INVALID_ARGUMENT, "conv_fprop: y must not alias x or w");
     TRB_REQUIRE(trb::aligned16(x) && trb::aligned16(w) && trb::aligned16(y), TRB200_ERR_INVALID_ARGUMENT,
                 "conv_fprop: tensors must be 16-byte aligned");
+    if (!trb::igemm_supports(*d, 2) && trb::strided_supports(*d, 2))
+        return trb::strided_fprop(*d, x, w, y, workspace, workspace_bytes, trb::as_stream(stream));
     TRB_REQUIRE(trb::igemm_supports(*d, 2), TRB200_ERR_UNSUPPORTED,
-                "conv_fprop: only 3x3 stride 1 pad 1 (c = 4 or a multiple of 64) and 1x1 stride 1 (c a multiple of 64), "
-                "with k = 64, 128 or a multiple of 256");
+                "conv_fprop: only 3x3 pad 1 (c = 4 at stride 1, or a multiple of 64) and 1x1 pad 0 (c a multiple of 64) "
+                "at stride 1 or 2, with k = 64, 128 or a multiple of 256");
     return trb::igemm_fprop(*d, x, w, y, workspace, workspace_bytes, trb::as_stream(stream));
 }
 

@@ -1,0 +1,184 @@
+// Stride-2 convolutions (3x3 pad 1 and 1x1 pad 0, the two kinds ResNet-50 has besides its 7x7 stem) on the
+// tensor-core kernels, by way of the stride-1 kernels plus one resampling pass:
+//
+//   3x3 s2 p1   y  = even pixels of the stride-1 convolution of x                 (forward)
+//               dx = stride-1 data gradient of dy with zeros put between its pixels
+//               dW = stride-1 weight gradient of that zero-stuffed dy against x
+//   1x1 s2 p0   y  = 1x1 convolution of the even pixels of x
+//               dW = 1x1 weight gradient of dy against the even pixels of x
+//               dx = 1x1 data gradient of dy, written to the even pixels of a zeroed dx
+//
+// The 3x3 route spends four times the flops of a native strided kernel (three of four output pixels of the
+// stride-1 convolution are dropped, three of four dy pixels are zeros), which still is two orders of magnitude
+// faster than the direct CUDA-core kernels these shapes would otherwise take; a network has one such layer per
+// resolution change.  Results equal the strided convolution's exactly up to summation order: the extra terms
+// are exact zeros.
+//
+// Reference counterparts: the same cuDNN-FE conv_dgrad / conv_wgrad / conv_fprop graphs with stride 2,
+// src/backend/ops/dtensor/cbr_op.cpp:622-917.
+#include "common.cuh"
+#include "conv.cuh"
+
+namespace trb {
+namespace {
+
+// out[n][oh][ow][:] = in[n][2*oh][2*ow][:], 16-byte vectors (vec = channels / 8)
+__global__ void __launch_bounds__(256)
+subsample2_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int n, int h, int w, int oh_n, int ow_n,
+                  int vec) {
+    const int64_t total = (int64_t)n * oh_n * ow_n * vec;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int v = (int)(i % vec);
+        int64_t pix = i / vec;
+        const int ow = (int)(pix % ow_n);
+        pix /= ow_n;
+        const int oh = (int)(pix % oh_n);
+        const int64_t img = pix / oh_n;
+        out[i] = in[((img * h + 2 * oh) * w + 2 * ow) * vec + v];
+    }
+}
+
+// out[n][ih][iw][:] = (ih, iw both even) ? in[n][ih/2][iw/2][:] : 0
+__global__ void __launch_bounds__(256)
+upsample_zero2_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int n, int h, int w, int oh_n, int ow_n,
+                      int vec) {
+    const int64_t total = (int64_t)n * h * w * vec;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int v = (int)(i % vec);
+        int64_t pix = i / vec;
+        const int iw = (int)(pix % w);
+        pix /= w;
+        const int ih = (int)(pix % h);
+        const int64_t img = pix / h;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (!(ih & 1) && !(iw & 1)) val = in[((img * oh_n + (ih >> 1)) * ow_n + (iw >> 1)) * vec + v];
+        out[i] = val;
+    }
+}
+
+int resample_blocks(int64_t total) {
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    return (int)(blocks > cap ? cap : (blocks < 1 ? 1 : blocks));
+}
+
+int subsample2(const void* in, void* out, int n, int h, int w, int ch, cudaStream_t st) {
+    const int oh = (h - 1) / 2 + 1, ow = (w - 1) / 2 + 1;
+    subsample2_kernel<<<resample_blocks((int64_t)n * oh * ow * (ch / 8)), 256, 0, st>>>(
+        static_cast<const uint4*>(in), static_cast<uint4*>(out), n, h, w, oh, ow, ch / 8);
+    TRB_LAUNCH_CHECK("subsample2_kernel");
+    return TRB200_OK;
+}
+
+int upsample_zero2(const void* in, void* out, int n, int h, int w, int ch, cudaStream_t st) {
+    const int oh = (h - 1) / 2 + 1, ow = (w - 1) / 2 + 1;
+    upsample_zero2_kernel<<<resample_blocks((int64_t)n * h * w * (ch / 8)), 256, 0, st>>>(
+        static_cast<const uint4*>(in), static_cast<uint4*>(out), n, h, w, oh, ow, ch / 8);
+    TRB_LAUNCH_CHECK("upsample_zero2_kernel");
+    return TRB200_OK;
+}
+
+bool is_3x3_s2_p1(const trb200_conv_desc& d) {
+    return d.r == 3 && d.s == 3 && d.pad_h == 1 && d.pad_w == 1 && d.stride_h == 2 && d.stride_w == 2;
+}
+bool is_1x1_s2_p0(const trb200_conv_desc& d) {
+    return d.r == 1 && d.s == 1 && d.pad_h == 0 && d.pad_w == 0 && d.stride_h == 2 && d.stride_w == 2;
+}
+
+int out_h(const trb200_conv_desc& d) { return (d.h - 1) / 2 + 1; }
+int out_w(const trb200_conv_desc& d) { return (d.w - 1) / 2 + 1; }
+
+// The stride-1 problem the tensor-core kernels are given: the 3x3 one at the input's resolution, the 1x1 one
+// at the output's.
+trb200_conv_desc dense_desc(const trb200_conv_desc& d) {
+    trb200_conv_desc e = d;
+    e.stride_h = e.stride_w = 1;
+    if (is_1x1_s2_p0(d)) { e.h = out_h(d); e.w = out_w(d); }
+    return e;
+}
+
+// bytes of the resampled tensor that sits at the front of the workspace
+size_t temp_bytes(const trb200_conv_desc& d, int which) {
+    int64_t elems;
+    if (is_3x3_s2_p1(d)) elems = (int64_t)d.n * d.h * d.w * d.k;                          // y or dy at full resolution
+    else elems = (int64_t)d.n * out_h(d) * out_w(d) * d.c;                                // x or dx at half resolution
+    (void)which;
+    return (size_t)align_up(elems * 2, 256);
+}
+
+size_t inner_bytes(const trb200_conv_desc& d, int which) {
+    const trb200_conv_desc e = dense_desc(d);
+    if (which == 0) return igemm_wgrad_workspace(e);
+    if (which == 1) return igemm_dgrad_workspace(e);
+    return igemm_fprop_workspace(e);
+}
+
+}  // namespace
+
+bool strided_supports(const trb200_conv_desc& d, int which) {
+    if (!is_3x3_s2_p1(d) && !is_1x1_s2_p0(d)) return false;
+    if (d.c % 64 != 0 || d.k % 64 != 0) return false;
+    return igemm_supports(dense_desc(d), which);
+}
+
+size_t strided_workspace(const trb200_conv_desc& d, int which) {
+    return temp_bytes(d, which) + (size_t)align_up((int64_t)inner_bytes(d, which), 256);
+}
+
+#define TRB_STRIDED_PROLOGUE(who)                                                                              \
+    const size_t need = strided_workspace(d, which);                                                           \
+    TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, who ": workspace of %zu bytes needed, %zu given", \
+                need, ws_bytes);                                                                               \
+    TRB_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255u) == 0, TRB200_ERR_INVALID_ARGUMENT,                     \
+                who ": workspace must be 256-byte aligned");                                                   \
+    unsigned char* temp = static_cast<unsigned char*>(ws);                                                     \
+    unsigned char* inner = temp + temp_bytes(d, which);                                                        \
+    const size_t inner_size = ws_bytes - temp_bytes(d, which);                                                 \
+    const trb200_conv_desc e = dense_desc(d)
+
+int strided_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* ws, size_t ws_bytes,
+                  cudaStream_t st) {
+    const int which = 0;
+    TRB_STRIDED_PROLOGUE("conv_wgrad");
+    int rc;
+    if (is_3x3_s2_p1(d)) {
+        rc = upsample_zero2(dy, temp, d.n, d.h, d.w, d.k, st);
+        if (rc) return rc;
+        return igemm_wgrad(e, temp, x, dw, inner, inner_size, st);
+    }
+    rc = subsample2(x, temp, d.n, d.h, d.w, d.c, st);
+    if (rc) return rc;
+    return igemm_wgrad(e, dy, temp, dw, inner, inner_size, st);
+}
+
+int strided_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes,
+                  cudaStream_t st) {
+    const int which = 1;
+    TRB_STRIDED_PROLOGUE("conv_dgrad");
+    int rc;
+    if (is_3x3_s2_p1(d)) {
+        rc = upsample_zero2(dy, temp, d.n, d.h, d.w, d.k, st);
+        if (rc) return rc;
+        return igemm_dgrad(e, temp, w, dx, inner, inner_size, st);
+    }
+    rc = igemm_dgrad(e, dy, w, temp, inner, inner_size, st);
+    if (rc) return rc;
+    return upsample_zero2(temp, dx, d.n, d.h, d.w, d.c, st);
+}
+
+int strided_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, void* ws, size_t ws_bytes,
+                  cudaStream_t st) {
+    const int which = 2;
+    TRB_STRIDED_PROLOGUE("conv_fprop");
+    int rc;
+    if (is_3x3_s2_p1(d)) {
+        rc = igemm_fprop(e, x, w, temp, inner, inner_size, st);
+        if (rc) return rc;
+        return subsample2(temp, y, d.n, d.h, d.w, d.k, st);
+    }
+    rc = subsample2(x, temp, d.n, d.h, d.w, d.c, st);
+    if (rc) return rc;
+    return igemm_fprop(e, temp, w, y, inner, inner_size, st);
+}
+
+}  // namespace trb

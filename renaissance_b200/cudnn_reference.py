@@ -50,9 +50,14 @@ class _Graph:
         self.graph.execute(self.pack, self.workspace, handle=_h())
 
 
-def _new_graph():
+def _io_type(t):
     import cudnn
-    return cudnn.pygraph(io_data_type=cudnn.data_type.HALF, intermediate_data_type=cudnn.data_type.FLOAT,
+    return cudnn.data_type.BFLOAT16 if t.dtype == torch.bfloat16 else cudnn.data_type.HALF
+
+
+def _new_graph(io=None):
+    import cudnn
+    return cudnn.pygraph(io_data_type=io or cudnn.data_type.HALF, intermediate_data_type=cudnn.data_type.FLOAT,
                          compute_data_type=cudnn.data_type.FLOAT, handle=_h())
 
 
@@ -66,20 +71,26 @@ def _finalize(g):
     g.build_plans(cudnn.build_plan_policy.HEURISTICS_CHOICE)
 
 
-def conv_fprop(x, w, y, genstats=None):
-    """x [n,h,w,c], w [k,3,3,c], y [n,h,w,k] (half, contiguous).  genstats = (sum, sqsum) float [k] adds the
-    statistics node the reference fuses behind the convolution."""
+def _krsc(k, c, r):
+    return [k, c, r, r], [r * r * c, 1, r * c, c]
+
+
+def conv_fprop(x, w, y, genstats=None, pad=1, stride=1):
+    """x [n,h,w,c], w [k,r,r,c], y [n,oh,ow,k] (half or bfloat16, contiguous).  genstats = (sum, sqsum) float [k]
+    adds the statistics node the reference fuses behind the convolution."""
     import cudnn
     n, h, wd, c = x.shape
-    k = w.shape[0]
-    g = _new_graph()
+    k, r = w.shape[0], w.shape[1]
+    io = _io_type(x)
+    g = _new_graph(io)
     dx, sx = _nhwc(n, c, h, wd)
-    X = g.tensor(name="X", dim=dx, stride=sx, data_type=cudnn.data_type.HALF)
-    W = g.tensor(name="W", dim=[k, c, 3, 3], stride=[9 * c, 1, 3 * c, c], data_type=cudnn.data_type.HALF)
-    Y = g.conv_fprop(image=X, weight=W, padding=[1, 1], stride=[1, 1], dilation=[1, 1],
+    X = g.tensor(name="X", dim=dx, stride=sx, data_type=io)
+    dwt, swt = _krsc(k, c, r)
+    W = g.tensor(name="W", dim=dwt, stride=swt, data_type=io)
+    Y = g.conv_fprop(image=X, weight=W, padding=[pad, pad], stride=[stride, stride], dilation=[1, 1],
                      compute_data_type=cudnn.data_type.FLOAT)
-    dy, sy = _nhwc(n, k, h, wd)
-    Y.set_output(True).set_dim(dy).set_stride(sy).set_data_type(cudnn.data_type.HALF)
+    dy, sy = _nhwc(n, k, y.shape[1], y.shape[2])
+    Y.set_output(True).set_dim(dy).set_stride(sy).set_data_type(io)
     pack = {X: x.data_ptr(), W: w.data_ptr(), Y: y.data_ptr()}
     if genstats is not None:
         S, Q = g.genstats(input=Y, compute_data_type=cudnn.data_type.FLOAT)
@@ -90,34 +101,38 @@ def conv_fprop(x, w, y, genstats=None):
     return _Graph(g, pack, (x, w, y, genstats))
 
 
-def conv_dgrad(dy, w, dx):
+def conv_dgrad(dy, w, dx, pad=1, stride=1):
     import cudnn
-    n, h, wd, k = dy.shape
-    c = w.shape[3]
-    g = _new_graph()
-    ddy, sdy = _nhwc(n, k, h, wd)
-    DY = g.tensor(name="dY", dim=ddy, stride=sdy, data_type=cudnn.data_type.HALF)
-    W = g.tensor(name="W", dim=[k, c, 3, 3], stride=[9 * c, 1, 3 * c, c], data_type=cudnn.data_type.HALF)
-    DX = g.conv_dgrad(loss=DY, filter=W, padding=[1, 1], stride=[1, 1], dilation=[1, 1],
+    n, oh, ow, k = dy.shape
+    c, r = w.shape[3], w.shape[1]
+    io = _io_type(dy)
+    g = _new_graph(io)
+    ddy, sdy = _nhwc(n, k, oh, ow)
+    DY = g.tensor(name="dY", dim=ddy, stride=sdy, data_type=io)
+    dwt, swt = _krsc(k, c, r)
+    W = g.tensor(name="W", dim=dwt, stride=swt, data_type=io)
+    DX = g.conv_dgrad(loss=DY, filter=W, padding=[pad, pad], stride=[stride, stride], dilation=[1, 1],
                       compute_data_type=cudnn.data_type.FLOAT)
-    ddx, sdx = _nhwc(n, c, h, wd)
-    DX.set_output(True).set_dim(ddx).set_stride(sdx).set_data_type(cudnn.data_type.HALF)
+    ddx, sdx = _nhwc(n, c, dx.shape[1], dx.shape[2])
+    DX.set_output(True).set_dim(ddx).set_stride(sdx).set_data_type(io)
     _finalize(g)
     return _Graph(g, {DY: dy.data_ptr(), W: w.data_ptr(), DX: dx.data_ptr()}, (dy, w, dx))
 
 
-def conv_wgrad(x, dy, dw):
+def conv_wgrad(x, dy, dw, pad=1, stride=1):
     import cudnn
     n, h, wd, c = x.shape
-    k = dy.shape[3]
-    g = _new_graph()
+    k, r = dy.shape[3], dw.shape[1]
+    io = _io_type(x)
+    g = _new_graph(io)
     dx_, sx = _nhwc(n, c, h, wd)
-    ddy, sdy = _nhwc(n, k, h, wd)
-    X = g.tensor(name="X", dim=dx_, stride=sx, data_type=cudnn.data_type.HALF)
-    DY = g.tensor(name="dY", dim=ddy, stride=sdy, data_type=cudnn.data_type.HALF)
-    DW = g.conv_wgrad(image=X, loss=DY, padding=[1, 1], stride=[1, 1], dilation=[1, 1],
+    ddy, sdy = _nhwc(n, k, dy.shape[1], dy.shape[2])
+    X = g.tensor(name="X", dim=dx_, stride=sx, data_type=io)
+    DY = g.tensor(name="dY", dim=ddy, stride=sdy, data_type=io)
+    DW = g.conv_wgrad(image=X, loss=DY, padding=[pad, pad], stride=[stride, stride], dilation=[1, 1],
                       compute_data_type=cudnn.data_type.FLOAT)
-    DW.set_output(True).set_dim([k, c, 3, 3]).set_stride([9 * c, 1, 3 * c, c]).set_data_type(cudnn.data_type.HALF)
+    dwt, swt = _krsc(k, c, r)
+    DW.set_output(True).set_dim(dwt).set_stride(swt).set_data_type(io)
     _finalize(g)
     return _Graph(g, {X: x.data_ptr(), DY: dy.data_ptr(), DW: dw.data_ptr()}, (x, dy, dw))
 

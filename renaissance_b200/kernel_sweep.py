@@ -4,6 +4,7 @@
     python -m renaissance_b200.kernel_sweep --only block    # BASELINE config 2 (one block backward)
     python -m renaissance_b200.kernel_sweep --only bnrelu --quick
     python -m renaissance_b200.kernel_sweep --only conv --quick --batch 64 --shape 56,256,256 --what fprop_stats
+    python -m renaissance_b200.kernel_sweep --only resnet50 --cudnn     # ResNet-50 conv shapes, bfloat16
 
 Covers BASELINE.json's config 2 (Conv3x3 C=K=64 + BN + ReLU backward at N=256, 56x56)
 and config 5 (BN+ReLU backward over N*H*W x C, fused softmax-CE over N x C), plus the
@@ -124,13 +125,14 @@ def softmax_point(t, b, c, ls, hbm, src):
          frac=round(byt / med / 1e6 / hbm, 4), peak_source=src)
 
 
-def conv_point(t, n, h, c, k, what, tc, src):
-    geo = ops.ConvGeometry(n, h, h, c, k)
+def conv_point(t, n, h, c, k, what, tc, src, r=3, pad=1, stride=1, dtype=torch.float16, hbm=None):
+    geo = ops.ConvGeometry(n, h, h, c, k, r, r, pad, stride, dtype=dtype)
+    oh = geo.oh
     g = torch.Generator(device="cuda").manual_seed(0)
-    x = torch.randn((n, h, h, c), generator=g, device="cuda").half()
-    w = (torch.randn((k, 3, 3, c), generator=g, device="cuda") * (2.0 / (9 * c)) ** 0.5).half()
-    dy = torch.randn((n, h, h, k), generator=g, device="cuda").half()
-    flop = 2.0 * n * h * h * c * k * 9
+    x = torch.randn((n, h, h, c), generator=g, device="cuda").to(dtype)
+    w = (torch.randn((k, r, r, c), generator=g, device="cuda") * (2.0 / (r * r * c)) ** 0.5).to(dtype)
+    dy = torch.randn((n, oh, oh, k), generator=g, device="cuda").to(dtype)
+    flop = 2.0 * n * oh * oh * c * k * r * r
     if what == "dgrad":
         dx = torch.empty_like(x)
         med, best = t(lambda: ops.conv_dgrad(geo, dy, w, dx=dx))
@@ -152,18 +154,29 @@ def conv_point(t, n, h, c, k, what, tc, src):
         if c < 8:
             raise RuntimeError("the reference pads the first layer to 4 channels; cuDNN tensor-core graphs need C % 8 == 0")
         if what == "dgrad":
-            return cr.conv_dgrad(dy, w, torch.empty_like(x))
+            return cr.conv_dgrad(dy, w, torch.empty_like(x), pad=pad, stride=stride)
         if what == "wgrad":
-            return cr.conv_wgrad(x, dy, torch.empty_like(w))
+            return cr.conv_wgrad(x, dy, torch.empty_like(w), pad=pad, stride=stride)
         if what == "fprop_stats":
             st = (torch.empty(k, device="cuda"), torch.empty(k, device="cuda"))
-            return cr.conv_fprop(x, w, torch.empty_like(dy), genstats=st)
-        return cr.conv_fprop(x, w, torch.empty_like(dy))
+            return cr.conv_fprop(x, w, torch.empty_like(dy), genstats=st, pad=pad, stride=stride)
+        return cr.conv_fprop(x, w, torch.empty_like(dy), pad=pad, stride=stride)
 
     lib = _library(t, build)
-    emit(kernel=f"conv {what}", shape=dict(n=n, h=h, w=h, c=c, k=k), ms=round(med, 4), best_ms=round(best, 4),
+    shape = dict(n=n, h=h, w=h, c=c, k=k)
+    extra = {}
+    if (r, pad, stride) != (3, 1, 1) or dtype != torch.float16:
+        # the ResNet-50 points: 1x1 layers move more bytes per flop than the tensor pipe can hide, so the
+        # HBM figure (activations in and out once, filters once) is reported beside the flop rate
+        shape.update(r=r, pad=pad, stride=stride)
+        byt = 2.0 * (n * oh * oh * k + n * h * h * c + k * r * r * c)
+        extra = dict(dtype=str(dtype).replace("torch.", ""), tensor_cores=ops.conv_uses_tensor_cores(
+            geo, "fprop" if what.startswith("fprop") else what), hbm_gbs=round(byt / med / 1e6, 1))
+        if hbm:
+            extra["hbm_frac"] = round(byt / med / 1e6 / hbm, 4)
+    emit(kernel=f"conv {what}", shape=shape, ms=round(med, 4), best_ms=round(best, 4),
          bound="tensor", achieved=round(flop / med / 1e9, 1), peak=tc, unit="TFLOP/s",
-         frac=round(flop / med / 1e9 / tc, 4), peak_source=src, **lib)
+         frac=round(flop / med / 1e9 / tc, 4), peak_source=src, **extra, **lib)
 
 
 def block_point(t, n, h, c, k, hbm, tc, src):
@@ -200,13 +213,25 @@ def block_point(t, n, h, c, k, hbm, tc, src):
          frac=round((flop / tc / 1e9 + byt / hbm / 1e6) / med, 4), peak_source=src)
 
 
+# ResNet-50's distinct convolutions: kernel, in channels, out channels, input extent, stride, padding
+RESNET50_CONVS = [
+    (7, 4, 64, 224, 2, 3),
+    (1, 64, 64, 56, 1, 0), (3, 64, 64, 56, 1, 1), (1, 64, 256, 56, 1, 0), (1, 256, 64, 56, 1, 0),
+    (1, 256, 128, 56, 1, 0), (1, 256, 512, 56, 2, 0), (3, 128, 128, 56, 2, 1),
+    (1, 128, 512, 28, 1, 0), (1, 512, 128, 28, 1, 0), (3, 128, 128, 28, 1, 1),
+    (1, 512, 256, 28, 1, 0), (1, 512, 1024, 28, 2, 0), (3, 256, 256, 28, 2, 1),
+    (1, 256, 1024, 14, 1, 0), (1, 1024, 256, 14, 1, 0), (3, 256, 256, 14, 1, 1),
+    (1, 1024, 512, 14, 1, 0), (1, 1024, 2048, 14, 2, 0), (3, 512, 512, 14, 2, 1),
+    (1, 512, 2048, 7, 1, 0), (1, 2048, 512, 7, 1, 0), (3, 512, 512, 7, 1, 1),
+]
+
 VGG_SHAPES = [(224, 64, 64), (112, 64, 128), (112, 128, 128), (56, 128, 256), (56, 256, 256), (28, 256, 512),
               (28, 512, 512), (14, 512, 512)]
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="all", choices=["all", "block", "bnrelu", "softmax", "conv"])
+    ap.add_argument("--only", default="all", choices=["all", "block", "bnrelu", "softmax", "conv", "resnet50"])
     ap.add_argument("--quick", action="store_true", help="one small point per kernel (for profiler captures)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--batch", type=int, default=256, help="images for the conv / block points")
@@ -245,6 +270,16 @@ def main():
         for h, c, k in shapes:
             for what in kinds:
                 conv_point(t, n, h, c, k, what, tc, src)
+    if args.only == "resnet50":
+        # BASELINE config 4 at the level the hot path reaches it: the data and weight gradients of every
+        # distinct convolution of ResNet-50 on bfloat16 tensors
+        kinds = tuple(args.what.split(",")) if args.what else ("dgrad", "wgrad")
+        for r, c, k, h, stride, pad in RESNET50_CONVS:
+            for what in kinds:
+                if what.startswith("fprop") and not ops.conv_uses_tensor_cores(
+                        ops.ConvGeometry(n, h, h, c, k, r, r, pad, stride, dtype=torch.bfloat16), "fprop"):
+                    continue
+                conv_point(t, n, h, c, k, what, tc, src, r=r, pad=pad, stride=stride, dtype=torch.bfloat16, hbm=hbm)
 
 
 if __name__ == "__main__":

@@ -59,13 +59,23 @@ def test_tensor_core_coverage_rule(lib):
     vgg = _lib.ConvDesc(256, 56, 56, 64, 64, 3, 3, 1, 1, 1, 1)
     first = _lib.ConvDesc(256, 224, 224, 4, 64, 3, 3, 1, 1, 1, 1)
     strided = _lib.ConvDesc(8, 56, 56, 64, 64, 3, 3, 1, 1, 2, 2)
+    one_by_one = _lib.ConvDesc(8, 56, 56, 256, 64, 1, 1, 0, 0, 1, 1, 1)       # bfloat16
+    stem = _lib.ConvDesc(8, 224, 224, 4, 64, 7, 7, 3, 3, 2, 2)
+    stride_three = _lib.ConvDesc(8, 56, 56, 64, 64, 3, 3, 1, 1, 3, 3)
     odd = _lib.ConvDesc(8, 56, 56, 24, 64, 3, 3, 1, 1, 1, 1)
     for which in (0, 1, 2):
         assert lib.trb200_conv_uses_tensor_cores(C.byref(vgg), which) == 1
         # the 4-channel first layer: weight gradient and forward only (it has no data gradient)
         assert lib.trb200_conv_uses_tensor_cores(C.byref(first), which) == (0 if which == 1 else 1)
-        assert lib.trb200_conv_uses_tensor_cores(C.byref(strided), which) == 0
-        assert lib.trb200_conv_uses_tensor_cores(C.byref(odd), which) == 0
+        # stride 2 goes through the stride-1 kernel and a resampling pass; 1x1 is the same kernel with one tap
+        assert lib.trb200_conv_uses_tensor_cores(C.byref(strided), which) == 1
+        assert lib.trb200_conv_uses_tensor_cores(C.byref(one_by_one), which) == 1
+        for direct in (stem, stride_three, odd):
+            assert lib.trb200_conv_uses_tensor_cores(C.byref(direct), which) == 0
+    # a strided layer needs room for the resampled tensor
+    assert lib.trb200_conv_dgrad_workspace_bytes(C.byref(strided)) >= 8 * 56 * 56 * 64 * 2
+    bad = _lib.ConvDesc(8, 56, 56, 64, 64, 3, 3, 1, 1, 1, 1, 7)
+    assert lib.trb200_conv_wgrad_workspace_bytes(C.byref(bad)) == 0        # unknown dtype
 
 
 def test_workspace_sizes_are_consistent(lib):

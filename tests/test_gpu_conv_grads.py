@@ -150,6 +150,36 @@ def test_one_by_one_convolutions_on_tensor_cores(orc, n, h, w, c, k):
     assert rel_l2(host(dx).astype(np.float32), host(dx3).astype(np.float32)) < 2e-3
 
 
+@pytest.mark.parametrize("n,h,w,c,k,r,pad", [(2, 8, 8, 64, 64, 3, 1), (2, 9, 7, 64, 128, 3, 1), (1, 14, 14, 128, 256, 3, 1),
+                                             (3, 8, 8, 128, 64, 1, 0), (2, 7, 9, 256, 512, 1, 0),
+                                             (2, 28, 28, 64, 128, 1, 0)])
+def test_stride_two_convolutions_on_tensor_cores(orc, n, h, w, c, k, r, pad):
+    """Stride 2 (3x3 pad 1, 1x1 pad 0): the stride-1 tensor-core kernels plus a resampling pass, against the
+    oracle's strided loops and the direct strided kernels; odd extents included."""
+    from renaissance_b200 import ops
+    x, wt, dy = _rand_case(n + h + c + k + r, n, h, w, c, k, r, pad, 2)
+    ref_dw, ref_dx = _oracle(orc, x, wt, dy, pad, 2)
+    g = ops.ConvGeometry(n, h, w, c, k, r, r, pad, 2)
+    for which in ("wgrad", "dgrad", "fprop"):
+        assert ops.conv_uses_tensor_cores(g, which)
+    dw = ops.conv_wgrad(g, dev(dy), dev(x))
+    dx = ops.conv_dgrad(g, dev(dy), dev(wt))
+    y = ops.conv_fprop(g, dev(x), dev(wt))
+    ops.device_status()
+    assert tuple(y.shape) == tuple(dy.shape)
+    assert rel_l2(host(dx).astype(np.float32), ref_dx) < 2e-3
+    assert rel_l2(host(dw).astype(np.float32), ref_dw) < 2e-3
+    ref_y = orc.conv_fwd(x.astype(np.float32), wt.astype(np.float32), pad=pad, stride=2)
+    assert rel_l2(host(y).astype(np.float32), ref_y) < 2e-3
+    ops.set_conv_backend(direct_only=True)
+    try:
+        dw3, dx3 = ops.conv_wgrad(g, dev(dy), dev(x)), ops.conv_dgrad(g, dev(dy), dev(wt))
+    finally:
+        ops.set_conv_backend(direct_only=False)
+    assert rel_l2(host(dw).astype(np.float32), host(dw3).astype(np.float32)) < 2e-3
+    assert rel_l2(host(dx).astype(np.float32), host(dx3).astype(np.float32)) < 2e-3
+
+
 def test_tensor_core_kernels_are_bitwise_reproducible_and_agree_with_direct():
     from renaissance_b200 import ops
     n, h, w, c, k = 8, 28, 28, 128, 256
