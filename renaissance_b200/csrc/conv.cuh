@@ -44,6 +44,15 @@ int strided_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void
 int strided_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, void* ws, size_t ws_bytes,
                   cudaStream_t st);
 
+// conv_strided.cu: a first layer (4 input channels, any filter / stride / padding) lowered to rows of r*s*4 values
+// and run as a 1x1 convolution; forward and weight gradient.
+bool stem_supports(const trb200_conv_desc& d, int which);
+size_t stem_workspace(const trb200_conv_desc& d, int which);
+int stem_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* ws, size_t ws_bytes,
+               cudaStream_t st);
+int stem_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, void* ws, size_t ws_bytes,
+               cudaStream_t st);
+
 int validate_conv_desc(const trb200_conv_desc* d, const char* who);
 
 }  // namespace trb

@@ -23,6 +23,10 @@ std::atomic<int> g_backend{0};   // 0 = automatic, 1 = direct kernels only
 
 bool use_igemm(const trb200_conv_desc& d, int which) { return g_backend.load() == 0 && igemm_supports(d, which); }
 bool use_strided(const trb200_conv_desc& d, int which) { return g_backend.load() == 0 && strided_supports(d, which); }
+// the in-kernel 3x3 first-layer variant (half) comes first; every other 4-channel first layer is lowered
+bool use_stem(const trb200_conv_desc& d, int which) {
+    return g_backend.load() == 0 && !igemm_supports(d, which) && stem_supports(d, which);
+}
 }  // namespace
 
 int validate_conv_desc(const trb200_conv_desc* d, const char* who) {
@@ -43,6 +47,7 @@ int validate_conv_desc(const trb200_conv_desc* d, const char* who) {
 
 using trb::use_igemm;
 using trb::use_strided;
+using trb::use_stem;
 
 extern "C" int trb200_set_conv_backend(int backend) {
     TRB_REQUIRE(backend == 0 || backend == 1, TRB200_ERR_INVALID_ARGUMENT, "set_conv_backend: 0 or 1 expected");
@@ -52,7 +57,7 @@ extern "C" int trb200_set_conv_backend(int backend) {
 
 extern "C" int trb200_conv_uses_tensor_cores(const trb200_conv_desc* d, int which) {
     if (!d || which < 0 || which > 2) return 0;
-    return (use_igemm(*d, which) || use_strided(*d, which)) ? 1 : 0;
+    return (use_igemm(*d, which) || use_strided(*d, which) || use_stem(*d, which)) ? 1 : 0;
 }
 
 extern "C" int trb200_device_status(void) {
@@ -71,6 +76,7 @@ extern "C" size_t trb200_conv_wgrad_workspace_bytes(const trb200_conv_desc* d) {
     if (trb::validate_conv_desc(d, "conv_wgrad_workspace_bytes")) return 0;
     if (use_igemm(*d, 0)) return trb::igemm_wgrad_workspace(*d);
     if (use_strided(*d, 0)) return trb::strided_workspace(*d, 0);
+    if (use_stem(*d, 0)) return trb::stem_workspace(*d, 0);
     return trb::wgrad_direct_workspace(*d);
 }
 
@@ -89,6 +95,7 @@ extern "C" int trb200_conv_wgrad(const trb200_conv_desc* d, const void* dy, cons
                 "conv_wgrad: tensors must be 16-byte aligned");
     if (use_igemm(*d, 0)) return trb::igemm_wgrad(*d, dy, x, dw, workspace, workspace_bytes, trb::as_stream(stream));
     if (use_strided(*d, 0)) return trb::strided_wgrad(*d, dy, x, dw, workspace, workspace_bytes, trb::as_stream(stream));
+    if (use_stem(*d, 0)) return trb::stem_wgrad(*d, dy, x, dw, workspace, workspace_bytes, trb::as_stream(stream));
     return trb::wgrad_direct(*d, dy, x, dw, workspace, workspace_bytes, trb::as_stream(stream));
 }
 
@@ -108,7 +115,8 @@ extern "C" int trb200_conv_dgrad(const trb200_conv_desc* d, const void* dy, cons
 extern "C" size_t trb200_conv_fprop_workspace_bytes(const trb200_conv_desc* d) {
     if (trb::validate_conv_desc(d, "conv_fprop_workspace_bytes")) return 0;
     if (trb::igemm_supports(*d, 2)) return trb::igemm_fprop_workspace(*d);
-    return trb::strided_supports(*d, 2) ? trb::strided_workspace(*d, 2) : 0;
+    if (trb::strided_supports(*d, 2)) return trb::strided_workspace(*d, 2);
+    return trb::stem_supports(*d, 2) ? trb::stem_workspace(*d, 2) : 0;
 }
 
 extern "C" int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const void* w, void* y, void* workspace,
@@ -121,6 +129,8 @@ extern "C" int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const
                 "conv_fprop: tensors must be 16-byte aligned");
     if (!trb::igemm_supports(*d, 2) && trb::strided_supports(*d, 2))
         return trb::strided_fprop(*d, x, w, y, workspace, workspace_bytes, trb::as_stream(stream));
+    if (!trb::igemm_supports(*d, 2) && trb::stem_supports(*d, 2))
+        return trb::stem_fprop(*d, x, w, y, workspace, workspace_bytes, trb::as_stream(stream));
     TRB_REQUIRE(trb::igemm_supports(*d, 2), TRB200_ERR_UNSUPPORTED,
                 "conv_fprop: only 3x3 pad 1 (c = 4 at stride 1, or a multiple of 64) and 1x1 pad 0 (c a multiple of 64) "
                 "at stride 1 or 2, with k = 64, 128 or a multiple of 256");

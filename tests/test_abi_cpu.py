@@ -70,7 +70,9 @@ def test_tensor_core_coverage_rule(lib):
         # stride 2 goes through the stride-1 kernel and a resampling pass; 1x1 is the same kernel with one tap
         assert lib.trb200_conv_uses_tensor_cores(C.byref(strided), which) == 1
         assert lib.trb200_conv_uses_tensor_cores(C.byref(one_by_one), which) == 1
-        for direct in (stem, stride_three, odd):
+        # a 7x7 first layer is lowered to rows and run as a 1x1 convolution (no data gradient)
+        assert lib.trb200_conv_uses_tensor_cores(C.byref(stem), which) == (0 if which == 1 else 1)
+        for direct in (stride_three, odd):
             assert lib.trb200_conv_uses_tensor_cores(C.byref(direct), which) == 0
     # a strided layer needs room for the resampled tensor
     assert lib.trb200_conv_dgrad_workspace_bytes(C.byref(strided)) >= 8 * 56 * 56 * 64 * 2

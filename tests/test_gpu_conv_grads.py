@@ -180,6 +180,31 @@ def test_stride_two_convolutions_on_tensor_cores(orc, n, h, w, c, k, r, pad):
     assert rel_l2(host(dx).astype(np.float32), host(dx3).astype(np.float32)) < 2e-3
 
 
+@pytest.mark.parametrize("n,h,w,k,r,pad,stride,dtype", [
+    (2, 32, 32, 64, 7, 3, 2, torch.float16), (1, 17, 23, 128, 5, 2, 1, torch.float16),
+    (3, 20, 12, 64, 7, 3, 2, torch.bfloat16), (2, 16, 16, 64, 3, 1, 1, torch.bfloat16),
+    (2, 15, 15, 256, 3, 0, 2, torch.float16)])
+def test_first_layers_lowered_to_rows(orc, n, h, w, k, r, pad, stride, dtype):
+    """Four input channels with any filter, stride and padding: receptive fields written out as rows, then a
+    1x1 convolution on the tensor cores (forward and weight gradient)."""
+    from renaissance_b200 import ops
+    x, wt, dy = _rand_case(n + h + k + r, n, h, w, 4, k, r, pad, stride)
+    x[..., 3] = 0
+    if dtype == torch.bfloat16:
+        rnd = lambda a: torch.from_numpy(a.astype(np.float32)).bfloat16().float().numpy()   # noqa: E731
+        x, wt, dy = rnd(x), rnd(wt), rnd(dy)
+    x32, w32, dy32 = (a.astype(np.float32) for a in (x, wt, dy))
+    g = ops.ConvGeometry(n, h, w, 4, k, r, r, pad, stride, dtype=dtype)
+    assert ops.conv_uses_tensor_cores(g, "wgrad") and ops.conv_uses_tensor_cores(g, "fprop")
+    assert not ops.conv_uses_tensor_cores(g, "dgrad")
+    dw = ops.conv_wgrad(g, dev(dy32).to(dtype), dev(x32).to(dtype))
+    y = ops.conv_fprop(g, dev(x32).to(dtype), dev(w32).to(dtype))
+    ops.device_status()
+    tol = 2e-3 if dtype == torch.float16 else 4e-3
+    assert rel_l2(host(dw.float()), orc.conv_wgrad(dy32, x32, wt.shape, pad=pad, stride=stride)) < tol
+    assert rel_l2(host(y.float()), orc.conv_fwd(x32, w32, pad=pad, stride=stride)) < tol
+
+
 def test_tensor_core_kernels_are_bitwise_reproducible_and_agree_with_direct():
     from renaissance_b200 import ops
     n, h, w, c, k = 8, 28, 28, 128, 256

@@ -49,11 +49,10 @@ def test_conv_gradients_bf16_match_oracle(orc, r, c, k, h, oh, stride, pad):
     dy = bf16_round(rng.standard_normal((n, oh, oh, k)))
     g = ops.ConvGeometry(n, h, h, c, k, r, r, pad, stride, dtype=torch.bfloat16)
     assert (g.oh, g.ow) == (oh, oh)
-    # every 3x3 and 1x1 layer runs on the tcgen05 kernels (the stride-2 ones through the stride-1 kernel and a
-    # resampling pass), the 7x7 stem on the direct kernels
-    on_tensor_cores = r in (1, 3)
-    assert ops.conv_uses_tensor_cores(g, "dgrad") == on_tensor_cores
-    assert ops.conv_uses_tensor_cores(g, "wgrad") == on_tensor_cores
+    # every layer runs on the tcgen05 kernels: the stride-2 ones through the stride-1 kernel and a resampling
+    # pass, the 7x7 stem lowered to rows (its data gradient, which no network needs, on the direct kernel)
+    assert ops.conv_uses_tensor_cores(g, "dgrad") == (r != 7)
+    assert ops.conv_uses_tensor_cores(g, "wgrad")
     ref_dw = orc.conv_wgrad(dy, x, wt.shape, pad=pad, stride=stride)
     ref_dx = orc.conv_dgrad(dy, wt, x.shape, pad=pad, stride=stride)
     dw = ops.conv_wgrad(g, dev_bf16(dy), dev_bf16(x))
