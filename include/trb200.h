@@ -85,6 +85,8 @@ typedef struct trb200_conv_desc {
 /*   dconv  = gamma*inv_std*(dy_m - dbeta/m - xhat*dgamma/m)   -> half        */
 /* m = n*h*w rows, c channels, c % 8 == 0.  dconv may be NULL (sums only) and */
 /* may alias neither input.  Sums are fixed-order (bitwise reproducible).     */
+/* mask_bits may be NULL: a BN with no ReLU behind it (a residual block's     */
+/* shortcut BN), i.e. the plain batch-norm backward, bn_op.cpp:119-168.       */
 /* ------------------------------------------------------------------------- */
 size_t trb200_bnrelu_bwd_workspace_bytes(int64_t m, int32_t c);
 int trb200_bnrelu_bwd(const void* dy, const void* mask_bits, const void* x,

@@ -99,7 +99,7 @@ bnrelu_bwd_reduce_body(const uint4* __restrict__ dy, const uint8_t* __restrict__
                     const int64_t v = r * tpr + vec;
                     vdy[u] = ld_stream(dy + v);
                     vx[u] = ld_stream(x + v);
-                    mb[u] = mask[v];
+                    mb[u] = mask ? mask[v] : 0xffu;
                 } else {
                     vdy[u] = make_uint4(0, 0, 0, 0);
                     vx[u] = make_uint4(0, 0, 0, 0);
@@ -205,7 +205,7 @@ bnrelu_bwd_apply_body(const uint4* __restrict__ dy, const uint8_t* __restrict__ 
                 const int64_t v = r * tpr + vec;
                 vdy[u] = ld_stream(dy + v);
                 vx[u] = ld_stream(x + v);
-                mb[u] = mask[v];
+                mb[u] = mask ? mask[v] : 0xffu;
             }
         }
 #pragma unroll
@@ -254,7 +254,8 @@ int bnrelu_bwd_launch(const void* dy, const void* mask_bits, const void* x, cons
                       size_t workspace_bytes, cudaStream_t s, int dtype) {
     TRB_REQUIRE(valid_dtype(dtype), TRB200_ERR_INVALID_ARGUMENT, "bnrelu_bwd: unknown dtype %d", dtype);
     const bool bf16 = dtype == TRB200_DTYPE_BF16;
-    TRB_REQUIRE(dy && mask_bits && x && gamma && saved_mean && saved_inv_std && dgamma && dbeta,
+    // mask_bits may be NULL: no ReLU behind this BN (every element kept), the plain batch-norm backward
+    TRB_REQUIRE(dy && x && gamma && saved_mean && saved_inv_std && dgamma && dbeta,
                 TRB200_ERR_INVALID_ARGUMENT, "bnrelu_bwd: null pointer");
     TRB_REQUIRE(m > 0 && c > 0 && c % 8 == 0, TRB200_ERR_UNSUPPORTED,
                 "bnrelu_bwd: need m > 0 and c a positive multiple of 8 (m=%lld c=%d)", (long long)m, c);

@@ -123,20 +123,22 @@ def conv_uses_tensor_cores(g: ConvGeometry, which: str) -> bool:
 
 def bnrelu_bwd(dy, mask_bits, conv_out, gamma, saved_mean, saved_inv_std, dconv=None,
                workspace: Workspace | None = None, stream=None, want_dconv=True):
-    """dconv, dgamma, dbeta of the block's BN+ReLU (cbr_op.cpp:1259-1353)."""
+    """dconv, dgamma, dbeta of the block's BN+ReLU (cbr_op.cpp:1259-1353).  mask_bits=None: a BN with no ReLU
+    behind it (plain batch-norm backward)."""
     lib = _lib.load()
     if dy.dtype not in DTYPE_CODE:
         raise TypeError(f"dy: float16 or bfloat16 expected, got {dy.dtype}")
     _need(dy, dy.dtype, "dy")
     _need(conv_out, dy.dtype, "conv_out")
-    _need(mask_bits, torch.uint8, "mask_bits")
+    if mask_bits is not None:
+        _need(mask_bits, torch.uint8, "mask_bits")
     for t, nm in ((gamma, "gamma"), (saved_mean, "saved_mean"), (saved_inv_std, "saved_inv_std")):
         _need(t, torch.float32, nm)
     c = dy.shape[-1]
     m = dy.numel() // c
     if conv_out.shape != dy.shape:
         raise ValueError("conv_out and dy must have the same shape")
-    if mask_bits.numel() * 8 < dy.numel():
+    if mask_bits is not None and mask_bits.numel() * 8 < dy.numel():
         raise ValueError("mask_bits holds fewer bits than dy has elements")
     if dconv is None and want_dconv:
         dconv = torch.empty_like(dy)

@@ -89,6 +89,28 @@ def test_bnrelu_bwd_bf16_matches_oracle(orc, m, c):
     assert rel_l2(host_f32(dconv), ref_dx) < 4e-3
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_bn_backward_without_relu_matches_oracle(orc, dtype):
+    """mask_bits = NULL: the BN of a residual block's shortcut has no ReLU behind it."""
+    from renaissance_b200 import ops
+    m, c = 2 * 28 * 28, 512
+    rng = np.random.default_rng(3)
+    rnd = bf16_round if dtype == torch.bfloat16 else (lambda a: a.astype(np.float16).astype(np.float32))
+    dy, x = rnd(rng.standard_normal((m, c))), rnd(rng.standard_normal((m, c)) * 1.5 + 0.3)
+    gamma = (1.0 + 0.2 * rng.standard_normal(c)).astype(np.float32)
+    mean = x.mean(axis=0).astype(np.float32)
+    inv_std = (1.0 / np.sqrt(x.var(axis=0) + 1e-5)).astype(np.float32)
+    ref_dx, ref_dg, ref_db = orc.bn_bwd(dy, x, gamma, mean, inv_std)
+    dconv, dg, db = ops.bnrelu_bwd(dev(dy).to(dtype), None, dev(x).to(dtype), dev(gamma), dev(mean), dev(inv_std))
+    torch.cuda.synchronize()
+    assert rel_max(host(dg), ref_dg) < 1e-4 and rel_max(host(db), ref_db) < 1e-4
+    assert rel_l2(host_f32(dconv), ref_dx) < (4e-3 if dtype == torch.bfloat16 else 2e-3)
+    # and it equals the masked operator with an all-ones mask, bit for bit
+    ones = torch.full((m * c // 8,), 255, dtype=torch.uint8, device="cuda")
+    d2, dg2, db2 = ops.bnrelu_bwd(dev(dy).to(dtype), ones, dev(x).to(dtype), dev(gamma), dev(mean), dev(inv_std))
+    assert torch.equal(dconv, d2) and torch.equal(dg, dg2) and torch.equal(db, db2)
+
+
 @pytest.mark.parametrize("n,h,w,c,k", [(2, 8, 8, 64, 64), (3, 7, 5, 64, 128), (2, 14, 14, 128, 256),
                                        (1, 9, 33, 64, 512), (5, 12, 20, 256, 64), (2, 28, 28, 128, 128),
                                        (4, 14, 14, 512, 512)])
