@@ -287,6 +287,29 @@ int trb200_scale_f32(float* data, int64_t n, float factor, void* stream);
 int trb200_cast_f16_to_f32(const void* src, float* dst, int64_t n, float factor, void* stream);
 
 /* ------------------------------------------------------------------------- */
+/* Element-wise pieces of a residual block (ResNet bottleneck) around the      */
+/* block kernels.  n elements, n % 8 == 0; 16-bit tensors of `dtype`           */
+/* (TRB200_DTYPE_*); masks are bit-packed like the block's ReLU mask.          */
+/* ------------------------------------------------------------------------- */
+
+/* out = a + b rounded to the 16-bit type: the join of two branches (forward)
+ * or of their gradients (backward).  AXPY with alpha = 1, axpy_op.cu:30-58, on
+ * 16-bit data.  out may be a or b. */
+int trb200_add16(const void* a, const void* b, void* out, int64_t n, int32_t dtype, void* stream);
+
+/* t = a + b rounded to the 16-bit type; out = max(t, 0); mask bit = t > 0: that
+ * AXPY followed by relu_fwd_amp_mask_kernel, relu_op.cu:101-114.  out may be a
+ * or b. */
+int trb200_add_relu_mask(const void* a, const void* b, void* out, void* mask_bits, int64_t n, int32_t dtype,
+                         void* stream);
+
+/* dx = mask bit ? dy : 0, relu_bwd_amp_kernel, relu_op.cu:116-126 (either 16-bit
+ * type).  dx may be dy.  The result is the gradient both branches of the join
+ * receive: the shortcut takes it as it is, the main branch's last BN takes it
+ * through trb200_bnrelu_bwd_dtype with mask_bits = NULL. */
+int trb200_relu_mask_bwd(const void* dy, const void* mask_bits, void* dx, int64_t n, void* stream);
+
+/* ------------------------------------------------------------------------- */
 /* Forward side of the block that produces the backward's inputs, and the     */
 /* steps after the all-reduce (the callers either side of the hot path).      */
 /* ------------------------------------------------------------------------- */

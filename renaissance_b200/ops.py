@@ -151,6 +151,38 @@ def bnrelu_bwd(dy, mask_bits, conv_out, gamma, saved_mean, saved_inv_std, dconv=
     return dconv, dgamma, dbeta
 
 
+# --------------------------------------------------------------------------- residual join
+
+def add16(a, b, out=None, stream=None):
+    """out = a + b in the tensors' 16-bit type (join of two branches or of their gradients)."""
+    _need(a, a.dtype, "a")
+    _need(b, a.dtype, "b")
+    out = torch.empty_like(a) if out is None else out
+    check(_lib.load().trb200_add16(_ptr(a), _ptr(b), _ptr(out), a.numel(), DTYPE_CODE[a.dtype], _stream(stream)))
+    return out
+
+
+def add_relu_mask(a, b, out=None, mask_bits=None, stream=None):
+    """relu(a + b) and its bit-packed mask: the end of a residual block."""
+    _need(a, a.dtype, "a")
+    _need(b, a.dtype, "b")
+    out = torch.empty_like(a) if out is None else out
+    if mask_bits is None:
+        mask_bits = torch.empty(a.numel() // 8, dtype=torch.uint8, device=a.device)
+    check(_lib.load().trb200_add_relu_mask(_ptr(a), _ptr(b), _ptr(out), _ptr(mask_bits), a.numel(),
+                                           DTYPE_CODE[a.dtype], _stream(stream)))
+    return out, mask_bits
+
+
+def relu_mask_bwd(dy, mask_bits, dx=None, stream=None):
+    """dx = mask ? dy : 0 with the block's bit-packed mask."""
+    _need(dy, dy.dtype, "dy")
+    _need(mask_bits, torch.uint8, "mask_bits")
+    dx = torch.empty_like(dy) if dx is None else dx
+    check(_lib.load().trb200_relu_mask_bwd(_ptr(dy), _ptr(mask_bits), _ptr(dx), dy.numel(), _stream(stream)))
+    return dx
+
+
 # --------------------------------------------------------------------------- conv gradients
 
 def conv_wgrad(g: ConvGeometry, dy, x, dw=None, workspace=None, stream=None):

@@ -159,3 +159,128 @@ def test_bf16_and_half_kernels_agree_on_values_both_types_hold(orc):
     torch.cuda.synchronize()
     for a, b in zip(out[torch.float16], out[torch.bfloat16]):
         assert rel_l2(host(b), host(a)) < 4e-3
+
+
+def _bn_stats(t):
+    """saved mean / inv_std of a stored [n,h,w,c] tensor (biased variance, eps 1e-5)."""
+    f = t.reshape(-1, t.shape[-1]).astype(np.float64)
+    return f.mean(axis=0).astype(np.float32), (1.0 / np.sqrt(f.var(axis=0) + 1e-5)).astype(np.float32)
+
+
+def _bn_relu_fwd(t, gamma, beta, relu=True):
+    mean, inv = _bn_stats(t)
+    y = bf16_round((t - mean) * inv * gamma + beta)
+    if not relu:
+        return y, mean, inv, None
+    mask = (y > 0).astype(np.int8)
+    return y * mask, mean, inv, mask
+
+
+@pytest.mark.parametrize("cin,mid,cout,stride", [(256, 64, 256, 1), (256, 128, 512, 2)])
+def test_bottleneck_backward_composed_from_the_entry_points(orc, cin, mid, cout, stride):
+    """A ResNet-50 bottleneck (1x1 -> 3x3 -> 1x1, BN after each, ReLU after the first two and after the join;
+    identity shortcut, or 1x1 stride-2 conv + BN when the block changes resolution) run backward through the
+    library's entry points on bfloat16 tensors.  Every operator is checked against the oracle on the inputs it
+    actually received (per-operator tolerances), and the block's dx against the oracle's whole chain."""
+    from renaissance_b200 import ops
+    bf = torch.bfloat16
+    n, h = 2, 14
+    oh = (h - 1) // stride + 1
+    rng = np.random.default_rng(cin + stride)
+    he = lambda k, r, c: bf16_round(rng.standard_normal((k, r, r, c)) * np.sqrt(2.0 / (r * r * c)))   # noqa: E731
+    gb = lambda c: ((1.0 + 0.2 * rng.standard_normal(c)).astype(np.float32),                         # noqa: E731
+                    (0.2 * rng.standard_normal(c)).astype(np.float32))
+    x0 = bf16_round(np.maximum(rng.standard_normal((n, h, h, cin)), 0))
+    w1, w2, w3 = he(mid, 1, cin), he(mid, 3, mid), he(cout, 1, mid)
+    (g1, b1), (g2, b2), (g3, b3) = gb(mid), gb(mid), gb(cout)
+    # forward by the oracle, every stored tensor rounded to bf16
+    c1 = bf16_round(orc.conv_fwd(x0, w1, pad=0))
+    a1, m1, i1, k1 = _bn_relu_fwd(c1, g1, b1)
+    c2 = bf16_round(orc.conv_fwd(a1, w2, pad=1, stride=stride))
+    a2, m2, i2, k2 = _bn_relu_fwd(c2, g2, b2)
+    c3 = bf16_round(orc.conv_fwd(a2, w3, pad=0))
+    y3, m3, i3, _ = _bn_relu_fwd(c3, g3, b3, relu=False)
+    if stride == 1:
+        sc = x0
+    else:
+        wd = he(cout, 1, cin)
+        gd, bd = gb(cout)
+        cd = bf16_round(orc.conv_fwd(x0, wd, pad=0, stride=stride))
+        sc, md, idv, _ = _bn_relu_fwd(cd, gd, bd, relu=False)
+    dout = bf16_round(rng.standard_normal((n, oh, oh, cout)))
+
+    D = dev_bf16
+    bits = lambda k: dev(orc.mask_pack(k.reshape(-1, k.shape[-1])))   # noqa: E731
+    # the join forward: relu(y3 + shortcut) and its mask, bit-exact against numpy
+    out_ref = bf16_round(y3 + sc)
+    kout = (out_ref > 0).astype(np.int8)
+    out_gpu, mout = ops.add_relu_mask(D(y3), D(sc))
+    assert np.array_equal(host_f32(out_gpu), out_ref * kout)
+    assert np.array_equal(host(mout), orc.mask_pack(kout.reshape(-1, cout)))
+
+    geo1 = ops.ConvGeometry(n, h, h, cin, mid, 1, 1, 0, 1, dtype=bf)
+    geo2 = ops.ConvGeometry(n, h, h, mid, mid, 3, 3, 1, stride, dtype=bf)
+    geo3 = ops.ConvGeometry(n, oh, oh, mid, cout, 1, 1, 0, 1, dtype=bf)
+
+    def check_bn(dy_t, mask_np, conv_np, gamma, mean, inv, got):
+        dy_np = host_f32(dy_t)
+        if mask_np is not None:
+            dy_np = dy_np * mask_np
+        rdx, rdg, rdb = orc.bn_bwd(dy_np.reshape(-1, dy_np.shape[-1]), conv_np.reshape(-1, conv_np.shape[-1]),
+                                   gamma, mean, inv)
+        dconv, dg, db = got
+        assert rel_max(host(dg), rdg) < 1e-4 and rel_max(host(db), rdb) < 1e-4
+        assert rel_l2(host_f32(dconv).reshape(rdx.shape), rdx) < 4e-3
+
+    def check_conv(geo, dconv_t, act_np, w_np, dw, dx):
+        dc = host_f32(dconv_t)
+        assert rel_l2(host_f32(dw), orc.conv_wgrad(dc, act_np, w_np.shape, pad=geo.pad, stride=geo.stride)) < 4e-3
+        if dx is not None:
+            assert rel_l2(host_f32(dx), orc.conv_dgrad(dc, w_np, act_np.shape, pad=geo.pad, stride=geo.stride)) < 4e-3
+
+    g = ops.relu_mask_bwd(D(dout), mout)
+    assert np.array_equal(host_f32(g), dout * kout)
+    r3 = ops.bnrelu_bwd(g, None, D(c3), dev(g3), dev(m3), dev(i3))
+    check_bn(g, None, c3, g3, m3, i3, r3)
+    dw3, da2 = ops.conv_wgrad(geo3, r3[0], D(a2)), ops.conv_dgrad(geo3, r3[0], D(w3))
+    check_conv(geo3, r3[0], a2, w3, dw3, da2)
+    r2 = ops.bnrelu_bwd(da2, bits(k2), D(c2), dev(g2), dev(m2), dev(i2))
+    check_bn(da2, k2, c2, g2, m2, i2, r2)
+    dw2, da1 = ops.conv_wgrad(geo2, r2[0], D(a1)), ops.conv_dgrad(geo2, r2[0], D(w2))
+    check_conv(geo2, r2[0], a1, w2, dw2, da1)
+    r1 = ops.bnrelu_bwd(da1, bits(k1), D(c1), dev(g1), dev(m1), dev(i1))
+    check_bn(da1, k1, c1, g1, m1, i1, r1)
+    dw1, dx_main = ops.conv_wgrad(geo1, r1[0], D(x0)), ops.conv_dgrad(geo1, r1[0], D(w1))
+    check_conv(geo1, r1[0], x0, w1, dw1, dx_main)
+    if stride == 1:
+        dx_sc = g
+    else:
+        geod = ops.ConvGeometry(n, h, h, cin, cout, 1, 1, 0, stride, dtype=bf)
+        rd = ops.bnrelu_bwd(g, None, D(cd), dev(gd), dev(md), dev(idv))
+        check_bn(g, None, cd, gd, md, idv, rd)
+        dwd, dx_sc = ops.conv_wgrad(geod, rd[0], D(x0)), ops.conv_dgrad(geod, rd[0], D(wd))
+        check_conv(geod, rd[0], x0, wd, dwd, dx_sc)
+    dx = ops.add16(dx_main, dx_sc)
+    ops.device_status()
+    assert np.array_equal(host_f32(dx), bf16_round(host_f32(dx_main) + host_f32(dx_sc)))
+
+    # the whole chain by the oracle (bf16 rounding where a tensor is stored): the block's dx within the 16-bit bound
+    def o_bn(dy_np, mask_np, conv_np, gamma, mean, inv):
+        if mask_np is not None:
+            dy_np = dy_np * mask_np
+        rdx, _, _ = orc.bn_bwd(dy_np.reshape(-1, dy_np.shape[-1]), conv_np.reshape(-1, conv_np.shape[-1]), gamma,
+                               mean, inv)
+        return bf16_round(rdx.reshape(conv_np.shape))
+
+    og = dout * kout
+    o3 = o_bn(og, None, c3, g3, m3, i3)
+    oa2 = bf16_round(orc.conv_dgrad(o3, w3, a2.shape, pad=0))
+    o2 = o_bn(oa2, k2, c2, g2, m2, i2)
+    oa1 = bf16_round(orc.conv_dgrad(o2, w2, a1.shape, pad=1, stride=stride))
+    o1 = o_bn(oa1, k1, c1, g1, m1, i1)
+    odx = bf16_round(orc.conv_dgrad(o1, w1, x0.shape, pad=0))
+    if stride == 1:
+        osc = og
+    else:
+        osc = bf16_round(orc.conv_dgrad(o_bn(og, None, cd, gd, md, idv), wd, x0.shape, pad=0, stride=stride))
+    assert rel_l2(host_f32(dx), bf16_round(odx + osc)) < 2e-2
