@@ -169,19 +169,20 @@ bn_apply_relu_mask(const uint4* __restrict__ x, const float* __restrict__ eq_sca
             // two channels per packed conversion and comparison; the roundings are those of the scalar form
             const __half2* h = reinterpret_cast<const __half2*>(&v[u]);
             const __half2 zero2 = __float2half2_rn(0.f);
-            uint32_t o[4];
-            uint32_t bits = 0;
+            uint32_t o[4], on[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float2 f = __half22float2(h[i]);
                 const float2 a = __half22float2(__floats2half2_rn(f.x * sc[2 * i], f.y * sc[2 * i + 1]));
                 const __half2 t = __floats2half2_rn(a.x + bi[2 * i], a.y + bi[2 * i + 1]);
-                const uint32_t on = __hgt2_mask(t, zero2);                     // 0xffff per lane with t > 0
-                o[i] = *reinterpret_cast<const uint32_t*>(&t) & on;            // ReLU: +0 where off
-                bits |= ((on & 1u) | ((on >> 15) & 2u)) << (2 * i);
+                on[i] = __hgt2_mask(t, zero2);                                 // 0xffff per lane with t > 0
+                o[i] = *reinterpret_cast<const uint32_t*>(&t) & on[i];         // ReLU: +0 where off
             }
+            // one byte of each lane's result gathered, each byte keeps its own bit, a multiply adds them up
+            const uint32_t lo = __byte_perm(on[0], on[1], 0x6420) & 0x08040201u;
+            const uint32_t hi = __byte_perm(on[2], on[3], 0x6420) & 0x08040201u;
             y[r * tpr + vec] = make_uint4(o[0], o[1], o[2], o[3]);
-            mask[r * tpr + vec] = (uint8_t)bits;
+            mask[r * tpr + vec] = (uint8_t)(((lo * 0x01010101u) >> 24) | (((hi * 0x01010101u) >> 24) << 4));
         }
     }
 }

@@ -60,7 +60,10 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
     }
 }
 
-// full-resolution vector index of window position q (q = kh*2 + kw) of pooled pixel pr
+// full-resolution vector index of window position q (q = kh*2 + kw) of pooled pixel pr.
+// Measured, not obvious: cheaper forms of this index (32-bit divisions; one division, using that pooled row t
+// starts at full-resolution row 2 * t) made all three pool kernels 7-18 % SLOWER at every size, although they
+// execute fewer instructions; the kernels are bound by memory latency, not by issue, and this form stays.
 __device__ __forceinline__ int64_t window_base(int64_t pr, int oh_n, int ow_n, int w, int tpr, int vec) {
     const int ow = (int)(pr % ow_n);
     const int64_t t = pr / ow_n;
@@ -80,6 +83,14 @@ __device__ __forceinline__ void bn_apply8(const uint4& v, const float (&sc)[8], 
     }
 }
 
+// One mask byte from four packed comparison results (0xffff per true lane): a byte of each lane is gathered, each
+// byte keeps its own bit, and a multiply adds the four bytes up in the top byte.
+__device__ __forceinline__ uint32_t mask_byte(const uint32_t (&on)[4]) {
+    const uint32_t lo = __byte_perm(on[0], on[1], 0x6420) & 0x08040201u;
+    const uint32_t hi = __byte_perm(on[2], on[3], 0x6420) & 0x08040201u;
+    return ((lo * 0x01010101u) >> 24) | (((hi * 0x01010101u) >> 24) << 4);
+}
+
 // One pooled pixel x 8 channels: ReLU output (to relu_out if asked), mask byte of each of the four window positions,
 // window maximum and the position of its first occurrence.  Comparisons and selections run on packed halfs.
 __device__ __forceinline__ void pool_window(const uint4 (&v)[4], const int64_t (&idx)[4], const float (&sc)[8],
@@ -93,19 +104,17 @@ __device__ __forceinline__ void pool_window(const uint4 (&v)[4], const int64_t (
     for (int q = 0; q < 4; ++q) {
         __half2 t[4];
         bn_apply8(v[q], sc, bi, t);
-        uint32_t y[4];
-        uint32_t bits = 0;
+        uint32_t y[4], on[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint32_t on = __hgt2_mask(t[i], zero2);                      // 0xffff per lane with t > 0
-            y[i] = *reinterpret_cast<const uint32_t*>(&t[i]) & on;             // ReLU: +0 where off
-            bits |= ((on & 1u) | ((on >> 15) & 2u)) << (2 * i);
+            on[i] = __hgt2_mask(t[i], zero2);                                  // 0xffff per lane with t > 0
+            y[i] = *reinterpret_cast<const uint32_t*>(&t[i]) & on[i];          // ReLU: +0 where off
             const uint32_t gt = __hgt2_mask(*reinterpret_cast<const __half2*>(&y[i]),
                                             *reinterpret_cast<const __half2*>(&best[i]));   // strictly greater: first wins
             best[i] = (y[i] & gt) | (best[i] & ~gt);
             am[i] = ((uint32_t)(q | (q << 16)) & gt) | (am[i] & ~gt);
         }
-        mask[idx[q]] = (uint8_t)bits;
+        mask[idx[q]] = (uint8_t)mask_byte(on);
         if (relu_out) relu_out[idx[q]] = make_uint4(y[0], y[1], y[2], y[3]);
     }
     best_out = make_uint4(best[0], best[1], best[2], best[3]);
