@@ -160,8 +160,20 @@ bnrelu_bwd_finalize(const float* __restrict__ partial, float* __restrict__ dgamm
     const int lane = threadIdx.x & 31;
     if (i >= 2 * c) return;
     const int stat = i / c, ch = i % c;
+    // same order of additions as a plain loop over this lane's strips; eight loads are in flight at a time
+    // (one dependent load per strip made this kernel as long as its strip count)
     double acc = 0.0;
-    for (int s = lane; s < strips; s += 32) acc += (double)partial[((size_t)s * 2 + stat) * c + ch];
+    for (int s0 = lane; s0 < strips; s0 += 32 * 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int s = s0 + 32 * u;
+            v[u] = s < strips ? partial[((size_t)s * 2 + stat) * c + ch] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (s0 + 32 * u < strips) acc += (double)v[u];
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (lane == 0) (stat == 0 ? dbeta : dgamma)[ch] = (float)acc;
