@@ -273,6 +273,16 @@ int trb200_softmax_ce_fused(const void* logits, int64_t logits_stride, const int
                             float* loss_partial, float* loss, float* inv_scaling,
                             int32_t batch, int32_t classes, void* stream);
 
+/* The fused call without probs for logits and d_logits of either 16-bit type
+ * (TRB200_DTYPE_*).  bfloat16: rows of whole 16-byte vectors and at most 2048
+ * classes (a 1000-class head), anything else returns TRB200_ERR_UNSUPPORTED;
+ * half: as trb200_softmax_ce_fused with probs = NULL. */
+int trb200_softmax_ce_fused_dtype(const void* logits, int64_t logits_stride, const int32_t* labels,
+                                  const float* scaling, const float* label_smoothing,
+                                  void* dlogits, int64_t dlogits_stride,
+                                  float* loss_partial, float* loss, float* inv_scaling,
+                                  int32_t batch, int32_t classes, int32_t dtype, void* stream);
+
 /* ------------------------------------------------------------------------- */
 /* Kernels either side of the gradient all-reduce (the collective itself is   */
 /* NCCL, issued by the host side).                                            */

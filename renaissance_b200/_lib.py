@@ -99,6 +99,7 @@ def load() -> C.CDLL:
         "trb200_softmax_ce_fwd": (C.c_int, [vp, i64, vp, vp, vp, i64, vp, vp, vp, i32, i32, vp]),
         "trb200_softmax_ce_bwd": (C.c_int, [vp, i64, vp, vp, vp, vp, vp, i64, i32, i32, vp]),
         "trb200_softmax_ce_fused": (C.c_int, [vp, i64, vp, vp, vp, vp, i64, vp, i64, vp, vp, vp, i32, i32, vp]),
+        "trb200_softmax_ce_fused_dtype": (C.c_int, [vp, i64, vp, vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, vp]),
         "trb200_bn_stats_workspace_bytes": (sz, [i64, i32]),
         "trb200_bn_stats_finalize": (C.c_int, [vp, vp, vp, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32,
                                                vp, sz, vp]),

@@ -260,13 +260,13 @@ __device__ __forceinline__ void loss_tail(const LossTail& t, float mine, int bat
     }
 }
 
-template <int VPL>
-__global__ void __launch_bounds__(256, VPL >= 8 ? 2 : 3)
-softmax_ce_rows_warp_lean(const __half* __restrict__ logits, int64_t logits_stride,
-                          const int32_t* __restrict__ labels, const float* __restrict__ scaling,
-                          const float* __restrict__ label_smoothing, __half* __restrict__ dlogits,
-                          int64_t dlogits_stride, float* __restrict__ loss_partial, int batch, int classes,
-                          LossTail tail) {
+template <int VPL, bool BF16>
+__device__ __forceinline__ void
+softmax_ce_rows_warp_lean_body(const uint16_t* __restrict__ logits, int64_t logits_stride,
+                               const int32_t* __restrict__ labels, const float* __restrict__ scaling,
+                               const float* __restrict__ label_smoothing, uint16_t* __restrict__ dlogits,
+                               int64_t dlogits_stride, float* __restrict__ loss_partial, int batch, int classes,
+                               LossTail tail) {
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
     const int nvec = classes >> 3;
@@ -274,7 +274,8 @@ softmax_ce_rows_warp_lean(const __half* __restrict__ logits, int64_t logits_stri
     const float keep = 1.0f - ls, spread = ls / (float)classes;
     const float inv_b = 1.0f / (float)batch;
     const float gscale = scaling[0] * inv_b;
-    const uint4 kNegInf = make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);   // -inf halfs
+    constexpr uint32_t kNegInf2 = BF16 ? 0xff80ff80u : 0xfc00fc00u;                         // two -inf values
+    const uint4 kNegInf = make_uint4(kNegInf2, kNegInf2, kNegInf2, kNegInf2);
     const int row_first = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     // the next row's vectors are requested before the current row is processed
     uint4 nxt[VPL];
@@ -291,7 +292,7 @@ softmax_ce_rows_warp_lean(const __half* __restrict__ logits, int64_t logits_stri
 #pragma unroll
         for (int i = 0; i < VPL; ++i) cur[i] = nxt[i];
         const int y = labels[row];
-        const float zy = __half2float(logits[(int64_t)row * logits_stride + y]);
+        const float zy = load16_t<BF16>(logits + (int64_t)row * logits_stride + y);
         {
             const int row_n = row + warps;
 #pragma unroll
@@ -304,14 +305,23 @@ softmax_ce_rows_warp_lean(const __half* __restrict__ logits, int64_t logits_stri
         }
         float zmax = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < VPL; ++i) zmax = fmaxf(zmax, half8_max(cur[i]));
+        for (int i = 0; i < VPL; ++i) {
+            if constexpr (BF16) {
+                float f[8];
+                unpack8_t<true>(cur[i], f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) zmax = fmaxf(zmax, f[j]);
+            } else {
+                zmax = fmaxf(zmax, half8_max(cur[i]));
+            }
+        }
         zmax = warp_max(zmax);
         const float shift = -zmax * kLog2e;
         float e[VPL][8];
         float sum = 0.f;
 #pragma unroll
         for (int i = 0; i < VPL; ++i) {
-            half8_to_float(cur[i], e[i]);
+            unpack8_t<BF16>(cur[i], e[i]);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 e[i][j] = fast_exp2(fmaf(e[i][j], kLog2e, shift));
@@ -321,17 +331,16 @@ softmax_ce_rows_warp_lean(const __half* __restrict__ logits, int64_t logits_stri
         sum = warp_sum(sum);
         const float inv_sum = 1.0f / (sum + 1e-8f);
         const float ga = inv_sum * gscale, gb = -spread * gscale;
-        __half* drow = dlogits + (int64_t)row * dlogits_stride;
+        uint16_t* drow = dlogits + (int64_t)row * dlogits_stride;
 #pragma unroll
         for (int i = 0; i < VPL; ++i) {
             const int vec = i * 32 + lane;
             if (vec < nvec) {
-                uint4 o;
-                __half2* oh = reinterpret_cast<__half2*>(&o);
+                uint32_t o[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    oh[j] = __floats2half2_rn(fmaf(e[i][2 * j], ga, gb), fmaf(e[i][2 * j + 1], ga, gb));
-                *reinterpret_cast<uint4*>(drow + vec * 8) = o;
+                    o[j] = pack2_t<BF16>(fmaf(e[i][2 * j], ga, gb), fmaf(e[i][2 * j + 1], ga, gb));
+                *reinterpret_cast<uint4*>(drow + vec * 8) = make_uint4(o[0], o[1], o[2], o[3]);
             }
         }
         float sum_log = 0.f;
@@ -347,13 +356,38 @@ softmax_ce_rows_warp_lean(const __half* __restrict__ logits, int64_t logits_stri
         // the label's class, by the lane that stored its vector
         if (((y >> 3) & 31) == lane) {
             const float py = fast_exp2(fmaf(zy, kLog2e, shift)) * inv_sum;
-            drow[y] = __float2half_rn((py - spread - keep) * gscale);
+            drow[y] = round16_t<BF16>((py - spread - keep) * gscale);
             const float row_loss = (-keep * logf(py + 1e-8f) - spread * sum_log) * inv_b;
             if (loss_partial) loss_partial[row] = row_loss;
             my_loss += row_loss;
         }
     }
     loss_tail(tail, my_loss, batch);
+}
+
+// The kernels proper: the half instantiation under the plain name, the bfloat16 one beside it.
+template <int VPL>
+__global__ void __launch_bounds__(256, VPL >= 8 ? 2 : 3)
+softmax_ce_rows_warp_lean(const __half* __restrict__ logits, int64_t logits_stride,
+                          const int32_t* __restrict__ labels, const float* __restrict__ scaling,
+                          const float* __restrict__ label_smoothing, __half* __restrict__ dlogits,
+                          int64_t dlogits_stride, float* __restrict__ loss_partial, int batch, int classes,
+                          LossTail tail) {
+    softmax_ce_rows_warp_lean_body<VPL, false>(reinterpret_cast<const uint16_t*>(logits), logits_stride, labels, scaling,
+                                               label_smoothing, reinterpret_cast<uint16_t*>(dlogits), dlogits_stride,
+                                               loss_partial, batch, classes, tail);
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(256, VPL >= 8 ? 2 : 3)
+softmax_ce_rows_warp_lean_bf16(const __half* __restrict__ logits, int64_t logits_stride,
+                               const int32_t* __restrict__ labels, const float* __restrict__ scaling,
+                               const float* __restrict__ label_smoothing, __half* __restrict__ dlogits,
+                               int64_t dlogits_stride, float* __restrict__ loss_partial, int batch, int classes,
+                               LossTail tail) {
+    softmax_ce_rows_warp_lean_body<VPL, true>(reinterpret_cast<const uint16_t*>(logits), logits_stride, labels, scaling,
+                                              label_smoothing, reinterpret_cast<uint16_t*>(dlogits), dlogits_stride,
+                                              loss_partial, batch, classes, tail);
 }
 
 // One block per row, the row is staged once in shared memory as halfs (classes * 2
@@ -945,9 +979,16 @@ softmax_ce_bwd_rows(const float* __restrict__ probs, int64_t probs_stride,
 
 int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels,
                 const float* scaling, const float* label_smoothing, RowOut out, float* loss,
-                float* inv_scaling, int batch, int classes, cudaStream_t s) {
+                float* inv_scaling, int batch, int classes, cudaStream_t s, int dtype = TRB200_DTYPE_F16) {
     const __half* z = static_cast<const __half*>(logits);
     const bool rows_aligned = aligned16(logits) && (logits_stride % 8 == 0);
+    const bool bf16 = dtype == TRB200_DTYPE_BF16;
+    // bfloat16 logits: the warp-per-row fused kernel only (what a 1000-class head needs)
+    TRB_REQUIRE(!bf16 || (rows_aligned && classes <= 2048 && classes % 8 == 0 && !out.probs && out.dlogits && scaling &&
+                          out.dlogits_stride % 8 == 0 && aligned16(out.dlogits)),
+                TRB200_ERR_UNSUPPORTED,
+                "softmax_ce: bfloat16 logits need the fused call without probs, 16-byte aligned rows and at most 2048 "
+                "classes in whole vectors of 8 (classes=%d)", classes);
     // kernels that finish the loss themselves draw a completion counter; `fused_tail` says one did
     LossTail tail{loss, inv_scaling, nullptr, nullptr};
     bool fused_tail = false;
@@ -973,10 +1014,10 @@ int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels
         if (blocks > resident) blocks = resident;
         if (blocks > kLossTailBlocks) blocks = kLossTailBlocks;
         dim3 grid(blocks), block(warps * 32);
-#define TRB_LEAN_LAUNCH(V)                                                                                       \
-    softmax_ce_rows_warp_lean<V><<<grid, block, 0, s>>>(z, logits_stride, labels, scaling, label_smoothing,      \
-                                                        out.dlogits, out.dlogits_stride, out.loss_partial, batch, \
-                                                        classes, tail)
+#define TRB_LEAN_LAUNCH(V)                                                                                        \
+    (bf16 ? softmax_ce_rows_warp_lean_bf16<V> : softmax_ce_rows_warp_lean<V>)<<<grid, block, 0, s>>>(              \
+        z, logits_stride, labels, scaling, label_smoothing, out.dlogits, out.dlogits_stride, out.loss_partial, batch, \
+        classes, tail)
         if (classes <= 256) TRB_LEAN_LAUNCH(1);
         else if (classes <= 512) TRB_LEAN_LAUNCH(2);
         else if (classes <= 1024) TRB_LEAN_LAUNCH(4);
@@ -1162,6 +1203,24 @@ extern "C" int trb200_softmax_ce_fused(const void* logits, int64_t logits_stride
     trb::RowOut out{probs, probs_stride, static_cast<__half*>(dlogits), dlogits_stride, loss_partial};
     return trb::launch_rows(logits, logits_stride, labels, scaling, label_smoothing, out, loss, inv_scaling,
                             batch, classes, trb::as_stream(stream));
+}
+
+extern "C" int trb200_softmax_ce_fused_dtype(const void* logits, int64_t logits_stride, const int32_t* labels,
+                                             const float* scaling, const float* label_smoothing, void* dlogits,
+                                             int64_t dlogits_stride, float* loss_partial, float* loss,
+                                             float* inv_scaling, int32_t batch, int32_t classes, int32_t dtype,
+                                             void* stream) {
+    TRB_REQUIRE(trb::valid_dtype(dtype), TRB200_ERR_INVALID_ARGUMENT, "softmax_ce_fused: unknown dtype %d", dtype);
+    TRB_REQUIRE(logits && labels && dlogits && scaling, TRB200_ERR_INVALID_ARGUMENT,
+                "softmax_ce_fused: null pointer");
+    TRB_REQUIRE(batch > 0 && classes > 0 && logits_stride >= classes && dlogits_stride >= classes,
+                TRB200_ERR_INVALID_ARGUMENT, "softmax_ce_fused: bad sizes (batch=%d classes=%d)", batch, classes);
+    TRB_REQUIRE(!loss || loss_partial, TRB200_ERR_INVALID_ARGUMENT,
+                "softmax_ce_fused: loss needs loss_partial");
+    TRB_REQUIRE(dlogits != logits, TRB200_ERR_INVALID_ARGUMENT, "softmax_ce_fused: dlogits must not alias logits");
+    trb::RowOut out{nullptr, 0, static_cast<__half*>(dlogits), dlogits_stride, loss_partial};
+    return trb::launch_rows(logits, logits_stride, labels, scaling, label_smoothing, out, loss, inv_scaling,
+                            batch, classes, trb::as_stream(stream), dtype);
 }
 
 extern "C" int trb200_softmax_ce_bwd(const float* probs, int64_t probs_stride, const int32_t* labels,

@@ -487,18 +487,28 @@ def softmax_ce_amp_bwd(probs, labels, scaling, inv_scaling, label_smoothing, dlo
 
 
 def softmax_ce_amp_fused(logits, labels, scaling, label_smoothing, want_probs=False, dlogits=None, stream=None):
-    """FWD + BWD nodes in one pass over the logits."""
+    """FWD + BWD nodes in one pass over the logits.  bfloat16 logits: without probs, at most 2048 classes."""
     lib = _lib.load()
-    _need(logits, torch.float16, "logits", 2)
+    if logits.dtype not in DTYPE_CODE:
+        raise TypeError(f"logits: float16 or bfloat16 expected, got {logits.dtype}")
+    _need(logits, logits.dtype, "logits", 2)
     _need(labels, torch.int32, "labels", 1)
     b, k = logits.shape
     dev = logits.device
     probs = torch.empty((b, k), dtype=torch.float32, device=dev) if want_probs else None
     if dlogits is None:
-        dlogits = torch.empty((b, k), dtype=torch.float16, device=dev)
+        dlogits = torch.empty((b, k), dtype=logits.dtype, device=dev)
     part = torch.empty(b, dtype=torch.float32, device=dev)
     loss = torch.empty(1, dtype=torch.float32, device=dev)
     inv = torch.empty(1, dtype=torch.float32, device=dev)
+    if logits.dtype == torch.bfloat16:
+        if want_probs:
+            raise ValueError("softmax_ce_amp_fused: bfloat16 logits are supported without probs only")
+        check(lib.trb200_softmax_ce_fused_dtype(_ptr(logits), logits.stride(0), _ptr(labels), _ptr(scaling),
+                                                _ptr(label_smoothing), _ptr(dlogits), dlogits.stride(0), _ptr(part),
+                                                _ptr(loss), _ptr(inv), b, k, DTYPE_CODE[logits.dtype],
+                                                _stream(stream)))
+        return dict(loss=loss, inv_scaling=inv, probs=None, loss_partial=part, dlogits=dlogits)
     check(lib.trb200_softmax_ce_fused(_ptr(logits), logits.stride(0), _ptr(labels), _ptr(scaling),
                                       _ptr(label_smoothing), _ptr(probs), 0 if probs is None else probs.stride(0),
                                       _ptr(dlogits), dlogits.stride(0), _ptr(part), _ptr(loss), _ptr(inv),

@@ -284,3 +284,33 @@ def test_bottleneck_backward_composed_from_the_entry_points(orc, cin, mid, cout,
     else:
         osc = bf16_round(orc.conv_dgrad(o_bn(og, None, cd, gd, md, idv), wd, x0.shape, pad=0, stride=stride))
     assert rel_l2(host_f32(dx), bf16_round(odx + osc)) < 2e-2
+
+
+@pytest.mark.parametrize("batch,classes,ls", [(256, 1000, 0.0), (64, 1000, 0.1), (33, 2048, 0.0), (7, 8, 0.1)])
+def test_softmax_ce_fused_on_bf16_logits(orc, batch, classes, ls):
+    """The loss head of a bfloat16 network.  The logits are multiples of 1/8 in [-6, 6], exact in half and in
+    bfloat16 alike, so the oracle's AMP operator (half logits) is the reference for loss and gradient; the
+    gradient is rounded to bfloat16 here and to half there."""
+    from renaissance_b200 import _lib, ops
+    rng = np.random.default_rng(batch + classes)
+    z = rng.integers(-48, 49, (batch, classes)).astype(np.float32) / 8
+    labels = rng.integers(0, classes, size=batch).astype(np.int32)
+    ref = orc.softmax_ce_amp(z.astype(np.float16), labels, scaling=1024.0, ls=ls)
+    sc = torch.tensor([1024.0], device="cuda")
+    lsd = torch.tensor([ls], device="cuda")
+    zd, ld = dev(z).bfloat16(), dev(labels)
+    assert np.array_equal(host_f32(zd), z)
+    out = ops.softmax_ce_amp_fused(zd, ld, sc, lsd)
+    torch.cuda.synchronize()
+    assert out["dlogits"].dtype == torch.bfloat16
+    assert abs(float(out["loss"]) - ref["loss"]) < 2e-5 * max(1.0, abs(ref["loss"]))
+    assert np.allclose(host(out["loss_partial"]), ref["loss_partial"], rtol=1e-4, atol=1e-7)
+    assert rel_l2(host_f32(out["dlogits"]), ref["dlogits"].astype(np.float32)) < 4e-3
+    # the same call on the same values as half agrees to the two roundings
+    half = ops.softmax_ce_amp_fused(dev(z).half(), ld, sc, lsd)
+    assert rel_l2(host_f32(out["dlogits"]), host_f32(half["dlogits"])) < 4e-3
+    assert abs(float(out["loss"]) - float(half["loss"])) < 1e-6 * max(1.0, abs(ref["loss"]))
+    # longer rows are refused for bfloat16, loudly
+    with pytest.raises(_lib.Trb200Error):
+        ops.softmax_ce_amp_fused(torch.zeros((4, 4096), device="cuda", dtype=torch.bfloat16),
+                                 torch.zeros(4, device="cuda", dtype=torch.int32), sc, lsd)
