@@ -319,6 +319,26 @@ int trb200_add_relu_mask(const void* a, const void* b, void* out, void* mask_bit
  * through trb200_bnrelu_bwd_dtype with mask_bits = NULL. */
 int trb200_relu_mask_bwd(const void* dy, const void* mask_bits, void* dx, int64_t n, void* stream);
 
+/* Max pooling with a k x k window, any stride and padding (ResNet: 3x3, stride 2,
+ * pad 1), NHWC tensors of `dtype`, c % 8 == 0.  argmax: one byte per output
+ * element = kh*k + kw of the first maximum (0xff for a window that lies outside
+ * the image): maxpool_amp_fwd_mask_kernel, maxpool_op.cu:83-133.  Backward: every
+ * input pixel gathers the dy of the windows whose argmax points at it, in float, in
+ * (oh, ow) order (no atomics): maxpool_bwd_deterministic_kernel, maxpool_op.cu:155-217.
+ * h, w are the input extents; the output is [n, (h+2*pad-k)/stride+1, ..., c]. */
+int trb200_maxpool_fwd(const void* x, void* y, void* argmax, int32_t n, int32_t h, int32_t w, int32_t c,
+                       int32_t k, int32_t stride, int32_t pad, int32_t dtype, void* stream);
+int trb200_maxpool_bwd(const void* dy, const void* argmax, void* dx, int32_t n, int32_t h, int32_t w, int32_t c,
+                       int32_t k, int32_t stride, int32_t pad, int32_t dtype, void* stream);
+
+/* Global average pooling [n,h,w,c] -> [n,c] and its backward: y = sum * 1/(h*w)
+ * with the sum in float over (h, w) in order, gap_op.cpp:137-155; dx = dy * 1/(h*w),
+ * gap_bwd_amp_compact_kernel, gap_op.cu:92-112. */
+int trb200_avgpool_global_fwd(const void* x, void* y, int32_t n, int32_t h, int32_t w, int32_t c, int32_t dtype,
+                              void* stream);
+int trb200_avgpool_global_bwd(const void* dy, void* dx, int32_t n, int32_t h, int32_t w, int32_t c, int32_t dtype,
+                              void* stream);
+
 /* ------------------------------------------------------------------------- */
 /* Forward side of the block that produces the backward's inputs, and the     */
 /* steps after the all-reduce (the callers either side of the hot path).      */

@@ -319,3 +319,68 @@ def maxpool2x2_bwd(dy16, argmax, x_shape):
     n, h, w, c = x_shape
     lib().orc_maxpool2x2_bwd_h16(_p(dy), _p(am), _p(dx), n, h, w, c)
     return dx
+
+
+# --------------------------------------------------------------------------- general pooling (numpy restatements)
+
+def maxpool_fwd(x, k, stride, pad):
+    """maxpool_amp_fwd_mask_kernel, maxpool_op.cu:83-133: first maximum wins (strict >, in float), mask byte
+    kh*k + kw, -1 (0xff) for a window with no pixel inside the image.  x: [n,h,w,c] float.  Returns (y, argmax uint8)."""
+    x = np.asarray(x, np.float32)
+    n, h, w, c = x.shape
+    oh, ow = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+    best = np.full((n, oh, ow, c), -np.inf, np.float32)
+    pos = np.full((n, oh, ow, c), -1, np.int32)
+    for kh in range(k):
+        for kw in range(k):
+            for o_h in range(oh):
+                ih = o_h * stride - pad + kh
+                if ih < 0 or ih >= h:
+                    continue
+                for o_w in range(ow):
+                    iw = o_w * stride - pad + kw
+                    if iw < 0 or iw >= w:
+                        continue
+                    v = x[:, ih, iw, :]
+                    gt = v > best[:, o_h, o_w, :]
+                    best[:, o_h, o_w, :] = np.where(gt, v, best[:, o_h, o_w, :])
+                    pos[:, o_h, o_w, :] = np.where(gt, kh * k + kw, pos[:, o_h, o_w, :])
+    return best, (pos & 0xff).astype(np.uint8)
+
+
+def maxpool_bwd(dy, argmax, x_shape, k, stride, pad):
+    """maxpool_bwd_deterministic_kernel, maxpool_op.cu:155-217: float gather per input pixel in (oh, ow) order."""
+    dy = np.asarray(dy, np.float32)
+    n, h, w, c = x_shape
+    _, oh, ow, _ = dy.shape
+    dx = np.zeros(x_shape, np.float32)
+    for o_h in range(oh):
+        for o_w in range(ow):
+            a = argmax[:, o_h, o_w, :].astype(np.int32)
+            for kh in range(k):
+                ih = o_h * stride - pad + kh
+                if ih < 0 or ih >= h:
+                    continue
+                for kw in range(k):
+                    iw = o_w * stride - pad + kw
+                    if iw < 0 or iw >= w:
+                        continue
+                    dx[:, ih, iw, :] += np.where(a == kh * k + kw, dy[:, o_h, o_w, :], np.float32(0))
+    return dx
+
+
+def avgpool_global_fwd(x):
+    """gap_op.cpp:137-155: y = (sum over h, w) * (1 / (h*w)), float."""
+    x = np.asarray(x, np.float32)
+    n, h, w, c = x.shape
+    acc = np.zeros((n, c), np.float32)
+    for i in range(h):
+        for j in range(w):
+            acc += x[:, i, j, :]
+    return acc * np.float32(1.0 / (h * w))
+
+
+def avgpool_global_bwd(dy, h, w):
+    """gap_op.cu:92-112: dx = dy * (1 / (h*w)) at every pixel."""
+    dy = np.asarray(dy, np.float32)
+    return np.broadcast_to((dy * np.float32(1.0 / (h * w)))[:, None, None, :], (dy.shape[0], h, w, dy.shape[1])).copy()

@@ -84,6 +84,10 @@ def load() -> C.CDLL:
         "trb200_add16": (C.c_int, [vp, vp, vp, i64, i32, vp]),
         "trb200_add_relu_mask": (C.c_int, [vp, vp, vp, vp, i64, i32, vp]),
         "trb200_relu_mask_bwd": (C.c_int, [vp, vp, vp, i64, vp]),
+        "trb200_maxpool_fwd": (C.c_int, [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]),
+        "trb200_maxpool_bwd": (C.c_int, [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]),
+        "trb200_avgpool_global_fwd": (C.c_int, [vp, vp, i32, i32, i32, i32, i32, vp]),
+        "trb200_avgpool_global_bwd": (C.c_int, [vp, vp, i32, i32, i32, i32, i32, vp]),
         "trb200_bnrelu_bwd_static": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, vp]),
         "trb200_conv_wgrad_workspace_bytes": (sz, [pdesc]),
         "trb200_conv_wgrad": (C.c_int, [pdesc, vp, vp, vp, vp, sz, vp]),

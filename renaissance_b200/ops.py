@@ -151,6 +151,46 @@ def bnrelu_bwd(dy, mask_bits, conv_out, gamma, saved_mean, saved_inv_std, dconv=
     return dconv, dgamma, dbeta
 
 
+# --------------------------------------------------------------------------- general pooling
+
+def maxpool_fwd(x, k=3, stride=2, pad=1, stream=None):
+    """k x k max pool; returns (y, argmax byte per element)."""
+    _need(x, x.dtype, "x", 4)
+    n, h, w, c = x.shape
+    oh, ow = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+    y = torch.empty((n, oh, ow, c), dtype=x.dtype, device=x.device)
+    am = torch.empty((n, oh, ow, c), dtype=torch.uint8, device=x.device)
+    check(_lib.load().trb200_maxpool_fwd(_ptr(x), _ptr(y), _ptr(am), n, h, w, c, k, stride, pad, DTYPE_CODE[x.dtype],
+                                         _stream(stream)))
+    return y, am
+
+
+def maxpool_bwd(dy, argmax, x_shape, k=3, stride=2, pad=1, stream=None):
+    _need(dy, dy.dtype, "dy", 4)
+    _need(argmax, torch.uint8, "argmax", 4)
+    n, h, w, c = x_shape
+    dx = torch.empty((n, h, w, c), dtype=dy.dtype, device=dy.device)
+    check(_lib.load().trb200_maxpool_bwd(_ptr(dy), _ptr(argmax), _ptr(dx), n, h, w, c, k, stride, pad,
+                                         DTYPE_CODE[dy.dtype], _stream(stream)))
+    return dx
+
+
+def avgpool_global_fwd(x, stream=None):
+    _need(x, x.dtype, "x", 4)
+    n, h, w, c = x.shape
+    y = torch.empty((n, c), dtype=x.dtype, device=x.device)
+    check(_lib.load().trb200_avgpool_global_fwd(_ptr(x), _ptr(y), n, h, w, c, DTYPE_CODE[x.dtype], _stream(stream)))
+    return y
+
+
+def avgpool_global_bwd(dy, h, w, stream=None):
+    _need(dy, dy.dtype, "dy", 2)
+    n, c = dy.shape
+    dx = torch.empty((n, h, w, c), dtype=dy.dtype, device=dy.device)
+    check(_lib.load().trb200_avgpool_global_bwd(_ptr(dy), _ptr(dx), n, h, w, c, DTYPE_CODE[dy.dtype], _stream(stream)))
+    return dx
+
+
 # --------------------------------------------------------------------------- residual join
 
 def add16(a, b, out=None, stream=None):

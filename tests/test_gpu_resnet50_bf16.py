@@ -314,3 +314,39 @@ def test_softmax_ce_fused_on_bf16_logits(orc, batch, classes, ls):
     with pytest.raises(_lib.Trb200Error):
         ops.softmax_ce_amp_fused(torch.zeros((4, 4096), device="cuda", dtype=torch.bfloat16),
                                  torch.zeros(4, device="cuda", dtype=torch.int32), sc, lsd)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("n,h,w,c,k,stride,pad", [(2, 112, 112, 64, 3, 2, 1), (3, 9, 7, 16, 3, 2, 1),
+                                                  (2, 8, 8, 8, 2, 2, 0), (1, 11, 13, 24, 5, 3, 2), (2, 6, 6, 8, 3, 1, 1)])
+def test_general_max_pool_matches_oracle(orc, dtype, n, h, w, c, k, stride, pad):
+    """ResNet's 3x3 stride-2 pool after the stem, and other windows: outputs and argmax bytes bit for bit, the
+    backward (a float gather per input pixel) to the rounding of the result."""
+    from renaissance_b200 import ops
+    rng = np.random.default_rng(h * 7 + c + k)
+    rnd = bf16_round if dtype == torch.bfloat16 else (lambda a: a.astype(np.float16).astype(np.float32))
+    x = rnd(rng.standard_normal((n, h, w, c)))
+    x[0, : min(h, 4), : min(w, 4), 0] = 1.0          # ties: the first maximum must win
+    ref_y, ref_am = orc.maxpool_fwd(x, k, stride, pad)
+    y, am = ops.maxpool_fwd(dev(x).to(dtype), k, stride, pad)
+    torch.cuda.synchronize()
+    assert np.array_equal(host_f32(y), ref_y)
+    assert np.array_equal(host(am), ref_am)
+    dy = rnd(rng.standard_normal(ref_y.shape))
+    dx = ops.maxpool_bwd(dev(dy).to(dtype), am, x.shape, k, stride, pad)
+    ref_dx = orc.maxpool_bwd(dy, ref_am, x.shape, k, stride, pad)
+    assert np.array_equal(host_f32(dx), rnd(ref_dx))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("n,h,w,c", [(4, 7, 7, 2048), (3, 5, 3, 8)])
+def test_global_average_pool_matches_oracle(orc, dtype, n, h, w, c):
+    from renaissance_b200 import ops
+    rng = np.random.default_rng(h + c)
+    rnd = bf16_round if dtype == torch.bfloat16 else (lambda a: a.astype(np.float16).astype(np.float32))
+    x = rnd(rng.standard_normal((n, h, w, c)))
+    y = ops.avgpool_global_fwd(dev(x).to(dtype))
+    assert np.array_equal(host_f32(y), rnd(orc.avgpool_global_fwd(x)))
+    dy = rnd(rng.standard_normal((n, c)))
+    dx = ops.avgpool_global_bwd(dev(dy).to(dtype), h, w)
+    assert np.array_equal(host_f32(dx), rnd(orc.avgpool_global_bwd(dy, h, w)))

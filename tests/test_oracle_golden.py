@@ -202,3 +202,34 @@ def test_maxpool_routes_gradient_to_first_maximum(orc):
     assert y[0, 0, 0].tolist() == [5.0, -0.5] and am[0, 0, 0].tolist() == [1, 3]
     dx = orc.maxpool2x2_bwd(np.full((1, 1, 1, 2), 7, np.float16), am, x.shape)
     assert dx[0, 0, 1, 0] == 7 and dx[0, 1, 1, 1] == 7 and dx.astype(np.float32).sum() == 14
+
+
+@pytest.mark.parametrize("k,stride,pad,h,w", [(3, 2, 1, 12, 9), (2, 2, 0, 8, 8), (3, 1, 1, 5, 7), (5, 3, 2, 11, 11)])
+def test_general_pooling_restatements_against_torch(orc, k, stride, pad, h, w):
+    """The numpy restatements of the reference's max pool (maxpool_op.cu:83-217) and global average pool
+    (gap_op.cpp:137-155, gap_op.cu:92-112) against torch's operators and their autograd."""
+    import torch
+    import torch.nn.functional as F
+    rng = np.random.default_rng(k * 10 + stride)
+    n, c = 2, 8
+    x = rng.standard_normal((n, h, w, c)).astype(np.float32)
+    y, am = orc.maxpool_fwd(x, k, stride, pad)
+    xt = torch.from_numpy(x).permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    yt = F.max_pool2d(xt, k, stride, pad)
+    assert np.array_equal(y, yt.detach().permute(0, 2, 3, 1).numpy())
+    dy = rng.standard_normal(y.shape).astype(np.float32)
+    yt.backward(torch.from_numpy(dy).permute(0, 3, 1, 2).contiguous())
+    dx = orc.maxpool_bwd(dy, am, x.shape, k, stride, pad)
+    assert np.allclose(dx, xt.grad.permute(0, 2, 3, 1).numpy(), rtol=1e-6, atol=1e-6)
+    # argmax bytes decode to the position of the maximum inside the window
+    kh, kw = am // k, am % k
+    assert am.max() < k * k and (kh < k).all() and (kw < k).all()
+    if (k, stride, pad) == (2, 2, 0):
+        y2, am2 = orc.maxpool2x2_fwd(x.astype(np.float16))
+        y16, am16 = orc.maxpool_fwd(x.astype(np.float16).astype(np.float32), 2, 2, 0)
+        assert np.array_equal(y2.astype(np.float32), y16) and np.array_equal(am2, am16)
+    g = orc.avgpool_global_fwd(x)
+    assert np.allclose(g, x.mean(axis=(1, 2)), rtol=1e-5, atol=1e-6)
+    dg = rng.standard_normal((n, c)).astype(np.float32)
+    assert np.allclose(orc.avgpool_global_bwd(dg, h, w), np.broadcast_to(dg[:, None, None, :] / (h * w), x.shape),
+                       rtol=1e-6)
