@@ -1,7 +1,7 @@
 """Per-kernel roofline sweep of the hot-path kernels on one GPU.
 
     python -m renaissance_b200.kernel_sweep                 # everything, JSON lines
-    python -m renaissance_b200.kernel_sweep --only block    # BASELINE config 2 (one block backward)
+    python -m renaissance_b200.kernel_sweep --only block    # BASELINE.json configuration 2 (one block backward)
     python -m renaissance_b200.kernel_sweep --only bnrelu --quick
     python -m renaissance_b200.kernel_sweep --only conv --quick --batch 64 --shape 56,256,256 --what fprop_stats
     python -m renaissance_b200.kernel_sweep --only resnet50 --cudnn     # ResNet-50 conv shapes, bfloat16
@@ -180,7 +180,7 @@ def conv_point(t, n, h, c, k, what, tc, src, r=3, pad=1, stride=1, dtype=torch.f
 
 
 def block_point(t, n, h, c, k, hbm, tc, src):
-    """BASELINE config 2: the whole block backward through trb200_cbr_bwd on three streams."""
+    """BASELINE.json configuration 2: the whole block backward through trb200_cbr_bwd on three streams."""
     geo = ops.ConvGeometry(n, h, h, c, k)
     g = torch.Generator(device="cuda").manual_seed(1)
     x0 = torch.randn((n, h, h, c), generator=g, device="cuda").half()
@@ -271,7 +271,7 @@ def main():
             for what in kinds:
                 conv_point(t, n, h, c, k, what, tc, src)
     if args.only == "resnet50":
-        # BASELINE config 4 at the level the hot path reaches it: the data and weight gradients of every
+        # BASELINE.json configuration 4 at the level the hot path reaches it: the data and weight gradients of every
         # distinct convolution of ResNet-50 on bfloat16 tensors
         kinds = tuple(args.what.split(",")) if args.what else ("dgrad", "wgrad")
         for r, c, k, h, stride, pad in RESNET50_CONVS:

@@ -140,7 +140,7 @@ def cbr_case(name, seed, n, h, w, c, k, first_layer=False):
 
 
 def mlp_case(name, seed, sizes, batch, lr, full=True):
-    """BASELINE config 1: Linear+ReLU MLP, softmax-CE (mean), one SGD step.  With
+    """BASELINE.json configuration 1: Linear+ReLU MLP, softmax-CE (mean), one SGD step.  With
     full=False only scalars and a few slices are stored (the tensors are rebuilt
     from the seed by the test)."""
     rng = np.random.default_rng(seed)

@@ -65,7 +65,7 @@ def test_sums_only_and_bitwise_reproducible(orc):
 
 
 def test_full_size_properties():
-    """BASELINE config 2 size (N=256, 56x56, C=64): properties that need no oracle.
+    """BASELINE.json configuration 2 size (N=256, 56x56, C=64): properties that need no oracle.
     sum_rows(dconv) = 0 and sum_rows(dconv * xhat) = 0 per channel (the BN backward
     projects both out), and dbeta / dgamma against torch float64 sums."""
     from renaissance_b200 import ops

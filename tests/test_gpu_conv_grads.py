@@ -226,7 +226,7 @@ def test_tensor_core_kernels_are_bitwise_reproducible_and_agree_with_direct():
 
 
 def test_full_size_config2_against_torch_fp32():
-    """BASELINE config 2 (N=256, 56x56, C=K=64): too large for the CPU oracle in a
+    """BASELINE.json configuration 2 (N=256, 56x56, C=K=64): too large for the CPU oracle in a
     test, so the check is against torch's float32 convolution gradients on the GPU
     plus linearity in dy."""
     from renaissance_b200 import ops

@@ -2,7 +2,7 @@
 
 The reference executes its block through cuDNN-frontend graphs (cbr_op.cpp:430-917, 1259-1353);
 renaissance_b200.cudnn_reference rebuilds those graphs with the cudnn-frontend Python package.  Tolerances are
-BASELINE's: <= 2e-2 relative L2 for half dx / dW (both sides round to half, ~1e-3 is what is reached), <= 1e-4
+BASELINE.json's: <= 2e-2 relative L2 for half dx / dW (both sides round to half, ~1e-3 is what is reached), <= 1e-4
 relative for the per-channel reductions against a float64 evaluation (cuDNN's own reduction order differs)."""
 import numpy as np
 import pytest

@@ -175,7 +175,7 @@ def test_mlp_small_step_matches_golden(orc):
 
 
 def test_mlp_config1_step_matches_golden(orc):
-    """BASELINE config 1 (784-512-256-10, batch 128, SGD lr 0.1) on the oracle's
+    """BASELINE.json configuration 1 (784-512-256-10, batch 128, SGD lr 0.1) on the oracle's
     restatement of the reference CPU backend; tensors rebuilt from the seed."""
     g = golden("mlp_config1")
     sizes, batch, seed = g["sizes"].tolist(), int(g["batch"]), int(g["seed"])
