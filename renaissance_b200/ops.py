@@ -341,10 +341,10 @@ def cbr_amp_bwd(g: ConvGeometry, dy, w, gamma, saved_mean, saved_inv_std, mask_b
     ``dx``) unless ``first_layer``.  With ``pool_argmax`` the block is followed by a 2x2 max pool and
     ``dy`` is the gradient of the pooled output.  Returns dict(dx, dw, dgamma, dbeta, dconv)."""
     lib = _lib.load()
-    _need(dy, torch.float16, "dy", 4)
-    _need(w, torch.float16, "w", 4)
-    _need(x, torch.float16, "x", 4)
-    _need(conv_out, torch.float16, "conv_out", 4)
+    _need(dy, g.dtype, "dy", 4)
+    _need(w, g.dtype, "w", 4)
+    _need(x, g.dtype, "x", 4)
+    _need(conv_out, g.dtype, "conv_out", 4)
     _need(mask_bits, torch.uint8, "mask_bits")
     for t, nm in ((gamma, "gamma"), (saved_mean, "saved_mean"), (saved_inv_std, "saved_inv_std")):
         _need(t, torch.float32, nm)

@@ -350,3 +350,37 @@ def test_global_average_pool_matches_oracle(orc, dtype, n, h, w, c):
     dy = rnd(rng.standard_normal((n, c)))
     dx = ops.avgpool_global_bwd(dev(dy).to(dtype), h, w)
     assert np.array_equal(host_f32(dx), rnd(orc.avgpool_global_bwd(dy, h, w)))
+
+
+@pytest.mark.parametrize("n,h,c,k,r,pad,stride", [(2, 28, 128, 128, 3, 1, 2), (2, 14, 256, 64, 1, 0, 1),
+                                                  (3, 14, 64, 64, 3, 1, 1), (2, 15, 256, 512, 1, 0, 2)])
+def test_block_backward_entry_point_on_resnet_blocks_bf16(orc, n, h, c, k, r, pad, stride):
+    """trb200_cbr_bwd (BN+ReLU backward, weight gradient, data gradient in place over x, three streams) on the
+    conv+BN+ReLU blocks a bottleneck is made of: 1x1, 3x3, and their stride-2 forms, bfloat16."""
+    from renaissance_b200 import ops
+    bf = torch.bfloat16
+    rng = np.random.default_rng(h + c + k + r)
+    oh = (h + 2 * pad - r) // stride + 1
+    x = bf16_round(rng.standard_normal((n, h, h, c)))
+    wt = bf16_round(rng.standard_normal((k, r, r, c)) * np.sqrt(2.0 / (r * r * c)))
+    conv = bf16_round(orc.conv_fwd(x, wt, pad=pad, stride=stride))
+    gamma = (1.0 + 0.2 * rng.standard_normal(k)).astype(np.float32)
+    beta = (0.2 * rng.standard_normal(k)).astype(np.float32)
+    _, mean, inv, mask = _bn_relu_fwd(conv, gamma, beta)
+    dy = bf16_round(rng.standard_normal((n, oh, oh, k)))
+    g = ops.ConvGeometry(n, h, h, c, k, r, r, pad, stride, dtype=bf)
+    xd = dev_bf16(x)
+    st = ops.BlockStreams.create()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(st.bn):
+        out = ops.cbr_amp_bwd(g, dev_bf16(dy), dev_bf16(wt), dev(gamma), dev(mean), dev(inv),
+                              dev(orc.mask_pack(mask.reshape(-1, k))), xd, dev_bf16(conv), streams=st)
+    torch.cuda.current_stream().wait_stream(st.bn)
+    ops.device_status()
+    assert out["dx"].data_ptr() == xd.data_ptr()          # in place over x, as in the reference
+    rdx, rdg, rdb = orc.bn_bwd((dy * mask).reshape(-1, k), conv.reshape(-1, k), gamma, mean, inv)
+    assert rel_max(host(out["dgamma"]), rdg) < 1e-4 and rel_max(host(out["dbeta"]), rdb) < 1e-4
+    assert rel_l2(host_f32(out["dconv"]).reshape(rdx.shape), rdx) < 4e-3
+    dconv = host_f32(out["dconv"])
+    assert rel_l2(host_f32(out["dw"]), orc.conv_wgrad(dconv, x, wt.shape, pad=pad, stride=stride)) < 4e-3
+    assert rel_l2(host_f32(out["dx"]), orc.conv_dgrad(dconv, wt, x.shape, pad=pad, stride=stride)) < 4e-3
