@@ -356,6 +356,19 @@ int trb200_bn_stats_finalize(const void* conv_out, const float* gamma, const flo
                              float* running_mean, float* running_var, int64_t m, int32_t c,
                              void* workspace, size_t workspace_bytes, void* stream);
 
+/* trb200_bn_stats_finalize for conv outputs of either 16-bit type (TRB200_DTYPE_*). */
+int trb200_bn_stats_finalize_dtype(const void* conv_out, const float* gamma, const float* beta, float eps,
+                                   float momentum, float* ch_sum, float* ch_sqsum, float* saved_mean,
+                                   float* saved_inv_std, float* eq_scale, float* eq_bias,
+                                   float* running_mean, float* running_var, int64_t m, int32_t c, int32_t dtype,
+                                   void* workspace, size_t workspace_bytes, void* stream);
+
+/* The apply stage for either 16-bit type, with the ReLU (relu != 0: as
+ * trb200_bn_apply_relu_mask below) or without it (out = t, mask_bits unused and may
+ * be NULL: the BN in front of a residual join and the BN of its shortcut). */
+int trb200_bn_apply_dtype(const void* conv_out, const float* eq_scale, const float* eq_bias, void* out,
+                          void* mask_bits, int64_t m, int32_t c, int32_t relu, int32_t dtype, void* stream);
+
 /* relu_out = max(t, 0), mask bit = (t > 0) with t = half(half(x*eq_scale) + eq_bias):
  * build_cbr_bn_relu_graph, cbr_op.cpp:534-616 (MUL, ADD with HALF intermediates,
  * RELU_FWD, CMP_GT -> BOOLEAN).  Mask layout as in trb200_bnrelu_bwd. */

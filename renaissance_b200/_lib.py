@@ -88,6 +88,9 @@ def load() -> C.CDLL:
         "trb200_maxpool_bwd": (C.c_int, [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp]),
         "trb200_avgpool_global_fwd": (C.c_int, [vp, vp, i32, i32, i32, i32, i32, vp]),
         "trb200_avgpool_global_bwd": (C.c_int, [vp, vp, i32, i32, i32, i32, i32, vp]),
+        "trb200_bn_stats_finalize_dtype": (C.c_int, [vp, vp, vp, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32,
+                                                    i32, vp, sz, vp]),
+        "trb200_bn_apply_dtype": (C.c_int, [vp, vp, vp, vp, vp, i64, i32, i32, i32, vp]),
         "trb200_bnrelu_bwd_static": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, vp]),
         "trb200_conv_wgrad_workspace_bytes": (sz, [pdesc]),
         "trb200_conv_wgrad": (C.c_int, [pdesc, vp, vp, vp, vp, sz, vp]),

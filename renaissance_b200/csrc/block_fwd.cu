@@ -59,7 +59,7 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 // per-strip partial sums of x and x*x, 8 channels per thread
 __global__ void __launch_bounds__(kThreads)
 bn_stats_partial(const uint4* __restrict__ x, float* __restrict__ partial, int64_t m, int c, int tpr, int bx,
-                 int by, int64_t rows_per_strip) {
+                 int by, int64_t rows_per_strip, int bf16) {
     __shared__ float s_red[kThreads * 16];
     const int tx = threadIdx.x % bx, ty = threadIdx.x / bx;
     const int vec = blockIdx.y * bx + tx;
@@ -80,7 +80,8 @@ bn_stats_partial(const uint4* __restrict__ x, float* __restrict__ partial, int64
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) {
                 float f[8];
-                unpack8(v[u], f);
+                if (bf16) unpack8_t<true>(v[u], f);
+                else unpack8(v[u], f);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) { s1[j] += f[j]; s2[j] = fmaf(f[j], f[j], s2[j]); }
             }
@@ -283,11 +284,11 @@ extern "C" size_t trb200_bn_stats_workspace_bytes(int64_t m, int32_t c) {
     return (size_t)p.gx * 2 * (size_t)c * sizeof(float);
 }
 
-extern "C" int trb200_bn_stats_finalize(const void* conv_out, const float* gamma, const float* beta, float eps,
-                                        float momentum, float* ch_sum, float* ch_sqsum, float* saved_mean,
-                                        float* saved_inv_std, float* eq_scale, float* eq_bias,
-                                        float* running_mean, float* running_var, int64_t m, int32_t c,
-                                        void* workspace, size_t workspace_bytes, void* stream) {
+static int bn_stats_finalize_any(const void* conv_out, const float* gamma, const float* beta, float eps,
+                                 float momentum, float* ch_sum, float* ch_sqsum, float* saved_mean,
+                                 float* saved_inv_std, float* eq_scale, float* eq_bias,
+                                 float* running_mean, float* running_var, int64_t m, int32_t c,
+                                 void* workspace, size_t workspace_bytes, void* stream, int bf16) {
     TRB_REQUIRE(conv_out && gamma && beta && saved_mean && saved_inv_std && eq_scale && eq_bias,
                 TRB200_ERR_INVALID_ARGUMENT, "bn_stats_finalize: null pointer");
     TRB_REQUIRE(m > 0 && c > 0 && c % 8 == 0, TRB200_ERR_UNSUPPORTED,
@@ -300,12 +301,102 @@ extern "C" int trb200_bn_stats_finalize(const void* conv_out, const float* gamma
     cudaStream_t s = trb::as_stream(stream);
     float* partial = static_cast<float*>(workspace);
     trb::bn_stats_partial<<<dim3(p.gx, p.gy), trb::kThreads, 0, s>>>(static_cast<const uint4*>(conv_out), partial, m, c,
-                                                                     p.tpr, p.bx, p.by, p.rows_per_strip);
+                                                                     p.tpr, p.bx, p.by, p.rows_per_strip, bf16);
     TRB_LAUNCH_CHECK("bn_stats_partial");
     trb::bn_stats_finalize<<<(c + 7) / 8, 256, 0, s>>>(partial, p.gx, c, m, gamma, beta, eps, momentum, ch_sum,
                                                           ch_sqsum, saved_mean, saved_inv_std, eq_scale, eq_bias,
                                                           running_mean, running_var);
     TRB_LAUNCH_CHECK("bn_stats_finalize");
+    return TRB200_OK;
+}
+
+extern "C" int trb200_bn_stats_finalize(const void* conv_out, const float* gamma, const float* beta, float eps,
+                                        float momentum, float* ch_sum, float* ch_sqsum, float* saved_mean,
+                                        float* saved_inv_std, float* eq_scale, float* eq_bias,
+                                        float* running_mean, float* running_var, int64_t m, int32_t c,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+    return bn_stats_finalize_any(conv_out, gamma, beta, eps, momentum, ch_sum, ch_sqsum, saved_mean, saved_inv_std,
+                                 eq_scale, eq_bias, running_mean, running_var, m, c, workspace, workspace_bytes, stream,
+                                 0);
+}
+
+extern "C" int trb200_bn_stats_finalize_dtype(const void* conv_out, const float* gamma, const float* beta, float eps,
+                                              float momentum, float* ch_sum, float* ch_sqsum, float* saved_mean,
+                                              float* saved_inv_std, float* eq_scale, float* eq_bias,
+                                              float* running_mean, float* running_var, int64_t m, int32_t c,
+                                              int32_t dtype, void* workspace, size_t workspace_bytes, void* stream) {
+    TRB_REQUIRE(trb::valid_dtype(dtype), TRB200_ERR_INVALID_ARGUMENT, "bn_stats_finalize: unknown dtype %d", dtype);
+    return bn_stats_finalize_any(conv_out, gamma, beta, eps, momentum, ch_sum, ch_sqsum, saved_mean, saved_inv_std,
+                                 eq_scale, eq_bias, running_mean, running_var, m, c, workspace, workspace_bytes, stream,
+                                 dtype == TRB200_DTYPE_BF16);
+}
+
+namespace trb {
+namespace {
+// The apply stage for either storage type, with or without the ReLU: t = round16(round16(x*s) + b);
+// RELU: y = max(t, 0) and mask bit = t > 0; otherwise y = t and no mask (a BN in front of a residual join).
+template <bool BF16, bool RELU>
+__device__ __forceinline__ void bn_apply_body(const uint4* __restrict__ x, const float* __restrict__ eq_scale,
+                                              const float* __restrict__ eq_bias, uint4* __restrict__ y,
+                                              uint8_t* __restrict__ mask, int64_t m, int tpr) {
+    const int64_t total = m * tpr;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int vec = (int)(i % tpr);
+        float f[8];
+        unpack8_t<BF16>(x[i], f);
+        uint32_t o[4], bits = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 a = unpack2_t<BF16>(pack2_t<BF16>(f[2 * j] * eq_scale[vec * 8 + 2 * j],
+                                                           f[2 * j + 1] * eq_scale[vec * 8 + 2 * j + 1]));
+            o[j] = pack2_t<BF16>(a.x + eq_bias[vec * 8 + 2 * j], a.y + eq_bias[vec * 8 + 2 * j + 1]);
+            if (RELU) {
+                const float2 t = unpack2_t<BF16>(o[j]);
+                const bool p0 = t.x > 0.f, p1 = t.y > 0.f;
+                bits |= (p0 ? 1u : 0u) << (2 * j) | (p1 ? 1u : 0u) << (2 * j + 1);
+                o[j] = (p0 ? o[j] & 0xffffu : 0u) | (p1 ? o[j] & 0xffff0000u : 0u);
+            }
+        }
+        y[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        if (RELU) mask[i] = (uint8_t)bits;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+bn_apply_any_kernel(const uint4* __restrict__ x, const float* __restrict__ eq_scale, const float* __restrict__ eq_bias,
+                    uint4* __restrict__ y, uint8_t* __restrict__ mask, int64_t m, int tpr, int bf16, int relu) {
+    if (bf16) {
+        if (relu) bn_apply_body<true, true>(x, eq_scale, eq_bias, y, mask, m, tpr);
+        else bn_apply_body<true, false>(x, eq_scale, eq_bias, y, mask, m, tpr);
+    } else {
+        if (relu) bn_apply_body<false, true>(x, eq_scale, eq_bias, y, mask, m, tpr);
+        else bn_apply_body<false, false>(x, eq_scale, eq_bias, y, mask, m, tpr);
+    }
+}
+}  // namespace
+}  // namespace trb
+
+extern "C" int trb200_bn_apply_dtype(const void* conv_out, const float* eq_scale, const float* eq_bias, void* out,
+                                     void* mask_bits, int64_t m, int32_t c, int32_t relu, int32_t dtype,
+                                     void* stream) {
+    TRB_REQUIRE(trb::valid_dtype(dtype), TRB200_ERR_INVALID_ARGUMENT, "bn_apply: unknown dtype %d", dtype);
+    TRB_REQUIRE(conv_out && eq_scale && eq_bias && out && (!relu || mask_bits), TRB200_ERR_INVALID_ARGUMENT,
+                "bn_apply: null pointer");
+    TRB_REQUIRE(m > 0 && c > 0 && c % 8 == 0, TRB200_ERR_UNSUPPORTED,
+                "bn_apply: need m > 0 and c a positive multiple of 8 (m=%lld c=%d)", (long long)m, c);
+    TRB_REQUIRE(trb::aligned16(conv_out) && trb::aligned16(out), TRB200_ERR_INVALID_ARGUMENT,
+                "bn_apply: tensors must be 16-byte aligned");
+    // the tuned kernel covers the half + ReLU case of the VGG path
+    if (dtype == TRB200_DTYPE_F16 && relu)
+        return trb200_bn_apply_relu_mask(conv_out, eq_scale, eq_bias, out, mask_bits, m, c, stream);
+    const int64_t items = m * (c / 8);
+    int64_t blocks = (items + 255) / 256;
+    const int64_t cap = (int64_t)trb::sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    trb::bn_apply_any_kernel<<<(int)blocks, 256, 0, trb::as_stream(stream)>>>(
+        static_cast<const uint4*>(conv_out), eq_scale, eq_bias, static_cast<uint4*>(out),
+        static_cast<uint8_t*>(mask_bits), m, c / 8, dtype == TRB200_DTYPE_BF16, relu != 0);
+    TRB_LAUNCH_CHECK("bn_apply_any_kernel");
     return TRB200_OK;
 }
 

@@ -392,7 +392,9 @@ def bn_stats_finalize(conv_out, gamma, beta, eps=1e-5, momentum=0.1, running_mea
     """Batch statistics of the conv output + bn_finalize (cbr_op.cpp:430-528, 622-718).
     Returns dict(saved_mean, saved_inv_std, eq_scale, eq_bias[, sum, sqsum])."""
     lib = _lib.load()
-    _need(conv_out, torch.float16, "conv_out")
+    if conv_out.dtype not in DTYPE_CODE:
+        raise TypeError(f"conv_out: float16 or bfloat16 expected, got {conv_out.dtype}")
+    _need(conv_out, conv_out.dtype, "conv_out")
     c = conv_out.shape[-1]
     m = conv_out.numel() // c
     dev = conv_out.device
@@ -403,12 +405,30 @@ def bn_stats_finalize(conv_out, gamma, beta, eps=1e-5, momentum=0.1, running_mea
         out["sum"] = torch.empty(c, dtype=torch.float32, device=dev)
         out["sqsum"] = torch.empty(c, dtype=torch.float32, device=dev)
     ws = (workspace or default_workspace()).ensure(lib.trb200_bn_stats_workspace_bytes(m, c))
-    check(lib.trb200_bn_stats_finalize(_ptr(conv_out), _ptr(gamma), _ptr(beta), float(eps), float(momentum),
-                                       _ptr(out.get("sum")), _ptr(out.get("sqsum")), _ptr(out["saved_mean"]),
-                                       _ptr(out["saved_inv_std"]), _ptr(out["eq_scale"]), _ptr(out["eq_bias"]),
-                                       _ptr(running_mean), _ptr(running_var), m, c, _ptr(ws), ws.numel(),
-                                       _stream(stream)))
+    check(lib.trb200_bn_stats_finalize_dtype(_ptr(conv_out), _ptr(gamma), _ptr(beta), float(eps), float(momentum),
+                                             _ptr(out.get("sum")), _ptr(out.get("sqsum")), _ptr(out["saved_mean"]),
+                                             _ptr(out["saved_inv_std"]), _ptr(out["eq_scale"]), _ptr(out["eq_bias"]),
+                                             _ptr(running_mean), _ptr(running_var), m, c, DTYPE_CODE[conv_out.dtype],
+                                             _ptr(ws), ws.numel(), _stream(stream)))
     return out
+
+
+def bn_apply(conv_out, eq_scale, eq_bias, relu=True, out=None, mask_bits=None, stream=None):
+    """The apply stage for half or bfloat16 tensors: with relu, (relu_out, bit-packed mask) as bn_apply_relu_mask;
+    without, (bn_out, None): the BN in front of a residual join."""
+    if conv_out.dtype not in DTYPE_CODE:
+        raise TypeError(f"conv_out: float16 or bfloat16 expected, got {conv_out.dtype}")
+    _need(conv_out, conv_out.dtype, "conv_out")
+    c = conv_out.shape[-1]
+    m = conv_out.numel() // c
+    if out is None:
+        out = torch.empty_like(conv_out)
+    if relu and mask_bits is None:
+        mask_bits = torch.empty(conv_out.numel() // 8, dtype=torch.uint8, device=conv_out.device)
+    check(_lib.load().trb200_bn_apply_dtype(_ptr(conv_out), _ptr(eq_scale), _ptr(eq_bias), _ptr(out),
+                                            _ptr(mask_bits) if relu else None, m, c, 1 if relu else 0,
+                                            DTYPE_CODE[conv_out.dtype], _stream(stream)))
+    return out, (mask_bits if relu else None)
 
 
 def bn_apply_relu_mask(conv_out, eq_scale, eq_bias, relu_out=None, mask_bits=None, stream=None):

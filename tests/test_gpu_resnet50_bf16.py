@@ -384,3 +384,32 @@ def test_block_backward_entry_point_on_resnet_blocks_bf16(orc, n, h, c, k, r, pa
     dconv = host_f32(out["dconv"])
     assert rel_l2(host_f32(out["dw"]), orc.conv_wgrad(dconv, x, wt.shape, pad=pad, stride=stride)) < 4e-3
     assert rel_l2(host_f32(out["dx"]), orc.conv_dgrad(dconv, wt, x.shape, pad=pad, stride=stride)) < 4e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("relu", [True, False])
+def test_bn_forward_stats_and_apply_either_type(orc, dtype, relu):
+    """Batch statistics + apply on a conv output of either type: t = round(round(x*s) + b), bit for bit; ReLU and
+    mask when asked for, the plain BN output otherwise (the BN in front of a residual join)."""
+    from renaissance_b200 import ops
+    m, c = 2 * 14 * 14, 256
+    rng = np.random.default_rng(17)
+    rnd = bf16_round if dtype == torch.bfloat16 else (lambda a: a.astype(np.float16).astype(np.float32))
+    x = rnd(rng.standard_normal((m, c)) * 1.3 + 0.2)
+    gamma = (1.0 + 0.2 * rng.standard_normal(c)).astype(np.float32)
+    beta = (0.2 * rng.standard_normal(c)).astype(np.float32)
+    st = ops.bn_stats_finalize(dev(x).to(dtype), dev(gamma), dev(beta), want_sums=True)
+    x64 = x.astype(np.float64)
+    assert rel_max(host(st["sum"]), x64.sum(axis=0)) < 1e-4
+    assert rel_max(host(st["sqsum"]), (x64 * x64).sum(axis=0)) < 1e-4
+    assert rel_max(host(st["saved_mean"]), x64.mean(axis=0)) < 1e-4
+    assert rel_max(host(st["saved_inv_std"]), 1.0 / np.sqrt(x64.var(axis=0) + 1e-5)) < 1e-4
+    es, eb = host(st["eq_scale"]), host(st["eq_bias"])
+    t = rnd(rnd(x * es) + eb)                                  # float32 products and sums, as the kernel's
+    out, bits = ops.bn_apply(dev(x).to(dtype), st["eq_scale"], st["eq_bias"], relu=relu)
+    torch.cuda.synchronize()
+    if relu:
+        assert np.array_equal(host_f32(out), np.maximum(t, 0))
+        assert np.array_equal(host(bits), orc.mask_pack((t > 0).astype(np.int8)))
+    else:
+        assert bits is None and np.array_equal(host_f32(out), t)
