@@ -140,6 +140,23 @@ class ResNet50:
         ops.device_status()
         return out["loss"]
 
+    def allreduce_gradients(self, group=None):
+        """Data parallelism: the mean over the ranks of every gradient, as one NCCL all-reduce of a flat float
+        buffer (RANGE_MEAN_ALLREDUCE of the reference, allreduce_op.cpp:37-105; not bucketed or overlapped here).
+        A single process is a no-op."""
+        import torch.distributed as dist
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+            return
+        tensors = [u.grads[k] for u in self.units() for k in ("w", "gamma", "beta")]
+        tensors += [self.fc_grads["w"], self.fc_grads["b"]]
+        flat = torch.cat([t.reshape(-1) for t in tensors])
+        dist.all_reduce(flat, group=group)
+        ops.scale_f32(flat, 1.0 / dist.get_world_size(group))
+        off = 0
+        for t in tensors:
+            t.copy_(flat[off:off + t.numel()].view_as(t))
+            off += t.numel()
+
     def sgd_step(self, lr=0.1, momentum=0.9, weight_decay=1e-4):
         def upd(key, p, g, decay):
             if decay:
@@ -176,25 +193,47 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f16"])
     args = ap.parse_args()
+    import os
+    import torch.distributed as dist
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
-    net = ResNet50(dtype=dtype)
-    img, lab = synthetic_batch(args.batch, dtype=dtype)
-    losses = []
-    for _ in range(2):
-        losses.append(float(net.forward_backward(img, lab)))
-        net.sgd_step(lr=0.05)
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    if world > 1:                                               # launched by torchrun: one process per GPU
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dist.init_process_group("nccl")
+    net = ResNet50(dtype=dtype)                                 # same seed: the ranks start from the same weights
+    img, lab = synthetic_batch(args.batch, dtype=dtype, seed=1 + rank)
+
+    def step():
+        loss = net.forward_backward(img, lab)
+        net.allreduce_gradients()
+        net.sgd_step(lr=0.01)
+        return float(loss)
+
+    losses = [step() for _ in range(2)]
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
     a.record()
-    for _ in range(args.steps):
-        losses.append(float(net.forward_backward(img, lab)))
-        net.sgd_step(lr=0.05)
+    losses += [step() for _ in range(args.steps)]
     b.record()
     torch.cuda.synchronize()
-    ms = a.elapsed_time(b) / args.steps
-    print(json.dumps({"model": "resnet50", "dtype": args.dtype, "batch": args.batch, "ms_per_step": round(ms, 2),
-                      "images_per_sec": round(args.batch / ms * 1e3, 1), "losses": [round(v, 4) for v in losses],
-                      "note": "untuned composition on one stream, same batch every step"}))
+    ms = torch.tensor([a.elapsed_time(b) / args.steps], device="cuda")
+    check = torch.stack([net.stem.w32.double().sum(), net.fc_w32.double().sum()])   # equal on every rank if in step
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        lo, hi = check.clone(), check.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        assert torch.equal(lo, hi), "the ranks' weights have diverged"
+    if rank == 0:
+        print(json.dumps({"model": "resnet50", "dtype": args.dtype, "n_gpus": world, "batch_per_gpu": args.batch,
+                          "ms_per_step": round(float(ms), 2),
+                          "images_per_sec": round(world * args.batch / float(ms) * 1e3, 1),
+                          "losses_rank0": [round(v, 4) for v in losses],
+                          "note": "untuned composition on one stream, same batch every step, all-reduce not overlapped"}))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
