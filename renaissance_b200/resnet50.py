@@ -4,8 +4,8 @@
 The reference names this network (its layer list is scripts/resnet50_conv.json, its block descriptors are in
 src/graph/layer_descriptor_registry.cpp:1313-1580) but has no backend for it, so this driver is not a drop-in for
 anything: it exists to run every operator the network needs, in the order and on the shapes the network uses them,
-through the same C ABI as the VGG16-BN path.  One stream, no fusion across operators, statistics taken by a separate
-pass; it is a correctness composition, not a tuned step.
+through the same C ABI as the VGG16-BN path.  One stream, no fusion across operators beyond the statistics epilogue
+of the stride-1 convolutions; it is a correctness composition, not a tuned step.
 
     forward   conv (tcgen05 kernels) -> batch statistics -> BN apply (+ ReLU + mask)      per conv + BN unit
               3x3 stride-2 max pool after the 7x7 stem, add + ReLU + mask at every residual join,
@@ -46,8 +46,13 @@ class ConvBN:
     def forward(self, x, relu):
         n, h, w, _ = x.shape
         g = self.geometry(n, h, w)
-        y = ops.conv_fprop(g, x, self.w)
-        st = ops.bn_stats_finalize(y, self.gamma, self.beta)
+        if self.stride == 1 and self.cin % 64 == 0:
+            # the batch statistics come out of the convolution kernel's epilogue
+            y, st = ops.conv_fprop_bn_stats(g, x, self.w, self.gamma, self.beta)
+        else:
+            # stride 2 and the stem go through a resampling / lowering pass: statistics by a pass of their own
+            y = ops.conv_fprop(g, x, self.w)
+            st = ops.bn_stats_finalize(y, self.gamma, self.beta)
         out, mask = ops.bn_apply(y, st["eq_scale"], st["eq_bias"], relu=relu)
         self.ctx = dict(g=g, x=x, y=y, st=st, mask=mask)
         return out
