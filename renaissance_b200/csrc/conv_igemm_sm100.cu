@@ -811,11 +811,17 @@ int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int 
 int conv3x3_stats_max_strips() { return sm_count(); }
 
 #include "conv_pixn_sm100.cuh"
+#include "conv_halo_pair_sm100.cuh"
 
-// 64 / 128 output channels go to the kernel with the pixels on N (development builds can switch it off)
+// 64 / 128 channels on both sides go to the CTA-pair kernel with the resident filters, other layers with 64 / 128
+// output channels to the kernel with the pixels on N (development builds can switch either off)
 int conv3x3_any_run(const void* in, const void* wv, int tap_is_dim1, void* out, int n, int h, int w, int cin, int cout,
                     cudaStream_t st, float* stats_partial = nullptr, int* stats_strips = nullptr, bool bf16 = false,
                     int taps = 9) {
+#ifndef TRB200_NO_HALO_PAIR
+    if (halo_pair_preferred(cin, cout, taps))
+        return conv3x3_halo_pair_run(in, wv, tap_is_dim1, out, n, h, w, cin, cout, st, stats_partial, stats_strips, bf16);
+#endif
 #ifndef TRB200_NO_PIXN
     if (pixn_preferred(cin, cout))
         return conv3x3_pixn_run(in, wv, tap_is_dim1, out, n, h, w, cin, cout, st, stats_partial, stats_strips, bf16,
