@@ -1163,6 +1163,7 @@ WgradParams wgrad_plan(const trb200_conv_desc& d, int nt, const TileShape& t, in
 }
 
 #include "wgrad_unitn_sm100.cuh"
+#include "wgrad_halo_sm100.cuh"
 
 // which weight-gradient kernel a layer gets: up to 128 filters the one with the units on N
 // (development builds can move the limit)
@@ -1171,6 +1172,16 @@ WgradParams wgrad_plan(const trb200_conv_desc& d, int nt, const TileShape& t, in
 #endif
 inline bool wgrad_use_unitn(const trb200_conv_desc& d) {
     return d.r == 3 && wgrad_unitn_supports(d) && d.k <= TRB200_UNITN_MAX_K;
+}
+
+// 64 -> 64 channels: the kernel that reads all nine taps from one halo copy (development builds can switch it off)
+inline bool wgrad_use_halo(const trb200_conv_desc& d) {
+#ifdef TRB200_NO_WGRAD_HALO
+    (void)d;
+    return false;
+#else
+    return wgrad_halo_supports(d) && d.s == 3 && d.pad_h == 1 && d.pad_w == 1 && d.stride_h == 1 && d.stride_w == 1;
+#endif
 }
 
 // ------------------------------------------------------------------ first layer (C = 4)
@@ -1241,6 +1252,7 @@ size_t igemm_wgrad_workspace(const trb200_conv_desc& d) {
         e.c = 64;
         return (size_t)align_up((int64_t)d.k * 64 * 2, 256) + wgrad_partial_bytes(e, 1);
     }
+    if (wgrad_use_halo(d)) return wgrad_halo_partial_bytes(d);
     if (wgrad_use_unitn(d)) return wgrad_unitn_partial_bytes(d);
     return wgrad_partial_bytes(d, igemm_taps(d));
 }
@@ -1345,6 +1357,7 @@ int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* 
     TRB_REQUIRE((reinterpret_cast<uintptr_t>(ws) & 255u) == 0, TRB200_ERR_INVALID_ARGUMENT,
                 "conv_wgrad: workspace must be 256-byte aligned");
     if (igemm_small_c(d)) return igemm_wgrad_small_c(d, dy, x, dw, ws, st);
+    if (wgrad_use_halo(d)) return wgrad_halo_run(d, dy, x, dw, static_cast<float*>(ws), st);
     if (wgrad_use_unitn(d)) return wgrad_unitn_run(d, dy, x, dw, static_cast<float*>(ws), st);
     return wgrad_run(d, igemm_taps(d), dy, x, dw, static_cast<float*>(ws), st);
 }
