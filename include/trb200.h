@@ -109,6 +109,10 @@ int trb200_bnrelu_bwd_dtype(const void* dy, const void* mask_bits, const void* x
  * calls no cudaMalloc, cudaFree or other allocating routine.
  *   - Limit: c <= 4096 (and c % 8 == 0); anything larger is rejected with
  *     TRB200_ERR_UNSUPPORTED.  m is not limited.
+ *   - Narrower than trb200_bnrelu_bwd in two ways: half tensors only (there is no
+ *     dtype argument, bfloat16 callers use trb200_bnrelu_bwd_dtype with a workspace),
+ *     and mask_bits is required (NULL is rejected with TRB200_ERR_INVALID_ARGUMENT;
+ *     the BN without a ReLU behind it is served by the workspace entry point only).
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current); make that first call before
  *     any stream capture begins.
@@ -182,6 +186,19 @@ int trb200_set_conv_backend(int backend);
  * TRB200_ERR_DEVICE_TIMEOUT if a kernel's bounded wait gave up since the last
  * call (the word is cleared).  Call it after synchronising, never in capture. */
 int trb200_device_status(void);
+
+/* Self-test of the bounded waits (failure detection without a fault): launches a
+ * two-warp kernel in which warp 0 waits, with the library's own wait routine and a
+ * limit of `limit_ns` (1 us .. 100 ms), on an mbarrier that nothing arrives on, and
+ * warp 1 waits on it with the kernels' normal one-second limit.  Warp 0 gives up
+ * after the limit, records a status code and raises the block's abort flag; warp 1
+ * sees the flag and leaves too.  out4 (device, 4 ints) = {warp 0 got the barrier (0
+ * expected), ns it waited, warp 1 got the barrier (0 expected), ns it waited}.
+ * Afterwards trb200_device_status() returns TRB200_ERR_DEVICE_TIMEOUT once and the
+ * context is as usable as before.  This is the path every tcgen05 kernel of the
+ * library takes when a copy or an MMA it waits for never completes; it has no
+ * counterpart in the reference (which waits inside cuDNN). */
+int trb200_selftest_wait_timeout(uint64_t limit_ns, int32_t* out4, void* stream);
 
 /* Which implementation the two conv entry points would pick for this shape:
  * 1 = tcgen05/TMEM implicit GEMM fed by TMA, 0 = direct CUDA-core kernel.
@@ -263,9 +280,17 @@ int trb200_softmax_ce_bwd(const float* probs, int64_t probs_stride, const int32_
  * arithmetic is that of the two nodes above.
  * When probs is NULL and the rows are whole 16-byte vectors of at most 32768
  * classes, the row kernel also finishes the loss (last block to end adds
- * per-block sums in block order; bitwise reproducible on a given GPU) using one
- * of 64 completion counters kept in the library: at most 64 such calls may be
- * in flight on a GPU at a time. */
+ * per-block sums in block order; bitwise reproducible on a given GPU) using a
+ * completion counter kept in the library.  A counter belongs to the (device,
+ * stream) of the call, so calls on one stream, which run in order, never share
+ * one while in flight; the 65th distinct (device, stream) pair gets none and
+ * its loss is finished by the separate reduction launch instead.  A captured
+ * call keeps the counter of the stream it was captured on: do not replay such
+ * a graph while eager calls on that same capture stream are in flight.
+ * A label outside [0, classes) matches no class (the reference reads through
+ * it unchecked): nothing is read or written through it, its probability counts
+ * as 0 in the loss and its row of d_logits gets no -(1 - ls) entry.  The same
+ * holds for trb200_softmax_ce_fwd / _bwd. */
 int trb200_softmax_ce_fused(const void* logits, int64_t logits_stride, const int32_t* labels,
                             const float* scaling, const float* label_smoothing,
                             float* probs, int64_t probs_stride,

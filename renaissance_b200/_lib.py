@@ -76,6 +76,7 @@ def load() -> C.CDLL:
         "trb200_device_arch": (C.c_int, []),
         "trb200_kernel_launch_count": (C.c_uint64, []),
         "trb200_device_status": (C.c_int, []),
+        "trb200_selftest_wait_timeout": (C.c_int, [C.c_uint64, vp, vp]),
         "trb200_set_conv_backend": (C.c_int, [C.c_int]),
         "trb200_conv_uses_tensor_cores": (C.c_int, [pdesc, C.c_int]),
         "trb200_bnrelu_bwd_workspace_bytes": (sz, [i64, i32]),

@@ -7,6 +7,7 @@
 namespace trb {
 
 int device_status_read_and_clear(int* out);
+int wait_timeout_selftest(unsigned long long limit_ns, int* out4, cudaStream_t st);
 int softmax_status_read_and_clear(int* out);
 size_t bnrelu_pool_bwd_workspace(int n, int h, int w, int c);
 int bnrelu_pool_bwd_launch(const void* dy_pooled, const void* argmax, const void* mask_bits, const void* x,
@@ -70,6 +71,10 @@ extern "C" int trb200_device_status(void) {
     if (v != 0)
         return trb::fail(TRB200_ERR_DEVICE_TIMEOUT, "a device-side wait gave up (role code %d)", v);
     return TRB200_OK;
+}
+
+extern "C" int trb200_selftest_wait_timeout(uint64_t limit_ns, int32_t* out4, void* stream) {
+    return trb::wait_timeout_selftest((unsigned long long)limit_ns, out4, trb::as_stream(stream));
 }
 
 extern "C" size_t trb200_conv_wgrad_workspace_bytes(const trb200_conv_desc* d) {

@@ -1362,6 +1362,50 @@ int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* 
     return wgrad_run(d, igemm_taps(d), dy, x, dw, static_cast<float*>(ws), st);
 }
 
+// ------------------------------------------------------------------ self-test of the give-up path
+// One warp initialises an mbarrier that nothing ever arrives on and waits for it with the kernels' own bounded wait
+// and a short limit.  The wait runs out, the status word gets kStatusSelfTest, the block's abort flag is raised
+// (which the second warp's wait then sees) and the kernel returns: nothing faults and the context stays usable.
+namespace {
+constexpr int kStatusSelfTest = 99;
+
+__global__ void __launch_bounds__(64, 1) wait_timeout_selftest_kernel(unsigned long long limit_ns, int* status, int* out) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        mbar_init(smem_u32(&bar), 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    const unsigned long long t0 = global_ns();
+    bool ok;
+    if (threadIdx.x < 32) {
+        ok = mbar_wait_limit(smem_u32(&bar), 0, &s_abort, status, kStatusSelfTest, limit_ns);
+    } else {
+        // a role that would wait a full second on its own: it must leave when the first one raises the abort flag
+        ok = mbar_wait(smem_u32(&bar), 0, &s_abort, status, kStatusSelfTest);
+    }
+    const unsigned long long waited = global_ns() - t0;
+    if ((threadIdx.x & 31) == 0) {
+        out[(threadIdx.x >> 5) * 2] = ok ? 1 : 0;
+        out[(threadIdx.x >> 5) * 2 + 1] = (int)(waited > 0x7fffffffull ? 0x7fffffffull : waited);
+    }
+}
+}  // namespace
+
+// out4: device array of four ints: {warp 0 returned true?, ns it waited, warp 1 returned true?, ns it waited}
+int wait_timeout_selftest(unsigned long long limit_ns, int* out4, cudaStream_t st) {
+    TRB_REQUIRE(out4 != nullptr, TRB200_ERR_INVALID_ARGUMENT, "selftest_wait_timeout: null output");
+    TRB_REQUIRE(limit_ns >= 1000ull && limit_ns <= 100ull * 1000ull * 1000ull, TRB200_ERR_INVALID_ARGUMENT,
+                "selftest_wait_timeout: limit of %llu ns outside [1 us, 100 ms]", limit_ns);
+    int* status = nullptr;
+    TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status));
+    wait_timeout_selftest_kernel<<<1, 64, 0, st>>>(limit_ns, status, out4);
+    TRB_LAUNCH_CHECK("wait_timeout_selftest_kernel");
+    return TRB200_OK;
+}
+
 #ifdef TRB200_ROLE_TIMERS
 extern "C" int trb200_debug_read_role_timers(long long* host_out, int count) {
     TRB_CUDA_TRY(cudaMemcpyFromSymbol(host_out, g_role_timers, sizeof(long long) * (size_t)count));

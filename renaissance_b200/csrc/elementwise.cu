@@ -45,8 +45,9 @@ cast_f16_f32_kernel(const __half* __restrict__ src, float* __restrict__ dst, int
 //   MODE 1: t = round16(a + b); out = max(t, 0); mask bit = t > 0 (that AXPY followed by relu_fwd_amp_mask_kernel,
 //           relu_op.cu:101-114, the mask bit-packed like the block's)
 template <bool BF16, int MODE>
-__device__ __forceinline__ void add_body(const uint4* __restrict__ a, const uint4* __restrict__ b,
-                                         uint4* __restrict__ out, uint8_t* __restrict__ mask, int64_t vecs) {
+// `out` may be `a` or `b` (in-place join), so none of the three tensor pointers is declared restrict
+__device__ __forceinline__ void add_body(const uint4* a, const uint4* b, uint4* out, uint8_t* __restrict__ mask,
+                                         int64_t vecs) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < vecs; v += stride) {
         float fa[8], fb[8];
@@ -69,14 +70,13 @@ __device__ __forceinline__ void add_body(const uint4* __restrict__ a, const uint
 }
 
 __global__ void __launch_bounds__(256)
-add16_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ out, int64_t vecs, int bf16) {
+add16_kernel(const uint4* a, const uint4* b, uint4* out, int64_t vecs, int bf16) {
     if (bf16) add_body<true, 0>(a, b, out, nullptr, vecs);
     else add_body<false, 0>(a, b, out, nullptr, vecs);
 }
 
 __global__ void __launch_bounds__(256)
-add_relu_mask_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ out,
-                     uint8_t* __restrict__ mask, int64_t vecs, int bf16) {
+add_relu_mask_kernel(const uint4* a, const uint4* b, uint4* out, uint8_t* __restrict__ mask, int64_t vecs, int bf16) {
     if (bf16) add_body<true, 1>(a, b, out, mask, vecs);
     else add_body<false, 1>(a, b, out, mask, vecs);
 }
@@ -84,7 +84,7 @@ add_relu_mask_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, u
 // dx = mask bit ? dy : 0 (relu_bwd_amp_kernel, relu_op.cu:116-126, with the bit-packed mask); a pure select on
 // 16-bit words, so the same for half and bfloat16
 __global__ void __launch_bounds__(256)
-relu_mask_bwd_kernel(const uint4* __restrict__ dy, const uint8_t* __restrict__ mask, uint4* __restrict__ dx,
+relu_mask_bwd_kernel(const uint4* dy, const uint8_t* __restrict__ mask, uint4* dx,   // dx may be dy
                      int64_t vecs) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < vecs; v += stride) {

@@ -72,22 +72,29 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` is a shared-memory word of the block; once any role
 // sets it every other wait of the block returns false at its next poll.
-// `status` is a global word: the first failure stores `code` there.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+// `status` is a global word: the first failure stores `code` there.  `limit_ns` is the
+// time after which the wait gives up (kWaitLimitNs in the kernels proper; the library's
+// self-test runs the same code with a short limit on a barrier nobody arrives on).
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                int* status, int code, unsigned long long limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 255u) == 0u) {
             if (*abort_flag) return false;
-            if (global_ns() - t0 > kWaitLimitNs) {
+            if (global_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;
             }
         }
     }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+    return mbar_wait_limit(bar, parity, abort_flag, status, code, kWaitLimitNs);
 }
 
 // The same for roles that are far ahead of (or behind) their partner most of the time: producers waiting for a

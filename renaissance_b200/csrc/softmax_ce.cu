@@ -17,6 +17,7 @@
 #include "sm100_ptx.cuh"
 
 #include <atomic>
+#include <mutex>
 
 namespace trb {
 
@@ -144,7 +145,8 @@ softmax_ce_rows_warp(const __half* __restrict__ logits, int64_t logits_stride,
             }
         sum = warp_sum(sum);
         const float inv_sum = 1.0f / (sum + 1e-8f);
-        const int y = labels[row];
+        const int y_raw = labels[row];
+        const int y = (unsigned)y_raw < (unsigned)classes ? y_raw : -1;   // out of range: matches no class
         float sum_log = 0.f, py = 0.f;
 #pragma unroll
         for (int i = 0; i < VPL; ++i) {
@@ -291,7 +293,11 @@ softmax_ce_rows_warp_lean_body(const uint16_t* __restrict__ logits, int64_t logi
         uint4 cur[VPL];
 #pragma unroll
         for (int i = 0; i < VPL; ++i) cur[i] = nxt[i];
-        const int y = labels[row];
+        // a label outside [0, classes) matches no class: nothing is read or written through it, its
+        // probability counts as 0 in the loss and no entry of the gradient gets the -(1 - ls) term
+        const int y_raw = labels[row];
+        const bool y_ok = (unsigned)y_raw < (unsigned)classes;
+        const int y = y_ok ? y_raw : 0;
         const float zy = load16_t<BF16>(logits + (int64_t)row * logits_stride + y);
         {
             const int row_n = row + warps;
@@ -355,8 +361,8 @@ softmax_ce_rows_warp_lean_body(const uint16_t* __restrict__ logits, int64_t logi
         }
         // the label's class, by the lane that stored its vector
         if (((y >> 3) & 31) == lane) {
-            const float py = fast_exp2(fmaf(zy, kLog2e, shift)) * inv_sum;
-            drow[y] = round16_t<BF16>((py - spread - keep) * gscale);
+            const float py = y_ok ? fast_exp2(fmaf(zy, kLog2e, shift)) * inv_sum : 0.f;
+            if (y_ok) drow[y] = round16_t<BF16>((py - spread - keep) * gscale);
             const float row_loss = (-keep * logf(py + 1e-8f) - spread * sum_log) * inv_b;
             if (loss_partial) loss_partial[row] = row_loss;
             my_loss += row_loss;
@@ -459,8 +465,10 @@ softmax_ce_rows_block(const __half* __restrict__ logits, int64_t logits_stride,
 
     // sweep 2: sum of exponentials
     float sum = 0.f;
-    const int y = labels[row];
-    const float zy = __half2float(z[y]);                  // from global: the staged row is about to be overwritten
+    const int y_raw = labels[row];                        // out of range: matches no class, see softmax_ce_rows_warp_lean
+    const bool y_ok = (unsigned)y_raw < (unsigned)classes;
+    const int y = y_ok ? y_raw : -1;
+    const float zy = y_ok ? __half2float(z[y]) : 0.f;     // from global: the staged row is about to be overwritten
     for (int vec = tid; vec < nfull; vec += THREADS) {
         float f[8];
         half8_to_float(*reinterpret_cast<const uint4*>(src + vec * 8), f);
@@ -549,7 +557,7 @@ softmax_ce_rows_block(const __half* __restrict__ logits, int64_t logits_stride,
     if (out.loss_partial) {
         sum_log = block_reduce(sum_log, false) * kLn2;
         if (tid == 0) {
-            const float py = fast_exp2(fmaf(zy, kLog2e, shift)) * inv_sum;
+            const float py = y_ok ? fast_exp2(fmaf(zy, kLog2e, shift)) * inv_sum : 0.f;
             out.loss_partial[row] = (-keep * logf(py + 1e-8f) - spread * sum_log) * inv_b;
         }
     }
@@ -622,8 +630,10 @@ softmax_ce_rows_staged(const __half* __restrict__ logits, int64_t logits_stride,
         const bool ok = ptx::mbar_wait(bar0 + 8u * b, ((uint32_t)it >> 1) & 1u, &s_abort, status, 4);
         if (__syncthreads_or(ok ? 0 : 1)) break;
         __half* srow = reinterpret_cast<__half*>(smem_raw + (size_t)b * buf_stride);
-        const int y = labels[row];
-        const float zy = __half2float(logits[(int64_t)row * logits_stride + y]);
+        const int y_raw = labels[row];                    // out of range: matches no class
+        const bool y_ok = (unsigned)y_raw < (unsigned)classes;
+        const int y = y_ok ? y_raw : -1;
+        const float zy = y_ok ? __half2float(logits[(int64_t)row * logits_stride + y]) : 0.f;
 
         float zmax = -INFINITY;
         for (int vec = tid; vec < nvec; vec += THREADS)
@@ -717,7 +727,7 @@ softmax_ce_rows_staged(const __half* __restrict__ logits, int64_t logits_stride,
         if (out.loss_partial) {
             sum_log = block_reduce(sum_log, false) * kLn2;
             if (tid == 0) {
-                const float py = fast_exp2(fmaf(zy, kLog2e, shift)) * inv_sum;
+                const float py = y_ok ? fast_exp2(fmaf(zy, kLog2e, shift)) * inv_sum : 0.f;
                 out.loss_partial[row] = (-keep * logf(py + 1e-8f) - spread * sum_log) * inv_b;
             }
         }
@@ -808,7 +818,9 @@ softmax_ce_rows_regs(const __half* __restrict__ logits, int64_t logits_stride, c
         const bool ok = ptx::mbar_wait(bar0 + 8u * b, phase, &s_abort, status, 4);
         if (__syncthreads_or(ok ? 0 : 1)) break;
         const __half* srow = reinterpret_cast<const __half*>(smem_raw + (size_t)b * buf_stride);
-        const int y = labels[row];
+        const int y_raw = labels[row];                    // out of range: matches no class
+        const bool y_ok = (unsigned)y_raw < (unsigned)classes;
+        const int y = y_ok ? y_raw : 0;
         const float zy = __half2float(srow[y]);
 
         uint4 raw[VPT];
@@ -880,8 +892,8 @@ softmax_ce_rows_regs(const __half* __restrict__ logits, int64_t logits_stride, c
         }
         // the label's class, by the thread that stored its vector
         if (((y >> 3) % THREADS) == tid) {
-            const float py = fast_exp2((zy - m) * kLog2e) * inv_sum;
-            drow[y] = __float2half_rn((py - spread - keep) * gscale);
+            const float py = y_ok ? fast_exp2((zy - m) * kLog2e) * inv_sum : 0.f;
+            if (y_ok) drow[y] = __float2half_rn((py - spread - keep) * gscale);
             const float row_loss = (-keep * logf(py + 1e-8f) - spread * sum_log) * inv_b;
             if (loss_partial) loss_partial[row] = row_loss;
             my_loss += row_loss;
@@ -993,15 +1005,40 @@ int launch_rows(const void* logits, int64_t logits_stride, const int32_t* labels
     LossTail tail{loss, inv_scaling, nullptr, nullptr};
     bool fused_tail = false;
 #ifndef TRB200_NO_LOSS_TAIL
-    if (loss || inv_scaling) {
-        static std::atomic<unsigned int> next_ticket{0};
-        unsigned int* pool = nullptr;
-        float* sums = nullptr;
-        TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&pool), g_loss_tickets));
-        TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&sums), g_loss_block_sums));
-        const unsigned int slot = next_ticket.fetch_add(1u) % kLossTickets;
-        tail.ticket = pool + slot;
-        tail.block_sums = sums + (size_t)slot * kLossTailBlocks;
+    // only the two kernels that finish the loss themselves need a counter
+    const bool lean_path = rows_aligned && classes <= 2048 && classes % 8 == 0 && !out.probs && out.dlogits && scaling &&
+                           out.dlogits_stride % 8 == 0 && aligned16(out.dlogits);
+    const bool regs_path = !lean_path && !(rows_aligned && classes <= 2048) && rows_aligned && classes % 8 == 0 &&
+                           classes <= 32768 && !out.probs && out.dlogits && scaling && out.dlogits_stride % 8 == 0 &&
+                           aligned16(out.dlogits);
+    if ((loss || inv_scaling) && (lean_path || regs_path)) {
+        // The counter (and its per-block sums) belongs to the (device, stream) of the call: work on one stream runs in
+        // order, so two launches never share a counter while both are in flight.  64 (device, stream) pairs get one; a
+        // call from a further stream does the loss with the separate reduction launch instead.
+        static std::mutex slot_mutex;
+        static struct { int dev; cudaStream_t stream; } owners[kLossTickets];
+        static int owners_used = 0;
+        int dev = 0;
+        TRB_CUDA_TRY(cudaGetDevice(&dev));
+        int slot = -1;
+        {
+            std::lock_guard<std::mutex> lock(slot_mutex);
+            for (int i = 0; i < owners_used; ++i)
+                if (owners[i].dev == dev && owners[i].stream == s) { slot = i; break; }
+            if (slot < 0 && owners_used < kLossTickets) {
+                slot = owners_used++;
+                owners[slot].dev = dev;
+                owners[slot].stream = s;
+            }
+        }
+        if (slot >= 0) {
+            unsigned int* pool = nullptr;
+            float* sums = nullptr;
+            TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&pool), g_loss_tickets));
+            TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&sums), g_loss_block_sums));
+            tail.ticket = pool + slot;
+            tail.block_sums = sums + (size_t)slot * kLossTailBlocks;
+        }
     }
 #endif
     if (rows_aligned && classes <= 2048 && classes % 8 == 0 && !out.probs && out.dlogits && scaling &&

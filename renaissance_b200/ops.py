@@ -109,6 +109,14 @@ def device_status() -> None:
     check(_lib.load().trb200_device_status())
 
 
+def selftest_wait_timeout(limit_ns: int = 1_000_000, stream=None):
+    """Runs the library's bounded wait on a barrier nobody arrives on.  Returns a 4-int device tensor
+    {warp 0 got it, ns waited, warp 1 got it, ns waited}; device_status() raises afterwards (once)."""
+    out = torch.zeros(4, dtype=torch.int32, device="cuda")
+    check(_lib.load().trb200_selftest_wait_timeout(int(limit_ns), _ptr(out), _stream(stream)))
+    return out
+
+
 def set_conv_backend(direct_only: bool) -> None:
     check(_lib.load().trb200_set_conv_backend(1 if direct_only else 0))
 

@@ -108,3 +108,22 @@ def test_product_package_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.lower(), f"{f} mentions the oracle"
+
+
+def test_adapter_compiles_against_the_reference_headers():
+    """The registry adapter must keep compiling against the reference's own headers (the drop-in claim).  Needs a
+    checkout of the reference: its path comes from TR_REFERENCE_ROOT; without one the test is skipped."""
+    import shutil
+    ref = os.environ.get("TR_REFERENCE_ROOT", "")
+    if not ref or not os.path.isdir(os.path.join(ref, "include")):
+        pytest.skip("TR_REFERENCE_ROOT does not name a checkout of the reference")
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("g++ not found")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(root, "renaissance_b200", "plugin", "b200_ops.cpp")
+    cuda_inc = "/usr/local/cuda/include"
+    cmd = [gxx, "-std=c++17", "-fsyntax-only", "-DTRB200_WITH_REFERENCE_HEADERS", "-DTR_USE_CUDA",
+           "-I", os.path.join(ref, "include"), "-I", os.path.join(root, "include"), "-I", cuda_inc, src]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-2000:]

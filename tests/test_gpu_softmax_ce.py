@@ -123,3 +123,89 @@ def test_large_sweep_point_properties():
     assert bool((d >= 0).all())
     full = out["dlogits"].double().sum(dim=1)
     assert float(full.abs().max()) < 1024.0 / batch * 2e-2
+
+
+@pytest.mark.parametrize("classes,stride", [(10, 16), (1000, 1008), (2056, 2064), (10000, 10008), (4999, 5000)])
+@pytest.mark.parametrize("want_probs", [False, True])
+def test_labels_out_of_range_touch_nothing(classes, stride, want_probs):
+    """Labels -1 and `classes` (an ignore index, a corrupt batch) match no class: no access goes through them.  The
+    d_logits buffer has a wider row stride with sentinel padding; the padding and the rows of the valid labels must
+    come out exactly as in a run in which the bad rows hold a valid label, and the bad rows must be the plain
+    (p - ls/C) * scale gradient.  Every row kernel is reached by one of the shapes."""
+    from renaissance_b200 import _lib
+    batch = 16
+    rng = np.random.default_rng(classes)
+    z = (rng.standard_normal((batch, classes)) * 2).astype(np.float16)
+    labels = rng.integers(0, classes, size=batch).astype(np.int32)
+    bad = labels.copy()
+    bad[3], bad[7], bad[12] = -1, classes, 2**31 - 1
+    zp = torch.full((batch, stride), 0.5, dtype=torch.float16, device="cuda")
+    zp[:, :classes] = dev(z)
+    sc, lsd = _scalars(8.0, 0.1)
+    lib = _lib.load()
+
+    def run(lab):
+        dl = torch.full((batch + 2, stride), -3.0, dtype=torch.float16, device="cuda")   # a guard row either side
+        probs = torch.full((batch, classes), -1.0, device="cuda") if want_probs else None
+        part = torch.empty(batch, device="cuda")
+        loss = torch.empty(1, device="cuda")
+        inv = torch.empty(1, device="cuda")
+        ld = dev(lab)
+        _lib.check(lib.trb200_softmax_ce_fused(zp.data_ptr(), stride, ld.data_ptr(), sc.data_ptr(), lsd.data_ptr(),
+                                               probs.data_ptr() if want_probs else None, classes if want_probs else 0,
+                                               dl[1:].data_ptr(), stride, part.data_ptr(), loss.data_ptr(),
+                                               inv.data_ptr(), batch, classes, None))
+        torch.cuda.synchronize()
+        return dl, part, loss
+
+    dl_ok, part_ok, _ = run(labels)
+    dl_bad, part_bad, loss_bad = run(bad)
+    assert float((dl_bad[0] + 3.0).abs().max()) == 0.0 and float((dl_bad[-1] + 3.0).abs().max()) == 0.0
+    assert float((dl_bad[1:-1, classes:] + 3.0).abs().max()) == 0.0                       # padding untouched
+    good = np.array([i for i in range(batch) if i not in (3, 7, 12)])
+    assert torch.equal(dl_bad[1:-1][good], dl_ok[1:-1][good])                             # neighbours unchanged
+    assert torch.equal(part_bad[good], part_ok[good])
+    p = torch.softmax(zp[:, :classes].float(), dim=1)
+    for r in (3, 7, 12):
+        expect = (p[r] - 0.1 / classes) * (8.0 / batch)
+        got = dl_bad[1 + r, :classes].float()
+        assert float((got - expect).abs().max()) < 2e-3 * float(expect.abs().max()) + 1e-6
+        assert bool(torch.isfinite(part_bad[r]))
+    assert bool(torch.isfinite(loss_bad).all())
+    # the two separate nodes: same rule
+    ld = dev(bad)
+    pr = torch.empty((batch, classes), device="cuda")
+    part = torch.empty(batch, device="cuda")
+    loss = torch.empty(1, device="cuda")
+    inv = torch.empty(1, device="cuda")
+    _lib.check(lib.trb200_softmax_ce_fwd(zp.data_ptr(), stride, ld.data_ptr(), lsd.data_ptr(), pr.data_ptr(), classes,
+                                         part.data_ptr(), loss.data_ptr(), inv.data_ptr(), batch, classes, None))
+    d2 = torch.full((batch, stride), -3.0, dtype=torch.float16, device="cuda")
+    _lib.check(lib.trb200_softmax_ce_bwd(pr.data_ptr(), classes, ld.data_ptr(), sc.data_ptr(), inv.data_ptr(),
+                                         lsd.data_ptr(), d2.data_ptr(), stride, batch, classes, None))
+    torch.cuda.synchronize()
+    assert float((d2[:, classes:] + 3.0).abs().max()) == 0.0
+    assert bool(torch.isfinite(part).all())
+    assert float((d2[:, :classes].float() - dl_bad[1:-1, :classes].float()).abs().max()) < 2e-3
+
+
+def test_loss_counters_belong_to_streams():
+    """The fused kernels finish the loss with a counter kept per (device, stream).  More streams than counters, all in
+    flight at once, still give every call its own loss."""
+    from renaissance_b200 import ops
+    batch, classes = 512, 1000
+    g = torch.Generator(device="cuda").manual_seed(3)
+    sc, lsd = _scalars(1024.0, 0.0)
+    streams = [torch.cuda.Stream() for _ in range(70)]
+    zs = [(torch.randn((batch, classes), generator=g, device="cuda") * (1.0 + 0.02 * i)).half() for i in range(70)]
+    labels = torch.randint(0, classes, (batch,), generator=g, device="cuda", dtype=torch.int32)
+    torch.cuda.synchronize()
+    outs = []
+    for rep in range(2):
+        outs = [ops.softmax_ce_amp_fused(z, labels, sc, lsd, stream=st) for z, st in zip(zs, streams)]
+    torch.cuda.synchronize()
+    rows = torch.arange(batch, device="cuda")
+    for z, o in zip(zs, outs):
+        p_y = torch.softmax(z.float(), dim=1)[rows, labels.long()]
+        ref = float((-torch.log(p_y + 1e-8)).double().mean())
+        assert abs(float(o["loss"]) - ref) < 1e-4
