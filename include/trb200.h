@@ -309,6 +309,51 @@ int trb200_softmax_ce_fused_dtype(const void* logits, int64_t logits_stride, con
                                   int32_t batch, int32_t classes, int32_t dtype, void* stream);
 
 /* ------------------------------------------------------------------------- */
+/* Classifier: fully connected layers of the AMP step.                        */
+/* FC_AMP_FWD / FC_AMP_BWD, src/backend/ops/dtensor/fc_op.cpp:259-480 (cuBLAS  */
+/* GEMMs + the bias kernels of fc_op.cu:20-101), with the ReLU                 */
+/* (relu_op.cu:101-126) and dropout (dropout_op.cu:50-274) that follow an FC   */
+/* layer folded into the bias pass.  The GEMMs run on this library's own       */
+/* tcgen05 kernel for batch-sized GEMMs, which reads x, w and dy in place;     */
+/* in_features and out_features must be multiples of 8.  x [batch][in],        */
+/* w [out][in], y [batch][out]: half, compact; bias and db float, as in the    */
+/* reference.                                                                  */
+/* ------------------------------------------------------------------------- */
+
+/* y = x W^T (+ bias, rounded to half as fc_fwd_bias_add_amp_kernel does), then, if
+ * asked, ReLU and inverted dropout: an element is dropped with probability
+ * dropout_p, kept ones are scaled by 1 / (1 - dropout_p).  The random bits come
+ * from Philox4x32-10 keyed by `seed`, with `offset` as the call's counter (give
+ * every step and layer its own) and the element index: nothing is stored.
+ * bias may be NULL (no bias).  The GEMM is split over in_features; workspace (of
+ * trb200_fc_amp_workspace_bytes(), 16-byte aligned; the same size serves the
+ * layer's backward) holds its float partial sums, which the bias pass adds in
+ * split order. */
+size_t trb200_fc_amp_workspace_bytes(int32_t batch, int32_t in_features, int32_t out_features);
+int trb200_fc_amp_fwd(const void* x, const void* w, const float* bias, void* y,
+                      int32_t batch, int32_t in_features, int32_t out_features,
+                      int32_t relu, float dropout_p, uint64_t seed, uint64_t offset,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* dz = act > 0 ? da * scale : 0 for n half elements, where `act` is the OUTPUT of
+ * trb200_fc_amp_fwd with relu and/or dropout (zero exactly where the ReLU or the
+ * dropout zeroed it) and scale = 1 / (1 - dropout_p).  dz may be da. */
+int trb200_fc_act_bwd(const void* da, const void* act, void* dz, int64_t n, float scale, void* stream);
+
+/* db[o] = sum_b dy[b][o] (float, rows added in a fixed order; NULL: not computed),
+ * dW = dy^T x (half, [out][in]), dx = dy W (half; NULL: not computed).  `act` (may
+ * be NULL) is the layer's INPUT as the previous layer's trb200_fc_amp_fwd wrote it
+ * with relu / dropout: dx then also carries that activation's backward,
+ * dx = act > 0 ? dx * act_scale : 0 (trb200_fc_act_bwd folded in).  The three run
+ * on `stream` in that order.  When the data gradient has few output tiles its GEMM
+ * is split over out_features and needs the workspace of
+ * trb200_fc_amp_workspace_bytes() for float partial sums (added in split order). */
+int trb200_fc_amp_bwd(const void* dy, const void* w, const void* x, void* dx, void* dw, float* db,
+                      const void* act, float act_scale,
+                      int32_t batch, int32_t in_features, int32_t out_features,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------- */
 /* Kernels either side of the gradient all-reduce (the collective itself is   */
 /* NCCL, issued by the host side).                                            */
 /* ------------------------------------------------------------------------- */

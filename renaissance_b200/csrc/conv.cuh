@@ -53,6 +53,16 @@ int stem_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* d
 int stem_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, void* ws, size_t ws_bytes,
                cudaStream_t st);
 
+// conv_igemm_sm100.cu (gemm_skinny_sm100.cuh): the three GEMMs of a fully connected layer, operands read in place
+bool fc_gemm_supports(int batch, int in_f, int out_f);
+size_t fc_gemm_fwd_partial_bytes(int batch, int in_f, int out_f);
+int fc_gemm_fwd(const void* x, const void* w, float* partial, int batch, int in_f, int out_f, int* splits,
+                cudaStream_t st);
+size_t fc_gemm_dgrad_partial_bytes(int batch, int in_f, int out_f);
+int fc_gemm_dgrad(const void* dy, const void* w, void* dx, float* partial, int batch, int in_f, int out_f, int* splits,
+                  cudaStream_t st);
+int fc_gemm_wgrad(const void* dy, const void* x, void* dw, int batch, int in_f, int out_f, cudaStream_t st);
+
 int validate_conv_desc(const trb200_conv_desc* d, const char* who);
 
 }  // namespace trb

@@ -1174,6 +1174,8 @@ inline bool wgrad_use_unitn(const trb200_conv_desc& d) {
     return d.r == 3 && wgrad_unitn_supports(d) && d.k <= TRB200_UNITN_MAX_K;
 }
 
+#include "gemm_skinny_sm100.cuh"
+
 // 64 -> 64 channels: the kernel that reads all nine taps from one halo copy (development builds can switch it off)
 inline bool wgrad_use_halo(const trb200_conv_desc& d) {
 #ifdef TRB200_NO_WGRAD_HALO
@@ -1360,6 +1362,103 @@ int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* 
     if (wgrad_use_halo(d)) return wgrad_halo_run(d, dy, x, dw, static_cast<float*>(ws), st);
     if (wgrad_use_unitn(d)) return wgrad_unitn_run(d, dy, x, dw, static_cast<float*>(ws), st);
     return wgrad_run(d, igemm_taps(d), dy, x, dw, static_cast<float*>(ws), st);
+}
+
+// ------------------------------------------------------------------ classifier GEMMs (gemm_skinny_sm100.cuh)
+static bool fc_dims_ok(int batch, int in_f, int out_f) {
+    return batch > 0 && in_f > 0 && out_f > 0 && in_f % 8 == 0 && out_f % 8 == 0;
+}
+
+bool fc_gemm_supports(int batch, int in_f, int out_f) { return fc_dims_ok(batch, in_f, out_f); }
+
+// k splits of a GEMM with `tiles` output tiles and `k_steps` stages of k: enough work items to fill the GPU, at
+// least 8 stages each
+static int fc_splits(int tiles, int k_steps) {
+    int splits = sm_count() / tiles;
+    if (splits > k_steps / 8) splits = k_steps / 8;
+    return splits < 1 ? 1 : splits;
+}
+
+static int fc_fwd_splits(int batch, int in_f, int out_f) {
+    return fc_splits(((batch + 255) / 256) * ((out_f + kSkN - 1) / kSkN), (in_f + 63) / 64);
+}
+
+static int fc_dgrad_splits(int batch, int in_f, int out_f) {
+    return fc_splits(((batch + 255) / 256) * ((in_f + kSkN - 1) / kSkN), (out_f + 63) / 64);
+}
+
+size_t fc_gemm_fwd_partial_bytes(int batch, int in_f, int out_f) {
+    return (size_t)fc_fwd_splits(batch, in_f, out_f) * (size_t)batch * (size_t)out_f * sizeof(float);
+}
+
+// 0 when the data-gradient GEMM writes its half output directly
+size_t fc_gemm_dgrad_partial_bytes(int batch, int in_f, int out_f) {
+    const int splits = fc_dgrad_splits(batch, in_f, out_f);
+    return splits == 1 ? 0 : (size_t)splits * (size_t)batch * (size_t)in_f * sizeof(float);
+}
+
+// partial[split][b][o] (float) = x[b][k range of the split] . w[o][same]; *splits receives the split count
+int fc_gemm_fwd(const void* x, const void* w, float* partial, int batch, int in_f, int out_f, int* splits,
+                cudaStream_t st) {
+    TRB_REQUIRE(fc_dims_ok(batch, in_f, out_f), TRB200_ERR_UNSUPPORTED, "fc: in_features=%d, out_features=%d must be multiples of 8", in_f, out_f);
+    CUtensorMap ta, tb;
+    int rc = make_matrix_tmap(&ta, x, batch, in_f, in_f, 128, "fc x");
+    if (rc) return rc;
+    rc = make_matrix_tmap(&tb, w, out_f, in_f, in_f, 256, "fc w");
+    if (rc) return rc;
+    SkinnyParams p;
+    p.m_real = batch; p.n_real = out_f;
+    p.k_steps = (in_f + 63) / 64;
+    p.m_tiles = (batch + 255) / 256; p.n_tiles = (out_f + kSkN - 1) / kSkN;
+    p.splits = fc_fwd_splits(batch, in_f, out_f);
+    p.ldd = out_f; p.d = partial; p.split_stride = (int64_t)batch * out_f; p.bf16 = 0;
+    *splits = p.splits;
+    return launch_skinny<false, false, 2, true>(ta, tb, ta, p, st);
+}
+
+// dx[b][i] = dy[b][:] . w[:][i]: half into dx when *splits comes back 1, else float partials [split][b][i]
+int fc_gemm_dgrad(const void* dy, const void* w, void* dx, float* partial, int batch, int in_f, int out_f, int* splits,
+                  cudaStream_t st) {
+    TRB_REQUIRE(fc_dims_ok(batch, in_f, out_f), TRB200_ERR_UNSUPPORTED, "fc: in_features=%d, out_features=%d must be multiples of 8", in_f, out_f);
+    CUtensorMap ta, tb, td;
+    int rc = make_matrix_tmap(&ta, dy, batch, out_f, out_f, 128, "fc dy");
+    if (rc) return rc;
+    rc = make_matrix_tmap(&tb, w, out_f, in_f, in_f, 64, "fc w (columns)");
+    if (rc) return rc;
+    rc = make_matrix_tmap(&td, dx, batch, in_f, in_f, 128, "fc dx");
+    if (rc) return rc;
+    SkinnyParams p;
+    p.m_real = batch; p.n_real = in_f;
+    p.k_steps = (out_f + 63) / 64;
+    p.m_tiles = (batch + 255) / 256; p.n_tiles = (in_f + kSkN - 1) / kSkN;
+    p.splits = fc_dgrad_splits(batch, in_f, out_f);
+    p.ldd = in_f; p.bf16 = 0;
+    *splits = p.splits;
+    if (p.splits == 1) {
+        p.d = dx; p.split_stride = 0;
+        return launch_skinny<false, true, 2, false>(ta, tb, td, p, st);
+    }
+    p.d = partial; p.split_stride = (int64_t)batch * in_f;
+    return launch_skinny<false, true, 2, true>(ta, tb, td, p, st);
+}
+
+// dw[o][i] = dy[:][o] . x[:][i]
+int fc_gemm_wgrad(const void* dy, const void* x, void* dw, int batch, int in_f, int out_f, cudaStream_t st) {
+    TRB_REQUIRE(fc_dims_ok(batch, in_f, out_f), TRB200_ERR_UNSUPPORTED, "fc: in_features=%d, out_features=%d must be multiples of 8", in_f, out_f);
+    CUtensorMap ta, tb, td;
+    int rc = make_matrix_tmap(&ta, dy, batch, out_f, out_f, 64, "fc dy (columns)");
+    if (rc) return rc;
+    rc = make_matrix_tmap(&tb, x, batch, in_f, in_f, 64, "fc x (columns)");
+    if (rc) return rc;
+    rc = make_matrix_tmap(&td, dw, out_f, in_f, in_f, 128, "fc dw");
+    if (rc) return rc;
+    SkinnyParams p;
+    p.m_real = out_f; p.n_real = in_f;
+    p.k_steps = (batch + 63) / 64;
+    p.m_tiles = (out_f + 127) / 128; p.n_tiles = (in_f + kSkN - 1) / kSkN;
+    p.splits = 1;
+    p.ldd = in_f; p.d = dw; p.split_stride = 0; p.bf16 = 0;
+    return launch_skinny<true, true, 1, false>(ta, tb, td, p, st);
 }
 
 // ------------------------------------------------------------------ self-test of the give-up path

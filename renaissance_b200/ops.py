@@ -559,7 +559,10 @@ def softmax_ce_amp_fused(logits, labels, scaling, label_smoothing, want_probs=Fa
     lib = _lib.load()
     if logits.dtype not in DTYPE_CODE:
         raise TypeError(f"logits: float16 or bfloat16 expected, got {logits.dtype}")
-    _need(logits, logits.dtype, "logits", 2)
+    if not (isinstance(logits, torch.Tensor) and logits.is_cuda and logits.dim() == 2 and logits.stride(1) == 1):
+        raise ValueError("logits: a 2-D CUDA tensor with unit column stride expected (rows may be padded)")
+    if dlogits is not None and not (dlogits.dim() == 2 and dlogits.stride(1) == 1 and dlogits.dtype == logits.dtype):
+        raise ValueError("dlogits: a 2-D tensor of the logits' type with unit column stride expected")
     _need(labels, torch.int32, "labels", 1)
     b, k = logits.shape
     dev = logits.device
@@ -582,6 +585,58 @@ def softmax_ce_amp_fused(logits, labels, scaling, label_smoothing, want_probs=Fa
                                       _ptr(dlogits), dlogits.stride(0), _ptr(part), _ptr(loss), _ptr(inv),
                                       b, k, _stream(stream)))
     return dict(loss=loss, inv_scaling=inv, probs=probs, loss_partial=part, dlogits=dlogits)
+
+
+# --------------------------------------------------------------------------- classifier
+
+def fc_amp_fwd(x, w, bias, y=None, relu=False, dropout_p=0.0, seed=0, offset=0, workspace=None, stream=None):
+    """y = act(x W^T + bias) (FC_AMP_FWD + ReLU + dropout, fc_op.cpp:259-347).  x [batch, in], w [out, in] half,
+    bias float."""
+    _need(x, torch.float16, "x", 2)
+    _need(w, torch.float16, "w", 2)
+    if bias is not None:
+        _need(bias, torch.float32, "bias", 1)
+    b, i_f = x.shape
+    o_f = w.shape[0]
+    if w.shape[1] != i_f:
+        raise ValueError("fc_amp_fwd: w must be [out, in]")
+    if y is None:
+        y = torch.empty((b, o_f), dtype=torch.float16, device=x.device)
+    lib = _lib.load()
+    ws = (workspace or default_workspace()).ensure(lib.trb200_fc_amp_workspace_bytes(b, i_f, o_f))
+    check(lib.trb200_fc_amp_fwd(_ptr(x), _ptr(w), _ptr(bias), _ptr(y), b, i_f, o_f, 1 if relu else 0,
+                                float(dropout_p), int(seed), int(offset), _ptr(ws), ws.numel(), _stream(stream)))
+    return y
+
+
+def fc_act_bwd(da, act, dz=None, scale=1.0, stream=None):
+    """dz = act > 0 ? da * scale : 0 (ReLU + dropout backward from the layer's own output)."""
+    _need(da, torch.float16, "da")
+    _need(act, torch.float16, "act")
+    dz = torch.empty_like(da) if dz is None else dz
+    check(_lib.load().trb200_fc_act_bwd(_ptr(da), _ptr(act), _ptr(dz), da.numel(), float(scale), _stream(stream)))
+    return dz
+
+
+def fc_amp_bwd(dy, w, x, dx=None, dw=None, db=None, want_dx=True, act=None, act_scale=1.0, workspace=None, stream=None):
+    """(dx, dw, db) of an FC layer (FC_AMP_BWD, fc_op.cpp:349-480): dw half [out, in], db float [out].  With act =
+    x as the previous layer's forward wrote it (ReLU / dropout applied), dx also carries that activation's backward."""
+    lib = _lib.load()
+    _need(dy, torch.float16, "dy", 2)
+    _need(w, torch.float16, "w", 2)
+    _need(x, torch.float16, "x", 2)
+    b, o_f = dy.shape
+    i_f = x.shape[1]
+    if dw is None:
+        dw = torch.empty((o_f, i_f), dtype=torch.float16, device=dy.device)
+    if db is None:
+        db = torch.empty(o_f, dtype=torch.float32, device=dy.device)
+    if dx is None and want_dx:
+        dx = torch.empty((b, i_f), dtype=torch.float16, device=dy.device)
+    ws = (workspace or default_workspace()).ensure(lib.trb200_fc_amp_workspace_bytes(b, i_f, o_f))
+    check(lib.trb200_fc_amp_bwd(_ptr(dy), _ptr(w), _ptr(x), _ptr(dx), _ptr(dw), _ptr(db), _ptr(act), float(act_scale),
+                                b, i_f, o_f, _ptr(ws), ws.numel(), _stream(stream)))
+    return dx, dw, db
 
 
 # --------------------------------------------------------------------------- all-reduce side

@@ -14,11 +14,12 @@ reference's ``DeepLearningTask::run_train_epoch_gpu`` plays
               per bucket overlapped with the rest of backward, non-finite check,
               SGD with momentum on float master weights + half working copy
 
-Everything on the named hot path (block backward, softmax-CE) and the convolution
-forward, BN forward, pooling, casts and the optimizer run in libtrb200.so.  The
-three FC GEMMs (cuBLAS through torch.mm, as the reference uses cublasGemmEx,
-src/backend/ops/dtensor/fc_op.cpp:259-480) and dropout use library kernels through
-torch.
+Every kernel of the step runs in libtrb200.so: the named hot path (block backward,
+softmax-CE), the convolution forward, BN forward, pooling, casts, the optimizer, and the
+classifier (the three FC layers on the library's own tensor-core GEMMs with bias, ReLU and
+dropout folded into one pass; the reference uses cublasGemmEx there,
+src/backend/ops/dtensor/fc_op.cpp:259-480).  torch supplies device memory, streams and
+torch.distributed only.
 
 Gradients follow the reference's in-place rule: dX of a block overwrites the block's
 input buffer (src/graph/compiler.cpp:1390-1396).
@@ -43,7 +44,8 @@ class ParamSlot:
     shape: tuple
     offset: int          # element offset in the flat buffers
     numel: int
-    half_grad: bool      # gradient produced in half (weights) or float (BN)
+    half_grad: bool      # gradient produced in half (weights) or float (BN vectors, FC biases)
+    stored: int = 0      # elements the slot holds (>= numel: an FC matrix keeps zero rows up to a GEMM-friendly count)
 
 
 @dataclass
@@ -63,6 +65,11 @@ def _align(n, a=64):
     return (n + a - 1) // a * a
 
 
+def _fc_width(n):
+    """Rows an FC weight matrix is stored with: the tensor-core GEMMs take 64, 128 or a multiple of 256."""
+    return 64 if n <= 64 else (128 if n <= 128 else _align(n, 256))
+
+
 class Vgg16BnTrainer:
     def __init__(self, batch=256, image=224, classes=1000, lr=0.01, momentum=0.9, weight_decay=5e-4,
                  loss_scale=1024.0, label_smoothing=0.0, bucket_mb=25.0, seed=0, device=None,
@@ -71,6 +78,8 @@ class Vgg16BnTrainer:
         self.batch, self.image, self.classes = batch, image, classes
         self.lr, self.beta, self.wd = lr, momentum, weight_decay
         self.dropout = dropout
+        self.seed = seed
+        self.steps_done = 0
         self.pg = process_group
         self.world = dist.get_world_size(process_group) if (dist.is_available() and dist.is_initialized()) else 1
 
@@ -90,24 +99,31 @@ class Vgg16BnTrainer:
         # ---- flat parameter space in BACKWARD completion order: fc3, fc2, fc1, conv13 .. conv1, then all BN vectors
         slots, off = [], 0
 
-        def add(name, shape, half_grad):
+        def add(name, shape, half_grad, rows_stored=None):
+            """`rows_stored` > shape[0]: the slot holds that many rows (the extra ones stay zero)."""
             nonlocal off
             n = int(math.prod(shape))
-            s = ParamSlot(name, tuple(shape), off, n, half_grad)
-            off += _align(n)
+            stored = n if rows_stored is None else n // shape[0] * rows_stored
+            s = ParamSlot(name, tuple(shape), off, n, half_grad, stored)
+            off += _align(stored)
             slots.append(s)
             return s
 
+        # an FC layer's weight is stored with a row count the tensor-core GEMMs take (1000 classes -> 1024 rows,
+        # the extra rows zero); its bias and bias gradient are float (fc_op.cpp:281-347) and sit with the BN vectors
+        self.classes_pad = _fc_width(classes)
         self.fc = []
         for j in reversed(range(3)):
             i_f, o_f = self.fc_dims[j]
-            self.fc.insert(0, dict(w=add(f"fc{j}.w", (o_f, i_f), True), b=add(f"fc{j}.b", (o_f,), True)))
+            self.fc.insert(0, dict(w=add(f"fc{j}.w", (o_f, i_f), True, rows_stored=_fc_width(o_f)), out_pad=_fc_width(o_f)))
         for L in reversed(self.convs):
             L.w = add(f"conv{L.idx}.w", (L.k, 3, 3, L.c), True)
         self.half_numel = off                 # everything before this offset has half gradients
         for L in reversed(self.convs):
             L.gamma = add(f"bn{L.idx}.gamma", (L.k,), False)
             L.beta = add(f"bn{L.idx}.beta", (L.k,), False)
+        for j, f in enumerate(self.fc):
+            f["b"] = add(f"fc{j}.b", (self.fc_dims[j][1],), False, rows_stored=f["out_pad"])
         self.total = off
         self.slots = slots
 
@@ -151,8 +167,14 @@ class Vgg16BnTrainer:
         self.bn_scratch = torch.empty(big, dtype=torch.float16, device=d)
         self.images = [torch.zeros((n, image, image, 4), dtype=torch.float16, device=d) for _ in range(2)]
         self.labels = [torch.zeros(n, dtype=torch.int32, device=d) for _ in range(2)]
-        self.logits = torch.empty((n, classes), dtype=torch.float16, device=d)
-        self.dlogits = torch.empty((n, classes), dtype=torch.float16, device=d)
+        # logits and their gradient live in rows of classes_pad elements (the row stride the softmax kernels take);
+        # the padding columns of d_logits stay zero, so the padded rows of the last layer's dW are zero too
+        self.logits_rows = torch.zeros((n, self.classes_pad), dtype=torch.float16, device=d)
+        self.dlogits_rows = torch.zeros((n, self.classes_pad), dtype=torch.float16, device=d)
+        self.logits = self.logits_rows[:, :classes]
+        self.dlogits = self.dlogits_rows[:, :classes]
+        self.fc_out = [torch.empty((n, self.fc[j]["out_pad"]), dtype=torch.float16, device=d) for j in range(2)]
+        self.fc_dx = [torch.empty((n, self.fc_dims[j][0]), dtype=torch.float16, device=d) for j in range(3)]
         self.loss_partial = torch.empty(n, dtype=torch.float32, device=d)
         self.loss = torch.zeros(1, dtype=torch.float32, device=d)
         self.inv_scaling = torch.zeros(1, dtype=torch.float32, device=d)
@@ -170,6 +192,11 @@ class Vgg16BnTrainer:
     # ------------------------------------------------------------------ parameters
     def view(self, buf, slot: ParamSlot):
         return buf[slot.offset:slot.offset + slot.numel].view(slot.shape)
+
+    def stored(self, buf, slot: ParamSlot):
+        """The slot with the rows it is stored with (an FC matrix padded to a GEMM-friendly row count)."""
+        rows = slot.stored // (slot.numel // slot.shape[0])
+        return buf[slot.offset:slot.offset + slot.stored].view((rows,) + tuple(slot.shape[1:]))
 
     def _init_params(self, seed):
         g = torch.Generator(device=self.dev).manual_seed(seed)
@@ -222,6 +249,7 @@ class Vgg16BnTrainer:
         self._forward(self.images[slot], self.labels[slot])
         self._backward(self.images[slot], self.labels[slot])
         self.slot_free[slot].record(cur)
+        self.steps_done += 1
         return self.loss
 
     def _forward(self, images, labels):
@@ -253,24 +281,18 @@ class Vgg16BnTrainer:
                 ops.bn_apply_relu_mask(b["conv_out"], b["eq_scale"], b["eq_bias"], relu_out=b["relu_out"],
                                        mask_bits=b["mask"])
                 x = b["relu_out"]
-        # classifier (cuBLAS): flatten is a view of the NHWC pool output
+        # classifier: flatten is a view of the NHWC pool output; bias, ReLU and dropout ride on the GEMM's output pass
         a = x.reshape(n, -1)
         self.fc_in = [a]
-        self.fc_keep = []
         for j, f in enumerate(self.fc):
-            z = torch.addmm(self.view(self.w16, f["b"]), a, self.view(self.w16, f["w"]).t())
-            if j < 2:
-                z = torch.relu_(z)
-                if self.dropout > 0:
-                    keep = (torch.rand_like(z) >= self.dropout).to(z.dtype).mul_(1.0 / (1.0 - self.dropout))
-                    z = z * keep
-                    self.fc_keep.append(keep)
-                else:
-                    self.fc_keep.append(None)
-                self.fc_in.append(z)
-                a = z
-            else:
-                self.logits.copy_(z)
+            last = j == 2
+            y = self.logits_rows if last else self.fc_out[j]
+            ops.fc_amp_fwd(a, self.stored(self.w16, f["w"]), self.stored(self.w32, f["b"]), y=y, relu=not last,
+                           dropout_p=0.0 if last else self.dropout, seed=self.seed,
+                           offset=self.steps_done * 2 + j, workspace=self.ws)
+            if not last:
+                self.fc_in.append(y)
+                a = y
         # loss + d_logits in one kernel (the FWD and BWD softmax-CE nodes fused)
         ops_out = ops.softmax_ce_amp_fused(self.logits, labels, self.scaling, self.label_smoothing,
                                            dlogits=self.dlogits)
@@ -279,20 +301,16 @@ class Vgg16BnTrainer:
     def _backward(self, images, labels):
         n = self.batch
         self.buckets.begin_step()
-        # ---- classifier
-        dz = self.dlogits
+        # ---- classifier: db, dW, dx of each layer, then ReLU + dropout backward from the layer input's own values
+        dz = self.dlogits_rows
+        keep_scale = 1.0 / (1.0 - self.dropout)
         for j in reversed(range(3)):
             f = self.fc[j]
-            a = self.fc_in[j]
-            torch.mm(dz.t(), a, out=self.view(self.g16, f["w"]))
-            torch.sum(dz, dim=0, out=self.view(self.g16, f["b"]))
-            da = torch.mm(dz, self.view(self.w16, f["w"]))
-            if j > 0:
-                if self.fc_keep[j - 1] is not None:
-                    da = da * self.fc_keep[j - 1]
-                dz = da * (self.fc_in[j] > 0).to(da.dtype)        # ReLU mask of the FC activation
-            else:
-                dz = da
+            # the layer's input carries the ReLU + dropout of the layer below: its backward rides on the dx pass
+            ops.fc_amp_bwd(dz, self.stored(self.w16, f["w"]), self.fc_in[j], dx=self.fc_dx[j],
+                           dw=self.stored(self.g16, f["w"]), db=self.stored(self.g32, f["b"]),
+                           act=self.fc_in[j] if j > 0 else None, act_scale=keep_scale, workspace=self.ws)
+            dz = self.fc_dx[j]
             self.buckets.mark_ready(self._end_of(f))
         # ---- feature extractor, last block first
         grad = dz.view(n, self.feat_hw, self.feat_hw, self.convs[-1].k)
@@ -321,5 +339,5 @@ class Vgg16BnTrainer:
 
     def _end_of(self, group):
         """End offset (exclusive) of the flat range whose half gradients are complete once `group` is done."""
-        last = group["b"] if "b" in group else group["w"]
-        return last.offset + _align(last.numel)
+        last = group["w"]
+        return last.offset + _align(getattr(last, "stored", last.numel))
