@@ -172,6 +172,7 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     tr.timing = []
+    tr.timing_bwd = []
     launches0 = ops.kernel_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -184,7 +185,9 @@ def run_ours(args):
     launches = ops.kernel_launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     roof_events = tr.timing
+    bwd_events = tr.timing_bwd
     tr.timing = None
+    tr.timing_bwd = None
     ops.device_status()
     loss_value = float(loss.item())
     ms_per_step = ms_total / args.steps
@@ -206,6 +209,34 @@ def run_ours(args):
                     traffic=round(ROOFLINE_TRAFFIC_RATIO * alg_bytes / n_l),
                     traffic_note="average algorithmic bytes per launch x 0.79 (ncu DRAM/algorithmic ratio)")
 
+    # ---------------- the named hot path inside the same timed region: every block backward's three stages, bracketed
+    # by CUDA events that trb200_cbr_bwd records on the launching stream(s) before the BN stage and after the BN,
+    # weight-gradient and data-gradient stages
+    hot = dict(bn=[0.0, 0.0], wgrad=[0.0, 0.0], dgrad=[0.0, 0.0])      # [ms, bytes or flop]
+    for L, ev in bwd_events:
+        e_bn = L.k * batch * L.h * L.h
+        hot["bn"][0] += ev[0].elapsed_time(ev[1])
+        # two sweeps over dy (pooled: a quarter of it + the argmax byte), x, mask; one write of dconv
+        hot["bn"][1] += (10.25 * e_bn if not L.pool_after else (2 * (2 + 0.125) + 2) * e_bn + 2 * (2 + 1) * e_bn / 4)
+        hot["wgrad"][0] += ev[1].elapsed_time(ev[2])
+        hot["wgrad"][1] += 2.0 * batch * L.h * L.h * L.k * 9 * (3 if L.idx == 0 else L.c)
+        if L.idx > 0:
+            hot["dgrad"][0] += ev[2].elapsed_time(ev[3])
+            hot["dgrad"][1] += 2.0 * batch * L.h * L.h * L.k * 9 * L.c
+    steps_f = float(args.steps)
+    roofline_hot_path = dict(
+        note="per step, summed over the 13 block backwards, CUDA events inside the timed region",
+        bnrelu_bwd=dict(bound="hbm", ms=round(hot["bn"][0] / steps_f, 4), algorithmic_gb=round(hot["bn"][1] / steps_f / 1e9, 3),
+                        achieved=round(hot["bn"][1] / (hot["bn"][0] / 1e3) / 1e9, 1), peak=peaks["hbm_gbs"], unit="GB/s",
+                        frac=round(hot["bn"][1] / (hot["bn"][0] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)),
+        wgrad=dict(bound="tensor", ms=round(hot["wgrad"][0] / steps_f, 4), tflop=round(hot["wgrad"][1] / steps_f / 1e12, 3),
+                   achieved=round(hot["wgrad"][1] / (hot["wgrad"][0] / 1e3) / 1e12, 1), peak=peaks["tflops"], unit="TFLOP/s",
+                   frac=round(hot["wgrad"][1] / (hot["wgrad"][0] / 1e3) / 1e12 / peaks["tflops"], 4)),
+        dgrad=dict(bound="tensor", ms=round(hot["dgrad"][0] / steps_f, 4), tflop=round(hot["dgrad"][1] / steps_f / 1e12, 3),
+                   achieved=round(hot["dgrad"][1] / (hot["dgrad"][0] / 1e3) / 1e12, 1), peak=peaks["tflops"], unit="TFLOP/s",
+                   frac=round(hot["dgrad"][1] / (hot["dgrad"][0] / 1e3) / 1e12 / peaks["tflops"], 4)),
+        peak_source=peaks["source"])
+
     # ---------------- end to end: host buffers, H2D of every step's batch and D2H of its loss inside the region
     barrier()
     t0 = time.perf_counter()
@@ -222,6 +253,54 @@ def run_ours(args):
     e2e = dict(value=round(world * batch * args.steps / e2e_s, 1), unit=UNIT, h2d_bytes_per_step=h2d,
                d2h_bytes_per_step=4)
 
+    # ---------------- the device-resident region once more, after the end-to-end one: the two regions run under a
+    # power-cap clock that drifts, so `value` and `e2e` are comparable only to the spread between these two
+    barrier()
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    r0.record()
+    for i in range(args.steps):
+        tr.step(i & 1)
+    r1.record()
+    barrier()
+    value_again = world * batch * args.steps / (max_over_ranks(r0.elapsed_time(r1)) / 1e3)
+
+    # ---------------- multi-GPU diagnostics (outside the reported regions): where the all-reduce costs time
+    comm = None
+    if world > 1:
+        def region(mode):
+            tr.buckets.mode = mode
+            for i in range(2):
+                tr.step(i & 1)
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for i in range(args.steps):
+                tr.step(i & 1)
+            b.record()
+            barrier()
+            tr.buckets.mode = "overlap"
+            return max_over_ranks(a.elapsed_time(b)) / args.steps
+        ms_none = region("skip")          # no all-reduce at all: the step's compute alone (the ranks' weights drift apart)
+        ms_after = region("after")        # every bucket all-reduced only after backward has finished: nothing overlaps
+        tr.sync_weights_from_rank0()      # the skip region let the ranks drift: make them equal again
+        comm = dict(step_ms_no_allreduce=round(ms_none, 3), step_ms_allreduce_after_backward=round(ms_after, 3),
+                    comm_exposed_ms=round(ms_per_step - ms_none, 3),
+                    comm_serial_ms=round(ms_after - ms_none, 3),
+                    note="comm_exposed = overlapped step - step without all-reduce (what the overlap fails to hide, plus "
+                         "what NCCL's CTAs take from the compute kernels); comm_serial = the all-reduce's own time")
+        # ranks must hold identical master weights after identical updates of all-reduced gradients
+        for i in range(2):
+            tr.step(i & 1)
+        barrier()
+        chk = torch.stack([tr.w32.double().sum(), tr.w32.double().abs().sum()])
+        lo, hi = chk.clone(), chk.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        if not bool(torch.equal(lo, hi)):
+            raise SystemExit(f"rank {rank}: master weights differ between ranks after the all-reduced update "
+                             f"(checksum min {lo.tolist()} max {hi.tolist()})")
+        comm["weights_identical_on_all_ranks"] = True
+
     # ---------------- CPU baseline beside it (rank 0, single GPU run only): the oracle's step on host cores
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -237,7 +316,10 @@ def run_ours(args):
                                 l2="activations (>15 GB per step) far exceed the 126 MB L2; no flush needed",
                                 conv_tflop_per_step_per_gpu=round(conv_flops_per_step(batch) / 1e12, 2),
                                 loss=round(loss_value, 4)),
-                    clocks=clocks, e2e=e2e, gpu_launches=int(launches // args.steps), roofline=roofline)
+                    clocks=clocks, e2e=e2e, gpu_launches=int(launches // args.steps), roofline=roofline,
+                    roofline_hot_path=roofline_hot_path, value_second_region=round(value_again, 1))
+        if comm is not None:
+            line["comm"] = comm
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)

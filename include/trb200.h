@@ -244,6 +244,10 @@ typedef struct trb200_cbr_bwd_args {
                                   gradient of the POOLED output [n,oh/2,ow/2,k]; this is the pool's
                                   argmax tensor (trb200_maxpool2x2_fwd layout).  NULL = dy is the
                                   gradient of the block's own output, as in the reference. */
+    void* ev_time[4];          /* optional (all NULL = off; never while capturing): timing events recorded
+                                  before the BN stage on stream_bn and after the BN, wgrad and dgrad stages
+                                  on their streams (the last one stays unrecorded in the first-layer
+                                  variant), so that a caller can read each stage's device time. */
 } trb200_cbr_bwd_args;
 
 size_t trb200_cbr_bwd_workspace_bytes(const trb200_conv_desc* d, int first_layer);

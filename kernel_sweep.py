@@ -1,10 +1,10 @@
 """Per-kernel roofline sweep of the hot-path kernels on one GPU.
 
-    python -m renaissance_b200.kernel_sweep                 # everything, JSON lines
-    python -m renaissance_b200.kernel_sweep --only block    # BASELINE.json configuration 2 (one block backward)
-    python -m renaissance_b200.kernel_sweep --only bnrelu --quick
-    python -m renaissance_b200.kernel_sweep --only conv --quick --batch 64 --shape 56,256,256 --what fprop_stats
-    python -m renaissance_b200.kernel_sweep --only resnet50 --cudnn     # ResNet-50 conv shapes, bfloat16
+    python kernel_sweep.py                 # everything, JSON lines
+    python kernel_sweep.py --only block    # BASELINE.json configuration 2 (one block backward)
+    python kernel_sweep.py --only bnrelu --quick
+    python kernel_sweep.py --only conv --quick --batch 64 --shape 56,256,256 --what fprop_stats
+    python kernel_sweep.py --only resnet50 --cudnn     # ResNet-50 conv shapes, bfloat16
 
 Covers BASELINE.json's config 2 (Conv3x3 C=K=64 + BN + ReLU backward at N=256, 56x56)
 and config 5 (BN+ReLU backward over N*H*W x C, fused softmax-CE over N x C), plus the
@@ -26,11 +26,15 @@ import json
 import os
 import statistics
 
+import sys
+
 import torch
 
-from . import ops
+_ROOT = os.path.dirname(os.path.abspath(__file__))
+if _ROOT not in sys.path:
+    sys.path.insert(0, _ROOT)
 
-_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+from renaissance_b200 import ops  # noqa: E402
 
 
 def peaks():
@@ -68,7 +72,7 @@ def emit(**kw):
 
 
 def _library(t, build):
-    """Times a cuDNN graph of the reference's path (renaissance_b200.cudnn_reference); {} when not asked for."""
+    """Times a cuDNN graph of the reference's path (cudnn_reference.py); {} when not asked for."""
     if not WITH_CUDNN:
         return {}
     try:
@@ -101,7 +105,7 @@ def bnrelu_point(t, m, c, hbm, src):
     byt = 10.25 * m * c + 20 * c
 
     def build():
-        from . import cudnn_reference as cr
+        import cudnn_reference as cr
         dg, db = torch.empty(c, device="cuda"), torch.empty(c, device="cuda")
         return cr.bnrelu_bwd(dy, bits, x, gamma, mean, inv, torch.empty_like(dy), dg, db, nhw=_nhw(m))
 
@@ -150,7 +154,7 @@ def conv_point(t, n, h, c, k, what, tc, src, r=3, pad=1, stride=1, dtype=torch.f
     ops.device_status()
 
     def build():
-        from . import cudnn_reference as cr
+        import cudnn_reference as cr
         if c < 8:
             raise RuntimeError("the reference pads the first layer to 4 channels; cuDNN tensor-core graphs need C % 8 == 0")
         if what == "dgrad":

@@ -46,6 +46,7 @@ class CbrBwdArgs(C.Structure):
         ("stream_bn", C.c_void_p), ("stream_wgrad", C.c_void_p), ("stream_dgrad", C.c_void_p),
         ("ev_bn", C.c_void_p), ("ev_wgrad", C.c_void_p), ("ev_dgrad", C.c_void_p),
         ("pool_argmax", C.c_void_p),
+        ("ev_time", C.c_void_p * 4),
     ]
 
 

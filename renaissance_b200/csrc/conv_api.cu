@@ -237,6 +237,7 @@ extern "C" int trb200_cbr_bwd(const trb200_cbr_bwd_args* a) {
     unsigned char* wsp = static_cast<unsigned char*>(a->workspace);
     const int oh = trb::conv_out(d.h, d.pad_h, d.r, d.stride_h), ow = trb::conv_out(d.w, d.pad_w, d.s, d.stride_w);
 
+    if (a->ev_time[0]) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_time[0]), s_bn));
     // 1) BN + ReLU backward: dconv -> bn_scratch, dgamma, dbeta
     TRB_REQUIRE(!a->pool_argmax || d.dtype == TRB200_DTYPE_F16, TRB200_ERR_UNSUPPORTED,
                 "cbr_bwd: the pooled variant is built for half tensors only");
@@ -250,12 +251,14 @@ extern "C" int trb200_cbr_bwd(const trb200_cbr_bwd_args* a) {
                                     ws.bn_bytes, s_bn, d.dtype);
     if (rc) return rc;
     if (a->ev_bn) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_bn), s_bn));
+    if (a->ev_time[1]) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_time[1]), s_bn));
 
     // 2) wgrad(dconv, x) -> dw
     if (s_wg != s_bn) TRB_CUDA_TRY(cudaStreamWaitEvent(s_wg, trb::as_event(a->ev_bn), 0));
     rc = trb200_conv_wgrad(&d, a->bn_scratch, a->x, a->dw, wsp + ws.wg_off, ws.wg_bytes, s_wg);
     if (rc) return rc;
     if (a->ev_wgrad) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_wgrad), s_wg));
+    if (a->ev_time[2]) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_time[2]), s_wg));
 
     // 3) dgrad(dconv, w) -> dx, after wgrad has read x (dx is x's buffer)
     if (!first) {
@@ -263,6 +266,7 @@ extern "C" int trb200_cbr_bwd(const trb200_cbr_bwd_args* a) {
         rc = trb200_conv_dgrad(&d, a->bn_scratch, a->w, a->dx, wsp + ws.dg_off, ws.dg_bytes, s_dg);
         if (rc) return rc;
         if (a->ev_dgrad) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_dgrad), s_dg));
+        if (a->ev_time[3]) TRB_CUDA_TRY(cudaEventRecord(trb::as_event(a->ev_time[3]), s_dg));
     }
 
     // 4) join back onto the BN stream

@@ -37,6 +37,10 @@ class GradientBuckets:
         self.next = 0
         self.works = []
         self.issued = []
+        # "overlap": a bucket is all-reduced as soon as backward has passed it (the product's schedule);
+        # "after": every bucket only once backward has finished; "skip": no all-reduce at all.  The last two exist
+        # for the benchmark's diagnostics of what the collective costs.
+        self.mode = "overlap"
 
     def begin_step(self):
         self.next = 0
@@ -46,6 +50,8 @@ class GradientBuckets:
     def mark_ready(self, upto: int, final: bool = False):
         """Backward has produced every half gradient below element `upto`."""
         inv = 1.0 / self.world
+        if self.mode == "after" and not final:
+            return
         if final and self.world > 1 and self.half_numel < self.g32.numel():
             self.scale(self.g32[self.half_numel:], inv)         # float-born gradients: mean folded in here
         while self.next < len(self.buckets):
@@ -55,7 +61,7 @@ class GradientBuckets:
             hi = min(b, self.half_numel)
             if a < hi:
                 self.cast(self.g16[a:hi], self.g32[a:hi], inv)
-            if self.world > 1:
+            if self.world > 1 and self.mode != "skip":
                 self.works.append(dist.all_reduce(self.g32[a:b], op=dist.ReduceOp.SUM, group=self.group,
                                                   async_op=True))
             self.issued.append((a, b))

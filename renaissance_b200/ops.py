@@ -340,7 +340,7 @@ class BlockStreams:
 
 def cbr_amp_bwd(g: ConvGeometry, dy, w, gamma, saved_mean, saved_inv_std, mask_bits, x, conv_out,
                 bn_scratch=None, dw=None, first_layer=False, streams: BlockStreams | None = None,
-                workspace=None, stream=None, dgamma=None, dbeta=None, pool_argmax=None):
+                workspace=None, stream=None, dgamma=None, dbeta=None, pool_argmax=None, timing_events=None):
     """CBR_AMP_BWD / CBR_AMP_BWD_FIRST_LAYER.
 
     Node ids of the reference: in [dY, W16, gamma, saved_mean, saved_inv_var, mask, X],
@@ -389,6 +389,11 @@ def cbr_amp_bwd(g: ConvGeometry, dy, w, gamma, saved_mean, saved_inv_std, mask_b
                                                       streams.dgrad.cuda_stream)
         a.ev_bn, a.ev_wgrad, a.ev_dgrad = (streams.ev_bn.cuda_event, streams.ev_wgrad.cuda_event,
                                            streams.ev_dgrad.cuda_event)
+    if timing_events is not None:        # four torch events (enable_timing=True): start, after BN, wgrad, dgrad
+        for i, ev in enumerate(timing_events):
+            if ev is not None and not (first_layer and i == 3):
+                ev.record(torch.cuda.current_stream())      # creates the handle; re-recorded inside the call
+                a.ev_time[i] = ev.cuda_event
     check(lib.trb200_cbr_bwd(C.byref(a)))
     return dict(dx=None if first_layer else x, dw=dw, dgamma=dgamma, dbeta=dbeta, dconv=bn_scratch)
 

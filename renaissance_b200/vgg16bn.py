@@ -183,6 +183,7 @@ class Vgg16BnTrainer:
         self.copy_done = [torch.cuda.Event(), torch.cuda.Event()]
         self.slot_free = [torch.cuda.Event(), torch.cuda.Event()]
         self.timing = None        # list of (start event, stop event, flop, bytes) per forward conv launch when enabled
+        self.timing_bwd = None    # list of (layer, [start, after BN, after wgrad, after dgrad] events) per block backward
         self.debug_hook = None    # called as hook(layer, dy, x) before every block backward (tests)
 
     @staticmethod
@@ -321,12 +322,17 @@ class Vgg16BnTrainer:
             geo = ops.ConvGeometry(n, L.h, L.h, L.c, L.k)
             if self.debug_hook is not None:
                 self.debug_hook(L, grad, x)
+            tev = None
+            if self.timing_bwd is not None:
+                tev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+                self.timing_bwd.append((L, tev))
             out = ops.cbr_amp_bwd(geo, grad, self.view(self.w16, L.w), self.view(self.w32, L.gamma),
                                   b["saved_mean"], b["saved_inv_std"], b["mask"], x, b["conv_out"],
                                   bn_scratch=self.bn_scratch[:b["conv_out"].numel()].view_as(b["conv_out"]),
                                   dw=self.view(self.g16, L.w), first_layer=(L.idx == 0), workspace=self.ws,
                                   dgamma=self.view(self.g32, L.gamma), dbeta=self.view(self.g32, L.beta),
-                                  pool_argmax=b["argmax"] if L.pool_after else None)   # pool backward fused in
+                                  pool_argmax=b["argmax"] if L.pool_after else None,   # pool backward fused in
+                                  timing_events=tev)
             grad = out["dx"]
             self.buckets.mark_ready(self._end_of(dict(w=L.w)))
         # BN gradients are float already and sit after every half-gradient slot
@@ -336,6 +342,13 @@ class Vgg16BnTrainer:
         ops.check_nonfinite(self.g32, self.nan_flag)
         ops.sgd_momentum(self.w32, self.g32, self.m32, self.w16, self.lr, self.wd, self.beta,
                          scaling=self.scaling, skip_flag=self.nan_flag)
+
+    def sync_weights_from_rank0(self):
+        """Every rank takes rank 0's master weights and momentum (after a diagnostic that let the ranks drift)."""
+        if self.world > 1:
+            dist.broadcast(self.w32, src=0, group=self.pg)
+            dist.broadcast(self.m32, src=0, group=self.pg)
+            self.w16.copy_(self.w32)
 
     def _end_of(self, group):
         """End offset (exclusive) of the flat range whose half gradients are complete once `group` is done."""

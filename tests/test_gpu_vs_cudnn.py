@@ -1,7 +1,7 @@
 """This repository's kernels against the reference's cuDNN path on identical seeded inputs.
 
 The reference executes its block through cuDNN-frontend graphs (cbr_op.cpp:430-917, 1259-1353);
-renaissance_b200.cudnn_reference rebuilds those graphs with the cudnn-frontend Python package.  Tolerances are
+cudnn_reference.py (beside bench.py) rebuilds those graphs with the cudnn-frontend Python package.  Tolerances are
 BASELINE.json's: <= 2e-2 relative L2 for half dx / dW (both sides round to half, ~1e-3 is what is reached), <= 1e-4
 relative for the per-channel reductions against a float64 evaluation (cuDNN's own reduction order differs)."""
 import numpy as np
@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _cr():
-    from renaissance_b200 import cudnn_reference as cr
+    import cudnn_reference as cr
     if not cr.available():
         pytest.skip("cudnn-frontend Python package not present")
     return cr
