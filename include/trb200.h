@@ -345,15 +345,16 @@ int trb200_fc_amp_fwd(const void* x, const void* w, const float* bias, void* y,
 int trb200_fc_act_bwd(const void* da, const void* act, void* dz, int64_t n, float scale, void* stream);
 
 /* db[o] = sum_b dy[b][o] (float, rows added in a fixed order; NULL: not computed),
- * dW = dy^T x (half, [out][in]), dx = dy W (half; NULL: not computed).  `act` (may
+ * dW = dy^T x ([out][in]; half, or float when dw_float != 0: the reference's
+ * FC_AMP_BWD writes float dW, fc_op.cpp:349-480), dx = dy W (half; NULL: not computed).  `act` (may
  * be NULL) is the layer's INPUT as the previous layer's trb200_fc_amp_fwd wrote it
  * with relu / dropout: dx then also carries that activation's backward,
  * dx = act > 0 ? dx * act_scale : 0 (trb200_fc_act_bwd folded in).  The three run
  * on `stream` in that order.  When the data gradient has few output tiles its GEMM
  * is split over out_features and needs the workspace of
  * trb200_fc_amp_workspace_bytes() for float partial sums (added in split order). */
-int trb200_fc_amp_bwd(const void* dy, const void* w, const void* x, void* dx, void* dw, float* db,
-                      const void* act, float act_scale,
+int trb200_fc_amp_bwd(const void* dy, const void* w, const void* x, void* dx, void* dw, int32_t dw_float,
+                      float* db, const void* act, float act_scale,
                       int32_t batch, int32_t in_features, int32_t out_features,
                       void* workspace, size_t workspace_bytes, void* stream);
 
@@ -488,6 +489,29 @@ int trb200_check_nonfinite(const float* grads, int64_t n, int32_t* flag, void* s
 int trb200_sgd_momentum(float* weights, const float* grads, float* momentum, void* weights_half,
                         int64_t n, float lr, float weight_decay, float beta, const float* scaling,
                         const int32_t* skip_flag, void* stream);
+
+/* The same sweep with Nesterov momentum (update_nesterov_kernel, optimizer_op.cu:68-93):
+ *   m = beta*m + g/scaling ; w = w*(1 - lr*wd) - lr*(beta*m + g/scaling) */
+int trb200_sgd_nesterov(float* weights, const float* grads, float* momentum, void* weights_half,
+                        int64_t n, float lr, float weight_decay, float beta, const float* scaling,
+                        const int32_t* skip_flag, void* stream);
+
+/* ... and without momentum (update_sgd_kernel, optimizer_op.cu:22-38):
+ *   w = w*(1 - lr*wd) - lr*g/scaling */
+int trb200_sgd_plain(float* weights, const float* grads, void* weights_half, int64_t n, float lr,
+                     float weight_decay, const float* scaling, const int32_t* skip_flag, void* stream);
+
+/* RANGE_CHECK_NAN with clipping (check_nan_and_clip_kernel, check_op.cu:54-79): a NaN
+ * raises *flag and stays as it is (the optimizer then skips the step); every other
+ * value, infinities included, is clamped to [-clip, clip] in place. */
+int trb200_check_nan_and_clip(float* grads, int64_t n, float clip, int32_t* flag, void* stream);
+
+/* RANGE_GRAD_SCALING (grad_scaling_kernel, grad_scaling_op.cu:15-22): after a step
+ * whose check raised the flag the loss scale is halved, never below 1:
+ *   if (*has_nan) *scaling = max(*scaling / 2, 1).
+ * clear_flag != 0 also resets *has_nan afterwards, ready for the next step's check
+ * (the reference's flag is reset by its host loop). */
+int trb200_grad_scaling(int32_t* has_nan, float* scaling, int32_t clear_flag, void* stream);
 
 #ifdef __cplusplus
 }

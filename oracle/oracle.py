@@ -239,6 +239,29 @@ def momentum(w, g, m, lr, wd=0.0, beta=0.9, scaling=1.0):
     return w, m
 
 
+def nesterov(w, g, m, lr, wd=0.0, beta=0.9, scaling=1.0):
+    """optimizer_op.cu:68-93.  Returns (w, m)."""
+    w, m = _f32(w).copy(), _f32(m).copy()
+    lib().orc_nesterov_f32(_p(w), _p(_f32(g)), _p(m), C.c_int64(w.size), C.c_float(lr), C.c_float(wd),
+                           C.c_float(beta), C.c_float(scaling))
+    return w, m
+
+
+def check_nan_and_clip(g, clip):
+    """check_op.cu:54-79.  Returns (clipped copy, flag)."""
+    g = _f32(g).copy()
+    fn = lib().orc_check_nan_and_clip_f32
+    fn.restype = C.c_int
+    return g, int(fn(_p(g), C.c_int64(g.size), C.c_float(clip)))
+
+
+def grad_scaling(has_nan, scaling):
+    """grad_scaling_op.cu:15-22."""
+    fn = lib().orc_grad_scaling
+    fn.restype = C.c_float
+    return float(fn(C.c_int(int(has_nan)), C.c_float(scaling)))
+
+
 # --------------------------------------------------------------------------- fused AMP block
 
 def cbr_fwd_amp(x16, w16, gamma, beta, pad=1, stride=1, eps=1e-5, momentum=0.1,

@@ -479,6 +479,41 @@ void orc_momentum_f32(float* w, const float* g, float* m, int64_t n,
     }
 }
 
+/* m_new = m*beta + g/scaling ; w <- w*(1 - lr*wd) - lr*(m_new*beta + g/scaling)
+ * (update_nesterov_kernel, optimizer_op.cu:68-93) */
+void orc_nesterov_f32(float* w, const float* g, float* m, int64_t n,
+                      float lr, float wd, float beta, float scaling) {
+    const float inv = scaling != 0.0f ? 1.0f / scaling : 1.0f;
+    for (int64_t i = 0; i < n; ++i) {
+        const float gi = g[i] * inv;
+        const float mn = m[i] * beta + gi;
+        m[i] = mn;
+        w[i] = w[i] * (1.0f - lr * wd) - lr * (mn * beta + gi);
+    }
+}
+
+/* NaN: flag, value kept; otherwise clamp to [-clip, clip] (check_nan_and_clip_kernel, check_op.cu:54-79).
+ * Returns the flag. */
+int orc_check_nan_and_clip_f32(float* g, int64_t n, float clip) {
+    int flag = 0;
+    for (int64_t i = 0; i < n; ++i) {
+        const float v = g[i];
+        if (v != v) { flag = 1; continue; }
+        const float c = v < -clip ? -clip : (v > clip ? clip : v);
+        if (c != v) g[i] = c;
+    }
+    return flag;
+}
+
+/* loss-scale back-off (grad_scaling_kernel, grad_scaling_op.cu:15-22) */
+float orc_grad_scaling(int has_nan, float scaling) {
+    if (has_nan != 0) {
+        const float s = scaling * 0.5f;
+        return s < 1.0f ? 1.0f : s;
+    }
+    return scaling;
+}
+
 /* ------------------------------------------------------------------------- */
 /* fused AMP block (CBR): what the reference asks cuDNN for                   */
 /* ------------------------------------------------------------------------- */

@@ -120,10 +120,14 @@ def load() -> C.CDLL:
         "trb200_bnrelu_pool_bwd": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, sz, vp]),
         "trb200_check_nonfinite": (C.c_int, [vp, i64, vp, vp]),
         "trb200_sgd_momentum": (C.c_int, [vp, vp, vp, vp, i64, f32, f32, f32, vp, vp, vp]),
+        "trb200_sgd_nesterov": (C.c_int, [vp, vp, vp, vp, i64, f32, f32, f32, vp, vp, vp]),
+        "trb200_sgd_plain": (C.c_int, [vp, vp, vp, i64, f32, f32, vp, vp, vp]),
+        "trb200_check_nan_and_clip": (C.c_int, [vp, i64, f32, vp, vp]),
+        "trb200_grad_scaling": (C.c_int, [vp, vp, i32, vp]),
         "trb200_fc_amp_workspace_bytes": (sz, [i32, i32, i32]),
         "trb200_fc_amp_fwd": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, i32, f32, C.c_uint64, C.c_uint64, vp, sz, vp]),
         "trb200_fc_act_bwd": (C.c_int, [vp, vp, vp, i64, f32, vp]),
-        "trb200_fc_amp_bwd": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, f32, i32, i32, i32, vp, sz, vp]),
+        "trb200_fc_amp_bwd": (C.c_int, [vp, vp, vp, vp, vp, i32, vp, vp, f32, i32, i32, i32, vp, sz, vp]),
         "trb200_scale_f32": (C.c_int, [vp, i64, f32, vp]),
         "trb200_cast_f16_to_f32": (C.c_int, [vp, vp, i64, f32, vp]),
     }

@@ -87,6 +87,9 @@ def build_plugin(force: bool = False) -> str:
                "-shared", "-o", PLUGIN_LIB, *srcs,
                "-I", os.path.join(ROOT, "include"), "-I", PLUGIN_DIR, "-L", LIB_DIR, "-ltrb200",
                "-Xlinker", "-rpath=$ORIGIN", "-lcudart"]
+        # the all-reduce launcher calls NCCL (as the reference's does under TR_USE_NCCL) when the header is there
+        if os.path.exists("/usr/include/nccl.h"):
+            cmd += ["-DTR_USE_NCCL", "-lnccl"]
         subprocess.check_call(cmd)
     return PLUGIN_LIB
 

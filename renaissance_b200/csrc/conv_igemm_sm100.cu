@@ -1442,15 +1442,15 @@ int fc_gemm_dgrad(const void* dy, const void* w, void* dx, float* partial, int b
     return launch_skinny<false, true, 2, true>(ta, tb, td, p, st);
 }
 
-// dw[o][i] = dy[:][o] . x[:][i]
-int fc_gemm_wgrad(const void* dy, const void* x, void* dw, int batch, int in_f, int out_f, cudaStream_t st) {
+// dw[o][i] = dy[:][o] . x[:][i], half or (dw_float) float as the reference's FC_AMP_BWD writes it
+int fc_gemm_wgrad(const void* dy, const void* x, void* dw, int dw_float, int batch, int in_f, int out_f, cudaStream_t st) {
     TRB_REQUIRE(fc_dims_ok(batch, in_f, out_f), TRB200_ERR_UNSUPPORTED, "fc: in_features=%d, out_features=%d must be multiples of 8", in_f, out_f);
     CUtensorMap ta, tb, td;
     int rc = make_matrix_tmap(&ta, dy, batch, out_f, out_f, 64, "fc dy (columns)");
     if (rc) return rc;
     rc = make_matrix_tmap(&tb, x, batch, in_f, in_f, 64, "fc x (columns)");
     if (rc) return rc;
-    rc = make_matrix_tmap(&td, dw, out_f, in_f, in_f, 128, "fc dw");
+    if (!dw_float) rc = make_matrix_tmap(&td, dw, out_f, in_f, in_f, 128, "fc dw");
     if (rc) return rc;
     SkinnyParams p;
     p.m_real = out_f; p.n_real = in_f;
@@ -1458,6 +1458,7 @@ int fc_gemm_wgrad(const void* dy, const void* x, void* dw, int batch, int in_f, 
     p.m_tiles = (out_f + 127) / 128; p.n_tiles = (in_f + kSkN - 1) / kSkN;
     p.splits = 1;
     p.ldd = in_f; p.d = dw; p.split_stride = 0; p.bf16 = 0;
+    if (dw_float) return launch_skinny<true, true, 1, true>(ta, tb, ta, p, st);
     return launch_skinny<true, true, 1, false>(ta, tb, td, p, st);
 }
 

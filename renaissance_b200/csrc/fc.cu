@@ -212,8 +212,8 @@ extern "C" int trb200_fc_act_bwd(const void* da, const void* act, void* dz, int6
     return TRB200_OK;
 }
 
-extern "C" int trb200_fc_amp_bwd(const void* dy, const void* w, const void* x, void* dx, void* dw, float* db,
-                                 const void* act, float act_scale, int32_t batch, int32_t in_features,
+extern "C" int trb200_fc_amp_bwd(const void* dy, const void* w, const void* x, void* dx, void* dw, int32_t dw_float,
+                                 float* db, const void* act, float act_scale, int32_t batch, int32_t in_features,
                                  int32_t out_features, void* workspace, size_t workspace_bytes, void* stream) {
     int rc = trb::check_dims(batch, in_features, out_features, "fc_amp_bwd");
     if (rc) return rc;
@@ -227,7 +227,7 @@ extern "C" int trb200_fc_amp_bwd(const void* dy, const void* w, const void* x, v
                                                                          out_features);
         TRB_LAUNCH_CHECK("fc_bias_grad_kernel");
     }
-    rc = trb::fc_gemm_wgrad(dy, x, dw, batch, in_features, out_features, st);
+    rc = trb::fc_gemm_wgrad(dy, x, dw, dw_float, batch, in_features, out_features, st);
     if (rc || !dx) return rc;
     const size_t need = trb::fc_gemm_dgrad_partial_bytes(batch, in_features, out_features);
     TRB_REQUIRE(need == 0 || (workspace && workspace_bytes >= need && trb::aligned16(workspace)), TRB200_ERR_WORKSPACE,

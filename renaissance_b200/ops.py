@@ -525,6 +525,26 @@ def sgd_momentum(w32, g32, m32, w16, lr, weight_decay, beta, scaling=None, skip_
                                           _stream(stream)))
 
 
+def sgd_nesterov(w32, g32, m32, w16, lr, weight_decay, beta, scaling=None, skip_flag=None, stream=None):
+    check(_lib.load().trb200_sgd_nesterov(_ptr(w32), _ptr(g32), _ptr(m32), _ptr(w16), w32.numel(), float(lr),
+                                          float(weight_decay), float(beta), _ptr(scaling), _ptr(skip_flag),
+                                          _stream(stream)))
+
+
+def sgd_plain(w32, g32, w16, lr, weight_decay, scaling=None, skip_flag=None, stream=None):
+    check(_lib.load().trb200_sgd_plain(_ptr(w32), _ptr(g32), _ptr(w16), w32.numel(), float(lr), float(weight_decay),
+                                       _ptr(scaling), _ptr(skip_flag), _stream(stream)))
+
+
+def check_nan_and_clip(flat_f32, clip, flag, stream=None):
+    check(_lib.load().trb200_check_nan_and_clip(_ptr(flat_f32), flat_f32.numel(), float(clip), _ptr(flag), _stream(stream)))
+
+
+def grad_scaling(flag, scaling, clear_flag=False, stream=None):
+    """Loss-scale back-off: halves `scaling` (never below 1) if `flag` is set; optionally resets the flag."""
+    check(_lib.load().trb200_grad_scaling(_ptr(flag), _ptr(scaling), 1 if clear_flag else 0, _stream(stream)))
+
+
 # --------------------------------------------------------------------------- softmax + CE
 
 def softmax_ce_amp_fwd(logits, labels, label_smoothing, probs=None, want_probs=True, stream=None):
@@ -634,12 +654,15 @@ def fc_amp_bwd(dy, w, x, dx=None, dw=None, db=None, want_dx=True, act=None, act_
     i_f = x.shape[1]
     if dw is None:
         dw = torch.empty((o_f, i_f), dtype=torch.float16, device=dy.device)
+    if dw.dtype not in (torch.float16, torch.float32):
+        raise TypeError("fc_amp_bwd: dw must be half or float")
     if db is None:
         db = torch.empty(o_f, dtype=torch.float32, device=dy.device)
     if dx is None and want_dx:
         dx = torch.empty((b, i_f), dtype=torch.float16, device=dy.device)
     ws = (workspace or default_workspace()).ensure(lib.trb200_fc_amp_workspace_bytes(b, i_f, o_f))
-    check(lib.trb200_fc_amp_bwd(_ptr(dy), _ptr(w), _ptr(x), _ptr(dx), _ptr(dw), _ptr(db), _ptr(act), float(act_scale),
+    check(lib.trb200_fc_amp_bwd(_ptr(dy), _ptr(w), _ptr(x), _ptr(dx), _ptr(dw), 1 if dw.dtype == torch.float32 else 0,
+                                _ptr(db), _ptr(act), float(act_scale),
                                 b, i_f, o_f, _ptr(ws), ws.numel(), _stream(stream)))
     return dx, dw, db
 

@@ -11,6 +11,9 @@
 //   include/renaissance/backend/device_context.h     DeviceContext
 //   include/renaissance/graph/capture_multi_stream.h MultiStreamCaptureState
 //   include/renaissance/core/tr_exception.h          TR_DEVICE_ERROR
+//   include/renaissance/core/global_registry.h       GlobalRegistry::world_size
+//   include/renaissance/backend/memory_arena.h       ArenaKeeper::ptr_at
+//   include/renaissance/graph/shape_id.h             MemRange
 // Outside that tree (this repository's tests) the same adapter compiles against
 // the declarations below, which carry only the members the adapter touches, with
 // the reference's names and meaning.
@@ -55,7 +58,30 @@ enum class ComputeOp : int {
     CBR_AMP_BWD_FIRST_LAYER,
     SOFTMAX_CE_AMP_FWD,
     SOFTMAX_CE_AMP_BWD,
+    CBR_AMP_FWD,
+    FC_AMP_FWD,
+    FC_AMP_BWD,
     COUNT
+};
+
+// op_kind.h:335-380: the range operators this plugin replaces
+enum class RangeOp : uint16_t {
+    UNKNOWN = 0,
+    RANGE_BN_STATS_ALLREDUCE,
+    RANGE_SUM_ALLREDUCE,
+    RANGE_MEAN_ALLREDUCE,
+    RANGE_CHECK_NAN,
+    RANGE_GRAD_SCALING,
+    COUNT
+};
+
+enum class Region : uint8_t { FIRST = 0 };                                    // types.h:241-340 (opaque here)
+
+struct MemRange {                                                             // shape_id.h:84-89
+    uint64_t offset = 0;
+    uint64_t size = 0;
+    int32_t start_region_id = -1;
+    int32_t end_region_id = -1;
 };
 
 struct ConvParams {                                                           // op_kind.h:22-29
@@ -77,21 +103,32 @@ struct CBRParams {                                                            //
 struct LossParams {
     float label_smoothing = 0.f;
 };
+struct FCParams {                                                             // op_kind.h:54-57
+    int out_features = 0;
+    bool bias = true;
+};
 struct OpParams {                                                             // op_kind.h:385-448
-    std::variant<std::monostate, ConvParams, BNParams, LossParams, CBRParams> data;
+    std::variant<std::monostate, ConvParams, BNParams, LossParams, CBRParams, FCParams> data;
     OpParams() = default;
     explicit OpParams(CBRParams p) : data(std::move(p)) {}
     explicit OpParams(LossParams p) : data(std::move(p)) {}
+    explicit OpParams(FCParams p) : data(std::move(p)) {}
     const CBRParams& cbr() const { return std::get<CBRParams>(data); }
 };
 
 struct GraphNode {                                                            // computation_graph.h:38-57
     enum class Kind : uint8_t { COMPUTE, RANGE };
     Kind kind = Kind::COMPUTE;
-    ComputeOp compute_op = ComputeOp::UNKNOWN;
+    union {
+        ComputeOp compute_op;
+        RangeOp range_op;
+    };
     OpParams params;
     std::vector<int32_t> input_ids;
     std::vector<int32_t> output_ids;
+    std::vector<MemRange> input_ranges;     // RANGE nodes: byte ranges of the arena, fixed at compile time
+    std::vector<MemRange> output_ranges;
+    GraphNode() : compute_op(ComputeOp::UNKNOWN) {}
 };
 
 struct Shape {
@@ -122,9 +159,49 @@ public:
         return it->second;
     }
     void add(const DTensor& t) { tensors_[t.id] = t; }
+    // memory_plan.h:273-274: byte (offset, size) of the span from the start of one region to the end of another
+    std::pair<uint64_t, uint64_t> resolve_region_bounds(Region start, Region end) const {
+        auto it = regions_.find((static_cast<uint32_t>(start) << 8) | static_cast<uint32_t>(end));
+        if (it == regions_.end()) return {0, 0};
+        return it->second;
+    }
+    void add_region_span(int start, int end, uint64_t offset, uint64_t size) {
+        regions_[(static_cast<uint32_t>(start) << 8) | static_cast<uint32_t>(end)] = {offset, size};
+    }
 
 private:
     std::unordered_map<int32_t, DTensor> tensors_;
+    std::unordered_map<uint32_t, std::pair<uint64_t, uint64_t>> regions_;
+};
+
+class GlobalRegistry {                                                        // global_registry.h:57-257
+public:
+    static GlobalRegistry& instance() {
+        static GlobalRegistry g;
+        return g;
+    }
+    int world_size() const { return world_size_; }
+    void set_world_size(int w) { world_size_ = w; }
+
+private:
+    int world_size_ = 1;
+};
+
+class ArenaKeeper {                                                           // memory_arena.h:196-276
+public:
+    static ArenaKeeper& instance() {
+        static ArenaKeeper a;
+        return a;
+    }
+    void* ptr_at(int rank, size_t offset) const noexcept {
+        return (rank >= 0 && rank < 8 && base_[rank]) ? static_cast<char*>(base_[rank]) + offset : nullptr;
+    }
+    void set_base(int rank, void* base) {
+        if (rank >= 0 && rank < 8) base_[rank] = base;
+    }
+
+private:
+    void* base_[8] = {};
 };
 
 class DeviceContext {                                                         // device_context.h:32-116
@@ -148,6 +225,10 @@ public:
         if (cudaMalloc(&w.ptr, req) != cudaSuccess) TR_DEVICE_ERROR("workspace cudaMalloc(" << req << ") failed");
         w.size = req;
     }
+    void* nccl_comm() const noexcept { return nccl_comm_; }                   // device_context.h:91-92
+    void set_nccl_comm(void* comm) noexcept { nccl_comm_ = comm; }
+    int rank_for_context() const noexcept { return rank_for_context_; }       // device_context.h:44-45
+    void set_rank(int rank) noexcept { rank_for_context_ = rank; }
     // harness side
     void bind(int id, void* p) { ptrs_[id] = p; }
     void set_stream(StreamKind kind, cudaStream_t s) { streams_[static_cast<int>(kind)] = s; }
@@ -164,6 +245,8 @@ private:
     std::unordered_map<int, void*> ptrs_;
     void* streams_[5] = {};
     mutable WSpace ws_[5];
+    void* nccl_comm_ = nullptr;
+    int rank_for_context_ = 0;
 };
 
 struct PerStreamState {                                                       // capture_multi_stream.h:25-29
@@ -208,6 +291,13 @@ struct ComputeOpEntry {                                                       //
                         MultiStreamCaptureState& state) = nullptr;
 };
 
+struct RangeOpEntry {                                                         // op_registry.h:71-82
+    RangeOp op = RangeOp::UNKNOWN;
+    void (*launch_cuda)(const GraphNode& node, const MemoryPlan& mp, const DeviceContext& ctx,
+                        MultiStreamCaptureState& state) = nullptr;
+};
+
 extern ComputeOpEntry g_compute_op_table[];                                   // op_registry.h:84
+extern RangeOpEntry g_range_op_table[];                                       // op_registry.h:85
 
 }  // namespace tr

@@ -337,11 +337,12 @@ class Vgg16BnTrainer:
             self.buckets.mark_ready(self._end_of(dict(w=L.w)))
         # BN gradients are float already and sit after every half-gradient slot
         self.buckets.finish()
-        # ---- guard + optimizer over the whole flat range
-        self.nan_flag.zero_()
+        # ---- guard + optimizer over the whole flat range, then the loss-scale back-off (a step that saw a non-finite
+        # gradient is skipped, halves the scale and resets the flag for the next step)
         ops.check_nonfinite(self.g32, self.nan_flag)
         ops.sgd_momentum(self.w32, self.g32, self.m32, self.w16, self.lr, self.wd, self.beta,
                          scaling=self.scaling, skip_flag=self.nan_flag)
+        ops.grad_scaling(self.nan_flag, self.scaling, clear_flag=True)
 
     def sync_weights_from_rank0(self):
         """Every rank takes rank 0's master weights and momentum (after a diagnostic that let the ranks drift)."""

@@ -33,6 +33,10 @@ def test_fc_matches_oracle(orc, batch, in_f, out_f):
     # ReLU folded in: bit-identical to the plain output passed through max(., 0)
     yr = ops.fc_amp_fwd(dev(x), dev(w), dev(b), relu=True)
     assert torch.equal(yr, torch.relu(y))
+    # float dW, as the reference's operator writes it
+    dwf = torch.empty((out_f, in_f), dtype=torch.float32, device="cuda")
+    ops.fc_amp_bwd(dev(dy), dev(w), dev(x), dw=dwf, want_dx=False)
+    assert rel_l2(host(dwf), dw_ref) < 1e-4 and torch.equal(dwf.half(), dw)
     # twice the same: reproducible
     dx2, dw2, db2 = ops.fc_amp_bwd(dev(dy), dev(w), dev(x))
     assert torch.equal(dx, dx2) and torch.equal(dw, dw2) and torch.equal(db, db2)

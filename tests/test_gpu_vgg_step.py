@@ -221,3 +221,52 @@ def test_whole_step_matches_oracle(orc):
         assert rel_l2(upd, upd_ref) < 0.35
     # the half working copy follows the master weights
     assert torch.equal(tr.w16, tr.w32.half())
+
+
+def test_nesterov_plain_sgd_clip_and_loss_scale_backoff(orc):
+    """The rest of the gradient post-processing chain (optimizer_op.cu:22-38, 68-93; check_op.cu:54-79;
+    grad_scaling_op.cu:15-22) against the oracle's restatements."""
+    from renaissance_b200 import ops
+    rng = np.random.default_rng(11)
+    n = 100003                                            # not a multiple of 4: the scalar tail runs too
+    w = rng.standard_normal(n).astype(np.float32)
+    g = (rng.standard_normal(n) * 1024).astype(np.float32)
+    m = rng.standard_normal(n).astype(np.float32)
+    scaling = torch.tensor([1024.0], device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    # Nesterov
+    wd_, gd, md = dev(w), dev(g), dev(m)
+    w16 = torch.empty(n, dtype=torch.float16, device="cuda")
+    ops.sgd_nesterov(wd_, gd, md, w16, 0.05, 5e-4, 0.9, scaling=scaling, skip_flag=flag)
+    w_ref, m_ref = orc.nesterov(w, g, m, 0.05, 5e-4, 0.9, 1024.0)
+    assert np.abs(host(wd_) - w_ref).max() < 1e-6 and np.abs(host(md) - m_ref).max() < 1e-6
+    assert torch.equal(w16, wd_.half())
+    # plain SGD
+    wd_ = dev(w)
+    ops.sgd_plain(wd_, gd, None, 0.05, 5e-4, scaling=scaling, skip_flag=flag)
+    assert np.abs(host(wd_) - orc.sgd(w, g, 0.05, 5e-4, 1024.0)).max() < 1e-6
+    # NaN check with clipping: NaN flagged and kept, infinities and large values clamped, the rest untouched
+    gc = g.copy()
+    gc[5], gc[77], gc[1000], gc[n - 1] = np.nan, np.inf, -np.inf, 5000.0
+    gcd = dev(gc)
+    ops.check_nan_and_clip(gcd, 2048.0, flag)
+    ref, ref_flag = orc.check_nan_and_clip(gc, 2048.0)
+    got = host(gcd)
+    assert int(flag) == 1 == ref_flag and np.isnan(got[5])
+    assert np.array_equal(np.delete(got, 5), np.delete(ref, 5))
+    clean = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.check_nan_and_clip(dev(g), 1e9, clean)
+    assert int(clean) == 0
+    # the optimizers skip a flagged step
+    before = wd_.clone()
+    ops.sgd_nesterov(wd_, gd, md, None, 0.05, 5e-4, 0.9, scaling=scaling, skip_flag=flag)
+    ops.sgd_plain(wd_, gd, None, 0.05, 5e-4, scaling=scaling, skip_flag=flag)
+    assert torch.equal(wd_, before)
+    # loss-scale back-off: halves on a flagged step, stops at 1, leaves a clean step alone
+    ops.grad_scaling(flag, scaling)
+    assert float(scaling) == 512.0 == orc.grad_scaling(1, 1024.0) and int(flag) == 1
+    ops.grad_scaling(clean, scaling)
+    assert float(scaling) == 512.0
+    low = torch.tensor([1.5], device="cuda")
+    ops.grad_scaling(flag, low, clear_flag=True)
+    assert float(low) == 1.0 == orc.grad_scaling(1, 1.5) and int(flag) == 0
