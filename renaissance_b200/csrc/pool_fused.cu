@@ -16,10 +16,14 @@
 // Bytes per full-resolution element: forward 2 + 1/8 + (2 + 1)/4 = 2.875 instead of
 // 6.875; backward 2 x (2 + 1/8 + 3/4) + 2 = 7.75 instead of 14.75.
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 #include <cuda_fp16.h>
 
 namespace trb {
+
+__device__ int g_pool_status = 0;   // set when a bounded wait of the ring kernels gives up
+
 namespace {
 
 constexpr int kThreads = 256;
@@ -307,6 +311,269 @@ bnrelu_pool_bwd_apply(const uint4* __restrict__ dy, const uint2* __restrict__ ar
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Backward on a ring of bulk copies.  The kernels above keep one window per thread in flight (ten dependent loads,
+// then ~300 instructions), so their time follows the SM clock and they lose a third of their bandwidth inside a
+// power-capped training step.  Here one thread of a producer warp streams whole row segments into shared memory
+// with bulk copies (four stages, ~40 KB each: what is in flight no longer depends on the consumers), and the
+// consumer warps work from shared memory.  One item = one pooled image row (or an aligned part of it): two
+// full-resolution rows of x and of the mask, one row of pooled dy and of the argmax.
+//
+// The selection runs on packed halfs: the gradient of a pooled pixel reaches ONE window position per channel (the
+// argmax), and only if the ReLU mask bit there is set.
+constexpr int kRingStages = 4;
+constexpr int kRingMaxConsumers = 512;
+
+struct RingPlan {
+    int ok;
+    int nchunk, cols_p;                // parts of a pooled row, pooled pixels per part
+    int ppp, consumers;                // pooled pixels per pass of the consumers, consumer threads
+    uint32_t x_bytes, dy_bytes, am_bytes, m_bytes, stage_bytes;
+    int64_t items;
+    int grid;
+};
+
+RingPlan make_ring_plan(int n, int h, int w, int c) {
+    RingPlan p{};
+    const int tpr = c / 8, ow = w / 2, oh = h / 2;
+    if (tpr > kRingMaxConsumers || (tpr & (tpr - 1)) != 0) return p;     // a thread keeps its channels: tpr | consumers
+    if (((int64_t)w * c) % 128 != 0) return p;                             // mask rows start on 16-byte boundaries
+    for (int nchunk = 1; nchunk <= ow; ++nchunk) {
+        if (ow % nchunk) continue;
+        const int cols_p = ow / nchunk;
+        if (((int64_t)cols_p * c) % 64 != 0) continue;                     // every segment a multiple of 16 bytes
+        const int64_t x_bytes = (int64_t)2 * cols_p * c * 2, dy_bytes = (int64_t)cols_p * c * 2,
+                      am_bytes = (int64_t)cols_p * c, m_bytes = (int64_t)2 * cols_p * c / 8;
+        const int64_t stage = align_up(2 * x_bytes + dy_bytes + am_bytes + 2 * m_bytes, 128);
+        if (stage > 48 * 1024) continue;
+        p.nchunk = nchunk;
+        p.cols_p = cols_p;
+        p.x_bytes = (uint32_t)x_bytes;
+        p.dy_bytes = (uint32_t)dy_bytes;
+        p.am_bytes = (uint32_t)am_bytes;
+        p.m_bytes = (uint32_t)m_bytes;
+        p.stage_bytes = (uint32_t)stage;
+        break;
+    }
+    if (p.nchunk == 0) return p;
+    // consumer threads: whole warps, pixels per pass chosen for the fewest idle lanes in the last pass
+    int best = 0;
+    double best_waste = 1e30;
+    for (int ppp = kRingMaxConsumers / tpr; ppp >= 1; --ppp) {
+        if ((ppp * tpr) % 32) continue;
+        const double waste = (double)((p.cols_p + ppp - 1) / ppp * ppp) / p.cols_p;
+        if (waste < best_waste - 1e-9 && ppp * tpr >= 128) { best_waste = waste; best = ppp; }
+    }
+    if (best == 0) return p;
+    p.ppp = best;
+    p.consumers = best * tpr;
+    p.items = (int64_t)n * oh * p.nchunk;
+    p.grid = (int)(p.items < sm_count() ? p.items : sm_count());
+    p.ok = 1;
+    return p;
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+struct WindowSelect {
+    uint32_t eq[4][4];      // [position][channel pair]: 0xffff in the half whose argmax is this position
+    uint32_t gsel[4];       // dy of the pooled pixel (packed halfs), zero where the mask bit at the argmax is clear
+};
+
+// m4: the mask bytes of window positions 0..3 in bytes 0..3
+__device__ __forceinline__ void window_select(const uint4& g4, const uint2& a2, uint32_t m4, WindowSelect& s) {
+    // argmax byte of a channel -> the half 1 + a / 1024 (a normal number, so the packed compare is exact)
+    const uint32_t am[4] = {__byte_perm(a2.x, 0x3c3c3c3cu, 0x4140), __byte_perm(a2.x, 0x3c3c3c3cu, 0x4342),
+                            __byte_perm(a2.y, 0x3c3c3c3cu, 0x4140), __byte_perm(a2.y, 0x3c3c3c3cu, 0x4342)};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const uint32_t qq = 0x3c003c00u | (uint32_t)q | ((uint32_t)q << 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            s.eq[q][i] = __heq2_mask(*reinterpret_cast<const __half2*>(&am[i]), *reinterpret_cast<const __half2*>(&qq));
+    }
+    // mask bit of channel j at its argmax position a: bit 8 a + j of m4, moved to bit 31 by a shift of
+    // 31 - j - 8 a (one byte per channel, no borrow between the bytes) and spread over the half by a sign-replicating
+    // byte permute
+    const uint32_t sh[2] = {0x1c1d1e1fu - (a2.x << 3), 0x18191a1bu - (a2.y << 3)};
+    const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t s2 = sh[i >> 1] >> (16 * (i & 1));
+        const uint32_t lo = __funnelshift_l(0u, m4, s2), hi = __funnelshift_l(0u, m4, s2 >> 8);
+        s.gsel[i] = gw[i] & prmt(lo, hi, 0xffbbu);
+    }
+}
+
+template <bool APPLY>
+__global__ void __launch_bounds__(kRingMaxConsumers + 32)
+bnrelu_pool_bwd_ring(const unsigned char* __restrict__ dy, const unsigned char* __restrict__ argmax,
+                     const unsigned char* __restrict__ mask, const unsigned char* __restrict__ x,
+                     const float* __restrict__ gamma, const float* __restrict__ mean,
+                     const float* __restrict__ inv_std, const float* __restrict__ dgamma,
+                     const float* __restrict__ dbeta, float* __restrict__ partial, uint4* __restrict__ out,
+                     int64_t m_full, int c, int oh_n, int ow_n, int w, int tpr, RingPlan pl, int* status) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t s_full[kRingStages], s_empty[kRingStages];
+    __shared__ int s_abort;
+    const int tid = threadIdx.x;
+    const int consumers = pl.consumers;
+    const uint32_t buf0 = ptx::smem_u32(smem_raw);
+    const uint32_t full0 = ptx::smem_u32(&s_full[0]), empty0 = ptx::smem_u32(&s_empty[0]);
+    if (tid == 0) {
+        s_abort = 0;
+        for (int i = 0; i < kRingStages; ++i) {
+            ptx::mbar_init(full0 + 8u * i, 1);
+            ptx::mbar_init(empty0 + 8u * i, (uint32_t)(consumers >> 5));
+        }
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+
+    const int64_t row_c = (int64_t)w * c;                       // elements of one full-resolution image row
+    // the apply pass walks the items backwards: what the reduce pass read last is still in L2
+    auto item_of = [&](int64_t k) -> int64_t {
+        const int64_t it = (int64_t)blockIdx.x + k * gridDim.x;
+        return APPLY ? pl.items - 1 - it : it;
+    };
+    const int64_t my_items = (pl.items - blockIdx.x + gridDim.x - 1) / gridDim.x;
+
+    if (tid >= consumers) {
+        // ---------------- producer: one thread
+        if (tid == consumers) {
+            for (int64_t k = 0; k < my_items; ++k) {
+                const int st = (int)(k % kRingStages);
+                if (k >= kRingStages &&
+                    !ptx::mbar_wait_relaxed(empty0 + 8u * st, (uint32_t)((k / kRingStages - 1) & 1), &s_abort, status, 21))
+                    break;
+                const int64_t it = item_of(k);
+                const int64_t prow = it / pl.nchunk;
+                const int ch = (int)(it % pl.nchunk);
+                const int64_t img = prow / oh_n;
+                const int oh = (int)(prow % oh_n);
+                const int64_t e0 = ((img * 2 * oh_n + 2 * oh) * (int64_t)w + (int64_t)ch * 2 * pl.cols_p) * c;   // x element
+                const int64_t p0 = (prow * ow_n + (int64_t)ch * pl.cols_p) * c;                                   // pooled element
+                const uint32_t dst = buf0 + (uint32_t)st * pl.stage_bytes;
+                const uint32_t bar = full0 + 8u * st;
+                ptx::mbar_expect_tx(bar, 2 * pl.x_bytes + pl.dy_bytes + pl.am_bytes + 2 * pl.m_bytes);
+                ptx::bulk_load_1d(dst, x + e0 * 2, pl.x_bytes, bar);
+                ptx::bulk_load_1d(dst + pl.x_bytes, x + (e0 + row_c) * 2, pl.x_bytes, bar);
+                ptx::bulk_load_1d(dst + 2 * pl.x_bytes, dy + p0 * 2, pl.dy_bytes, bar);
+                ptx::bulk_load_1d(dst + 2 * pl.x_bytes + pl.dy_bytes, argmax + p0, pl.am_bytes, bar);
+                ptx::bulk_load_1d(dst + 2 * pl.x_bytes + pl.dy_bytes + pl.am_bytes, mask + e0 / 8, pl.m_bytes, bar);
+                ptx::bulk_load_1d(dst + 2 * pl.x_bytes + pl.dy_bytes + pl.am_bytes + pl.m_bytes, mask + (e0 + row_c) / 8,
+                                  pl.m_bytes, bar);
+            }
+        }
+    } else {
+        // ---------------- consumers: a thread keeps its 8 channels, the passes walk the pooled pixels of the item
+        const int vec = tid % tpr, lane_p = tid / tpr;
+        float k0[8], k1[8], k2[8], k3[8];
+        // reduce: k0 = mean, k1 = inv_std, k2 / k3 = the two sums;  apply: dconv = (x - k0) * k1 + (k2 * g + k3)
+        const float inv_m = 1.0f / (float)m_full;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int chn = vec * 8 + j;
+            k0[j] = mean[chn];
+            if (APPLY) {
+                const float is = inv_std[chn];
+                k2[j] = gamma[chn] * is;
+                k1[j] = -k2[j] * (is * (dgamma[chn] * inv_m));
+                k3[j] = -k2[j] * (dbeta[chn] * inv_m);
+            } else {
+                k1[j] = inv_std[chn];
+                k2[j] = 0.f;
+                k3[j] = 0.f;
+            }
+        }
+        for (int64_t k = 0; k < my_items; ++k) {
+            const int st = (int)(k % kRingStages);
+            if (!ptx::mbar_wait(full0 + 8u * st, (uint32_t)((k / kRingStages) & 1), &s_abort, status, 22)) break;
+            const unsigned char* sx = smem_raw + (size_t)st * pl.stage_bytes;
+            const unsigned char* sdy = sx + 2 * pl.x_bytes;
+            const unsigned char* sam = sdy + pl.dy_bytes;
+            const unsigned char* sm0 = sam + pl.am_bytes;
+            int64_t o0 = 0;
+            if (APPLY) {
+                const int64_t it = item_of(k);
+                const int64_t prow = it / pl.nchunk;
+                const int chk = (int)(it % pl.nchunk);
+                const int64_t img = prow / oh_n;
+                const int oh = (int)(prow % oh_n);
+                o0 = ((img * 2 * oh_n + 2 * oh) * (int64_t)w + (int64_t)chk * 2 * pl.cols_p) * tpr;     // 16-byte vectors
+            }
+            for (int p = lane_p; p < pl.cols_p; p += pl.ppp) {
+                const int v0 = (2 * p) * tpr + vec;                 // vector index inside a row segment
+                const uint4 g4 = *reinterpret_cast<const uint4*>(sdy + (size_t)(p * tpr + vec) * 16);
+                const uint2 a2 = *reinterpret_cast<const uint2*>(sam + (size_t)(p * tpr + vec) * 8);
+                uint4 xv[4];
+                xv[0] = *reinterpret_cast<const uint4*>(sx + (size_t)v0 * 16);
+                xv[1] = *reinterpret_cast<const uint4*>(sx + (size_t)(v0 + tpr) * 16);
+                xv[2] = *reinterpret_cast<const uint4*>(sx + pl.x_bytes + (size_t)v0 * 16);
+                xv[3] = *reinterpret_cast<const uint4*>(sx + pl.x_bytes + (size_t)(v0 + tpr) * 16);
+                const uint32_t m4 = (uint32_t)sm0[v0] | ((uint32_t)sm0[v0 + tpr] << 8) |
+                                    ((uint32_t)sm0[pl.m_bytes + v0] << 16) | ((uint32_t)sm0[pl.m_bytes + v0 + tpr] << 24);
+                WindowSelect ws;
+                window_select(g4, a2, m4, ws);
+                const uint32_t xw[4][4] = {{xv[0].x, xv[0].y, xv[0].z, xv[0].w}, {xv[1].x, xv[1].y, xv[1].z, xv[1].w},
+                                           {xv[2].x, xv[2].y, xv[2].z, xv[2].w}, {xv[3].x, xv[3].y, xv[3].z, xv[3].w}};
+                if (!APPLY) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t xa = (xw[0][i] & ws.eq[0][i]) | (xw[1][i] & ws.eq[1][i]) | (xw[2][i] & ws.eq[2][i]) |
+                                            (xw[3][i] & ws.eq[3][i]);          // x at the channel's argmax position
+                        const float2 gf = __half22float2(*reinterpret_cast<const __half2*>(&ws.gsel[i]));
+                        const float2 xf = __half22float2(*reinterpret_cast<const __half2*>(&xa));
+                        k2[2 * i] += gf.x;
+                        k2[2 * i + 1] += gf.y;
+                        k3[2 * i] += gf.x * ((xf.x - k0[2 * i]) * k1[2 * i]);
+                        k3[2 * i + 1] += gf.y * ((xf.y - k0[2 * i + 1]) * k1[2 * i + 1]);
+                    }
+                } else {
+                    const int64_t ov[4] = {o0 + v0, o0 + v0 + tpr, o0 + v0 + (int64_t)w * tpr, o0 + v0 + (int64_t)w * tpr + tpr};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint4 o;
+                        __half2* ohh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const uint32_t gq = ws.gsel[i] & ws.eq[q][i];
+                            const float2 gf = __half22float2(*reinterpret_cast<const __half2*>(&gq));
+                            const float2 xf = __half22float2(*reinterpret_cast<const __half2*>(&xw[q][i]));
+                            const float o0f = fmaf(xf.x - k0[2 * i], k1[2 * i], fmaf(k2[2 * i], gf.x, k3[2 * i]));
+                            const float o1f = fmaf(xf.y - k0[2 * i + 1], k1[2 * i + 1], fmaf(k2[2 * i + 1], gf.y, k3[2 * i + 1]));
+                            ohh[i] = __floats2half2_rn(o0f, o1f);
+                        }
+                        out[ov[q]] = o;
+                    }
+                }
+            }
+            __syncwarp();
+            if ((tid & 31) == 0) ptx::mbar_arrive(empty0 + 8u * st);
+        }
+        if (!APPLY) {
+            // block sums in a fixed order: the ring is idle now (every copy issued has been waited for), its first
+            // bytes hold the per-thread sums
+            ptx::named_barrier(1, consumers);
+            float* s_red = reinterpret_cast<float*>(smem_raw);
+            float* mine = s_red + (size_t)tid * 16;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { mine[j] = k2[j]; mine[8 + j] = k3[j]; }
+            ptx::named_barrier(1, consumers);
+            for (int t = tid; t < tpr * 16; t += consumers) {
+                const int ovec = t / 16, j = t % 16;
+                float acc = 0.f;
+                for (int y = 0; y < pl.ppp; ++y) acc += s_red[(size_t)(y * tpr + ovec) * 16 + j];
+                partial[((size_t)blockIdx.x * 2 + (j >> 3)) * c + ovec * 8 + (j & 7)] = acc;
+            }
+        }
+    }
+}
+
 int check_pool_shape(int n, int h, int w, int c, const char* who) {
     TRB_REQUIRE(n > 0 && h > 0 && w > 0 && h % 2 == 0 && w % 2 == 0 && c > 0 && c % 8 == 0, TRB200_ERR_UNSUPPORTED,
                 "%s: need even h, w and c a positive multiple of 8 (n=%d h=%d w=%d c=%d)", who, n, h, w, c);
@@ -317,7 +584,20 @@ int check_pool_shape(int n, int h, int w, int c, const char* who) {
 
 size_t bnrelu_pool_bwd_workspace(int n, int h, int w, int c) {
     const PoolPlan p = make_pool_plan((int64_t)n * (h / 2) * (w / 2), c);
-    return (size_t)p.gx * 2 * (size_t)c * sizeof(float);
+    const RingPlan rp = make_ring_plan(n, h, w, c);
+    const int strips = rp.ok && rp.grid > p.gx ? rp.grid : p.gx;
+    return (size_t)strips * 2 * (size_t)c * sizeof(float);
+}
+
+int pool_status_read_and_clear(int* out) {
+    int v = 0;
+    TRB_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_pool_status, sizeof(int)));
+    if (v != 0) {
+        const int zero = 0;
+        TRB_CUDA_TRY(cudaMemcpyToSymbol(g_pool_status, &zero, sizeof(int)));
+    }
+    *out = v;
+    return TRB200_OK;
 }
 
 int bnrelu_pool_bwd_launch(const void* dy_pooled, const void* argmax, const void* mask_bits, const void* x,
@@ -335,8 +615,37 @@ int bnrelu_pool_bwd_launch(const void* dy_pooled, const void* argmax, const void
     TRB_REQUIRE(workspace && workspace_bytes >= need, TRB200_ERR_WORKSPACE,
                 "bnrelu_pool_bwd: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
     const int64_t pooled = (int64_t)n * (h / 2) * (w / 2);
-    const PoolPlan p = make_pool_plan(pooled, c);
     float* partial = static_cast<float*>(workspace);
+    const RingPlan rp = make_ring_plan(n, h, w, c);
+    if (rp.ok) {
+        static bool attr_done[64] = {false};
+        int dev = 0;
+        TRB_CUDA_TRY(cudaGetDevice(&dev));
+        if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+            const int lim = kRingStages * 48 * 1024;
+            TRB_CUDA_TRY(cudaFuncSetAttribute(bnrelu_pool_bwd_ring<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+            TRB_CUDA_TRY(cudaFuncSetAttribute(bnrelu_pool_bwd_ring<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+            attr_done[dev] = true;
+        }
+        int* status = nullptr;
+        TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_pool_status));
+        size_t smem = (size_t)kRingStages * rp.stage_bytes;
+        if (smem < (size_t)rp.consumers * 64) smem = (size_t)rp.consumers * 64;     // the block's sums at the end
+        const int threads = rp.consumers + 32;
+        auto b = [](const void* q) { return static_cast<const unsigned char*>(q); };
+        bnrelu_pool_bwd_ring<false><<<rp.grid, threads, smem, s>>>(
+            b(dy_pooled), b(argmax), b(mask_bits), b(x), gamma, saved_mean, saved_inv_std, dgamma, dbeta, partial, nullptr,
+            (int64_t)n * h * w, c, h / 2, w / 2, w, c / 8, rp, status);
+        TRB_LAUNCH_CHECK("bnrelu_pool_bwd_ring<reduce>");
+        bnrelu_pool_bwd_finalize<<<(2 * c + 7) / 8, 256, 0, s>>>(partial, dgamma, dbeta, c, rp.grid);
+        TRB_LAUNCH_CHECK("bnrelu_pool_bwd_finalize");
+        bnrelu_pool_bwd_ring<true><<<rp.grid, threads, smem, s>>>(
+            b(dy_pooled), b(argmax), b(mask_bits), b(x), gamma, saved_mean, saved_inv_std, dgamma, dbeta, partial,
+            static_cast<uint4*>(dconv), (int64_t)n * h * w, c, h / 2, w / 2, w, c / 8, rp, status);
+        TRB_LAUNCH_CHECK("bnrelu_pool_bwd_ring<apply>");
+        return TRB200_OK;
+    }
+    const PoolPlan p = make_pool_plan(pooled, c);
     dim3 grid(p.gx, p.gy);
     bnrelu_pool_bwd_reduce<<<grid, kThreads, 0, s>>>(
         static_cast<const uint4*>(dy_pooled), static_cast<const uint2*>(argmax), static_cast<const uint8_t*>(mask_bits),
