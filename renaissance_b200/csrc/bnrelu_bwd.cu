@@ -19,10 +19,14 @@
 //
 // Algorithmic HBM bytes: 2 x (2 + 2 + 1/8) read + 2 written = 10.25 B / element.
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 #include <mutex>
 
 namespace trb {
+
+__device__ int g_bn_status = 0;   // set when a bounded wait of the ring kernels gives up
+
 namespace {
 
 constexpr int kThreads = 256;
@@ -258,7 +262,253 @@ __global__ void __launch_bounds__(kThreads) bnrelu_bwd_apply_bf16(TRB_BN_APPLY_A
                                 rows_per_strip);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same two sweeps on a ring of bulk copies.  In the kernels above a thread keeps four rows in flight and then
+// works through them, so what is in flight follows the SM clock and the occupancy; inside a power-capped training
+// step they lose 10-25 % of the bandwidth they reach alone.  Here one thread of a producer warp streams the three
+// operands of a run of rows into shared memory with bulk copies (stages of ~33 KB), and 512 consumer threads, each
+// keeping its 8 channels, work from shared memory.  The ReLU mask is applied on packed halfs (two channels per
+// operation).  Rows beyond the last whole item are read with plain loads by block 0.
+constexpr int kRingStages = 5;
+constexpr int kRingConsumers = 512;
+constexpr int kRingPasses = 2;       // rows of an item = passes x (consumers / vectors per row)
+
+struct BnRingPlan {
+    int ok;
+    int ppp, item_rows, grid;
+    uint32_t v_bytes, m_bytes, stage_bytes;     // one operand of an item, its mask bytes, a stage
+    int64_t items;                              // whole items
+};
+
+BnRingPlan make_bn_ring_plan(int64_t m, int c) {
+    BnRingPlan p{};
+    const int tpr = c / 8;
+    if (tpr > kRingConsumers || (tpr & (tpr - 1)) != 0) return p;
+    p.ppp = kRingConsumers / tpr;
+    p.item_rows = p.ppp * kRingPasses;
+    p.items = m / p.item_rows;
+    if (p.items < 4 * (int64_t)sm_count()) return p;          // short tensors stay on the strip kernels
+    p.v_bytes = (uint32_t)kRingConsumers * kRingPasses * 16u;
+    p.m_bytes = (uint32_t)kRingConsumers * kRingPasses;
+    p.stage_bytes = 2 * p.v_bytes + p.m_bytes;
+    p.grid = sm_count();
+    p.ok = 1;
+    return p;
+}
+
+// lane masks (0xffff per half) of the four channel pairs from one mask byte: the low and the high nibble are
+// spread to the top bits of four bytes by one multiply each, a sign-replicating byte permute widens them
+__device__ __forceinline__ void lane_masks(uint32_t mb, uint32_t (&lm)[4]) {
+    const uint32_t lo = (mb & 15u) * 0x10204080u, hi = (mb >> 4) * 0x10204080u;
+    lm[0] = ptx::prmt_b32(lo, 0u, 0x9988u);
+    lm[1] = ptx::prmt_b32(lo, 0u, 0xbbaau);
+    lm[2] = ptx::prmt_b32(hi, 0u, 0x9988u);
+    lm[3] = ptx::prmt_b32(hi, 0u, 0xbbaau);
+}
+
+template <bool APPLY, bool BF16, bool MASK>
+__global__ void __launch_bounds__(kRingConsumers + 32)
+bnrelu_bwd_ring(const unsigned char* __restrict__ dy, const unsigned char* __restrict__ mask,
+                const unsigned char* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ mean,
+                const float* __restrict__ inv_std, const float* __restrict__ dgamma, const float* __restrict__ dbeta,
+                float* __restrict__ partial, uint4* __restrict__ out, int64_t m, int c, int tpr, BnRingPlan pl,
+                int* status) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t s_full[kRingStages], s_empty[kRingStages];
+    __shared__ int s_abort;
+    const int tid = threadIdx.x;
+    const uint32_t buf0 = ptx::smem_u32(smem_raw);
+    const uint32_t full0 = ptx::smem_u32(&s_full[0]), empty0 = ptx::smem_u32(&s_empty[0]);
+    if (tid == 0) {
+        s_abort = 0;
+        for (int i = 0; i < kRingStages; ++i) {
+            ptx::mbar_init(full0 + 8u * i, 1);
+            ptx::mbar_init(empty0 + 8u * i, kRingConsumers / 32);
+        }
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+
+    // the apply pass walks the items backwards: what the reduce pass read last is still in L2
+    auto item_of = [&](int64_t k) -> int64_t {
+        const int64_t it = (int64_t)blockIdx.x + k * gridDim.x;
+        return APPLY ? pl.items - 1 - it : it;
+    };
+    const int64_t my_items = (pl.items - blockIdx.x + gridDim.x - 1) / gridDim.x;
+
+    if (tid >= kRingConsumers) {
+        if (tid == kRingConsumers) {
+            for (int64_t k = 0; k < my_items; ++k) {
+                const int st = (int)(k % kRingStages);
+                if (k >= kRingStages &&
+                    !ptx::mbar_wait_relaxed(empty0 + 8u * st, (uint32_t)((k / kRingStages - 1) & 1), &s_abort, status, 23))
+                    break;
+                const int64_t v0 = item_of(k) * (int64_t)(kRingConsumers * kRingPasses);     // first 16-byte vector
+                const uint32_t dst = buf0 + (uint32_t)st * pl.stage_bytes;
+                const uint32_t bar = full0 + 8u * st;
+                ptx::mbar_expect_tx(bar, 2 * pl.v_bytes + (MASK ? pl.m_bytes : 0u));
+                ptx::bulk_load_1d(dst, dy + v0 * 16, pl.v_bytes, bar);
+                ptx::bulk_load_1d(dst + pl.v_bytes, x + v0 * 16, pl.v_bytes, bar);
+                if (MASK) ptx::bulk_load_1d(dst + 2 * pl.v_bytes, mask + v0, pl.m_bytes, bar);
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers
+    const int vec = tid % tpr;
+    float k0[8], k1[8], k2[8], k3[8];
+    // reduce: k0 = mean, k2 = sum dy_m, k3 = sum dy_m (x - mean);  apply: dconv = (x - k0) * k1 + (k2 * g + k3)
+    const float inv_m = 1.0f / (float)m;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int chn = vec * 8 + j;
+        k0[j] = mean[chn];
+        if (APPLY) {
+            const float is = inv_std[chn];
+            k2[j] = gamma[chn] * is;
+            k1[j] = -k2[j] * (is * (dgamma[chn] * inv_m));
+            k3[j] = -k2[j] * (dbeta[chn] * inv_m);
+        } else {
+            k1[j] = 0.f;
+            k2[j] = 0.f;
+            k3[j] = 0.f;
+        }
+    }
+    auto work = [&](const uint4& g4, const uint4& x4, uint32_t mb, int64_t ovec) {
+        const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, xw[4] = {x4.x, x4.y, x4.z, x4.w};
+        uint32_t lm[4];
+        if (MASK) lane_masks(mb, lm);
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 gf = unpack2_t<BF16>(MASK ? (gw[i] & lm[i]) : gw[i]);
+            const float2 xf = unpack2_t<BF16>(xw[i]);
+            if (!APPLY) {
+                k2[2 * i] += gf.x;
+                k2[2 * i + 1] += gf.y;
+                k3[2 * i] = fmaf(gf.x, xf.x - k0[2 * i], k3[2 * i]);
+                k3[2 * i + 1] = fmaf(gf.y, xf.y - k0[2 * i + 1], k3[2 * i + 1]);
+            } else {
+                ow[i] = pack2_t<BF16>(fmaf(xf.x - k0[2 * i], k1[2 * i], fmaf(k2[2 * i], gf.x, k3[2 * i])),
+                                      fmaf(xf.y - k0[2 * i + 1], k1[2 * i + 1], fmaf(k2[2 * i + 1], gf.y, k3[2 * i + 1])));
+            }
+        }
+        if (APPLY) out[ovec] = o;
+    };
+    auto tail = [&]() {
+        // rows past the last whole item: block 0, plain loads
+        if (blockIdx.x != 0) return;
+        const int64_t v_end = m * tpr;
+        for (int64_t v = pl.items * (int64_t)(kRingConsumers * kRingPasses) + tid; v < v_end; v += kRingConsumers) {
+            const uint4 g4 = *reinterpret_cast<const uint4*>(dy + v * 16);
+            const uint4 x4 = *reinterpret_cast<const uint4*>(x + v * 16);
+            work(g4, x4, MASK ? (uint32_t)mask[v] : 0xffu, v);
+        }
+    };
+    if (APPLY) tail();
+    for (int64_t k = 0; k < my_items; ++k) {
+        const int st = (int)(k % kRingStages);
+        if (!ptx::mbar_wait(full0 + 8u * st, (uint32_t)((k / kRingStages) & 1), &s_abort, status, 24)) break;
+        const unsigned char* sdy = smem_raw + (size_t)st * pl.stage_bytes;
+        const unsigned char* sx = sdy + pl.v_bytes;
+        const unsigned char* sm = sx + pl.v_bytes;
+        const int64_t v0 = APPLY ? item_of(k) * (int64_t)(kRingConsumers * kRingPasses) : 0;
+#pragma unroll
+        for (int ps = 0; ps < kRingPasses; ++ps) {
+            const int v = ps * kRingConsumers + tid;            // consecutive threads, consecutive vectors
+            work(*reinterpret_cast<const uint4*>(sdy + (size_t)v * 16), *reinterpret_cast<const uint4*>(sx + (size_t)v * 16),
+                 MASK ? (uint32_t)sm[v] : 0xffu, v0 + v);
+        }
+        __syncwarp();
+        if ((tid & 31) == 0) ptx::mbar_arrive(empty0 + 8u * st);
+    }
+    if (!APPLY) {
+        tail();
+        // block sums in a fixed order; the ring is idle now (every copy issued has been waited for)
+        ptx::named_barrier(1, kRingConsumers);
+        float* s_red = reinterpret_cast<float*>(smem_raw);
+        float* mine = s_red + (size_t)tid * 16;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { mine[j] = k2[j]; mine[8 + j] = k3[j]; }
+        ptx::named_barrier(1, kRingConsumers);
+        for (int t = tid; t < tpr * 16; t += kRingConsumers) {
+            const int ovec = t / 16, j = t % 16;
+            float acc = 0.f;
+            for (int y = 0; y < pl.ppp; ++y) acc += s_red[(size_t)(y * tpr + ovec) * 16 + j];
+            const int chn = ovec * 8 + (j & 7);
+            if (j >> 3) acc *= inv_std[chn];                    // sum dy_m (x - mean) -> sum dy_m x_hat
+            partial[((size_t)blockIdx.x * 2 + (j >> 3)) * c + chn] = acc;
+        }
+    }
+}
+
 }  // namespace
+
+namespace {
+
+template <bool BF16, bool MASK>
+int bnrelu_bwd_ring_launch_t(const BnRingPlan& rp, const void* dy, const void* mask_bits, const void* x, const float* gamma,
+                             const float* saved_mean, const float* saved_inv_std, void* dconv, float* dgamma,
+                             float* dbeta, float* partial, int64_t m, int c, cudaStream_t s) {
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    TRB_CUDA_TRY(cudaGetDevice(&dev));
+    const size_t smem = (size_t)kRingStages * rp.stage_bytes;
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        TRB_CUDA_TRY(cudaFuncSetAttribute(bnrelu_bwd_ring<false, BF16, MASK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)smem));
+        TRB_CUDA_TRY(cudaFuncSetAttribute(bnrelu_bwd_ring<true, BF16, MASK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)smem));
+        attr_done[dev] = true;
+    }
+    int* status = nullptr;
+    TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_bn_status));
+    auto b = [](const void* q) { return static_cast<const unsigned char*>(q); };
+    const int threads = kRingConsumers + 32;
+    bnrelu_bwd_ring<false, BF16, MASK><<<rp.grid, threads, smem, s>>>(b(dy), b(mask_bits), b(x), gamma, saved_mean,
+                                                                      saved_inv_std, dgamma, dbeta, partial, nullptr, m, c,
+                                                                      c / 8, rp, status);
+    TRB_LAUNCH_CHECK("bnrelu_bwd_ring<reduce>");
+    bnrelu_bwd_finalize<<<(2 * c + 7) / 8, 256, 0, s>>>(partial, dgamma, dbeta, c, rp.grid);
+    TRB_LAUNCH_CHECK("bnrelu_bwd_finalize");
+    if (dconv) {
+        bnrelu_bwd_ring<true, BF16, MASK><<<rp.grid, threads, smem, s>>>(b(dy), b(mask_bits), b(x), gamma, saved_mean,
+                                                                         saved_inv_std, dgamma, dbeta, partial,
+                                                                         static_cast<uint4*>(dconv), m, c, c / 8, rp, status);
+        TRB_LAUNCH_CHECK("bnrelu_bwd_ring<apply>");
+    }
+    return TRB200_OK;
+}
+
+int bnrelu_bwd_ring_launch(const BnRingPlan& rp, const void* dy, const void* mask_bits, const void* x, const float* gamma,
+                           const float* saved_mean, const float* saved_inv_std, void* dconv, float* dgamma, float* dbeta,
+                           float* partial, int64_t m, int c, cudaStream_t s, bool bf16) {
+#define TRB_RING_CASE(B, M)                                                                                              \
+    return bnrelu_bwd_ring_launch_t<B, M>(rp, dy, mask_bits, x, gamma, saved_mean, saved_inv_std, dconv, dgamma, dbeta, \
+                                          partial, m, c, s)
+    if (bf16) {
+        if (mask_bits) TRB_RING_CASE(true, true);
+        TRB_RING_CASE(true, false);
+    }
+    if (mask_bits) TRB_RING_CASE(false, true);
+    TRB_RING_CASE(false, false);
+#undef TRB_RING_CASE
+}
+
+}  // namespace
+
+int bn_status_read_and_clear(int* out) {
+    int v = 0;
+    TRB_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_bn_status, sizeof(int)));
+    if (v != 0) {
+        const int zero = 0;
+        TRB_CUDA_TRY(cudaMemcpyToSymbol(g_bn_status, &zero, sizeof(int)));
+    }
+    *out = v;
+    return TRB200_OK;
+}
 
 int bnrelu_bwd_launch(const void* dy, const void* mask_bits, const void* x, const float* gamma,
                       const float* saved_mean, const float* saved_inv_std, void* dconv,
@@ -278,8 +528,14 @@ int bnrelu_bwd_launch(const void* dy, const void* mask_bits, const void* x, cons
     const size_t need = trb200_bnrelu_bwd_workspace_bytes(m, c);
     TRB_REQUIRE(workspace && workspace_bytes >= need, TRB200_ERR_WORKSPACE,
                 "bnrelu_bwd: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
-    const BnPlan p = make_plan(m, c);
     float* partial = static_cast<float*>(workspace);
+    const BnRingPlan rp = make_bn_ring_plan(m, c);
+    if (rp.ok && (!mask_bits || aligned16(mask_bits))) {
+        const int rc = bnrelu_bwd_ring_launch(rp, dy, mask_bits, x, gamma, saved_mean, saved_inv_std, dconv, dgamma, dbeta,
+                                              partial, m, c, s, bf16);
+        if (rc != TRB200_ERR_UNSUPPORTED) return rc;
+    }
+    const BnPlan p = make_plan(m, c);
     dim3 grid(p.gx, p.gy);
     (bf16 ? bnrelu_bwd_reduce_bf16 : bnrelu_bwd_reduce)<<<grid, kThreads, 0, s>>>(
         static_cast<const uint4*>(dy), static_cast<const uint8_t*>(mask_bits),
@@ -298,12 +554,18 @@ int bnrelu_bwd_launch(const void* dy, const void* mask_bits, const void* x, cons
     return TRB200_OK;
 }
 
+int bn_ring_strips(int64_t m, int c) {
+    const BnRingPlan rp = make_bn_ring_plan(m, c);
+    return rp.ok ? rp.grid : 0;
+}
+
 }  // namespace trb
 
 extern "C" size_t trb200_bnrelu_bwd_workspace_bytes(int64_t m, int32_t c) {
     if (m <= 0 || c <= 0 || c % 8 != 0) return 0;
     const trb::BnPlan p = trb::make_plan(m, c);
-    return (size_t)p.gx * 2 * (size_t)c * sizeof(float);
+    const int ring = trb::bn_ring_strips(m, c);
+    return (size_t)(ring > p.gx ? ring : p.gx) * 2 * (size_t)c * sizeof(float);
 }
 
 extern "C" int trb200_bnrelu_bwd(const void* dy, const void* mask_bits, const void* x,

@@ -10,6 +10,7 @@ int device_status_read_and_clear(int* out);
 int wait_timeout_selftest(unsigned long long limit_ns, int* out4, cudaStream_t st);
 int softmax_status_read_and_clear(int* out);
 int pool_status_read_and_clear(int* out);
+int bn_status_read_and_clear(int* out);
 size_t bnrelu_pool_bwd_workspace(int n, int h, int w, int c);
 int bnrelu_pool_bwd_launch(const void* dy_pooled, const void* argmax, const void* mask_bits, const void* x,
                            const float* gamma, const float* saved_mean, const float* saved_inv_std, void* dconv,
@@ -70,6 +71,9 @@ extern "C" int trb200_device_status(void) {
     if (rc) return rc;
     if (v == 0) v = v2;
     rc = trb::pool_status_read_and_clear(&v2);
+    if (rc) return rc;
+    if (v == 0) v = v2;
+    rc = trb::bn_status_read_and_clear(&v2);
     if (rc) return rc;
     if (v == 0) v = v2;
     if (v != 0)

@@ -373,12 +373,6 @@ RingPlan make_ring_plan(int n, int h, int w, int c) {
     return p;
 }
 
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
-}
-
 struct WindowSelect {
     uint32_t eq[4][4];      // [position][channel pair]: 0xffff in the half whose argmax is this position
     uint32_t gsel[4];       // dy of the pooled pixel (packed halfs), zero where the mask bit at the argmax is clear
@@ -405,7 +399,7 @@ __device__ __forceinline__ void window_select(const uint4& g4, const uint2& a2, 
     for (int i = 0; i < 4; ++i) {
         const uint32_t s2 = sh[i >> 1] >> (16 * (i & 1));
         const uint32_t lo = __funnelshift_l(0u, m4, s2), hi = __funnelshift_l(0u, m4, s2 >> 8);
-        s.gsel[i] = gw[i] & prmt(lo, hi, 0xffbbu);
+        s.gsel[i] = gw[i] & ptx::prmt_b32(lo, hi, 0xffbbu);
     }
 }
 

@@ -27,6 +27,14 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
+// byte permute with the selector's sign-replication bit honoured (selector nibble 8 + k: the top bit of byte k
+// replicated over the target byte)
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
