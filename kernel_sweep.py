@@ -233,9 +233,38 @@ VGG_SHAPES = [(224, 64, 64), (112, 64, 128), (112, 128, 128), (56, 128, 256), (5
               (28, 512, 512), (14, 512, 512)]
 
 
+
+def pool_point(t, n, h, c, hbm, src):
+    """The block's HBM-bound kernels around a 2x2 max pool: BN apply + ReLU + mask + pool forward, and the pool + BN +
+    ReLU backward (bytes per full-resolution element: 2.875 and 7.75), and the forward without a pool (4.125)."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((n, h, h, c), generator=g, device="cuda").half()
+    sc = 0.5 + torch.rand(c, generator=g, device="cuda")
+    bi = 0.3 * torch.randn(c, generator=g, device="cuda")
+    po, am, mb = ops.bn_apply_relu_mask_pool(x, sc, bi)
+    e = x.numel()
+    med, best = t(lambda: ops.bn_apply_relu_mask_pool(x, sc, bi, mask_bits=mb, pool_out=po, argmax=am))
+    emit(kernel="bn_apply_relu_mask_pool (forward)", shape=dict(n=n, h=h, w=h, c=c), ms=round(med, 4), best_ms=round(best, 4),
+         bound="hbm", achieved=round(2.875 * e / med / 1e6, 1), peak=hbm, unit="GB/s",
+         frac=round(2.875 * e / med / 1e6 / hbm, 4), peak_source=src)
+    dy = torch.randn((n, h // 2, h // 2, c), generator=g, device="cuda").half()
+    gamma = 1 + 0.2 * torch.randn(c, generator=g, device="cuda")
+    mean = 0.1 * torch.randn(c, generator=g, device="cuda")
+    inv = 0.5 + torch.rand(c, generator=g, device="cuda")
+    out = torch.empty_like(x)
+    med, best = t(lambda: ops.bnrelu_pool_bwd(dy, am, mb, x, gamma, mean, inv, dconv=out))
+    emit(kernel="bnrelu_pool_bwd (reduce + finalize + apply)", shape=dict(n=n, h=h, w=h, c=c), ms=round(med, 4),
+         best_ms=round(best, 4), bound="hbm", achieved=round(7.75 * e / med / 1e6, 1), peak=hbm, unit="GB/s",
+         frac=round(7.75 * e / med / 1e6 / hbm, 4), peak_source=src)
+    y = out
+    med, best = t(lambda: ops.bn_apply_relu_mask(x, sc, bi, relu_out=y, mask_bits=mb))
+    emit(kernel="bn_apply_relu_mask (forward)", shape=dict(n=n, h=h, w=h, c=c), ms=round(med, 4), best_ms=round(best, 4),
+         bound="hbm", achieved=round(4.125 * e / med / 1e6, 1), peak=hbm, unit="GB/s",
+         frac=round(4.125 * e / med / 1e6 / hbm, 4), peak_source=src)
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="all", choices=["all", "block", "bnrelu", "softmax", "conv", "resnet50"])
+    ap.add_argument("--only", default="all", choices=["all", "block", "bnrelu", "pool", "softmax", "conv", "resnet50"])
     ap.add_argument("--quick", action="store_true", help="one small point per kernel (for profiler captures)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--batch", type=int, default=256, help="images for the conv / block points")
@@ -258,17 +287,24 @@ def main():
             pts.insert(0, (256 * 56 * 56, 64))
         for m, c in pts:
             bnrelu_point(t, m, c, hbm, src)
+    if args.only in ("all", "pool"):
+        # the pooled layers of VGG16-BN; --shape H,C picks one, --batch the images
+        pts = [(224, 64)] if args.quick else [(224, 64), (112, 128), (56, 256), (28, 512), (14, 512)]
+        if args.shape and args.only == "pool":
+            pts = [tuple(int(v) for v in args.shape.split(","))[:2]]
+        for h, c in pts:
+            pool_point(t, n, h, c, hbm, src)
     if args.only in ("all", "softmax"):
         pts = [(4096, 32000, 0.1)] if args.quick else \
             [(b, c, ls) for b in (4096, 65536) for c in (1000, 10000, 32000) for ls in (0.0, 0.1)] + [(256, 1000, 0.0)]
-        if args.shape:
+        if args.shape and args.only == "softmax":
             b, c = (int(v) for v in args.shape.split(","))
             pts = [(b, c, 0.0)]
         for b, c, ls in pts:
             softmax_point(t, b, c, ls, hbm, src)
     if args.only in ("all", "conv"):
         shapes = [(56, 64, 64), (28, 256, 512)] if args.quick else [(56, 64, 64)] + VGG_SHAPES
-        if args.shape:
+        if args.shape and args.only == "conv":
             shapes = [tuple(int(v) for v in args.shape.split(","))]
         kinds = tuple(args.what.split(",")) if args.what else ("dgrad", "wgrad", "fprop", "fprop_stats")
         for h, c, k in shapes:

@@ -8,6 +8,7 @@
 //   y = relu(t), mask = t > 0, t = half(half(x*eq_scale) + eq_bias) cbr_op.cpp:534-616
 //   max pooling with argmax byte (kh*k + kw, first maximum wins)    maxpool_op.cu:23-217
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 #include <cuda_fp16.h>
 #include "conv.cuh"
@@ -184,6 +185,101 @@ bn_apply_relu_mask(const uint4* __restrict__ x, const float* __restrict__ eq_sca
             const uint32_t hi = __byte_perm(on[2], on[3], 0x6420) & 0x08040201u;
             y[r * tpr + vec] = make_uint4(o[0], o[1], o[2], o[3]);
             mask[r * tpr + vec] = (uint8_t)(((lo * 0x01010101u) >> 24) | (((hi * 0x01010101u) >> 24) << 4));
+        }
+    }
+}
+
+// The same on a ring of bulk copies, for tensors of four or more items per SM: one thread of a producer warp streams
+// runs of 1024 vectors into shared memory (eight stages of 16 KB: what is in flight does not depend on the consumers'
+// progress or on the SM clock), 512 consumer threads, each keeping its 8 channels, write y and the mask bytes from
+// registers.  Vectors past the last whole item are handled by block 0 with plain loads.
+constexpr int kApplyRingStages = 8;
+constexpr int kApplyRingConsumers = 512;
+constexpr int kApplyRingPasses = 2;
+
+__device__ __forceinline__ void apply_relu_mask_vector(const uint4& v, const float (&sc)[8], const float (&bi)[8],
+                                                       uint4& yv, uint8_t& mbyte) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    const __half2 zero2 = __float2half2_rn(0.f);
+    uint32_t o[4], on[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        const float2 a = __half22float2(__floats2half2_rn(f.x * sc[2 * i], f.y * sc[2 * i + 1]));
+        const __half2 t = __floats2half2_rn(a.x + bi[2 * i], a.y + bi[2 * i + 1]);
+        on[i] = __hgt2_mask(t, zero2);
+        o[i] = *reinterpret_cast<const uint32_t*>(&t) & on[i];
+    }
+    const uint32_t lo = __byte_perm(on[0], on[1], 0x6420) & 0x08040201u;
+    const uint32_t hi = __byte_perm(on[2], on[3], 0x6420) & 0x08040201u;
+    yv = make_uint4(o[0], o[1], o[2], o[3]);
+    mbyte = (uint8_t)(((lo * 0x01010101u) >> 24) | (((hi * 0x01010101u) >> 24) << 4));
+}
+
+__global__ void __launch_bounds__(kApplyRingConsumers + 32)
+bn_apply_relu_mask_ring(const unsigned char* __restrict__ x, const float* __restrict__ eq_scale,
+                        const float* __restrict__ eq_bias, uint4* __restrict__ y, uint8_t* __restrict__ mask,
+                        int64_t vectors, int tpr, int64_t items, int* status) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t s_full[kApplyRingStages], s_empty[kApplyRingStages];
+    __shared__ int s_abort;
+    constexpr int kItemVectors = kApplyRingConsumers * kApplyRingPasses;
+    constexpr uint32_t kStageBytes = kItemVectors * 16u;
+    const int tid = threadIdx.x;
+    const uint32_t buf0 = ptx::smem_u32(smem_raw);
+    const uint32_t full0 = ptx::smem_u32(&s_full[0]), empty0 = ptx::smem_u32(&s_empty[0]);
+    if (tid == 0) {
+        s_abort = 0;
+        for (int i = 0; i < kApplyRingStages; ++i) {
+            ptx::mbar_init(full0 + 8u * i, 1);
+            ptx::mbar_init(empty0 + 8u * i, kApplyRingConsumers / 32);
+        }
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+    const int64_t my_items = (items - blockIdx.x + gridDim.x - 1) / gridDim.x;
+    if (tid >= kApplyRingConsumers) {
+        if (tid == kApplyRingConsumers) {
+            for (int64_t k = 0; k < my_items; ++k) {
+                const int st = (int)(k % kApplyRingStages);
+                if (k >= kApplyRingStages &&
+                    !ptx::mbar_wait_relaxed(empty0 + 8u * st, (uint32_t)((k / kApplyRingStages - 1) & 1), &s_abort, status, 27))
+                    break;
+                const int64_t v0 = ((int64_t)blockIdx.x + k * gridDim.x) * kItemVectors;
+                ptx::mbar_expect_tx(full0 + 8u * st, kStageBytes);
+                ptx::bulk_load_1d(buf0 + (uint32_t)st * kStageBytes, x + v0 * 16, kStageBytes, full0 + 8u * st);
+            }
+        }
+        return;
+    }
+    const int vec = tid % tpr;
+    float sc[8], bi[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { sc[j] = eq_scale[vec * 8 + j]; bi[j] = eq_bias[vec * 8 + j]; }
+    for (int64_t k = 0; k < my_items; ++k) {
+        const int st = (int)(k % kApplyRingStages);
+        if (!ptx::mbar_wait(full0 + 8u * st, (uint32_t)((k / kApplyRingStages) & 1), &s_abort, status, 28)) break;
+        const unsigned char* sx = smem_raw + (size_t)st * kStageBytes;
+        const int64_t v0 = ((int64_t)blockIdx.x + k * gridDim.x) * kItemVectors;
+#pragma unroll
+        for (int ps = 0; ps < kApplyRingPasses; ++ps) {
+            const int v = ps * kApplyRingConsumers + tid;
+            uint4 yv;
+            uint8_t mb;
+            apply_relu_mask_vector(*reinterpret_cast<const uint4*>(sx + (size_t)v * 16), sc, bi, yv, mb);
+            y[v0 + v] = yv;
+            mask[v0 + v] = mb;
+        }
+        __syncwarp();
+        if ((tid & 31) == 0) ptx::mbar_arrive(empty0 + 8u * st);
+    }
+    if (blockIdx.x == 0) {
+        for (int64_t v = items * kItemVectors + tid; v < vectors; v += kApplyRingConsumers) {
+            uint4 yv;
+            uint8_t mb;
+            apply_relu_mask_vector(*reinterpret_cast<const uint4*>(x + v * 16), sc, bi, yv, mb);
+            y[v] = yv;
+            mask[v] = mb;
         }
     }
 }
@@ -408,6 +504,30 @@ extern "C" int trb200_bn_apply_relu_mask(const void* conv_out, const float* eq_s
                 "bn_apply_relu_mask: need m > 0 and c a positive multiple of 8 (m=%lld c=%d)", (long long)m, c);
     TRB_REQUIRE(trb::aligned16(conv_out) && trb::aligned16(relu_out), TRB200_ERR_INVALID_ARGUMENT,
                 "bn_apply_relu_mask: tensors must be 16-byte aligned");
+    {
+        const int tpr = c / 8;
+        const int64_t vectors = m * tpr;
+        const int64_t items = vectors / (trb::kApplyRingConsumers * trb::kApplyRingPasses);
+        if (tpr <= trb::kApplyRingConsumers && (tpr & (tpr - 1)) == 0 && items >= 4 * (int64_t)trb::sm_count()) {
+            static bool attr_done[64] = {false};
+            int dev = 0;
+            TRB_CUDA_TRY(cudaGetDevice(&dev));
+            const size_t smem = (size_t)trb::kApplyRingStages * trb::kApplyRingConsumers * trb::kApplyRingPasses * 16;
+            if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+                TRB_CUDA_TRY(cudaFuncSetAttribute(trb::bn_apply_relu_mask_ring, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  (int)smem));
+                attr_done[dev] = true;
+            }
+            int* status = nullptr;
+            const int rc = trb::ring_status_ptr(&status);
+            if (rc) return rc;
+            trb::bn_apply_relu_mask_ring<<<trb::sm_count(), trb::kApplyRingConsumers + 32, smem, trb::as_stream(stream)>>>(
+                static_cast<const unsigned char*>(conv_out), eq_scale, eq_bias, static_cast<uint4*>(relu_out),
+                static_cast<uint8_t*>(mask_bits), vectors, tpr, items, status);
+            TRB_LAUNCH_CHECK("bn_apply_relu_mask_ring");
+            return TRB200_OK;
+        }
+    }
     const trb::RowPlan p = trb::make_row_plan(m, c);
     trb::bn_apply_relu_mask<<<dim3(p.gx, p.gy), trb::kThreads, 0, trb::as_stream(stream)>>>(
         static_cast<const uint4*>(conv_out), eq_scale, eq_bias, static_cast<uint4*>(relu_out),

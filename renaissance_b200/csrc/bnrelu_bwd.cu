@@ -499,6 +499,12 @@ int bnrelu_bwd_ring_launch(const BnRingPlan& rp, const void* dy, const void* mas
 
 }  // namespace
 
+// device address of the status word the bulk-copy ring kernels (this file, pool_fused.cu, block_fwd.cu) report to
+int ring_status_ptr(int** out) {
+    TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(out), g_bn_status));
+    return TRB200_OK;
+}
+
 int bn_status_read_and_clear(int* out) {
     int v = 0;
     TRB_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_bn_status, sizeof(int)));

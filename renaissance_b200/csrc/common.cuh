@@ -26,6 +26,7 @@ inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+int ring_status_ptr(int** out);     // status word of the bulk-copy ring kernels (bounded waits)
 
 // Counts kernel launches made by this library (every launch site goes through
 // TRB_LAUNCH_CHECK); read by trb200_kernel_launch_count().

@@ -18,6 +18,15 @@ bool igemm_supports(const trb200_conv_desc& d, int which);   // 0 wgrad, 1 dgrad
 bool igemm_small_c(const trb200_conv_desc& d);
 size_t igemm_wgrad_workspace(const trb200_conv_desc& d);
 size_t igemm_dgrad_workspace(const trb200_conv_desc& d);
+// stride 2 (3x3 pad 1, 1x1 pad 0) on the tensor-core kernels without a resampling pass: forward and weight gradient
+// read x through a tensor map that steps two pixels, the 3x3 data gradient runs as four parity classes
+bool igemm_s2_supports(const trb200_conv_desc& d, int which);
+size_t igemm_s2_workspace(const trb200_conv_desc& d, int which);
+int igemm_s2_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, cudaStream_t st);
+int igemm_s2_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* ws, size_t ws_bytes,
+                   cudaStream_t st);
+int igemm_s2_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes,
+                   cudaStream_t st);
 size_t igemm_fprop_workspace(const trb200_conv_desc& d);
 size_t igemm_fprop_stats_bytes(const trb200_conv_desc& d);
 int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, void* ws, size_t ws_bytes,

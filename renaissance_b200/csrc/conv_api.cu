@@ -9,7 +9,6 @@ namespace trb {
 int device_status_read_and_clear(int* out);
 int wait_timeout_selftest(unsigned long long limit_ns, int* out4, cudaStream_t st);
 int softmax_status_read_and_clear(int* out);
-int pool_status_read_and_clear(int* out);
 int bn_status_read_and_clear(int* out);
 size_t bnrelu_pool_bwd_workspace(int n, int h, int w, int c);
 int bnrelu_pool_bwd_launch(const void* dy_pooled, const void* argmax, const void* mask_bits, const void* x,
@@ -68,9 +67,6 @@ extern "C" int trb200_device_status(void) {
     int rc = trb::device_status_read_and_clear(&v);
     if (rc) return rc;
     rc = trb::softmax_status_read_and_clear(&v2);
-    if (rc) return rc;
-    if (v == 0) v = v2;
-    rc = trb::pool_status_read_and_clear(&v2);
     if (rc) return rc;
     if (v == 0) v = v2;
     rc = trb::bn_status_read_and_clear(&v2);

@@ -134,7 +134,7 @@ EncodeTiledFn encode_fn() {
 
 // Half tensor, `rank` dims (innermost first), 128-byte swizzle, zero fill.
 int make_tmap(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-              const uint32_t* box, const char* what) {
+              const uint32_t* box, const char* what, const uint32_t* elem_strides = nullptr) {
     EncodeTiledFn fn = encode_fn();
     TRB_REQUIRE(fn, TRB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t gdim[5];
@@ -143,7 +143,7 @@ int make_tmap(CUtensorMap* m, const void* base, int rank, const uint64_t* dims, 
     for (int i = 0; i < rank; ++i) {
         gdim[i] = dims[i];
         bx[i] = box[i];
-        es[i] = 1;
+        es[i] = elem_strides ? elem_strides[i] : 1;
         if (i > 0) gstr[i - 1] = strides_bytes[i];
     }
     const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim,
@@ -161,6 +161,32 @@ int make_act_tmap(CUtensorMap* m, const void* base, int n, int h, int w, int c, 
     const uint64_t str[4] = {2, (uint64_t)c * 2, (uint64_t)w * c * 2, (uint64_t)h * w * c * 2};
     const uint32_t box[4] = {64, (uint32_t)t.bw, (uint32_t)t.bh, (uint32_t)t.bn};
     return make_tmap(m, base, 4, dims, str, box, what);
+}
+
+// The same tensor read with a step of `step` pixels along w and h (a stride-2 convolution's input): the box spans
+// bw * step x bh * step pixels and holds every step-th of them, so the tile in shared memory is the bw x bh x bn pixels
+// of the stride-1 case.  Box coordinates stay in the tensor's own pixel grid.
+int make_act_tmap_stepped(CUtensorMap* m, const void* base, int n, int h, int w, int c, const TileShape& t, int step,
+                          const char* what) {
+    const uint64_t dims[4] = {(uint64_t)c, (uint64_t)w, (uint64_t)h, (uint64_t)n};
+    const uint64_t str[4] = {2, (uint64_t)c * 2, (uint64_t)w * c * 2, (uint64_t)h * w * c * 2};
+    const uint32_t box[4] = {64, (uint32_t)(t.bw * step), (uint32_t)(t.bh * step), (uint32_t)t.bn};
+    const uint32_t es[4] = {1, (uint32_t)step, (uint32_t)step, 1};
+    TRB_REQUIRE(box[1] <= 256 && box[2] <= 256, TRB200_ERR_UNSUPPORTED, "%s: a stepped box of %u x %u pixels", what, box[1],
+                box[2]);
+    return make_tmap(m, base, 4, dims, str, box, what, es);
+}
+
+// Every second pixel of an [n,h,w,c] tensor, starting at pixel (py, px): a plain tensor map over the pixels of one
+// parity (the outputs one class of a stride-2 data gradient writes).
+int make_act_tmap_parity(CUtensorMap* m, const void* base, int n, int h, int w, int c, int py, int px, const TileShape& t,
+                         const char* what) {
+    const int hc = (h - py + 1) / 2, wc = (w - px + 1) / 2;
+    const uint64_t dims[4] = {(uint64_t)c, (uint64_t)wc, (uint64_t)hc, (uint64_t)n};
+    const uint64_t str[4] = {2, (uint64_t)c * 4, (uint64_t)w * c * 4, (uint64_t)h * w * c * 2};
+    const uint32_t box[4] = {64, (uint32_t)t.bw, (uint32_t)t.bh, (uint32_t)t.bn};
+    const unsigned char* b = static_cast<const unsigned char*>(base) + ((int64_t)py * w + px) * c * 2;
+    return make_tmap(m, b, 4, dims, str, box, what);
 }
 
 // 4-channel half image [n,h,w] of 8-byte pixels viewed as (w, h, n) with a {bw + 4, bh + 2, bn} box,
@@ -255,6 +281,8 @@ __device__ __forceinline__ void build_im2col_row_c4(const uint2* __restrict__ x4
 struct FpropParams {
     int taps;            // 9 (3x3, pad 1) or 1 (1x1, pad 0)
     int tap_base;        // 0 for 3x3; 4 for 1x1 (the centre tap: offset (0, 0))
+    int step;            // input pixels per output pixel (1, or 2 for a stride-2 convolution)
+    unsigned long long tap_offsets;   // 4 bits per tap: input offset of the tap, (dw + 1) | (dh + 1) << 2
     int cin_slices;      // Cin / 64
     int n_tiles;         // Cout / NT
     int m_tiles;         // tw * th * tn
@@ -350,8 +378,6 @@ conv3x3_igemm_body(const CUtensorMap& tm_in, const CUtensorMap& tm_w, const CUte
     static_assert(!IM2COL || kStages % (kBuilderThreads / 128) == 0, "a stage keeps its builder group");
     const int total_tiles = p.m_tiles * p.n_tiles;
     const int ksteps = p.taps * p.cin_slices;
-    // tap window: 3x3 walks r, s in [0, 3); 1x1 is the centre tap only
-    const int t_lo = p.taps == 9 ? 0 : 1, t_hi = p.taps == 9 ? 3 : 2;
 
     // The single-thread roles below are paced by their own instruction count (a lone
     // thread issues roughly one dependent instruction every few clocks), so their inner
@@ -421,8 +447,9 @@ conv3x3_igemm_body(const CUtensorMap& tm_in, const CUtensorMap& tm_w, const CUte
                 const int mt = tile / p.n_tiles;
                 const int w0 = (mt % p.tw) * p.bw, h0 = ((mt / p.tw) % p.th) * p.bh;
                 const int n0 = (mt / (p.tw * p.th)) * p.bn;
-                for (int r = t_lo; r < t_hi && ok; ++r)
-                    for (int s = t_lo; s < t_hi && ok; ++s)
+                const int wi0 = w0 * p.step - 1, hi0 = h0 * p.step - 1;
+                for (int tap = 0; tap < p.taps && ok; ++tap) {
+                        const int s = (int)((p.tap_offsets >> (4 * tap)) & 3ull), r = (int)((p.tap_offsets >> (4 * tap + 2)) & 3ull);
                         for (int slice = 0; slice < p.cin_slices; ++slice) {
                             if (kAProd == 1 || turn == pidx) {
                                 RT_ADD(1);
@@ -433,14 +460,14 @@ conv3x3_igemm_body(const CUtensorMap& tm_in, const CUtensorMap& tm_w, const CUte
                                 const uint32_t fb = full0 + 8u * stage;
                                 if (lane == 0) {
                                     mbar_expect_tx(fb, kATileBytes);
-                                    tma_load_4d(a_base + stage * kATileBytes, &tm_in, fb, slice * 64, w0 + s - 1,
-                                                h0 + r - 1, n0);
+                                    tma_load_4d(a_base + stage * kATileBytes, &tm_in, fb, slice * 64, wi0 + s, hi0 + r, n0);
                                 }
                                 __syncwarp();
                             }
                             if (kAProd > 1 && ++turn == kAProd) turn = 0;
                             if (++stage == kStages) { stage = 0; phase ^= 1u; }
                         }
+                }
             }
             RT_ADD(1);
             if (lane == 0 && warp == 0) RT_STORE(0);
@@ -754,19 +781,37 @@ int pick_nt(int cout) {
 // the number of strips through *stats_strips.
 // x4 != nullptr: `in` is ignored, the A tiles are built in the kernel from the 4-channel image x4 (taps must be 1,
 // cin 64: the 36 neighbourhood values + 28 zeros).
+// What a convolution that is not the plain stride-1 case adds (h, w of conv3x3_run are then the output grid):
+struct ConvRunEx {
+    int step = 1;                          // input pixels per output pixel; the input is [n, in_h, in_w, cin]
+    int in_h = 0, in_w = 0;
+    unsigned long long tap_offsets = 0;    // 0: the 3x3 window (or the centre tap) around the output pixel
+    int parity = -1;                       // py * 2 + px: the output grid is that parity class of [n, full_h, full_w, cout]
+    int full_h = 0, full_w = 0;
+};
+
+constexpr unsigned long long kTapOffsets3x3 = 0xa98654210ull;     // tap = r * 3 + s: nibble s | r << 2
+constexpr unsigned long long kTapOffsets1x1 = 0x5ull;
+
 int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int n, int h, int w, int cin, int cout,
                 cudaStream_t st, int taps = 9, float* stats_partial = nullptr, int* stats_strips = nullptr,
-                const void* x4 = nullptr, bool bf16 = false) {
+                const void* x4 = nullptr, bool bf16 = false, const ConvRunEx* ex = nullptr) {
     const int nt = pick_nt(cout);
     TRB_REQUIRE(nt != 0 && cin % 64 == 0, TRB200_ERR_UNSUPPORTED, "conv3x3 igemm: cin=%d cout=%d not covered", cin,
                 cout);
     const TileShape t = pick_tile(n, h, w, 128);
     CUtensorMap tin, tw, tout;
-    int rc = make_act_tmap(&tout, out, n, h, w, cout, t, "conv output");
+    int rc;
+    if (ex && ex->parity >= 0)
+        rc = make_act_tmap_parity(&tout, out, n, ex->full_h, ex->full_w, cout, ex->parity >> 1, ex->parity & 1, t,
+                                  "conv output (parity class)");
+    else
+        rc = make_act_tmap(&tout, out, n, h, w, cout, t, "conv output");
     if (rc) return rc;
     const bool raw_ring = x4 && raw_ring_fits(t, w, x4);
     if (raw_ring) rc = make_raw_x4_tmap(&tin, x4, n, h, w, t);
     else if (x4) tin = tout;      // not used by the kernel
+    else if (ex && ex->in_h) rc = make_act_tmap_stepped(&tin, in, n, ex->in_h, ex->in_w, cin, t, ex->step, "conv input");
     else rc = make_act_tmap(&tin, in, n, h, w, cin, t, "conv input");
     if (rc) return rc;
     const int b_rows = (nt == 256 && !x4) ? 128 : nt;      // rows of one filter box (the 256-row tile takes two)
@@ -786,6 +831,8 @@ int conv3x3_run(const void* in, const void* wv, int tap_is_dim1, void* out, int 
     FpropParams p;
     p.taps = taps;
     p.tap_base = taps == 1 ? 4 : 0;
+    p.step = ex ? ex->step : 1;
+    p.tap_offsets = (ex && ex->tap_offsets) ? ex->tap_offsets : (taps == 9 ? kTapOffsets3x3 : kTapOffsets1x1);
     p.cin_slices = cin / 64;
     p.n_tiles = cout / nt;
     p.m_tiles = t.tw * t.th * t.tn;
@@ -835,6 +882,7 @@ int conv3x3_any_run(const void* in, const void* wv, int tap_is_dim1, void* out, 
 struct WgradParams {
     int taps;           // 9 (3x3, pad 1) or 1 (1x1)
     int tap_base;       // 0 for 3x3; 4 for 1x1 (centre tap)
+    int step;           // pixels of x per pixel of dy (1, or 2 for a stride-2 convolution)
     int cblocks;        // C / 64
     int units;          // taps * cblocks  (unit u: tap = u / cblocks, cblock = u % cblocks)
     int m_tiles;        // ceil(units / 2)
@@ -986,8 +1034,8 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 const uint32_t a_dst = a_base + stage * L::kABytes;
                 if (lane == 0) {
                     mbar_expect_tx(fb, L::kABytes);
-                    tma_load_4d(a_dst, &tm_x, fb, c0, w0 + dw0, h0 + dh0, n0);
-                    tma_load_4d(a_dst + kStageTileBytes, &tm_x, fb, c1, w0 + dw1, h0 + dh1, n0);
+                    tma_load_4d(a_dst, &tm_x, fb, c0, w0 * p.step + dw0, h0 * p.step + dh0, n0);
+                    tma_load_4d(a_dst + kStageTileBytes, &tm_x, fb, c1, w0 * p.step + dw1, h0 * p.step + dh1, n0);
                 }
                 __syncwarp();
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -1140,6 +1188,7 @@ WgradParams wgrad_plan(const trb200_conv_desc& d, int nt, const TileShape& t, in
     WgradParams p;
     p.taps = taps;
     p.tap_base = taps == 1 ? 4 : 0;
+    p.step = 1;
     p.cblocks = d.c / 64;
     p.units = taps * p.cblocks;
     p.m_tiles = (p.units + 1) / 2;
@@ -1308,11 +1357,13 @@ int igemm_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y
 }
 
 // x4 != nullptr: `x` is ignored and the operand rows are built in the kernel from the 4-channel image x4
+// step > 1: d.h, d.w are the extents of dy and x is [n, x_h, x_w, c], read every step-th pixel
 static int wgrad_run(const trb200_conv_desc& d, int taps, const void* dy, const void* x, void* dw, float* partial,
-                     cudaStream_t st, const void* x4 = nullptr) {
+                     cudaStream_t st, const void* x4 = nullptr, int step = 1, int x_h = 0, int x_w = 0) {
     const int nt = pick_nt(d.k);
     const TileShape t = pick_tile(d.n, d.h, d.w, 64);
     WgradParams p = wgrad_plan(d, nt, t, taps);
+    p.step = step;
     p.x4 = static_cast<const uint2*>(x4);
     p.raw_ring = (x4 && raw_ring_fits(t, d.w, x4)) ? 1 : 0;
     CUtensorMap tx, tdy;
@@ -1320,6 +1371,7 @@ static int wgrad_run(const trb200_conv_desc& d, int taps, const void* dy, const 
     if (rc) return rc;
     if (p.raw_ring) rc = make_raw_x4_tmap(&tx, x4, d.n, d.h, d.w, t);
     else if (x4) tx = tdy;      // not used by the kernel
+    else if (step > 1) rc = make_act_tmap_stepped(&tx, x, d.n, x_h, x_w, d.c, t, step, "wgrad x");
     else rc = make_act_tmap(&tx, x, d.n, d.h, d.w, d.c, t, "wgrad x");
     if (rc) return rc;
     if (nt == 256) rc = launch_wgrad<256>(tx, tdy, partial, p, st);
@@ -1362,6 +1414,101 @@ int igemm_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* 
     if (wgrad_use_halo(d)) return wgrad_halo_run(d, dy, x, dw, static_cast<float*>(ws), st);
     if (wgrad_use_unitn(d)) return wgrad_unitn_run(d, dy, x, dw, static_cast<float*>(ws), st);
     return wgrad_run(d, igemm_taps(d), dy, x, dw, static_cast<float*>(ws), st);
+}
+
+// ------------------------------------------------------------------ stride 2 (3x3 pad 1, 1x1 pad 0) without resampling
+// d describes the strided convolution: x is [n, h, w, c], y / dy [n, oh, ow, k] with oh = (h - 1) / 2 + 1.
+// Forward and weight gradient read x through a tensor map that steps two pixels (the tile in shared memory is the
+// stride-1 tile).  The data gradient of the 3x3 case is four stride-1 convolutions of dy, one per parity class of
+// the dx pixel (iy, ix) = (2 ty + py, 2 tx + px): a row tap r contributes when iy + 1 - r is even, i.e. r = 1 for
+// even rows (dy row ty) and r = 0 (dy row ty + 1), r = 2 (dy row ty) for odd rows; the same along w.  The classes
+// use 1, 2, 2 and 4 of the nine taps, so the flop count is that of the forward convolution.
+static bool native_s2_shape(const trb200_conv_desc& d) {
+    const bool k3 = d.r == 3 && d.s == 3 && d.pad_h == 1 && d.pad_w == 1;
+    const bool k1 = d.r == 1 && d.s == 1 && d.pad_h == 0 && d.pad_w == 0;
+    return (k3 || k1) && d.stride_h == 2 && d.stride_w == 2 && d.c % 64 == 0 && d.k % 64 == 0;
+}
+
+bool igemm_s2_supports(const trb200_conv_desc& d, int which) {
+    if (!native_s2_shape(d) || !valid_dtype(d.dtype)) return false;
+    if (which == 1) return d.r == 3 && pick_nt(d.c) != 0;          // the 1x1 data gradient stays with the resampling path
+    return pick_nt(d.k) != 0;
+}
+
+size_t igemm_s2_workspace(const trb200_conv_desc& d, int which) {
+    if (which == 1) return (size_t)align_up((int64_t)9 * d.k * d.c * 2, 256);
+    if (which == 0) {
+        trb200_conv_desc e = d;
+        e.h = (d.h - 1) / 2 + 1; e.w = (d.w - 1) / 2 + 1; e.stride_h = e.stride_w = 1;
+        return wgrad_partial_bytes(e, d.r * d.s);
+    }
+    return 0;
+}
+
+int igemm_s2_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, cudaStream_t st) {
+    ConvRunEx ex;
+    ex.step = 2; ex.in_h = d.h; ex.in_w = d.w;
+    const int oh = (d.h - 1) / 2 + 1, ow = (d.w - 1) / 2 + 1;
+    return conv3x3_run(x, w, 1, y, d.n, oh, ow, d.c, d.k, st, d.r * d.s, nullptr, nullptr, nullptr,
+                       d.dtype == TRB200_DTYPE_BF16, &ex);
+}
+
+int igemm_s2_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* ws, size_t ws_bytes,
+                   cudaStream_t st) {
+    const size_t need = igemm_s2_workspace(d, 0);
+    TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, "conv_wgrad: workspace of %zu bytes needed, %zu given", need,
+                ws_bytes);
+    trb200_conv_desc e = d;
+    e.h = (d.h - 1) / 2 + 1; e.w = (d.w - 1) / 2 + 1; e.stride_h = e.stride_w = 1;
+    return wgrad_run(e, d.r * d.s, dy, x, dw, static_cast<float*>(ws), st, nullptr, 2, d.h, d.w);
+}
+
+// out[j][c][k] = W[k][tap_j][c] for the nine taps in class order
+__global__ void __launch_bounds__(256)
+dgrad_s2_filter_view_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__ out, int kk, int cc) {
+    // class (py, px) = (0,0): tap 4; (0,1): taps 3, 5; (1,0): taps 1, 7; (1,1): taps 0, 2, 6, 8
+    const int order[9] = {4, 3, 5, 1, 7, 0, 2, 6, 8};
+    const int total = 9 * kk * cc;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int k = i % kk, c = (i / kk) % cc, j = i / (kk * cc);
+        out[i] = w[((int64_t)k * 9 + order[j]) * cc + c];
+    }
+}
+
+int igemm_s2_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes,
+                   cudaStream_t st) {
+    const size_t need = igemm_s2_workspace(d, 1);
+    TRB_REQUIRE(ws && ws_bytes >= need, TRB200_ERR_WORKSPACE, "conv_dgrad: workspace of %zu bytes needed, %zu given", need,
+                ws_bytes);
+    const int total = 9 * d.k * d.c;
+    int blocks = (total + 255) / 256;
+    if (blocks > sm_count() * 4) blocks = sm_count() * 4;
+    dgrad_s2_filter_view_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(w), static_cast<uint16_t*>(ws), d.k, d.c);
+    TRB_LAUNCH_CHECK("dgrad_s2_filter_view_kernel");
+    const int oh = (d.h - 1) / 2 + 1, ow = (d.w - 1) / 2 + 1;
+    // a tap's dy offset: r (or s) = 1 -> 0 on the even class; r = 0 -> +1, r = 2 -> 0 on the odd class; nibble = (dw+1) | (dh+1) << 2
+    auto nib = [](int dh, int dw) { return (unsigned long long)((dw + 1) | ((dh + 1) << 2)); };
+    const int first[4] = {0, 1, 3, 5}, count[4] = {1, 2, 2, 4};
+    const unsigned long long offs[4] = {
+        nib(0, 0),                                                             // tap (1,1)
+        nib(0, 1) | nib(0, 0) << 4,                                            // taps (1,0), (1,2)
+        nib(1, 0) | nib(0, 0) << 4,                                            // taps (0,1), (2,1)
+        nib(1, 1) | nib(1, 0) << 4 | nib(0, 1) << 8 | nib(0, 0) << 12};        // taps (0,0), (0,2), (2,0), (2,2)
+    for (int cls = 0; cls < 4; ++cls) {
+        const int py = cls >> 1, px = cls & 1;
+        const int hc = (d.h - py + 1) / 2, wc = (d.w - px + 1) / 2;
+        if (hc <= 0 || wc <= 0) continue;
+        ConvRunEx ex;
+        ex.step = 1; ex.in_h = oh; ex.in_w = ow;
+        ex.tap_offsets = offs[cls];
+        ex.parity = cls; ex.full_h = d.h; ex.full_w = d.w;
+        const uint16_t* view = static_cast<const uint16_t*>(ws) + (size_t)first[cls] * d.k * d.c;
+        // in = dY [n, oh, ow, k], filter view (ci = k, co = c, tap), out = the class's pixels of dX
+        const int rc = conv3x3_run(dy, view, 0, dx, d.n, hc, wc, d.k, d.c, st, count[cls], nullptr, nullptr, nullptr,
+                                   d.dtype == TRB200_DTYPE_BF16, &ex);
+        if (rc) return rc;
+    }
+    return TRB200_OK;
 }
 
 // ------------------------------------------------------------------ classifier GEMMs (gemm_skinny_sm100.cuh)

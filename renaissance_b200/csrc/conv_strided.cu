@@ -1,18 +1,20 @@
 // Stride-2 convolutions (3x3 pad 1 and 1x1 pad 0, the two kinds ResNet-50 has besides its 7x7 stem) on the
-// tensor-core kernels, by way of the stride-1 kernels plus one resampling pass:
+// tensor-core kernels.
+//
+// Channel counts the implicit-GEMM kernels tile (multiples of 64 with 64, 128 or a multiple of 256 on the output
+// side) run without any resampling (conv_igemm_sm100.cu, igemm_s2_*): forward and weight gradient read x through a
+// tensor map that steps two pixels, the 3x3 data gradient is four stride-1 convolutions of dy, one per parity class
+// of the dx pixel, with 1 + 2 + 2 + 4 taps.  What is left takes the stride-1 kernels plus one resampling pass:
 //
 //   3x3 s2 p1   y  = even pixels of the stride-1 convolution of x                 (forward)
 //               dx = stride-1 data gradient of dy with zeros put between its pixels
 //               dW = stride-1 weight gradient of that zero-stuffed dy against x
 //   1x1 s2 p0   y  = 1x1 convolution of the even pixels of x
 //               dW = 1x1 weight gradient of dy against the even pixels of x
-//               dx = 1x1 data gradient of dy, written to the even pixels of a zeroed dx
+//               dx = 1x1 data gradient of dy, written to the even pixels of a zeroed dx   (always this route)
 //
-// The 3x3 route spends four times the flops of a native strided kernel (three of four output pixels of the
-// stride-1 convolution are dropped, three of four dy pixels are zeros), which still is two orders of magnitude
-// faster than the direct CUDA-core kernels these shapes would otherwise take; a network has one such layer per
-// resolution change.  Results equal the strided convolution's exactly up to summation order: the extra terms
-// are exact zeros.
+// The 3x3 resampling route spends four times the flops of the native one.  Results equal the strided convolution's
+// exactly up to summation order: the extra terms are exact zeros.
 //
 // A network's first convolution (4 input channels = RGB + 1 pad, any filter size, stride and padding; ResNet-50's
 // 7x7 stride-2 stem) is lowered instead: every output pixel's receptive field is written out as one row of
@@ -249,6 +251,7 @@ bool strided_supports(const trb200_conv_desc& d, int which) {
 }
 
 size_t strided_workspace(const trb200_conv_desc& d, int which) {
+    if (igemm_s2_supports(d, which)) return igemm_s2_workspace(d, which);
     return temp_bytes(d, which) + (size_t)align_up((int64_t)inner_bytes(d, which), 256);
 }
 
@@ -266,6 +269,7 @@ size_t strided_workspace(const trb200_conv_desc& d, int which) {
 int strided_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* ws, size_t ws_bytes,
                   cudaStream_t st) {
     const int which = 0;
+    if (igemm_s2_supports(d, which)) return igemm_s2_wgrad(d, dy, x, dw, ws, ws_bytes, st);
     TRB_STRIDED_PROLOGUE("conv_wgrad");
     int rc;
     if (is_3x3_s2_p1(d)) {
@@ -281,6 +285,7 @@ int strided_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void
 int strided_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes,
                   cudaStream_t st) {
     const int which = 1;
+    if (igemm_s2_supports(d, which)) return igemm_s2_dgrad(d, dy, w, dx, ws, ws_bytes, st);
     TRB_STRIDED_PROLOGUE("conv_dgrad");
     int rc;
     if (is_3x3_s2_p1(d)) {
@@ -296,6 +301,7 @@ int strided_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void
 int strided_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, void* ws, size_t ws_bytes,
                   cudaStream_t st) {
     const int which = 2;
+    if (igemm_s2_supports(d, which)) return igemm_s2_fprop(d, x, w, y, st);
     TRB_STRIDED_PROLOGUE("conv_fprop");
     int rc;
     if (is_3x3_s2_p1(d)) {

@@ -22,8 +22,6 @@
 
 namespace trb {
 
-__device__ int g_pool_status = 0;   // set when a bounded wait of the ring kernels gives up
-
 namespace {
 
 constexpr int kThreads = 256;
@@ -583,17 +581,6 @@ size_t bnrelu_pool_bwd_workspace(int n, int h, int w, int c) {
     return (size_t)strips * 2 * (size_t)c * sizeof(float);
 }
 
-int pool_status_read_and_clear(int* out) {
-    int v = 0;
-    TRB_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_pool_status, sizeof(int)));
-    if (v != 0) {
-        const int zero = 0;
-        TRB_CUDA_TRY(cudaMemcpyToSymbol(g_pool_status, &zero, sizeof(int)));
-    }
-    *out = v;
-    return TRB200_OK;
-}
-
 int bnrelu_pool_bwd_launch(const void* dy_pooled, const void* argmax, const void* mask_bits, const void* x,
                            const float* gamma, const float* saved_mean, const float* saved_inv_std, void* dconv,
                            float* dgamma, float* dbeta, int n, int h, int w, int c, void* workspace,
@@ -622,7 +609,10 @@ int bnrelu_pool_bwd_launch(const void* dy_pooled, const void* argmax, const void
             attr_done[dev] = true;
         }
         int* status = nullptr;
-        TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_pool_status));
+        {
+            const int rc2 = ring_status_ptr(&status);
+            if (rc2) return rc2;
+        }
         size_t smem = (size_t)kRingStages * rp.stage_bytes;
         if (smem < (size_t)rp.consumers * 64) smem = (size_t)rp.consumers * 64;     // the block's sums at the end
         const int threads = rp.consumers + 32;

@@ -92,3 +92,43 @@ def test_full_size_properties():
     # projections: small compared with the size of the terms they cancel
     scale = float(dym.abs().sum(dim=0).max())
     assert float(dconv.double().sum(dim=0).abs().max()) / scale < 1e-3
+
+
+@pytest.mark.parametrize("m,c,dtype,with_mask", [
+    (592 * 128 + 77, 64, torch.float16, True),       # the smallest tensor on the bulk-copy ring, 77 rows past the last item
+    (80011, 256, torch.float16, True),
+    (40003, 512, torch.float16, False),              # no ReLU behind the BN (mask absent)
+    (592 * 128 + 5, 64, torch.bfloat16, True),
+    (30001, 2048, torch.bfloat16, False),
+])
+def test_ring_kernels_with_ragged_tails(m, c, dtype, with_mask):
+    """Tensors of four or more 1024-vector items per SM run on the bulk-copy ring kernels; rows past the last whole
+    item are handled by one block with plain loads.  Against float64 sums taken by torch on the same GPU; two runs
+    give the same bits."""
+    from renaissance_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(m + c)
+    dy = torch.randn((m, c), generator=g, device="cuda", dtype=torch.float32).to(dtype)
+    x = (torch.randn((m, c), generator=g, device="cuda", dtype=torch.float32) * 1.2 + 0.1).to(dtype)
+    bits = torch.randint(0, 256, (m * c // 8,), generator=g, device="cuda", dtype=torch.int32).to(torch.uint8)
+    gamma = 1 + 0.2 * torch.randn(c, generator=g, device="cuda")
+    mean = x.float().mean(dim=0)
+    inv_std = 1.0 / torch.sqrt(x.float().var(dim=0, unbiased=False) + 1e-5)
+    dconv, dg, db = ops.bnrelu_bwd(dy, bits if with_mask else None, x, gamma, mean, inv_std)
+    dconv2, dg2, db2 = ops.bnrelu_bwd(dy, bits if with_mask else None, x, gamma, mean, inv_std)
+    assert torch.equal(dconv, dconv2) and torch.equal(dg, dg2) and torch.equal(db, db2)
+    if with_mask:
+        shifts = torch.arange(8, device="cuda", dtype=torch.uint8)
+        mask = ((bits.view(-1, 1) >> shifts) & 1).view(m, c).double()
+    else:
+        mask = 1.0
+    dym = dy.double() * mask
+    xhat = (x.double() - mean.double()) * inv_std.double()
+    ref_db = dym.sum(dim=0)
+    ref_dg = (dym * xhat).sum(dim=0)
+    assert float((db.double() - ref_db).abs().max() / ref_db.abs().max()) < 1e-4
+    assert float((dg.double() - ref_dg).abs().max() / ref_dg.abs().max()) < 1e-4
+    ref = gamma.double() * inv_std.double() * (dym - ref_db / m - xhat * ref_dg / m)
+    tol = 2e-3 if dtype == torch.float16 else 1e-2
+    assert float((dconv.double() - ref).norm() / ref.norm()) < tol
+    # the last rows (the ragged tail) on their own
+    assert float((dconv[-100:].double() - ref[-100:]).norm() / ref[-100:].norm()) < tol

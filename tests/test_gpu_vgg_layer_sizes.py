@@ -179,3 +179,19 @@ def test_bn_relu_pool_forward_and_backward_at_benchmark_size(h, c):
     a = relu[i].float().permute(2, 0, 1)[None].requires_grad_(True)
     F.max_pool2d(a, 2).backward(dyp[i].float().permute(2, 0, 1)[None])
     assert torch.equal(dy_full[i], a.grad[0].permute(1, 2, 0).half())
+
+
+@pytest.mark.parametrize("m,c", [(75776 + 3, 64), (9472 * 4 + 1, 512), (20000, 24)])
+def test_bn_apply_relu_mask_ring_and_strip_kernels_bit_exact(m, c):
+    """bn_apply_relu_mask on the bulk-copy ring (tensors of four or more 1024-vector items per SM, here with rows
+    past the last whole item) and on the strip kernel (channel counts the ring does not take): relu output and mask
+    bits equal torch's half(half(x * s) + b) bit for bit."""
+    from renaissance_b200 import ops
+    gen = torch.Generator(device="cuda").manual_seed(m + c)
+    x = (torch.randn((m, c), generator=gen, device="cuda") * 1.2 + 0.1).half()
+    es = 0.5 + torch.rand(c, generator=gen, device="cuda")
+    eb = 0.3 * torch.randn(c, generator=gen, device="cuda")
+    relu, bits = ops.bn_apply_relu_mask(x, es, eb)
+    yb = ((x.float() * es).half().float() + eb).half()
+    assert torch.equal(relu, torch.relu(yb))
+    assert torch.equal(_mask_bits_to_bool(bits, (m, c)), yb > 0)
