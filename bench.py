@@ -327,6 +327,140 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_resnet50(args):
+    """BASELINE.json configuration 4 (ResNet-50, bfloat16, batch 256 per GPU, bucketed all-reduce overlapped with
+    backward) through renaissance_b200/resnet50.py.  Not the headline metric: the reference has no backend for this
+    network, so there is no reference arm and no CPU baseline for it; the line carries the same timing rules."""
+    import torch
+    import torch.distributed as dist
+
+    from renaissance_b200 import ops
+    from renaissance_b200 import resnet50 as R
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world == 1 and args.gpus > 1:
+        raise SystemExit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    batch = args.batch
+    dtype = torch.bfloat16
+    net = R.ResNet50(dtype=dtype, seed=1234)                   # same seed: the ranks start from the same weights
+    gen = torch.Generator().manual_seed(100 + rank)
+    host_images, host_labels, dev_images, dev_labels = [], [], [], []
+    for _ in range(2):
+        img = torch.zeros((batch, IMAGE, IMAGE, 4), dtype=dtype).pin_memory()
+        img[..., :3] = torch.randn((batch, IMAGE, IMAGE, 3), generator=gen).to(dtype)
+        host_images.append(img)
+        host_labels.append(torch.randint(0, CLASSES, (batch,), generator=gen, dtype=torch.int32).pin_memory())
+        dev_images.append(img.cuda())
+        dev_labels.append(host_labels[-1].cuda())
+    copy_stream = torch.cuda.Stream()
+
+    for i in range(args.warmup):
+        net.step(dev_images[i & 1], dev_labels[i & 1])
+    ops.device_status()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    net.timing_bn = []
+    launches0 = ops.kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        loss = net.step(dev_images[i & 1], dev_labels[i & 1])
+    e1.record()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    launches = ops.kernel_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    bn_events = net.timing_bn
+    net.timing_bn = None
+    ops.device_status()
+    ms_per_step = ms_total / args.steps
+    value = world * batch * args.steps / (ms_total / 1e3)
+
+    # the dominant kernels of this network are the BN backward sweeps (HBM-bound): 53 launches groups per step,
+    # bracketed by CUDA events inside the timed region; 10.25 B per element with a ReLU mask, 10 without
+    peaks = measured_peaks()
+    bn_ms = sum(ev[0].elapsed_time(ev[1]) for ev, _, _ in bn_events)
+    bn_bytes = sum((10.25 if masked else 10.0) * elems for _, elems, masked in bn_events)
+    n_l = max(len(bn_events), 1)
+    achieved = bn_bytes / (bn_ms / 1e3) / 1e9 if bn_ms > 0 else 0.0
+    roofline = dict(kernel="bnrelu_bwd (reduce + finalize + apply; 53 per step)", bound="hbm", achieved=round(achieved, 1),
+                    peak=peaks["hbm_gbs"], unit="GB/s", frac=round(achieved / peaks["hbm_gbs"], 4),
+                    peak_source=peaks["source"], bytes_per_launch=bn_bytes / n_l, ms_per_launch=bn_ms / n_l,
+                    launches_timed=len(bn_events), traffic=None)
+
+    # end to end: the step's batch copied from pinned host memory (double buffered), the loss read back every step
+    barrier()
+    t0 = time.perf_counter()
+    done = [torch.cuda.Event(), torch.cuda.Event()]
+    with torch.cuda.stream(copy_stream):
+        dev_images[0].copy_(host_images[0], non_blocking=True)
+        dev_labels[0].copy_(host_labels[0], non_blocking=True)
+        done[0].record()
+    for i in range(args.steps):
+        sl = i & 1
+        if i + 1 < args.steps:
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_stream(torch.cuda.current_stream())      # the slot's previous step has finished with it
+                dev_images[sl ^ 1].copy_(host_images[sl ^ 1], non_blocking=True)
+                dev_labels[sl ^ 1].copy_(host_labels[sl ^ 1], non_blocking=True)
+                done[sl ^ 1].record()
+        torch.cuda.current_stream().wait_event(done[sl])
+        l = net.step(dev_images[sl], dev_labels[sl])
+        _ = float(l.item())
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    h2d = host_images[0].numel() * 2 + host_labels[0].numel() * 4
+    e2e = dict(value=round(world * batch * args.steps / e2e_s, 1), unit=UNIT, h2d_bytes_per_step=h2d, d2h_bytes_per_step=4)
+
+    identical = None
+    if world > 1:
+        chk = torch.stack([net.w32.double().sum(), net.w32.double().abs().sum()])
+        lo, hi = chk.clone(), chk.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        if not bool(torch.equal(lo, hi)):
+            raise SystemExit(f"rank {rank}: master weights differ between ranks after the all-reduced update")
+        identical = True
+    if rank == 0:
+        line = dict(metric="resnet50_fwd_bwd_images_per_sec", value=round(value, 1), unit=UNIT, n_gpus=world,
+                    steps=args.steps, warmup=args.warmup, ms_per_step=round(ms_per_step, 3), higher_is_better=True,
+                    scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
+                    config=dict(workload="ResNet-50 (bottleneck 3-4-6-3) bf16 fwd+bwd+allreduce+SGD-momentum, NHWC "
+                                         "224x224x3(+1 pad), batch 256/GPU, loss scale 1024, 25 MB buckets; not the "
+                                         "headline configuration",
+                                global_batch=world * batch, parallelism=f"dp{world}",
+                                l2="activations (>10 GB per step) far exceed the 126 MB L2; no flush needed",
+                                loss=round(float(loss.item()), 4)),
+                    clocks=clocks, e2e=e2e, gpu_launches=int(launches // args.steps), roofline=roofline)
+        if identical is not None:
+            line["weights_identical_on_all_ranks"] = identical
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def cpu_baseline(sample_batch=1, repeats=1):
     """Times the CPU oracle's VGG16-BN step (all host threads) on `sample_batch` images."""
     from oracle import oracle as orc
@@ -384,11 +518,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU (the metric is quoted at 256)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="vgg16bn", choices=["vgg16bn", "resnet50"],
+                    help="vgg16bn: the headline configuration; resnet50: BASELINE configuration 4 (information only)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "resnet50":
+        run_resnet50(args)
     else:
         run_ours(args)
 
