@@ -67,15 +67,19 @@ def test_tensor_core_coverage_rule(lib):
         assert lib.trb200_conv_uses_tensor_cores(C.byref(vgg), which) == 1
         # the 4-channel first layer: weight gradient and forward only (it has no data gradient)
         assert lib.trb200_conv_uses_tensor_cores(C.byref(first), which) == (0 if which == 1 else 1)
-        # stride 2 goes through the stride-1 kernel and a resampling pass; 1x1 is the same kernel with one tap
+        # stride 2 runs on the same kernels through stepped tensor maps / parity classes; 1x1 is one tap
         assert lib.trb200_conv_uses_tensor_cores(C.byref(strided), which) == 1
         assert lib.trb200_conv_uses_tensor_cores(C.byref(one_by_one), which) == 1
         # a 7x7 first layer is lowered to rows and run as a 1x1 convolution (no data gradient)
         assert lib.trb200_conv_uses_tensor_cores(C.byref(stem), which) == (0 if which == 1 else 1)
         for direct in (stride_three, odd):
             assert lib.trb200_conv_uses_tensor_cores(C.byref(direct), which) == 0
-    # a strided layer needs room for the resampled tensor
-    assert lib.trb200_conv_dgrad_workspace_bytes(C.byref(strided)) >= 8 * 56 * 56 * 64 * 2
+    # the strided data gradient needs room for its filter view (nine taps in parity-class order)
+    assert lib.trb200_conv_dgrad_workspace_bytes(C.byref(strided)) >= 9 * 64 * 64 * 2
+    # channel counts the tiled kernels do not cover fall back to the stride-1 kernel plus a resampled tensor
+    wide = _lib.ConvDesc(8, 56, 56, 64, 192, 3, 3, 1, 1, 2, 2)
+    if lib.trb200_conv_uses_tensor_cores(C.byref(wide), 0):
+        assert lib.trb200_conv_wgrad_workspace_bytes(C.byref(wide)) >= 8 * 56 * 56 * 192 * 2
     bad = _lib.ConvDesc(8, 56, 56, 64, 64, 3, 3, 1, 1, 1, 1, 7)
     assert lib.trb200_conv_wgrad_workspace_bytes(C.byref(bad)) == 0        # unknown dtype
 
