@@ -130,8 +130,8 @@ int trb200_bnrelu_bwd_static(const void* dy, const void* mask_bits, const void* 
 /* 16-bit in (d->dtype), float accumulate, 16-bit out, fixed-order split      */
 /* reduction.  3x3 pad 1 and 1x1 pad 0 at stride 1 or 2 with c and k          */
 /* multiples of 64 (k = 64, 128 or a multiple of 256), and half 3x3 stride 1  */
-/* with c = 4, run on the tcgen05 kernels (stride 2 through the stride-1      */
-/* kernel and a resampling pass); every other geometry on the direct kernels. */
+/* with c = 4, run on the tcgen05 kernels (stride 2 through tensor maps that   */
+/* step two pixels); every other geometry on the direct kernels.              */
 /* Replaces build_cbr_conv_amp_wgrad_graph + execute,                         */
 /* src/backend/ops/dtensor/cbr_op.cpp:763-840, 1431-1468.                     */
 /* ------------------------------------------------------------------------- */

@@ -901,17 +901,19 @@ struct WgradParams {
 
 template <int NT, bool IM2COL = false>
 struct WgradSmem {
-    static constexpr int kABytes = 2 * kStageTileBytes;            // two units
+    // two units; the first-layer variant has a single unit, stored once: the descriptor's block offset of 0 makes the
+    // second 64-row block of the M = 128 operand read the same tile
+    static constexpr int kABytes = (IM2COL ? 1 : 2) * kStageTileBytes;
     static constexpr int kBBytes = (NT / 64) * kStageTileBytes;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kRawBytes = IM2COL ? kRawStages * kRawStageBytes : 0;
     static constexpr int kStagesRaw = (kSmemBudget - 2048 - kRawBytes) / kStageBytes;
     // the first-layer builder groups take stages in turn: a ring of 8 or 4 keeps every stage with one group
-    static constexpr int kStages = kStagesRaw >= 8 ? 8 : (IM2COL && kStagesRaw >= 4 ? 4 : kStagesRaw);
+    static constexpr int kStages = (IM2COL && kStagesRaw >= 12) ? 12 : (kStagesRaw >= 8 ? 8 : (IM2COL && kStagesRaw >= 4 ? 4 : kStagesRaw));
     static constexpr int kTotal = kStages * kStageBytes + kRawBytes + 2048;
 };
 
-// IM2COL: 8 more warps (four groups of 64 threads) build the A tiles (one unit, written twice) from the 4-channel image.
+// IM2COL: 8 more warps (four groups of 64 threads) build the A tiles (one unit, read twice by the MMA) from the 4-channel image.
 template <int NT, bool IM2COL>
 __global__ void __launch_bounds__(IM2COL ? kThreads + kBuilderThreads : kThreads, 1)
 wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dy,
@@ -920,7 +922,12 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     constexpr int kStages = L::kStages;
     constexpr int kBBlocks = NT / 64;                       // 64-channel boxes of dy per stage
     constexpr int kBProducers = kBBlocks >= 2 ? 2 : 1;
-    constexpr uint32_t kTmemCols = NT < 32 ? 32 : NT;
+    // first-layer variant: a stage is only 64 pixels x 128 bytes of dy, and one thread issues four MMAs, a commit and a
+    // wait per stage at about the rate HBM delivers the stages; two issuing warps on alternate stages, each with its
+    // own accumulator (added up in the epilogue), lift that ceiling
+    constexpr int kIssuers = (IM2COL && kBProducers == 1) ? 2 : 1;      // warp 3 is free when one warp loads dy
+    static_assert(kStages % kIssuers == 0, "a stage keeps its issuer");
+    constexpr uint32_t kTmemCols = (NT < 32 ? 32 : NT) * kIssuers;
     extern __shared__ unsigned char smem_dyn[];
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     const uint32_t a_base = base;
@@ -940,7 +947,7 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             mbar_init(full0 + 8u * s, (IM2COL ? 64 : 1) + kBProducers);
             mbar_init(empty0 + 8u * s, 1);
         }
-        mbar_init(done_bar, 1);
+        mbar_init(done_bar, kIssuers);
         if (IM2COL)
             for (int s = 0; s < kRawStages; ++s) { mbar_init(rfull0 + 8u * s, 1); mbar_init(rempty0 + 8u * s, 64); }
         fence_barrier_init();
@@ -971,7 +978,7 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
     if (IM2COL && warp >= 8) {
         // A-tile builders: thread = one of the stage's 64 pixels; both 64-row halves of the M = 128
-        // operand get the same rows (there is a single (tap, channel) unit)
+        // operand read the same rows (there is a single (tap, channel) unit)
         // group g takes the block's stages g, g + 4, ...
         constexpr int kGroups = kBuilderThreads / 64;
         static_assert(!IM2COL || kStages % kGroups == 0, "a stage keeps its builder group");
@@ -995,7 +1002,6 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 }
                 if (!mbar_wait_relaxed(empty0 + 8u * stage, phase ^ 1u, abort_flag, status, kStatusProducerTimeout)) break;
                 store_im2col_row_c4(t, a_dst, row);
-                store_im2col_row_c4(t, a_dst + kStageTileBytes, row);
                 if (p.raw_ring) mbar_arrive(rempty0 + 8u * (uint32_t)(it % kRawStages));
                 fence_proxy_async_smem();
                 mbar_arrive(full0 + 8u * stage);
@@ -1067,16 +1073,18 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 if (w0 >= w_end) { w0 = 0; h0 += p.bh; if (h0 >= h_end) { h0 = 0; n0 += p.bn; } }
             }
         }
-    } else if (warp == 1) {
-        {                                                  // MMA issuer
+    } else if (warp == 1 || (kIssuers == 2 && warp == 3)) {
+        {                                                  // MMA issuer(s): issuer i takes stages i, i + kIssuers, ...
+            const int issuer = warp == 1 ? 0 : 1;
             const uint32_t idesc = idesc_f16(128, NT, true, true) | (p.bf16 ? idesc_ab_bf16() : 0u);
             // MN-major: 64-element blocks of M/N are one 8 KB tile apart, 8 pixels are 1024 bytes apart
             constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
-            const uint32_t a_lo0 = smem_desc_lo(a_base, kStageTileBytes), b_lo0 = smem_desc_lo(b_base, kStageTileBytes);
-            uint32_t stage = 0, phase = 0;
+            const uint32_t a_lo0 = smem_desc_lo(a_base, IM2COL ? 0 : kStageTileBytes), b_lo0 = smem_desc_lo(b_base, kStageTileBytes);
+            const uint32_t d_tmem = tmem_base + (uint32_t)(issuer * NT);
+            uint32_t stage = (uint32_t)issuer, phase = 0;
             uint32_t accumulate = 0;
             bool ok = true;
-            for (int pt = pt0; pt < pt1; ++pt) {
+            for (int pt = pt0 + issuer; pt < pt1; pt += kIssuers) {
                 ok = mbar_wait(full0 + 8u * stage, phase, abort_flag, status, kStatusMmaTimeout);
                 if (!ok) break;
                 tc_fence_after();
@@ -1084,15 +1092,16 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 const uint32_t b_lo = b_lo0 + stage * (L::kBBytes >> 4);
                 // 4 x (K = 16 pixels = 2048 bytes: +128 in the address field)
                 if (lane == 0) {
-                    umma_f16_lohi(tmem_base, a_lo, desc_hi, b_lo, desc_hi, idesc, accumulate);
-                    umma_f16_lohi(tmem_base, a_lo + 128, desc_hi, b_lo + 128, desc_hi, idesc, 1u);
-                    umma_f16_lohi(tmem_base, a_lo + 256, desc_hi, b_lo + 256, desc_hi, idesc, 1u);
-                    umma_f16_lohi(tmem_base, a_lo + 384, desc_hi, b_lo + 384, desc_hi, idesc, 1u);
+                    umma_f16_lohi(d_tmem, a_lo, desc_hi, b_lo, desc_hi, idesc, accumulate);
+                    umma_f16_lohi(d_tmem, a_lo + 128, desc_hi, b_lo + 128, desc_hi, idesc, 1u);
+                    umma_f16_lohi(d_tmem, a_lo + 256, desc_hi, b_lo + 256, desc_hi, idesc, 1u);
+                    umma_f16_lohi(d_tmem, a_lo + 384, desc_hi, b_lo + 384, desc_hi, idesc, 1u);
                     umma_commit(empty0 + 8u * stage);
                 }
                 __syncwarp();
                 accumulate = 1u;
-                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                stage += kIssuers;
+                if (stage >= (uint32_t)kStages) { stage -= kStages; phase ^= 1u; }
             }
             if (ok && lane == 0) umma_commit(done_bar);
             __syncwarp();
@@ -1109,6 +1118,13 @@ wgrad_igemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                     uint32_t v[32];
                     tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
                     tmem_ld_wait();
+                    if (kIssuers == 2 && pt1 - pt0 >= 2) {     // the second issuer's accumulator (it has seen a stage)
+                        uint32_t v2[32];
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(NT + c0), v2);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
+                    }
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
                         reinterpret_cast<float4*>(dst + c0)[j] =
