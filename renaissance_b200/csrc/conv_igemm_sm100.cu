@@ -320,7 +320,8 @@ template <int NT> __host__ __device__ constexpr int conv3x3_a_producers() { retu
 // the 256-row filter tile is fetched as two 128-row boxes by two warps (warp 2 and warp 8)
 template <int NT, bool IM2COL> __host__ __device__ constexpr int conv3x3_b_split() { return (NT == 256 && !IM2COL) ? 2 : 1; }
 template <int NT, bool IM2COL> __host__ __device__ constexpr int conv3x3_threads() {
-    return IM2COL ? kThreads + kBuilderThreads : (NT == 64 ? kThreads + 64 : (NT == 256 ? kThreads + 32 : kThreads));
+    // IM2COL: 8 builder warps and, for 64 filters, a second group of 4 epilogue warps
+    return IM2COL ? kThreads + kBuilderThreads + (NT == 64 ? 128 : 0) : (NT == 64 ? kThreads + 64 : (NT == 256 ? kThreads + 32 : kThreads));
 }
 
 // IM2COL: 8 more warps (two groups of 128 threads) build the A tiles from the 4-channel image instead of TMA.
@@ -347,13 +348,17 @@ conv3x3_igemm_body(const CUtensorMap& tm_in, const CUtensorMap& tm_w, const CUte
     const uint32_t rfull0 = bar_base + 8u * (2 * kStages + 4), rempty0 = rfull0 + 8u * kRawStages;
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
-    __shared__ int s_epi_fail;
-    __shared__ uint32_t s_valid[4];      // STATS: which of the tile's 128 rows are real pixels
+    // First-layer variant: a tile is one K step, so the kernel runs at the pace of its epilogue (~1300 clocks per
+    // 128-pixel tile for TMEM -> half -> staging -> TMA store and the channel sums).  Two epilogue groups of four warps
+    // take alternate tiles, each with its own accumulator, staging buffer and named barriers.
+    constexpr int kEpiGroups = (IM2COL && NT == 64) ? 2 : 1;
+    __shared__ int s_epi_fail[2];
+    __shared__ uint32_t s_valid[2][4];   // STATS: which of the tile's 128 rows are real pixels
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         s_abort = 0;
-        s_epi_fail = 0;
+        s_epi_fail[0] = 0; s_epi_fail[1] = 0;
         // a stage is full once its B tile has landed and its A tile has (one TMA box, or 128 built rows)
         for (int s = 0; s < kStages; ++s) { mbar_init(full0 + 8u * s, IM2COL ? 129 : 1 + conv3x3_b_split<NT, IM2COL>()); mbar_init(empty0 + 8u * s, 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), kEpiThreads); }
@@ -386,7 +391,7 @@ conv3x3_igemm_body(const CUtensorMap& tm_in, const CUtensorMap& tm_w, const CUte
     // only the instructions that must come from one thread are predicated on lane 0: the
     // compiler can then keep addresses, coordinates and descriptors in uniform registers,
     // which is where the TMA and MMA instructions take them from.
-    if (IM2COL && warp >= 8) {
+    if (IM2COL && warp >= 8 && warp < 8 + kBuilderThreads / 32) {
         // A-tile builders: thread = one pixel row of the tile, one K step (= one stage) per tile;
         // group g takes the block's tiles g, g + 2, ...
         constexpr int kGroups = kBuilderThreads / 128;
@@ -548,24 +553,27 @@ conv3x3_igemm_body(const CUtensorMap& tm_in, const CUtensorMap& tm_w, const CUte
             }
             __syncwarp();
         }
-    } else if (warp >= 4 && warp < 8) {
-        // epilogue: warp w may touch TMEM lanes [32*(w%4), +32)
+    } else if ((warp >= 4 && warp < 8) || (kEpiGroups == 2 && warp >= 16)) {
+        // epilogue: warp w may touch TMEM lanes [32*(w%4), +32).  Group eg takes the block's tiles eg, eg + kEpiGroups, ...
+        const int eg = (kEpiGroups == 2 && warp >= 16) ? 1 : 0;
+        const int et = (int)threadIdx.x - (eg ? 512 : 128);     // thread of the group
+        const int bar_a = 1 + 2 * eg, bar_b = 2 + 2 * eg;        // the group's named barriers
         const int q = warp & 3;
         const int row = q * 32 + lane;             // pixel of the tile = TMEM lane
-        const bool leader = threadIdx.x == 128;    // first epilogue thread issues the TMA stores
-        int iter = 0;
+        const bool leader = et == 0;               // first thread of the group issues its TMA stores
+        int iter = eg;
         int chunk_count = 0;
         // STATS: thread (16-byte column st_cc, row group st_rg) adds its 8 channels of every 64-channel
         // chunk over 8 rows of the half-rounded tile in shared memory; the sums run over all tiles of
         // this block and meet once, in row-group order, when the block is done
-        const int st_cc = (threadIdx.x - 128) & 7, st_rg = (threadIdx.x - 128) >> 3;
+        const int st_cc = et & 7, st_rg = et >> 3;
         float run_s[NT / 64][8], run_q[NT / 64][8];
 #pragma unroll
         for (int i = 0; i < NT / 64; ++i)
 #pragma unroll
             for (int e = 0; e < 8; ++e) { run_s[i][e] = 0.f; run_q[i][e] = 0.f; }
         RT_DECL;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
+        for (int tile = blockIdx.x + eg * gridDim.x; tile < total_tiles; tile += kEpiGroups * gridDim.x, iter += kEpiGroups) {
             const int acc = iter & 1;
             const int nt = tile % p.n_tiles, mt = tile / p.n_tiles;
             const int w0 = (mt % p.tw) * p.bw, h0 = ((mt / p.tw) % p.th) * p.bh;
@@ -576,23 +584,27 @@ conv3x3_igemm_body(const CUtensorMap& tm_in, const CUtensorMap& tm_w, const CUte
                 const int bx = row & (p.bw - 1), by = (row >> p.lbw) & (p.bh - 1), bi = row >> (p.lbw + p.lbh);
                 const bool real = (w0 + bx < p.ext_w) && (h0 + by < p.ext_h) && (n0 + bi < p.ext_n);
                 const uint32_t m = __ballot_sync(0xffffffffu, real);
-                if (lane == 0) s_valid[q] = m;
+                if (lane == 0) s_valid[eg][q] = m;
             }
             if (!mbar_wait_relaxed(tfull_bar(acc), ((uint32_t)iter >> 1) & 1u, abort_flag, status, kStatusEpilogueTimeout))
-                s_epi_fail = 1;
-            // the 128 epilogue threads must take the same decision: they meet at named barriers below
-            named_barrier(2, kEpiThreads);
+                s_epi_fail[eg] = 1;
+            // the 128 threads of the group must take the same decision: they meet at named barriers below
+            named_barrier(bar_b, kEpiThreads);
             RT_ADD(0);
-            if (*(volatile int*)&s_epi_fail) break;
+            if (*(volatile int*)&s_epi_fail[eg]) break;
             tc_fence_after();
             uint32_t vm = 0xffu;      // which of this thread's 8 rows are real pixels
-            if (STATS && p.has_padding) vm = (s_valid[st_rg >> 2] >> ((st_rg & 3) * 8)) & 0xffu;
+            if (STATS && p.has_padding) vm = (s_valid[eg][st_rg >> 2] >> ((st_rg & 3) * 8)) & 0xffu;
 #pragma unroll
             for (int chunk = 0; chunk < NT / 64; ++chunk, ++chunk_count) {
-                const uint32_t buf = epi_base + (uint32_t)(chunk_count & 1) * kATileBytes;
+                // one group: two staging buffers in turn; two groups: one buffer each
+                const uint32_t buf = epi_base + (uint32_t)(kEpiGroups == 2 ? eg : (chunk_count & 1)) * kATileBytes;
                 RT_ADD(2);
-                if (leader) tma_store_wait_read<1>();     // the store that last read this buffer is done
-                named_barrier(1, kEpiThreads);
+                if (leader) {                              // the store that last read this buffer is done
+                    if (kEpiGroups == 2) tma_store_wait_read<0>();
+                    else tma_store_wait_read<1>();
+                }
+                named_barrier(bar_a, kEpiThreads);
                 RT_ADD(1);
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * NT + chunk * 64);
                 uint32_t v0[32], v1[32];
@@ -616,7 +628,7 @@ conv3x3_igemm_body(const CUtensorMap& tm_in, const CUtensorMap& tm_w, const CUte
                                  : "memory");
                 }
                 fence_proxy_async_smem();
-                named_barrier(1, kEpiThreads);
+                named_barrier(bar_a, kEpiThreads);
                 if (leader) {
                     tma_store_4d(&tm_out, buf, nt * NT + chunk * 64, w0, h0, n0);
                     tma_store_commit();
@@ -650,10 +662,13 @@ conv3x3_igemm_body(const CUtensorMap& tm_in, const CUtensorMap& tm_w, const CUte
             mbar_arrive(tempty_bar(acc));
         }
         if (leader) tma_store_wait_all();
-        if (STATS && !*(volatile int*)&s_epi_fail) {
-            // the 16 row groups meet through the (now idle) output staging buffers: red[rg][sum | sumsq][NT]
-            named_barrier(1, kEpiThreads);
-            float* red = reinterpret_cast<float*>(smem_dyn + (epi_base - smem_u32(smem_dyn)));
+        if (STATS) {
+            // the row groups meet through the (now idle) output staging buffers: red[rg][sum | sumsq][NT], one buffer
+            // per epilogue group.  Every epilogue thread reaches these barriers, also after a failed wait.
+            named_barrier(bar_a, kEpiThreads);
+            float* red = reinterpret_cast<float*>(smem_dyn + (epi_base - smem_u32(smem_dyn))) +
+                         (kEpiGroups == 2 ? (size_t)eg * (kATileBytes / 4) : 0);
+            static_assert(kEpiGroups == 1 || 16 * 2 * NT * 4 <= kATileBytes, "a group's sums fit its staging buffer");
 #pragma unroll
             for (int i = 0; i < NT / 64; ++i) {
                 float4* ds = reinterpret_cast<float4*>(red + (st_rg * 2) * NT + i * 64 + st_cc * 8);
@@ -663,19 +678,28 @@ conv3x3_igemm_body(const CUtensorMap& tm_in, const CUtensorMap& tm_w, const CUte
                 dq[0] = make_float4(run_q[i][0], run_q[i][1], run_q[i][2], run_q[i][3]);
                 dq[1] = make_float4(run_q[i][4], run_q[i][5], run_q[i][6], run_q[i][7]);
             }
-            named_barrier(1, kEpiThreads);
+            if (kEpiGroups == 2) named_barrier(5, 2 * kEpiThreads);     // both groups' sums are in place
+            else named_barrier(bar_a, kEpiThreads);
+            const bool failed = *(volatile int*)&s_epi_fail[0] || *(volatile int*)&s_epi_fail[1];
             // this block only ever sees one N tile (the grid is a multiple of n_tiles)
             const int strip = blockIdx.x / p.n_tiles;
             const int ch0 = (blockIdx.x % p.n_tiles) * NT;
-            for (int ch = threadIdx.x - 128; ch < NT; ch += kEpiThreads) {
-                float s1 = 0.f, s2 = 0.f;
+            if (eg == 0 && !failed) {
+                const float* red0 = reinterpret_cast<const float*>(smem_dyn + (epi_base - smem_u32(smem_dyn)));
+                for (int ch = et; ch < NT; ch += kEpiThreads) {
+                    float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-                for (int g = 0; g < 16; ++g) {
-                    s1 += red[(g * 2) * NT + ch];
-                    s2 += red[(g * 2 + 1) * NT + ch];
+                    for (int gq = 0; gq < kEpiGroups; ++gq) {
+                        const float* rg = red0 + (size_t)gq * (kATileBytes / 4);
+#pragma unroll
+                        for (int g = 0; g < 16; ++g) {
+                            s1 += rg[(g * 2) * NT + ch];
+                            s2 += rg[(g * 2 + 1) * NT + ch];
+                        }
+                    }
+                    p.stats_partial[((size_t)strip * 2) * p.cout + ch0 + ch] = s1;
+                    p.stats_partial[((size_t)strip * 2 + 1) * p.cout + ch0 + ch] = s2;
                 }
-                p.stats_partial[((size_t)strip * 2) * p.cout + ch0 + ch] = s1;
-                p.stats_partial[((size_t)strip * 2 + 1) * p.cout + ch0 + ch] = s2;
             }
         }
         RT_ADD(2);
