@@ -118,6 +118,58 @@ def conv_flops_per_step(batch):
     return total
 
 
+def config2_block(peaks_burst_tflops, hbm_gbs, iters=7):
+    """BASELINE.json configuration 2 beside the step: one Conv3x3(64 -> 64) + BN + ReLU block backward at batch 256,
+    56 x 56, through trb200_cbr_bwd on its three streams; CUDA events, a 512 MB write between calls (L2 flushed),
+    median.  ideal = the two convolutions' flop at the measured burst tensor peak (the block is timed alone) + the BN
+    backward's 10.25 B/element at the measured copy bandwidth."""
+    import torch
+    from renaissance_b200 import ops
+    n, h, c, k = 256, 56, 64, 64
+    geo = ops.ConvGeometry(n, h, h, c, k)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn((n, h, h, c), generator=g, device="cuda").half()
+    w = (torch.randn((k, 3, 3, c), generator=g, device="cuda") * (2.0 / (9 * c)) ** 0.5).half()
+    dy = torch.randn((n, h, h, k), generator=g, device="cuda").half()
+    conv_out = torch.randn((n, h, h, k), generator=g, device="cuda").half()
+    bits = torch.randint(0, 256, (n * h * h * k // 8,), generator=g, device="cuda", dtype=torch.int32).to(torch.uint8)
+    gamma = torch.ones(k, device="cuda")
+    mean = conv_out.float().mean(dim=(0, 1, 2))
+    inv = 1.0 / torch.sqrt(conv_out.float().var(dim=(0, 1, 2), unbiased=False) + 1e-5)
+    scratch = torch.empty_like(dy)
+    dw = torch.empty_like(w)
+    st = ops.BlockStreams.create()
+    flush = torch.empty(512 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+
+    def call():
+        with torch.cuda.stream(st.bn):
+            ops.cbr_amp_bwd(geo, dy, w, gamma, mean, inv, bits, x, conv_out, bn_scratch=scratch, dw=dw, streams=st)
+        torch.cuda.current_stream().wait_stream(st.bn)
+
+    torch.cuda.current_stream().wait_stream(st.bn)
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        call()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ops.device_status()
+    med = statistics.median(ts)
+    flop = 2 * 2.0 * n * h * h * c * k * 9
+    byt = 10.25 * n * h * h * k
+    ideal = flop / peaks_burst_tflops / 1e9 + byt / hbm_gbs / 1e6
+    return dict(workload="Conv3x3 64->64 + BN + ReLU block backward, batch 256, 56x56, fp16", ms=round(med, 4),
+                ideal_ms=round(ideal, 4), frac=round(ideal / med, 4),
+                note="ideal = conv flop at the measured burst tensor peak + BN bytes at the measured copy bandwidth")
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -301,6 +353,18 @@ def run_ours(args):
                              f"(checksum min {lo.tolist()} max {hi.tolist()})")
         comm["weights_identical_on_all_ranks"] = True
 
+    # ---------------- BASELINE configuration 2 (the single block backward) beside the step, single GPU run only
+    block2 = None
+    if rank == 0 and world == 1:
+        burst = peaks["tflops"]
+        path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(path):
+            with open(path) as f:
+                burst = json.load(f).get("bf16_tflops", burst)
+        del tr
+        torch.cuda.empty_cache()
+        block2 = config2_block(burst, peaks["hbm_gbs"])
+
     # ---------------- CPU baseline beside it (rank 0, single GPU run only): the oracle's step on host cores
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -318,6 +382,8 @@ def run_ours(args):
                                 loss=round(loss_value, 4)),
                     clocks=clocks, e2e=e2e, gpu_launches=int(launches // args.steps), roofline=roofline,
                     roofline_hot_path=roofline_hot_path, value_second_region=round(value_again, 1))
+        if block2 is not None:
+            line["roofline_hot_path"]["config2_block"] = block2
         if comm is not None:
             line["comm"] = comm
         if cpu is not None:
