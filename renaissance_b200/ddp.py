@@ -41,10 +41,6 @@ class GradientBuckets:
         # "after": every bucket only once backward has finished; "skip": no all-reduce at all.  The last two exist
         # for the benchmark's diagnostics of what the collective costs.
         self.mode = "overlap"
-        # On a GPU the casts, scales and all-reduce launches of a bucket go to a side stream that waits for the work
-        # enqueued so far: the ~10 us cast kernels then run beside the backward kernels instead of between them.
-        self.side = torch.cuda.Stream(device=g32.device) if g32.is_cuda else None
-        self._ready = torch.cuda.Event() if g32.is_cuda else None
 
     def begin_step(self):
         self.next = 0
@@ -53,20 +49,9 @@ class GradientBuckets:
 
     def mark_ready(self, upto: int, final: bool = False):
         """Backward has produced every half gradient below element `upto`."""
+        inv = 1.0 / self.world
         if self.mode == "after" and not final:
             return
-        if not final and (self.next >= len(self.buckets) or self.buckets[self.next][1] > upto):
-            return                                              # no bucket completes at this mark
-        if self.side is None:
-            self._issue(upto, final)
-            return
-        self._ready.record()                                    # on the current stream: everything produced so far
-        with torch.cuda.stream(self.side):
-            self.side.wait_event(self._ready)
-            self._issue(upto, final)
-
-    def _issue(self, upto: int, final: bool):
-        inv = 1.0 / self.world
         if final and self.world > 1 and self.half_numel < self.g32.numel():
             self.scale(self.g32[self.half_numel:], inv)         # float-born gradients: mean folded in here
         while self.next < len(self.buckets):
@@ -87,5 +72,3 @@ class GradientBuckets:
         for w in self.works:
             w.wait()
         self.works = []
-        if self.side is not None:
-            torch.cuda.current_stream().wait_stream(self.side)
