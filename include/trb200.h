@@ -339,6 +339,13 @@ int trb200_fc_amp_fwd(const void* x, const void* w, const float* bias, void* y,
                       int32_t relu, float dropout_p, uint64_t seed, uint64_t offset,
                       void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same with x, w and y in d-type `dtype` (TRB200_DTYPE_F16 or TRB200_DTYPE_BF16): the classifier of a bfloat16
+ * network (BASELINE configuration 4; the reference has no counterpart). */
+int trb200_fc_amp_fwd_dtype(const void* x, const void* w, const float* bias, void* y,
+                            int32_t batch, int32_t in_features, int32_t out_features,
+                            int32_t relu, float dropout_p, uint64_t seed, uint64_t offset, int32_t dtype,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
 /* dz = act > 0 ? da * scale : 0 for n half elements, where `act` is the OUTPUT of
  * trb200_fc_amp_fwd with relu and/or dropout (zero exactly where the ReLU or the
  * dropout zeroed it) and scale = 1 / (1 - dropout_p).  dz may be da. */
@@ -357,6 +364,11 @@ int trb200_fc_amp_bwd(const void* dy, const void* w, const void* x, void* dx, vo
                       float* db, const void* act, float act_scale,
                       int32_t batch, int32_t in_features, int32_t out_features,
                       void* workspace, size_t workspace_bytes, void* stream);
+/* ... with dy, w, x, dx, act (and dW unless dw_float) in d-type `dtype`. */
+int trb200_fc_amp_bwd_dtype(const void* dy, const void* w, const void* x, void* dx, void* dw, int32_t dw_float,
+                            float* db, const void* act, float act_scale,
+                            int32_t batch, int32_t in_features, int32_t out_features, int32_t dtype,
+                            void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------- */
 /* Kernels either side of the gradient all-reduce (the collective itself is   */

@@ -128,6 +128,9 @@ def load() -> C.CDLL:
         "trb200_fc_amp_fwd": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, i32, f32, C.c_uint64, C.c_uint64, vp, sz, vp]),
         "trb200_fc_act_bwd": (C.c_int, [vp, vp, vp, i64, f32, vp]),
         "trb200_fc_amp_bwd": (C.c_int, [vp, vp, vp, vp, vp, i32, vp, vp, f32, i32, i32, i32, vp, sz, vp]),
+        "trb200_fc_amp_fwd_dtype": (C.c_int, [vp, vp, vp, vp, i32, i32, i32, i32, f32, C.c_uint64, C.c_uint64, i32, vp, sz,
+                                              vp]),
+        "trb200_fc_amp_bwd_dtype": (C.c_int, [vp, vp, vp, vp, vp, i32, vp, vp, f32, i32, i32, i32, i32, vp, sz, vp]),
         "trb200_scale_f32": (C.c_int, [vp, i64, f32, vp]),
         "trb200_cast_f16_to_f32": (C.c_int, [vp, vp, i64, f32, vp]),
     }

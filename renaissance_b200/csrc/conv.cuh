@@ -66,12 +66,12 @@ int stem_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y,
 bool fc_gemm_supports(int batch, int in_f, int out_f);
 size_t fc_gemm_fwd_partial_bytes(int batch, int in_f, int out_f);
 int fc_gemm_fwd(const void* x, const void* w, float* partial, int batch, int in_f, int out_f, int* splits,
-                cudaStream_t st);
+                cudaStream_t st, bool bf16 = false);
 size_t fc_gemm_dgrad_partial_bytes(int batch, int in_f, int out_f);
 int fc_gemm_dgrad(const void* dy, const void* w, void* dx, float* partial, int batch, int in_f, int out_f, int* splits,
-                  cudaStream_t st);
+                  cudaStream_t st, bool bf16 = false);
 int fc_gemm_wgrad(const void* dy, const void* x, void* dw, int dw_float, int batch, int in_f, int out_f,
-                  cudaStream_t st);
+                  cudaStream_t st, bool bf16 = false);
 
 int validate_conv_desc(const trb200_conv_desc* d, const char* who);
 

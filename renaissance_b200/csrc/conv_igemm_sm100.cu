@@ -1622,7 +1622,7 @@ size_t fc_gemm_dgrad_partial_bytes(int batch, int in_f, int out_f) {
 
 // partial[split][b][o] (float) = x[b][k range of the split] . w[o][same]; *splits receives the split count
 int fc_gemm_fwd(const void* x, const void* w, float* partial, int batch, int in_f, int out_f, int* splits,
-                cudaStream_t st) {
+                cudaStream_t st, bool bf16) {
     TRB_REQUIRE(fc_dims_ok(batch, in_f, out_f), TRB200_ERR_UNSUPPORTED, "fc: in_features=%d, out_features=%d must be multiples of 8", in_f, out_f);
     CUtensorMap ta, tb;
     int rc = make_matrix_tmap(&ta, x, batch, in_f, in_f, 128, "fc x");
@@ -1634,14 +1634,14 @@ int fc_gemm_fwd(const void* x, const void* w, float* partial, int batch, int in_
     p.k_steps = (in_f + 63) / 64;
     p.m_tiles = (batch + 255) / 256; p.n_tiles = (out_f + kSkN - 1) / kSkN;
     p.splits = fc_fwd_splits(batch, in_f, out_f);
-    p.ldd = out_f; p.d = partial; p.split_stride = (int64_t)batch * out_f; p.bf16 = 0;
+    p.ldd = out_f; p.d = partial; p.split_stride = (int64_t)batch * out_f; p.bf16 = bf16 ? 1 : 0;
     *splits = p.splits;
     return launch_skinny<false, false, 2, true>(ta, tb, ta, p, st);
 }
 
 // dx[b][i] = dy[b][:] . w[:][i]: half into dx when *splits comes back 1, else float partials [split][b][i]
 int fc_gemm_dgrad(const void* dy, const void* w, void* dx, float* partial, int batch, int in_f, int out_f, int* splits,
-                  cudaStream_t st) {
+                  cudaStream_t st, bool bf16) {
     TRB_REQUIRE(fc_dims_ok(batch, in_f, out_f), TRB200_ERR_UNSUPPORTED, "fc: in_features=%d, out_features=%d must be multiples of 8", in_f, out_f);
     CUtensorMap ta, tb, td;
     int rc = make_matrix_tmap(&ta, dy, batch, out_f, out_f, 128, "fc dy");
@@ -1655,7 +1655,7 @@ int fc_gemm_dgrad(const void* dy, const void* w, void* dx, float* partial, int b
     p.k_steps = (out_f + 63) / 64;
     p.m_tiles = (batch + 255) / 256; p.n_tiles = (in_f + kSkN - 1) / kSkN;
     p.splits = fc_dgrad_splits(batch, in_f, out_f);
-    p.ldd = in_f; p.bf16 = 0;
+    p.ldd = in_f; p.bf16 = bf16 ? 1 : 0;
     *splits = p.splits;
     if (p.splits == 1) {
         p.d = dx; p.split_stride = 0;
@@ -1666,7 +1666,8 @@ int fc_gemm_dgrad(const void* dy, const void* w, void* dx, float* partial, int b
 }
 
 // dw[o][i] = dy[:][o] . x[:][i], half or (dw_float) float as the reference's FC_AMP_BWD writes it
-int fc_gemm_wgrad(const void* dy, const void* x, void* dw, int dw_float, int batch, int in_f, int out_f, cudaStream_t st) {
+int fc_gemm_wgrad(const void* dy, const void* x, void* dw, int dw_float, int batch, int in_f, int out_f, cudaStream_t st,
+                  bool bf16) {
     TRB_REQUIRE(fc_dims_ok(batch, in_f, out_f), TRB200_ERR_UNSUPPORTED, "fc: in_features=%d, out_features=%d must be multiples of 8", in_f, out_f);
     CUtensorMap ta, tb, td;
     int rc = make_matrix_tmap(&ta, dy, batch, out_f, out_f, 64, "fc dy (columns)");
@@ -1680,7 +1681,7 @@ int fc_gemm_wgrad(const void* dy, const void* x, void* dw, int dw_float, int bat
     p.k_steps = (batch + 63) / 64;
     p.m_tiles = (out_f + 127) / 128; p.n_tiles = (in_f + kSkN - 1) / kSkN;
     p.splits = 1;
-    p.ldd = in_f; p.d = dw; p.split_stride = 0; p.bf16 = 0;
+    p.ldd = in_f; p.d = dw; p.split_stride = 0; p.bf16 = bf16 ? 1 : 0;
     if (dw_float) return launch_skinny<true, true, 1, true>(ta, tb, ta, p, st);
     return launch_skinny<true, true, 1, false>(ta, tb, td, p, st);
 }

@@ -615,10 +615,12 @@ def softmax_ce_amp_fused(logits, labels, scaling, label_smoothing, want_probs=Fa
 # --------------------------------------------------------------------------- classifier
 
 def fc_amp_fwd(x, w, bias, y=None, relu=False, dropout_p=0.0, seed=0, offset=0, workspace=None, stream=None):
-    """y = act(x W^T + bias) (FC_AMP_FWD + ReLU + dropout, fc_op.cpp:259-347).  x [batch, in], w [out, in] half,
-    bias float."""
-    _need(x, torch.float16, "x", 2)
-    _need(w, torch.float16, "w", 2)
+    """y = act(x W^T + bias) (FC_AMP_FWD + ReLU + dropout, fc_op.cpp:259-347).  x [batch, in], w [out, in] half
+    (or both bfloat16), bias float."""
+    if x.dtype not in DTYPE_CODE:
+        raise TypeError(f"x: float16 or bfloat16 expected, got {x.dtype}")
+    _need(x, x.dtype, "x", 2)
+    _need(w, x.dtype, "w", 2)
     if bias is not None:
         _need(bias, torch.float32, "bias", 1)
     b, i_f = x.shape
@@ -626,11 +628,12 @@ def fc_amp_fwd(x, w, bias, y=None, relu=False, dropout_p=0.0, seed=0, offset=0, 
     if w.shape[1] != i_f:
         raise ValueError("fc_amp_fwd: w must be [out, in]")
     if y is None:
-        y = torch.empty((b, o_f), dtype=torch.float16, device=x.device)
+        y = torch.empty((b, o_f), dtype=x.dtype, device=x.device)
     lib = _lib.load()
     ws = (workspace or default_workspace()).ensure(lib.trb200_fc_amp_workspace_bytes(b, i_f, o_f))
-    check(lib.trb200_fc_amp_fwd(_ptr(x), _ptr(w), _ptr(bias), _ptr(y), b, i_f, o_f, 1 if relu else 0,
-                                float(dropout_p), int(seed), int(offset), _ptr(ws), ws.numel(), _stream(stream)))
+    check(lib.trb200_fc_amp_fwd_dtype(_ptr(x), _ptr(w), _ptr(bias), _ptr(y), b, i_f, o_f, 1 if relu else 0,
+                                      float(dropout_p), int(seed), int(offset), DTYPE_CODE[x.dtype], _ptr(ws), ws.numel(),
+                                      _stream(stream)))
     return y
 
 
@@ -647,23 +650,25 @@ def fc_amp_bwd(dy, w, x, dx=None, dw=None, db=None, want_dx=True, act=None, act_
     """(dx, dw, db) of an FC layer (FC_AMP_BWD, fc_op.cpp:349-480): dw half [out, in], db float [out].  With act =
     x as the previous layer's forward wrote it (ReLU / dropout applied), dx also carries that activation's backward."""
     lib = _lib.load()
-    _need(dy, torch.float16, "dy", 2)
-    _need(w, torch.float16, "w", 2)
-    _need(x, torch.float16, "x", 2)
+    if dy.dtype not in DTYPE_CODE:
+        raise TypeError(f"dy: float16 or bfloat16 expected, got {dy.dtype}")
+    _need(dy, dy.dtype, "dy", 2)
+    _need(w, dy.dtype, "w", 2)
+    _need(x, dy.dtype, "x", 2)
     b, o_f = dy.shape
     i_f = x.shape[1]
     if dw is None:
-        dw = torch.empty((o_f, i_f), dtype=torch.float16, device=dy.device)
-    if dw.dtype not in (torch.float16, torch.float32):
-        raise TypeError("fc_amp_bwd: dw must be half or float")
+        dw = torch.empty((o_f, i_f), dtype=dy.dtype, device=dy.device)
+    if dw.dtype not in (dy.dtype, torch.float32):
+        raise TypeError("fc_amp_bwd: dw must be of the layer's 16-bit type or float")
     if db is None:
         db = torch.empty(o_f, dtype=torch.float32, device=dy.device)
     if dx is None and want_dx:
-        dx = torch.empty((b, i_f), dtype=torch.float16, device=dy.device)
+        dx = torch.empty((b, i_f), dtype=dy.dtype, device=dy.device)
     ws = (workspace or default_workspace()).ensure(lib.trb200_fc_amp_workspace_bytes(b, i_f, o_f))
-    check(lib.trb200_fc_amp_bwd(_ptr(dy), _ptr(w), _ptr(x), _ptr(dx), _ptr(dw), 1 if dw.dtype == torch.float32 else 0,
-                                _ptr(db), _ptr(act), float(act_scale),
-                                b, i_f, o_f, _ptr(ws), ws.numel(), _stream(stream)))
+    check(lib.trb200_fc_amp_bwd_dtype(_ptr(dy), _ptr(w), _ptr(x), _ptr(dx), _ptr(dw), 1 if dw.dtype == torch.float32 else 0,
+                                      _ptr(db), _ptr(act), float(act_scale), b, i_f, o_f, DTYPE_CODE[dy.dtype],
+                                      _ptr(ws), ws.numel(), _stream(stream)))
     return dx, dw, db
 
 

@@ -9,7 +9,7 @@ the same C ABI as the VGG16-BN path.
     forward   conv (tcgen05 kernels; stride 2 through stepped tensor maps) -> batch statistics (the conv epilogue
               for stride-1 layers) -> BN apply (+ ReLU + mask)                               per conv + BN unit
               3x3 stride-2 max pool after the 7x7 stem, add + ReLU + mask at every residual join,
-              global average pool, classifier GEMM (torch matmul on the 16-bit tensors), fused softmax cross-entropy
+              global average pool, classifier (the skinny tcgen05 GEMM + bias pass), fused softmax cross-entropy
     backward  the same operators' gradients in reverse; the BN in front of a join and the shortcut BN take the
               BN backward without a mask
     exchange  float master weights, float gradients, momentum and the 16-bit working weights are four flat buffers
@@ -19,8 +19,8 @@ the same C ABI as the VGG16-BN path.
     update    non-finite check, SGD with momentum on the whole flat range in one sweep (the loss scale is removed
               there), loss-scale back-off
 
-torch supplies device memory, the classifier's matmul and the 16-bit copy of the weights in bfloat16; every
-convolution, BN, pooling, join, loss and optimizer kernel is libtrb200's.
+torch supplies device memory and the 16-bit copy of the weights in bfloat16; every convolution, BN, pooling, join,
+classifier, loss and optimizer kernel is libtrb200's.
 """
 from __future__ import annotations
 
@@ -224,13 +224,11 @@ class ResNet50:
             x = b.forward(x)
         _, fh, fw, _ = x.shape
         feat = ops.avgpool_global_fwd(x)
-        logits = (torch.matmul(feat, self.fc_w.t()).float() + self.fc_b32).to(self.dtype).contiguous()
+        logits = ops.fc_amp_fwd(feat, self.fc_w, self.fc_b32)
         out = ops.softmax_ce_amp_fused(logits, labels, self.scaling, self.label_smoothing)
         dlogits = out["dlogits"]                               # d(mean loss) / d logits, times the loss scale
-        torch.matmul(dlogits.t(), feat, out=self.fc_dw16)
-        self.fc_db.copy_(dlogits.float().sum(dim=0))
+        dfeat, _, _ = ops.fc_amp_bwd(dlogits, self.fc_w, feat, dw=self.fc_dw16, db=self.fc_db)
         self.buckets.mark_ready(self._end["fc"])
-        dfeat = torch.matmul(dlogits, self.fc_w).contiguous()
         dx = ops.avgpool_global_bwd(dfeat, fh, fw)
         for b in reversed(self.blocks):
             dx = b.backward(dx)

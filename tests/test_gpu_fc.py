@@ -118,3 +118,34 @@ def test_unsupported_width_is_refused():
     rc = lib.trb200_fc_amp_fwd(x.data_ptr(), w.data_ptr(), None, y.data_ptr(), 8, 4096, 1000, 0, 0.0, 0, 0,
                                ws.data_ptr(), 16, None)
     assert rc == _lib.ERR_WORKSPACE
+
+
+@pytest.mark.parametrize("batch,in_f,out_f", [(256, 2048, 1000), (7, 128, 256), (130, 1280, 512)])
+def test_fc_bfloat16_against_torch_float32(batch, in_f, out_f):
+    """The classifier of a bfloat16 network (ResNet-50's 2048 -> 1000 head): forward with bias, data gradient, weight
+    gradient in bfloat16 and in float, bias gradient; against float32 torch on the bfloat16-rounded operands.
+    bfloat16 keeps 8 significant bits: 4e-3 relative L2 on its outputs."""
+    from renaissance_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(batch + out_f)
+    x = torch.randn((batch, in_f), generator=g, device="cuda").bfloat16()
+    w = (torch.randn((out_f, in_f), generator=g, device="cuda") * (2.0 / in_f) ** 0.5).bfloat16()
+    b = 0.1 * torch.randn(out_f, generator=g, device="cuda")
+    dy = torch.randn((batch, out_f), generator=g, device="cuda").bfloat16()
+    y = ops.fc_amp_fwd(x, w, b)
+    dx, dw, db = ops.fc_amp_bwd(dy, w, x)
+    dwf = torch.empty((out_f, in_f), dtype=torch.float32, device="cuda")
+    ops.fc_amp_bwd(dy, w, x, dw=dwf, want_dx=False)
+    ops.device_status()
+    assert y.dtype == torch.bfloat16 and dx.dtype == torch.bfloat16 and dw.dtype == torch.bfloat16
+
+    def rel(a, ref):
+        return float((a.float() - ref).norm() / ref.norm())
+
+    y_ref = x.float() @ w.float().t() + b
+    assert rel(y, y_ref) < 4e-3
+    assert rel(dx, dy.float() @ w.float()) < 4e-3
+    dw_ref = dy.float().t() @ x.float()
+    assert rel(dw, dw_ref) < 4e-3 and rel(dwf, dw_ref) < 1e-4
+    db_ref = dy.float().sum(dim=0)
+    assert float((db - db_ref).abs().max() / db_ref.abs().max()) < 1e-4
+    assert torch.equal(ops.fc_amp_fwd(x, w, b, relu=True), torch.relu(y))
