@@ -132,3 +132,34 @@ def test_ring_kernels_with_ragged_tails(m, c, dtype, with_mask):
     assert float((dconv.double() - ref).norm() / ref.norm()) < tol
     # the last rows (the ragged tail) on their own
     assert float((dconv[-100:].double() - ref[-100:]).norm() / ref[-100:].norm()) < tol
+
+
+def test_ring_kernels_replay_from_a_cuda_graph():
+    """The bulk-copy ring kernels enqueue only: after one eager call (which sets the kernels' shared-memory
+    attribute) the same call is captured into a CUDA graph in thread-local mode and replayed; the replay's results
+    equal the eager ones bit for bit."""
+    from renaissance_b200 import ops
+    m, c = 256 * 56 * 56, 64
+    g = torch.Generator(device="cuda").manual_seed(5)
+    dy = torch.randn((m, c), generator=g, device="cuda", dtype=torch.float32).half()
+    x = (torch.randn((m, c), generator=g, device="cuda", dtype=torch.float32) * 1.2 + 0.1).half()
+    bits = torch.randint(0, 256, (m * c // 8,), generator=g, device="cuda", dtype=torch.int32).to(torch.uint8)
+    gamma = 1 + 0.2 * torch.randn(c, generator=g, device="cuda")
+    mean = x.float().mean(dim=0)
+    inv_std = 1.0 / torch.sqrt(x.float().var(dim=0, unbiased=False) + 1e-5)
+    ws = ops.Workspace(torch.device("cuda"))
+    eager = ops.bnrelu_bwd(dy, bits, x, gamma, mean, inv_std, workspace=ws)
+    torch.cuda.synchronize()
+    out = torch.empty_like(dy)
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+            replayed = ops.bnrelu_bwd(dy, bits, x, gamma, mean, inv_std, dconv=out, workspace=ws, stream=side)
+    torch.cuda.current_stream().wait_stream(side)
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(replayed[0], eager[0]) and torch.equal(replayed[1], eager[1]) and torch.equal(replayed[2], eager[2])
+    ops.device_status()
