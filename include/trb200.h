@@ -169,8 +169,9 @@ int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const void* w, v
  * bn_finalize: the reference's conv_fprop + genstats graph and its bn_finalize graph
  * (cbr_op.cpp:622-718, 430-528) in two launches, without a separate pass over the
  * conv output.  Outputs and optional pointers as in trb200_bn_stats_finalize; the
- * statistics are those of the stored (half) output.  Same shape coverage as
- * trb200_conv_fprop. */
+ * statistics are those of the stored (half) output.  Shapes: what the tensor-core
+ * kernels run at stride 1, and 3x3 pad 1 / 1x1 pad 0 at stride 2 with c a multiple
+ * of 64 and k = 64, 128 or a multiple of 256. */
 size_t trb200_conv_fprop_bn_stats_workspace_bytes(const trb200_conv_desc* d);
 int trb200_conv_fprop_bn_stats(const trb200_conv_desc* d, const void* x, const void* w, void* y,
                                const float* gamma, const float* beta, float eps, float momentum,

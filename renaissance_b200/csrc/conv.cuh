@@ -22,7 +22,8 @@ size_t igemm_dgrad_workspace(const trb200_conv_desc& d);
 // read x through a tensor map that steps two pixels, the 3x3 data gradient runs as four parity classes
 bool igemm_s2_supports(const trb200_conv_desc& d, int which);
 size_t igemm_s2_workspace(const trb200_conv_desc& d, int which);
-int igemm_s2_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, cudaStream_t st);
+int igemm_s2_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, cudaStream_t st,
+                   float* stats_partial = nullptr, int* stats_strips = nullptr);
 int igemm_s2_wgrad(const trb200_conv_desc& d, const void* dy, const void* x, void* dw, void* ws, size_t ws_bytes,
                    cudaStream_t st);
 int igemm_s2_dgrad(const trb200_conv_desc& d, const void* dy, const void* w, void* dx, void* ws, size_t ws_bytes,

@@ -148,6 +148,7 @@ extern "C" int trb200_conv_fprop(const trb200_conv_desc* d, const void* x, const
 
 extern "C" size_t trb200_conv_fprop_bn_stats_workspace_bytes(const trb200_conv_desc* d) {
     if (trb::validate_conv_desc(d, "conv_fprop_bn_stats_workspace_bytes")) return 0;
+    if (trb::igemm_s2_supports(*d, 2)) return trb::igemm_fprop_stats_bytes(*d);
     if (!trb::igemm_supports(*d, 2)) return 0;
     return (size_t)trb::align_up((int64_t)trb::igemm_fprop_workspace(*d), 256) + trb::igemm_fprop_stats_bytes(*d);
 }
@@ -164,9 +165,10 @@ extern "C" int trb200_conv_fprop_bn_stats(const trb200_conv_desc* d, const void*
     TRB_REQUIRE(y != x && y != w, TRB200_ERR_INVALID_ARGUMENT, "conv_fprop_bn_stats: y must not alias x or w");
     TRB_REQUIRE(trb::aligned16(x) && trb::aligned16(w) && trb::aligned16(y), TRB200_ERR_INVALID_ARGUMENT,
                 "conv_fprop_bn_stats: tensors must be 16-byte aligned");
-    TRB_REQUIRE(trb::igemm_supports(*d, 2), TRB200_ERR_UNSUPPORTED,
-                "conv_fprop_bn_stats: only 3x3 stride 1 pad 1 (c = 4 or a multiple of 64) and 1x1 stride 1 (c a multiple "
-                "of 64), with k = 64, 128 or a multiple of 256");
+    const bool s2 = trb::igemm_s2_supports(*d, 2);
+    TRB_REQUIRE(s2 || trb::igemm_supports(*d, 2), TRB200_ERR_UNSUPPORTED,
+                "conv_fprop_bn_stats: only 3x3 pad 1 (c = 4 at stride 1, or a multiple of 64 at stride 1 or 2) and 1x1 pad 0 "
+                "(c a multiple of 64, stride 1 or 2), with k = 64, 128 or a multiple of 256");
     const size_t need = trb200_conv_fprop_bn_stats_workspace_bytes(d);
     TRB_REQUIRE(workspace && workspace_bytes >= need, TRB200_ERR_WORKSPACE,
                 "conv_fprop_bn_stats: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
@@ -178,7 +180,8 @@ extern "C" int trb200_conv_fprop_bn_stats(const trb200_conv_desc* d, const void*
     const size_t stats_bytes = trb::igemm_fprop_stats_bytes(*d);
     float* partial = reinterpret_cast<float*>(base + (workspace_bytes - stats_bytes) / 256 * 256);
     int strips = 0;
-    rc = trb::igemm_fprop(*d, x, w, y, workspace, workspace_bytes - stats_bytes, trb::as_stream(stream), partial, &strips);
+    if (s2) rc = trb::igemm_s2_fprop(*d, x, w, y, trb::as_stream(stream), partial, &strips);
+    else rc = trb::igemm_fprop(*d, x, w, y, workspace, workspace_bytes - stats_bytes, trb::as_stream(stream), partial, &strips);
     if (rc) return rc;
     const int oh = trb::conv_out(d->h, d->pad_h, d->r, d->stride_h), ow = trb::conv_out(d->w, d->pad_w, d->s, d->stride_w);
     return trb::bn_finalize_from_partials(partial, strips, d->k, (int64_t)d->n * oh * ow, gamma, beta, eps, momentum,

@@ -1492,11 +1492,13 @@ size_t igemm_s2_workspace(const trb200_conv_desc& d, int which) {
     return 0;
 }
 
-int igemm_s2_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, cudaStream_t st) {
+// stats_partial / stats_strips as in igemm_fprop: the BN batch statistics of y from the epilogue
+int igemm_s2_fprop(const trb200_conv_desc& d, const void* x, const void* w, void* y, cudaStream_t st, float* stats_partial,
+                   int* stats_strips) {
     ConvRunEx ex;
     ex.step = 2; ex.in_h = d.h; ex.in_w = d.w;
     const int oh = (d.h - 1) / 2 + 1, ow = (d.w - 1) / 2 + 1;
-    return conv3x3_run(x, w, 1, y, d.n, oh, ow, d.c, d.k, st, d.r * d.s, nullptr, nullptr, nullptr,
+    return conv3x3_run(x, w, 1, y, d.n, oh, ow, d.c, d.k, st, d.r * d.s, stats_partial, stats_strips, nullptr,
                        d.dtype == TRB200_DTYPE_BF16, &ex);
 }
 

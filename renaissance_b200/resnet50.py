@@ -54,8 +54,8 @@ class ConvBN:
     def forward(self, x, relu):
         n, h, w, _ = x.shape
         g = self.geometry(n, h, w)
-        if self.stride == 1 and self.cin % 64 == 0:
-            # the batch statistics come out of the convolution kernel's epilogue
+        if self.cin % 64 == 0:
+            # the batch statistics come out of the convolution kernel's epilogue (stride 1 and 2)
             y, st = ops.conv_fprop_bn_stats(g, x, self.w, self.gamma, self.beta)
         else:
             y = ops.conv_fprop(g, x, self.w)

@@ -154,8 +154,9 @@ def test_one_by_one_convolutions_on_tensor_cores(orc, n, h, w, c, k):
                                              (3, 8, 8, 128, 64, 1, 0), (2, 7, 9, 256, 512, 1, 0),
                                              (2, 28, 28, 64, 128, 1, 0)])
 def test_stride_two_convolutions_on_tensor_cores(orc, n, h, w, c, k, r, pad):
-    """Stride 2 (3x3 pad 1, 1x1 pad 0): the stride-1 tensor-core kernels plus a resampling pass, against the
-    oracle's strided loops and the direct strided kernels; odd extents included."""
+    """Stride 2 (3x3 pad 1, 1x1 pad 0) on the tensor-core kernels (stepped tensor maps, parity classes of the data
+    gradient), against the oracle's strided loops and the direct strided kernels; odd extents included.  The forward
+    with the statistics epilogue gives the same output and the sums of that output."""
     from renaissance_b200 import ops
     x, wt, dy = _rand_case(n + h + c + k + r, n, h, w, c, k, r, pad, 2)
     ref_dw, ref_dx = _oracle(orc, x, wt, dy, pad, 2)
@@ -171,6 +172,12 @@ def test_stride_two_convolutions_on_tensor_cores(orc, n, h, w, c, k, r, pad):
     assert rel_l2(host(dw).astype(np.float32), ref_dw) < 2e-3
     ref_y = orc.conv_fwd(x.astype(np.float32), wt.astype(np.float32), pad=pad, stride=2)
     assert rel_l2(host(y).astype(np.float32), ref_y) < 2e-3
+    gamma, beta = torch.ones(k, device="cuda"), torch.zeros(k, device="cuda")
+    y2, st = ops.conv_fprop_bn_stats(g, dev(x), dev(wt), gamma, beta, want_sums=True)
+    assert torch.equal(y2, y)
+    rows = y.double().reshape(-1, k)
+    assert float((st["sum"].double() - rows.sum(dim=0)).abs().max() / rows.abs().sum(dim=0).max()) < 1e-5
+    assert float((st["sqsum"].double() - (rows * rows).sum(dim=0)).abs().max() / (rows * rows).sum(dim=0).max()) < 1e-5
     ops.set_conv_backend(direct_only=True)
     try:
         dw3, dx3 = ops.conv_wgrad(g, dev(dy), dev(x)), ops.conv_dgrad(g, dev(dy), dev(wt))
