@@ -234,6 +234,30 @@ VGG_SHAPES = [(224, 64, 64), (112, 64, 128), (112, 128, 128), (56, 128, 256), (5
 
 
 
+def softmax_split_point(t, b, c, hbm, src):
+    """The two separate nodes as the registry adapter runs them when the graph is not patched for the fused kernel:
+    SOFTMAX_CE_AMP_FWD (logits -> float probabilities + loss) and SOFTMAX_CE_AMP_BWD (probabilities -> half d_logits):
+    2 + 4 bytes written and read per class in the forward, 4 + 2 in the backward = 12 B per class."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    z = (torch.randn((b, c), generator=g, device="cuda") * 2).half()
+    lab = torch.randint(0, c, (b,), generator=g, device="cuda", dtype=torch.int32)
+    sc = torch.tensor([1024.0], device="cuda")
+    lsd = torch.tensor([0.0], device="cuda")
+    probs = torch.empty((b, c), dtype=torch.float32, device="cuda")
+    d = torch.empty_like(z)
+    fwd = ops.softmax_ce_amp_fwd(z, lab, lsd, probs=probs)
+
+    def both():
+        f = ops.softmax_ce_amp_fwd(z, lab, lsd, probs=probs)
+        ops.softmax_ce_amp_bwd(probs, lab, sc, f["inv_scaling"], lsd, dlogits=d)
+
+    med, best = t(both)
+    byt = 12.0 * b * c + 12 * b
+    emit(kernel="softmax_ce split nodes (fwd with probs, bwd)", rows=b, classes=c, label_smoothing=0.0, ms=round(med, 4),
+         best_ms=round(best, 4), bound="hbm", achieved=round(byt / med / 1e6, 1), peak=hbm, unit="GB/s",
+         frac=round(byt / med / 1e6 / hbm, 4), peak_source=src)
+
+
 def pool_point(t, n, h, c, hbm, src):
     """The block's HBM-bound kernels around a 2x2 max pool: BN apply + ReLU + mask + pool forward, and the pool + BN +
     ReLU backward (bytes per full-resolution element: 2.875 and 7.75), and the forward without a pool (4.125)."""
@@ -302,6 +326,9 @@ def main():
             pts = [(b, c, 0.0)]
         for b, c, ls in pts:
             softmax_point(t, b, c, ls, hbm, src)
+        if not args.quick and not args.shape:
+            for b, c in ((65536, 1000), (65536, 10000), (16384, 32000)):
+                softmax_split_point(t, b, c, hbm, src)
     if args.only in ("all", "conv"):
         shapes = [(56, 64, 64), (28, 256, 512)] if args.quick else [(56, 64, 64)] + VGG_SHAPES
         if args.shape and args.only == "conv":
