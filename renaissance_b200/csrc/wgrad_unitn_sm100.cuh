@@ -12,9 +12,12 @@
 // clocks per K step of four MMAs hide behind the tensor pipe only at N = 256 (4 x 128 clocks): with the filters on N
 // (wgrad_igemm_kernel) a 64-filter layer needs one instruction per two units and 16 pixels, here one per four units.
 //
-// Work item = (split of the pixel range, block of 128 filters, group of 4 units); every item
+// Work item = (split of the pixel range, block of 128 filters, group of units); every item
 // leaves a float partial tile and wgrad_unitn_reduce adds the splits in split order (bitwise
-// reproducible) and writes half KRSC.  With 64 filters the second half of the A operand is
+// reproducible) and writes half KRSC.  A group is 4 units, or 3 where that divides the unit count: 64 input
+// channels have 9 units, and groups of 4, 4, 1 make the last third of the work items a third as long as the others
+// (the kernel runs as long as its longest item); groups of 3, 3, 3 at N = 192 keep the pipe as busy and the items
+// equal (0.46 -> 0.39 ms at 256 x 112 x 112, 64 -> 128).  With 64 filters the second half of the A operand is
 // never loaded and lanes 64-127 of the accumulator are never read.
 //
 // This file is included by conv_igemm_sm100.cu inside its anonymous namespace.
@@ -23,7 +26,9 @@
 struct WgradUnitnParams {
     int cblocks;        // C / 64
     int units;          // 9 * cblocks
-    int n_tiles;        // ceil(units / 4)
+    int upg;            // units per group: 4, or 3 when that divides the units (9 units: groups of 3, 3, 3 instead of
+                        // 4, 4, 1, so that every work item is the same length)
+    int n_tiles;        // ceil(units / upg)
     int k_blocks;       // ceil(K / 128)
     int k_halves;       // 64-filter blocks in a filter block: 1 (K = 64) or 2
     int splits;
@@ -83,8 +88,8 @@ wgrad_unitn_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     const int split = item / (p.n_tiles * p.k_blocks);
     const int pt0 = (int)((long)p.pix_tiles * split / p.splits);
     const int pt1 = (int)((long)p.pix_tiles * (split + 1) / p.splits);
-    const int u0 = nt * 4;
-    const int nu = p.units - u0 < 4 ? p.units - u0 : 4;          // units of this group
+    const int u0 = nt * p.upg;
+    const int nu = p.units - u0 < p.upg ? p.units - u0 : p.upg;  // units of this group
     // pixel tiles are walked with running box origins (w fastest, then h, then n)
     const int w_first = (pt0 % p.tw) * p.bw, h_first = ((pt0 / p.tw) % p.th) * p.bh;
     const int n_first = (pt0 / (p.tw * p.th)) * p.bn;
@@ -213,7 +218,7 @@ wgrad_unitn_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
 }
 
-// dW[k][col] = half or bfloat16(sum over splits, in split order, of partial[split][kb][nt][k % 128][col % 256]);
+// dW[k][col] = half or bfloat16(sum over splits, in split order, of partial[split][kb][nt][k % 128][col % (64 upg)]);
 // one thread = 4 consecutive columns of one filter row.
 __global__ void __launch_bounds__(256)
 wgrad_unitn_reduce(const float* __restrict__ partial, uint16_t* __restrict__ dw, WgradUnitnParams p) {
@@ -224,7 +229,8 @@ wgrad_unitn_reduce(const float* __restrict__ partial, uint16_t* __restrict__ dw,
     const size_t split_stride = (size_t)p.k_blocks * p.n_tiles * item_elems;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
         const int k = (int)(i / quads), col = (int)(i % quads) * 4;
-        const size_t off = ((size_t)(k / 128) * p.n_tiles + col / 256) * item_elems + (size_t)(k % 128) * 256 + col % 256;
+        const int gcols = p.upg * 64;                 // columns of one unit group
+        const size_t off = ((size_t)(k / 128) * p.n_tiles + col / gcols) * item_elems + (size_t)(k % 128) * 256 + col % gcols;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int s = 0; s < p.splits; ++s) {
             const float4 v = *reinterpret_cast<const float4*>(partial + (size_t)s * split_stride + off);
@@ -241,7 +247,8 @@ WgradUnitnParams wgrad_unitn_plan(const trb200_conv_desc& d, const TileShape& t)
     WgradUnitnParams p;
     p.cblocks = d.c / 64;
     p.units = 9 * p.cblocks;
-    p.n_tiles = (p.units + 3) / 4;
+    p.upg = (p.units % 4 != 0 && p.units % 3 == 0) ? 3 : 4;
+    p.n_tiles = (p.units + p.upg - 1) / p.upg;
     p.k_blocks = (d.k + 127) / 128;
     p.k_halves = d.k >= 128 ? 2 : 1;
     p.pix_tiles = t.tw * t.th * t.tn;
