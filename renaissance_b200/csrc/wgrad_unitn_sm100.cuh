@@ -14,8 +14,8 @@
 //
 // Work item = (split of the pixel range, block of 128 filters, group of units); every item
 // leaves a float partial tile and wgrad_unitn_reduce adds the splits in split order (bitwise
-// reproducible) and writes half KRSC.  A group is 4 units, or 3 where that divides the unit count: 64 input
-// channels have 9 units, and groups of 4, 4, 1 make the last third of the work items a third as long as the others
+// reproducible) and writes half KRSC.  A group is 4 units, or 3 for 64 input channels: they have 9 units, and groups
+// of 4, 4, 1 make the last third of the work items a third as long as the others
 // (the kernel runs as long as its longest item); groups of 3, 3, 3 at N = 192 keep the pipe as busy and the items
 // equal (0.46 -> 0.39 ms at 256 x 112 x 112, 64 -> 128).  With 64 filters the second half of the A operand is
 // never loaded and lanes 64-127 of the accumulator are never read.
@@ -247,7 +247,7 @@ WgradUnitnParams wgrad_unitn_plan(const trb200_conv_desc& d, const TileShape& t)
     WgradUnitnParams p;
     p.cblocks = d.c / 64;
     p.units = 9 * p.cblocks;
-    p.upg = (p.units % 4 != 0 && p.units % 3 == 0) ? 3 : 4;
+    p.upg = p.units == 9 ? 3 : 4;      // 18 units (128 channels) stay at 4, 4, 4, 4, 2: N = 192 MMAs are paced by their issue
     p.n_tiles = (p.units + p.upg - 1) / p.upg;
     p.k_blocks = (d.k + 127) / 128;
     p.k_halves = d.k >= 128 ? 2 : 1;
