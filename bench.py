@@ -8,7 +8,7 @@
 
 One step = forward + backward + gradient all-reduce + SGD-momentum of VGG16-BN on a
 synthetic batch of 256 images per GPU (NHWC half, 224x224x3 padded to 4 channels,
-N(0,1); labels uniform in 0..999; random-init weights), loss scale 1024, 25 MB
+N(0,1); labels uniform in 0..999; random-init weights), loss scale 1024, 50 MB
 gradient buckets.  Prints ONE JSON line (rank 0).
 """
 from __future__ import annotations
@@ -186,7 +186,10 @@ def run_ours(args):
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        opts = None
+        if args.nccl_high_priority:
+            opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), pg_options=opts)
 
     def barrier():
         if world > 1:
@@ -201,7 +204,8 @@ def run_ours(args):
         return float(t.item())
 
     batch = args.batch
-    tr = Vgg16BnTrainer(batch=batch, image=IMAGE, classes=CLASSES, loss_scale=1024.0, bucket_mb=25.0, seed=1234)
+    tr = Vgg16BnTrainer(batch=batch, image=IMAGE, classes=CLASSES, loss_scale=1024.0, bucket_mb=args.bucket_mb,
+                        seed=1234)
     # synthetic batches in pinned host memory (two, alternated): images ~ N(0,1), 4th channel zero
     gen = torch.Generator().manual_seed(100 + rank)
     host_images, host_labels = [], []
@@ -375,7 +379,7 @@ def run_ours(args):
                     ms_per_step=round(ms_per_step, 3), higher_is_better=True, scaling="weak", vs_baseline=None,
                     dtype="fp16", data="synthetic",
                     config=dict(workload="VGG16-BN AMP fwd+bwd+allreduce+SGD-momentum, NHWC 224x224x3(+1 pad), "
-                                         "batch 256/GPU, loss scale 1024, 25 MB buckets",
+                                         "batch 256/GPU, loss scale 1024, %g MB buckets" % args.bucket_mb,
                                 global_batch=world * batch, parallelism=f"dp{world}",
                                 l2="activations (>15 GB per step) far exceed the 126 MB L2; no flush needed",
                                 conv_tflop_per_step_per_gpu=round(conv_flops_per_step(batch) / 1e12, 2),
@@ -584,6 +588,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU (the metric is quoted at 256)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--bucket-mb", type=float, default=50.0, help="size of a gradient all-reduce bucket")
+    ap.add_argument("--nccl-high-priority", action="store_true",
+                    help="run NCCL's kernels on a high-priority stream (N > 1)")
     ap.add_argument("--workload", default="vgg16bn", choices=["vgg16bn", "resnet50"],
                     help="vgg16bn: the headline configuration; resnet50: BASELINE configuration 4 (information only)")
     args = ap.parse_args()

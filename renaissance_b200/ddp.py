@@ -4,8 +4,8 @@ The reference reduces two fixed region ranges with one in-place FP32 ncclAllRedu
 each and scales by 1/world afterwards (src/backend/ops/range/allreduce_op.cpp:37-105,
 buckets at src/graph/compiler.cpp:1836-1847); only the first is overlapped with
 compute.  Here the flat float gradient buffer is laid out in the order in which
-backward completes its parameters and is cut into ~25 MB buckets; a bucket is cast
-half -> float (the reference's RANGE_CAST_FP16_TO_FP32, with the 1/world of the mean
+backward completes its parameters and is cut into buckets (25 MB unless the caller
+says otherwise; the VGG16-BN driver uses 50 MB); a bucket is cast half -> float (the reference's RANGE_CAST_FP16_TO_FP32, with the 1/world of the mean
 folded in) and handed to NCCL as soon as backward has passed its end, so the
 collective runs under the remaining backward kernels.  The wire format stays FP32
 and the reduction is NCCL's (NVLink / NVSwitch), as in the reference.

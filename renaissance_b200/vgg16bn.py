@@ -10,7 +10,7 @@ reference's ``DeepLearningTask::run_train_epoch_gpu`` plays
               FC 25088-4096-4096-1000 with ReLU + dropout, softmax-CE
     backward: softmax-CE, FC, 13 x CBR_AMP_BWD (first layer without dgrad; max-pool backward fused into
               the BN stage of the pooled blocks)
-    gradients: half -> float cast per ~25 MB bucket in backward order, NCCL all-reduce
+    gradients: half -> float cast per ~50 MB bucket in backward order, NCCL all-reduce
               per bucket overlapped with the rest of backward, non-finite check,
               SGD with momentum on float master weights + half working copy
 
@@ -72,7 +72,7 @@ def _fc_width(n):
 
 class Vgg16BnTrainer:
     def __init__(self, batch=256, image=224, classes=1000, lr=0.01, momentum=0.9, weight_decay=5e-4,
-                 loss_scale=1024.0, label_smoothing=0.0, bucket_mb=25.0, seed=0, device=None,
+                 loss_scale=1024.0, label_smoothing=0.0, bucket_mb=50.0, seed=0, device=None,
                  process_group=None, dropout=0.5, fc_width=4096):
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.batch, self.image, self.classes = batch, image, classes
@@ -135,7 +135,7 @@ class Vgg16BnTrainer:
         self.g16 = torch.zeros(self.half_numel, dtype=torch.float16, device=d)
         self._init_params(seed)
 
-        # ---- ~25 MB buckets over the flat float gradient buffer, all-reduced as backward passes them
+        # ---- ~50 MB buckets over the flat float gradient buffer, all-reduced as backward passes them
         self.buckets = GradientBuckets(
             self.g16, self.g32, self.half_numel, bucket_bytes=bucket_mb * 1024 * 1024, group=process_group,
             cast=lambda src, dst, factor: ops.cast_f16_to_f32(src, dst, factor=factor),
