@@ -5,10 +5,14 @@ each and scales by 1/world afterwards (src/backend/ops/range/allreduce_op.cpp:37
 buckets at src/graph/compiler.cpp:1836-1847); only the first is overlapped with
 compute.  Here the flat float gradient buffer is laid out in the order in which
 backward completes its parameters and is cut into buckets (25 MB unless the caller
-says otherwise; the VGG16-BN driver uses 50 MB); a bucket is cast half -> float (the reference's RANGE_CAST_FP16_TO_FP32, with the 1/world of the mean
-folded in) and handed to NCCL as soon as backward has passed its end, so the
-collective runs under the remaining backward kernels.  The wire format stays FP32
-and the reduction is NCCL's (NVLink / NVSwitch), as in the reference.
+says otherwise; the VGG16-BN driver uses 50 MB); a bucket's half gradients are
+cast half -> float (the reference's RANGE_CAST_FP16_TO_FP32) and the bucket is handed
+to NCCL as soon as backward has passed its end, so the collective runs under the
+remaining backward kernels.  The wire format stays FP32 and the reduction is NCCL's
+(NVLink / NVSwitch), as in the reference.  The 1/world of the mean is NCCL's own
+(ncclAvg) where the backend has it; otherwise it is folded into the cast, and the
+gradients born in float (the reference's FC_AMP_BWD writes dW in float,
+fc_op.cpp:434-446; BN vectors; biases) are scaled in place before their bucket goes out.
 """
 from __future__ import annotations
 
@@ -23,14 +27,19 @@ def plan_buckets(total_elems: int, bucket_bytes: float, elem_bytes: int = 4):
 
 
 class GradientBuckets:
-    """g16: flat half gradients of the first `half_numel` elements; g32: flat float gradients of
-    everything (elements past half_numel are produced in float directly).  `cast` converts a half
-    range into the float buffer times a factor; `scale` scales a float range in place."""
+    """g32: flat float gradients of everything.  Elements [half_begin, half_numel) are produced in half, in
+    `g16` (whose element 0 is flat element half_begin); every other element is produced in float directly.
+    `cast` converts a half range into the float buffer times a factor; `scale` scales a float range in place."""
 
-    def __init__(self, g16, g32, half_numel, bucket_bytes=25 * 1024 * 1024, group=None, cast=None, scale=None):
-        self.g16, self.g32, self.half_numel = g16, g32, int(half_numel)
+    def __init__(self, g16, g32, half_numel, bucket_bytes=25 * 1024 * 1024, group=None, cast=None, scale=None,
+                 half_begin=0):
+        self.g16, self.g32 = g16, g32
+        self.half_begin, self.half_numel = int(half_begin), int(half_numel)
         self.group = group
-        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        live = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if live else 1
+        # the mean: NCCL divides inside the collective; other backends (gloo) sum what was scaled beforehand
+        self.native_mean = bool(live and self.world > 1 and dist.get_backend(group) == "nccl")
         self.buckets = plan_buckets(g32.numel(), bucket_bytes)
         self.cast = cast or (lambda src, dst, factor: dst.copy_(src.float().mul_(factor)))
         self.scale = scale or (lambda t, factor: t.mul_(factor))
@@ -48,22 +57,25 @@ class GradientBuckets:
         self.issued = []
 
     def mark_ready(self, upto: int, final: bool = False):
-        """Backward has produced every half gradient below element `upto`."""
-        inv = 1.0 / self.world
+        """Backward has produced every gradient below element `upto` (`final`: every gradient)."""
+        pre = 1.0 if (self.native_mean or self.world == 1) else 1.0 / self.world
         if self.mode == "after" and not final:
             return
-        if final and self.world > 1 and self.half_numel < self.g32.numel():
-            self.scale(self.g32[self.half_numel:], inv)         # float-born gradients: mean folded in here
+        hb, he = self.half_begin, self.half_numel
         while self.next < len(self.buckets):
             a, b = self.buckets[self.next]
-            if b > upto and not final:
+            if (b > upto or b > he) and not final:      # elements past the half range are complete only at the end
                 break
-            hi = min(b, self.half_numel)
-            if a < hi:
-                self.cast(self.g16[a:hi], self.g32[a:hi], inv)
+            lo, hi = max(a, hb), min(b, he)
+            if lo < hi:
+                self.cast(self.g16[lo - hb:hi - hb], self.g32[lo:hi], pre)
+            if pre != 1.0:
+                for fa, fb in ((a, min(b, hb)), (max(a, he), b)):
+                    if fa < fb:
+                        self.scale(self.g32[fa:fb], pre)
             if self.world > 1 and self.mode != "skip":
-                self.works.append(dist.all_reduce(self.g32[a:b], op=dist.ReduceOp.SUM, group=self.group,
-                                                  async_op=True))
+                op = dist.ReduceOp.AVG if self.native_mean else dist.ReduceOp.SUM
+                self.works.append(dist.all_reduce(self.g32[a:b], op=op, group=self.group, async_op=True))
             self.issued.append((a, b))
             self.next += 1
 

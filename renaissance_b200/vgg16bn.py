@@ -10,7 +10,8 @@ reference's ``DeepLearningTask::run_train_epoch_gpu`` plays
               FC 25088-4096-4096-1000 with ReLU + dropout, softmax-CE
     backward: softmax-CE, FC, 13 x CBR_AMP_BWD (first layer without dgrad; max-pool backward fused into
               the BN stage of the pooled blocks)
-    gradients: half -> float cast per ~50 MB bucket in backward order, NCCL all-reduce
+    gradients: FC weights in float from their GEMM, conv weights half -> float per ~50 MB bucket in backward
+              order, NCCL all-reduce
               per bucket overlapped with the rest of backward, non-finite check,
               SGD with momentum on float master weights + half working copy
 
@@ -44,7 +45,7 @@ class ParamSlot:
     shape: tuple
     offset: int          # element offset in the flat buffers
     numel: int
-    half_grad: bool      # gradient produced in half (weights) or float (BN vectors, FC biases)
+    half_grad: bool      # gradient produced in half (conv weights) or float (FC weights and biases, BN vectors)
     stored: int = 0      # elements the slot holds (>= numel: an FC matrix keeps zero rows up to a GEMM-friendly count)
 
 
@@ -110,15 +111,18 @@ class Vgg16BnTrainer:
             return s
 
         # an FC layer's weight is stored with a row count the tensor-core GEMMs take (1000 classes -> 1024 rows,
-        # the extra rows zero); its bias and bias gradient are float (fc_op.cpp:281-347) and sit with the BN vectors
+        # the extra rows zero); its gradient is written in float, as the reference's FC_AMP_BWD does
+        # (fc_op.cpp:434-446: cublasGemmEx with a CUDA_R_32F output), so no cast pass follows it; its bias and bias
+        # gradient are float too (fc_op.cpp:281-347) and sit with the BN vectors
         self.classes_pad = _fc_width(classes)
         self.fc = []
         for j in reversed(range(3)):
             i_f, o_f = self.fc_dims[j]
-            self.fc.insert(0, dict(w=add(f"fc{j}.w", (o_f, i_f), True, rows_stored=_fc_width(o_f)), out_pad=_fc_width(o_f)))
+            self.fc.insert(0, dict(w=add(f"fc{j}.w", (o_f, i_f), False, rows_stored=_fc_width(o_f)), out_pad=_fc_width(o_f)))
+        self.half_begin = off                 # the half gradients (conv weights) start here
         for L in reversed(self.convs):
             L.w = add(f"conv{L.idx}.w", (L.k, 3, 3, L.c), True)
-        self.half_numel = off                 # everything before this offset has half gradients
+        self.half_numel = off                 # ... and end here
         for L in reversed(self.convs):
             L.gamma = add(f"bn{L.idx}.gamma", (L.k,), False)
             L.beta = add(f"bn{L.idx}.beta", (L.k,), False)
@@ -132,14 +136,14 @@ class Vgg16BnTrainer:
         self.g32 = torch.zeros(self.total, dtype=torch.float32, device=d)
         self.m32 = torch.zeros(self.total, dtype=torch.float32, device=d)
         self.w16 = torch.zeros(self.total, dtype=torch.float16, device=d)
-        self.g16 = torch.zeros(self.half_numel, dtype=torch.float16, device=d)
+        self.g16 = torch.zeros(self.half_numel - self.half_begin, dtype=torch.float16, device=d)
         self._init_params(seed)
 
         # ---- ~50 MB buckets over the flat float gradient buffer, all-reduced as backward passes them
         self.buckets = GradientBuckets(
             self.g16, self.g32, self.half_numel, bucket_bytes=bucket_mb * 1024 * 1024, group=process_group,
             cast=lambda src, dst, factor: ops.cast_f16_to_f32(src, dst, factor=factor),
-            scale=lambda t, factor: ops.scale_f32(t, factor))
+            scale=lambda t, factor: ops.scale_f32(t, factor), half_begin=self.half_begin)
 
         # ---- scalars that the reference keeps as DTensors
         self.scaling = torch.tensor([loss_scale], dtype=torch.float32, device=d)
@@ -193,6 +197,11 @@ class Vgg16BnTrainer:
     # ------------------------------------------------------------------ parameters
     def view(self, buf, slot: ParamSlot):
         return buf[slot.offset:slot.offset + slot.numel].view(slot.shape)
+
+    def half_grad(self, slot: ParamSlot):
+        """A conv weight's gradient in the half buffer (whose element 0 is flat element half_begin)."""
+        o = slot.offset - self.half_begin
+        return self.g16[o:o + slot.numel].view(slot.shape)
 
     def stored(self, buf, slot: ParamSlot):
         """The slot with the rows it is stored with (an FC matrix padded to a GEMM-friendly row count)."""
@@ -309,7 +318,7 @@ class Vgg16BnTrainer:
             f = self.fc[j]
             # the layer's input carries the ReLU + dropout of the layer below: its backward rides on the dx pass
             ops.fc_amp_bwd(dz, self.stored(self.w16, f["w"]), self.fc_in[j], dx=self.fc_dx[j],
-                           dw=self.stored(self.g16, f["w"]), db=self.stored(self.g32, f["b"]),
+                           dw=self.stored(self.g32, f["w"]), db=self.stored(self.g32, f["b"]),
                            act=self.fc_in[j] if j > 0 else None, act_scale=keep_scale, workspace=self.ws)
             dz = self.fc_dx[j]
             self.buckets.mark_ready(self._end_of(f))
@@ -329,7 +338,7 @@ class Vgg16BnTrainer:
             out = ops.cbr_amp_bwd(geo, grad, self.view(self.w16, L.w), self.view(self.w32, L.gamma),
                                   b["saved_mean"], b["saved_inv_std"], b["mask"], x, b["conv_out"],
                                   bn_scratch=self.bn_scratch[:b["conv_out"].numel()].view_as(b["conv_out"]),
-                                  dw=self.view(self.g16, L.w), first_layer=(L.idx == 0), workspace=self.ws,
+                                  dw=self.half_grad(L.w), first_layer=(L.idx == 0), workspace=self.ws,
                                   dgamma=self.view(self.g32, L.gamma), dbeta=self.view(self.g32, L.beta),
                                   pool_argmax=b["argmax"] if L.pool_after else None,   # pool backward fused in
                                   timing_events=tev)

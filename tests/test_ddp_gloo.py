@@ -37,6 +37,20 @@ def test_single_rank_is_cast_only():
     assert torch.equal(g32[:100], g16.float()) and bool((g32[100:] == 5.0).all())
 
 
+def test_single_rank_float_born_head():
+    h16 = torch.arange(40, dtype=torch.float16)
+    g32 = torch.full((130,), 5.0)
+    gb = GradientBuckets(h16, g32, 100, bucket_bytes=4 * 32, half_begin=60)
+    gb.begin_step()
+    gb.mark_ready(60)
+    assert gb.issued == [(0, 32)]
+    gb.mark_ready(100)
+    assert gb.issued == [(0, 32), (32, 64), (64, 96)]
+    gb.finish()
+    assert len(gb.issued) == 5
+    assert torch.equal(g32[60:100], h16.float()) and bool((g32[:60] == 5.0).all()) and bool((g32[100:] == 5.0).all())
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -75,6 +89,27 @@ def _worker(rank, world, port, results):
             exp[:700] += h / world
             exp[700:] += f / world
         ok_bucket = bool(torch.allclose(g32, exp, atol=1e-6))
+        # (3) the VGG16-BN driver's layout: float-born gradients first (the FC weights), then the half range, then
+        # float-born vectors; the half buffer holds the middle range only
+        gen = torch.Generator().manual_seed(10 + rank)
+        f32 = torch.randn(900, generator=gen)
+        h16 = torch.randn(400, generator=gen).half()
+        g32 = f32.clone()
+        gb = GradientBuckets(h16, g32, 700, bucket_bytes=4 * 256, half_begin=300)
+        gb.begin_step()
+        gb.mark_ready(300)               # the float-born head is complete: one whole bucket lies inside it
+        head_only = list(gb.issued)
+        gb.mark_ready(700)
+        gb.finish()
+        exp = torch.zeros(900)
+        for r in range(world):
+            gr = torch.Generator().manual_seed(10 + r)
+            f = torch.randn(900, generator=gr)
+            h = torch.randn(400, generator=gr).half().float()
+            f[300:700] = h
+            exp += f / world
+        ok_bucket = ok_bucket and bool(torch.allclose(g32, exp, atol=1e-6)) and head_only == [(0, 256)] \
+            and list(gb.issued) == [(0, 256), (256, 512), (512, 768), (768, 900)]
         results[rank] = (ok_mean, ok_bucket, issued_before_finish, list(gb.issued))
     finally:
         dist.destroy_process_group()
@@ -91,4 +126,4 @@ def test_two_ranks_gloo():
         ok_mean, ok_bucket, before, after = results[rank]
         assert ok_mean and ok_bucket
         assert before == [(0, 256), (256, 512)]
-        assert after == [(0, 256), (256, 512), (512, 760)]
+        assert after == [(0, 256), (256, 512), (512, 768), (768, 900)]
