@@ -74,7 +74,7 @@ def _fc_width(n):
 class Vgg16BnTrainer:
     def __init__(self, batch=256, image=224, classes=1000, lr=0.01, momentum=0.9, weight_decay=5e-4,
                  loss_scale=1024.0, label_smoothing=0.0, bucket_mb=50.0, seed=0, device=None,
-                 process_group=None, dropout=0.5, fc_width=4096):
+                 process_group=None, dropout=0.5, fc_width=4096, nccl_registered=None):
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.batch, self.image, self.classes = batch, image, classes
         self.lr, self.beta, self.wd = lr, momentum, weight_decay
@@ -133,7 +133,7 @@ class Vgg16BnTrainer:
 
         d = self.dev
         self.w32 = torch.zeros(self.total, dtype=torch.float32, device=d)
-        self.g32 = torch.zeros(self.total, dtype=torch.float32, device=d)
+        self.g32 = self._alloc_gradients(nccl_registered, process_group)
         self.m32 = torch.zeros(self.total, dtype=torch.float32, device=d)
         self.w16 = torch.zeros(self.total, dtype=torch.float16, device=d)
         self.g16 = torch.zeros(self.half_numel - self.half_begin, dtype=torch.float16, device=d)
@@ -197,6 +197,19 @@ class Vgg16BnTrainer:
     # ------------------------------------------------------------------ parameters
     def view(self, buf, slot: ParamSlot):
         return buf[slot.offset:slot.offset + slot.numel].view(slot.shape)
+
+    def _alloc_gradients(self, mode, group):
+        """The flat float gradient buffer.  `mode` "user" / "symm": from NCCL's own allocator and registered with the
+        communicator (a user buffer / a symmetric window), which lets NCCL's NVLink-SHARP and peer paths read and
+        write it in place; None: an ordinary allocation."""
+        if mode in ("user", "symm") and self.world > 1 and dist.get_backend(group) == "nccl":
+            backend = (group or dist.group.WORLD)._get_backend(self.dev)
+            self._nccl_pool = torch.cuda.MemPool(backend.mem_allocator)
+            with torch.cuda.use_mem_pool(self._nccl_pool):
+                g32 = torch.zeros(self.total, dtype=torch.float32, device=self.dev)
+            backend.register_mem_pool(self._nccl_pool, mode == "symm")
+            return g32
+        return torch.zeros(self.total, dtype=torch.float32, device=self.dev)
 
     def half_grad(self, slot: ParamSlot):
         """A conv weight's gradient in the half buffer (whose element 0 is flat element half_begin)."""
