@@ -13,8 +13,8 @@
 // masked in the epilogue: any extent that keeps rows 16-byte aligned (a multiple of 8 elements) is accepted.
 //
 // Roles as in conv3x3_igemm_kernel: warp 0 = producer A, warp 2 = producer B, warp 1 = MMA issuer + TMEM, warps 4-7 =
-// epilogue (thread = accumulator row: writes half rows, or float partial rows when the k range is split, 512 or
-// 1024 contiguous bytes per row).  MA = 2 keeps two 128 x 256 accumulators (512 TMEM columns) that share every B
+// epilogue (thread = accumulator row: half rows, or float rows when the k range is split or D is float, staged in
+// shared memory and written by TMA).  MA = 2 keeps two 128 x 256 accumulators (512 TMEM columns) that share every B
 // tile; MA = 1 double-buffers one so that the epilogue of a tile overlaps the next tile's MMAs.
 //
 // This file is included by conv_igemm_sm100.cu inside its anonymous namespace.
@@ -195,7 +195,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     } else if (warp >= 4) {
         // epilogue: thread = accumulator row.  Half output: 64-column chunks are rounded, staged in shared memory in
         // the 128-byte swizzle and written by TMA (whole 128-byte rows; the copy clips what hangs over the matrix).
-        // Float partials: each thread writes its row's 128-byte pieces directly.
+        // Float output (partials of a split, or a float D): the same in 32-column chunks, through a tensor map that
+        // views the float matrix as rows of twice as many 16-bit elements, with the split as third coordinate.
         const int q = warp & 3;
         const int trow = q * 32 + lane;
         const bool leader = threadIdx.x == 128;
@@ -215,23 +216,35 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
                 const int row = row0 + trow;
                 const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((kBufs == 2 ? buf : a) * kSkN);
                 if (F32OUT) {
-                    const bool row_ok = row < p.m_real;
+                    // 32 float columns of the thread's row are one 128-byte row of the staging tile
 #pragma unroll 1
-                    for (int c0 = 0; c0 < kSkN; c0 += 32) {
+                    for (int chunk = 0; chunk < kSkN / 32; ++chunk) {
+                        if (n0 + chunk * 32 >= p.n_real || row0 >= p.m_real) continue;      // block-uniform
+                        const uint32_t sbuf = epi_base + (uint32_t)(chunk_count & 1) * kATileBytes;
+                        if (leader) tma_store_wait_read<1>();
+                        named_barrier(1, kEpiThreads);
                         uint32_t v[32];
-                        tmem_ld_32x32(t0 + (uint32_t)c0, v);
+                        tmem_ld_32x32(t0 + (uint32_t)(chunk * 32), v);
                         tmem_ld_wait();
-                        if (!row_ok) continue;
-                        float* dst = static_cast<float*>(p.d) + (int64_t)split * p.split_stride + (int64_t)row * p.ldd + n0 + c0;
+                        const uint32_t row_addr = sbuf + (uint32_t)trow * 128u;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            if (n0 + c0 + 4 * j < p.n_real)
-                                reinterpret_cast<float4*>(dst)[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                                               __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                        for (int j = 0; j < 8; ++j) {
+                            const uint32_t dst = row_addr + (uint32_t)((j ^ (trow & 7)) << 4);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[4 * j]),
+                                         "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                                         : "memory");
+                        }
+                        fence_proxy_async_smem();
+                        named_barrier(1, kEpiThreads);
+                        if (leader) {
+                            tma_store_3d(&tm_d, sbuf, (n0 + chunk * 32) * 2, row0, split);
+                            tma_store_commit();
+                        }
+                        ++chunk_count;          // the staging buffers alternate per store, not per chunk
                     }
                 } else {
 #pragma unroll 1
-                    for (int chunk = 0; chunk < kSkN / 64; ++chunk, ++chunk_count) {
+                    for (int chunk = 0; chunk < kSkN / 64; ++chunk) {
                         if (n0 + chunk * 64 >= p.n_real || row0 >= p.m_real) continue;      // block-uniform
                         const uint32_t sbuf = epi_base + (uint32_t)(chunk_count & 1) * kATileBytes;
                         if (leader) tma_store_wait_read<1>();
@@ -260,13 +273,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
                             tma_store_2d(&tm_d, sbuf, n0 + chunk * 64, row0);
                             tma_store_commit();
                         }
+                        ++chunk_count;
                     }
                 }
             }
             tc_fence_before();
             mbar_arrive(tempty_bar(buf));
         }
-        if (!F32OUT && leader) tma_store_wait_all();
+        if (leader) tma_store_wait_all();
     }
 
     abort_drain(abort_flag);
@@ -303,7 +317,17 @@ int launch_skinny(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
     TRB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status));
     const int items = p.splits * p.m_tiles * p.n_tiles;
     const int grid = items < sm_count() ? items : sm_count();
-    gemm_skinny_kernel<A_MN, B_MN, MA, F32OUT><<<grid, kThreads, L::kTotal, st>>>(ta, tb, td, p, status);
+    CUtensorMap tdf;
+    if (F32OUT) {
+        // float D [split][m_real][ldd] as 16-bit elements: box = 32 floats x 128 rows of one split
+        const int64_t plane = p.split_stride ? p.split_stride : (int64_t)p.m_real * p.ldd;
+        const uint64_t dims[3] = {(uint64_t)p.n_real * 2, (uint64_t)p.m_real, (uint64_t)p.splits};
+        const uint64_t str[3] = {2, (uint64_t)p.ldd * 4, (uint64_t)plane * 4};
+        const uint32_t box[3] = {64, 128, 1};
+        const int rc = make_tmap(&tdf, p.d, 3, dims, str, box, "float D");
+        if (rc) return rc;
+    }
+    gemm_skinny_kernel<A_MN, B_MN, MA, F32OUT><<<grid, kThreads, L::kTotal, st>>>(ta, tb, F32OUT ? tdf : td, p, status);
     TRB_LAUNCH_CHECK("gemm_skinny_kernel");
     return TRB200_OK;
 }
