@@ -4,6 +4,7 @@
     python kernel_sweep.py --only block    # BASELINE.json configuration 2 (one block backward)
     python kernel_sweep.py --only bnrelu --quick
     python kernel_sweep.py --only conv --quick --batch 64 --shape 56,256,256 --what fprop_stats
+    python kernel_sweep.py --only fc                   # the classifier layers of VGG16 at batch 256
     python kernel_sweep.py --only resnet50 --cudnn     # ResNet-50 conv shapes, bfloat16
 
 Covers BASELINE.json's config 2 (Conv3x3 C=K=64 + BN + ReLU backward at N=256, 56x56)
@@ -286,9 +287,36 @@ def pool_point(t, n, h, c, hbm, src):
          bound="hbm", achieved=round(4.125 * e / med / 1e6, 1), peak=hbm, unit="GB/s",
          frac=round(4.125 * e / med / 1e6 / hbm, 4), peak_source=src)
 
+def fc_point(t, batch, in_f, out_f, hbm, src):
+    """A classifier layer at batch 256: forward (y = x.w^T + b with ReLU) and backward (dx, float dW as the
+    reference's FC_AMP_BWD writes it, db).  Both are bound by the weight matrix in HBM: the forward reads it once
+    (2 B per weight), the backward reads it once and writes the float gradient (6 B per weight)."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((batch, in_f), generator=g, device="cuda").half()
+    w = (torch.randn((out_f, in_f), generator=g, device="cuda") * (2.0 / in_f) ** 0.5).half()
+    b = torch.zeros(out_f, device="cuda")
+    dy = torch.randn((batch, out_f), generator=g, device="cuda").half()
+    y = ops.fc_amp_fwd(x, w, b, relu=True)
+    dx = torch.empty_like(x)
+    dw = torch.empty((out_f, in_f), dtype=torch.float32, device="cuda")
+    db = torch.empty(out_f, device="cuda")
+    wb = float(in_f) * out_f
+    act = 2.0 * batch * (in_f + out_f)
+    med, best = t(lambda: ops.fc_amp_fwd(x, w, b, relu=True, y=y))
+    byt = 2 * wb + act
+    emit(kernel="fc_amp_fwd (gemm_skinny_kernel + fc_bias_act_kernel)", shape=dict(batch=batch, in_features=in_f, out_features=out_f),
+         ms=round(med, 4), best_ms=round(best, 4), bound="hbm", achieved=round(byt / med / 1e6, 1), peak=hbm, unit="GB/s",
+         frac=round(byt / med / 1e6 / hbm, 4), peak_source=src)
+    med, best = t(lambda: ops.fc_amp_bwd(dy, w, x, dx=dx, dw=dw, db=db))
+    byt = 6 * wb + 2 * act
+    emit(kernel="fc_amp_bwd (dW float, dx, db)", shape=dict(batch=batch, in_features=in_f, out_features=out_f),
+         ms=round(med, 4), best_ms=round(best, 4), bound="hbm", achieved=round(byt / med / 1e6, 1), peak=hbm, unit="GB/s",
+         frac=round(byt / med / 1e6 / hbm, 4), peak_source=src)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="all", choices=["all", "block", "bnrelu", "pool", "softmax", "conv", "resnet50"])
+    ap.add_argument("--only", default="all", choices=["all", "block", "bnrelu", "pool", "softmax", "conv", "fc", "resnet50"])
     ap.add_argument("--quick", action="store_true", help="one small point per kernel (for profiler captures)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--batch", type=int, default=256, help="images for the conv / block points")
@@ -337,6 +365,9 @@ def main():
         for h, c, k in shapes:
             for what in kinds:
                 conv_point(t, n, h, c, k, what, tc, src)
+    if args.only in ("all", "fc"):
+        for in_f, out_f in ([(25088, 4096)] if args.quick else [(25088, 4096), (4096, 4096), (4096, 1024)]):
+            fc_point(t, 256, in_f, out_f, hbm, src)
     if args.only == "resnet50":
         # BASELINE.json configuration 4 at the level the hot path reaches it: the data and weight gradients of every
         # distinct convolution of ResNet-50 on bfloat16 tensors
