@@ -205,7 +205,8 @@ def run_ours(args):
 
     batch = args.batch
     tr = Vgg16BnTrainer(batch=batch, image=IMAGE, classes=CLASSES, loss_scale=1024.0, bucket_mb=args.bucket_mb,
-                        seed=1234, nccl_registered=None if args.nccl_registered == "off" else args.nccl_registered)
+                        seed=1234, nccl_registered=None if args.nccl_registered == "off" else args.nccl_registered,
+                        bucket_plan=args.bucket_plan)
     # synthetic batches in pinned host memory (two, alternated): images ~ N(0,1), 4th channel zero
     gen = torch.Generator().manual_seed(100 + rank)
     host_images, host_labels = [], []
@@ -589,6 +590,8 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU (the metric is quoted at 256)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--bucket-mb", type=float, default=50.0, help="size of a gradient all-reduce bucket")
+    ap.add_argument("--bucket-plan", default="tensors", choices=["tensors", "uniform"],
+                    help="buckets that end where a weight gradient ends (at least --bucket-mb each), or equal buckets")
     ap.add_argument("--nccl-registered", default="off", choices=["off", "user", "symm"],
                     help="gradient buffer from NCCL's allocator, registered as a user buffer / a symmetric window (N > 1)")
     ap.add_argument("--nccl-high-priority", action="store_true",

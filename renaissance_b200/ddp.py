@@ -26,13 +26,30 @@ def plan_buckets(total_elems: int, bucket_bytes: float, elem_bytes: int = 4):
     return [(a, min(a + per, total_elems)) for a in range(0, total_elems, per)]
 
 
+def plan_buckets_at(cuts, total_elems: int, bucket_bytes: float, elem_bytes: int = 4):
+    """Buckets that end only at the given element offsets (ascending; the ends of the tensors backward completes one
+    after the other), each closed as soon as it holds bucket_bytes: a tensor that becomes ready in one piece (the
+    411 MB weight gradient of VGG16's first FC layer) goes out as one collective instead of many that all start at
+    the same moment.  What follows the last cut is the final bucket."""
+    out, a = [], 0
+    for c in cuts:
+        c = min(int(c), total_elems)
+        if c > a and (c - a) * elem_bytes >= bucket_bytes:
+            out.append((a, c))
+            a = c
+    if a < total_elems:
+        out.append((a, total_elems))
+    return out
+
+
 class GradientBuckets:
     """g32: flat float gradients of everything.  Elements [half_begin, half_numel) are produced in half, in
     `g16` (whose element 0 is flat element half_begin); every other element is produced in float directly.
-    `cast` converts a half range into the float buffer times a factor; `scale` scales a float range in place."""
+    `cast` converts a half range into the float buffer times a factor; `scale` scales a float range in place.
+    `cuts`: element offsets at which a bucket may end (plan_buckets_at); None cuts equal buckets."""
 
     def __init__(self, g16, g32, half_numel, bucket_bytes=25 * 1024 * 1024, group=None, cast=None, scale=None,
-                 half_begin=0):
+                 half_begin=0, cuts=None):
         self.g16, self.g32 = g16, g32
         self.half_begin, self.half_numel = int(half_begin), int(half_numel)
         self.group = group
@@ -40,7 +57,8 @@ class GradientBuckets:
         self.world = dist.get_world_size(group) if live else 1
         # the mean: NCCL divides inside the collective; other backends (gloo) sum what was scaled beforehand
         self.native_mean = bool(live and self.world > 1 and dist.get_backend(group) == "nccl")
-        self.buckets = plan_buckets(g32.numel(), bucket_bytes)
+        self.buckets = plan_buckets(g32.numel(), bucket_bytes) if cuts is None else \
+            plan_buckets_at(cuts, g32.numel(), bucket_bytes)
         self.cast = cast or (lambda src, dst, factor: dst.copy_(src.float().mul_(factor)))
         self.scale = scale or (lambda t, factor: t.mul_(factor))
         self.next = 0

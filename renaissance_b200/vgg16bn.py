@@ -74,7 +74,7 @@ def _fc_width(n):
 class Vgg16BnTrainer:
     def __init__(self, batch=256, image=224, classes=1000, lr=0.01, momentum=0.9, weight_decay=5e-4,
                  loss_scale=1024.0, label_smoothing=0.0, bucket_mb=50.0, seed=0, device=None,
-                 process_group=None, dropout=0.5, fc_width=4096, nccl_registered=None):
+                 process_group=None, dropout=0.5, fc_width=4096, nccl_registered=None, bucket_plan="tensors"):
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.batch, self.image, self.classes = batch, image, classes
         self.lr, self.beta, self.wd = lr, momentum, weight_decay
@@ -143,7 +143,11 @@ class Vgg16BnTrainer:
         self.buckets = GradientBuckets(
             self.g16, self.g32, self.half_numel, bucket_bytes=bucket_mb * 1024 * 1024, group=process_group,
             cast=lambda src, dst, factor: ops.cast_f16_to_f32(src, dst, factor=factor),
-            scale=lambda t, factor: ops.scale_f32(t, factor), half_begin=self.half_begin)
+            scale=lambda t, factor: ops.scale_f32(t, factor), half_begin=self.half_begin,
+            # "tensors": a bucket ends only where a weight gradient ends (each is ready in one piece), as soon as it
+            # holds bucket_mb; "uniform": equal buckets of bucket_mb
+            cuts=[s_.offset + _align(s_.stored) for s_ in slots if s_.offset < self.half_numel]
+            if bucket_plan == "tensors" else None)
 
         # ---- scalars that the reference keeps as DTensors
         self.scaling = torch.tensor([loss_scale], dtype=torch.float32, device=d)

@@ -10,7 +10,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from renaissance_b200.ddp import GradientBuckets, plan_buckets
+from renaissance_b200.ddp import GradientBuckets, plan_buckets, plan_buckets_at
 
 
 def test_plan_buckets_covers_range_once():
@@ -21,6 +21,17 @@ def test_plan_buckets_covers_range_once():
     # VGG16-BN: 138.4 M parameters in 25 MB float buckets
     big = plan_buckets(138_365_992, 25 * 1024 * 1024)
     assert len(big) == 22 and big[-1][1] == 138_365_992 and all(e - s <= 6_553_600 for s, e in big)
+
+
+def test_plan_buckets_at_tensor_ends():
+    # buckets end only at the cuts, as soon as they hold the size asked for; the rest is the final bucket
+    assert plan_buckets_at([100, 150, 1000, 1040, 1100], 1200, 4 * 120) == [(0, 150), (150, 1000), (1000, 1200)]
+    assert plan_buckets_at([100, 200], 200, 4 * 1000) == [(0, 200)]
+    assert plan_buckets_at([], 50, 4) == [(0, 50)]
+    assert plan_buckets_at([10, 20, 30], 30, 4 * 10) == [(0, 10), (10, 20), (20, 30)]
+    g32 = torch.zeros(1200)
+    gb = GradientBuckets(torch.zeros(0, dtype=torch.float16), g32, 0, bucket_bytes=4 * 120, cuts=[100, 150, 1000])
+    assert gb.buckets == [(0, 150), (150, 1000), (1000, 1200)]
 
 
 def test_single_rank_is_cast_only():
