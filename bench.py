@@ -8,8 +8,8 @@
 
 One step = forward + backward + gradient all-reduce + SGD-momentum of VGG16-BN on a
 synthetic batch of 256 images per GPU (NHWC half, 224x224x3 padded to 4 channels,
-N(0,1); labels uniform in 0..999; random-init weights), loss scale 1024, 50 MB
-gradient buckets.  Prints ONE JSON line (rank 0).
+N(0,1); labels uniform in 0..999; random-init weights), loss scale 1024, gradient
+buckets of 50 MB or more that end at tensor ends.  Prints ONE JSON line (rank 0).
 """
 from __future__ import annotations
 
@@ -380,7 +380,7 @@ def run_ours(args):
                     ms_per_step=round(ms_per_step, 3), higher_is_better=True, scaling="weak", vs_baseline=None,
                     dtype="fp16", data="synthetic",
                     config=dict(workload="VGG16-BN AMP fwd+bwd+allreduce+SGD-momentum, NHWC 224x224x3(+1 pad), "
-                                         "batch 256/GPU, loss scale 1024, %g MB buckets" % args.bucket_mb,
+                                         "batch 256/GPU, loss scale 1024, %g MB buckets (%s)" % (args.bucket_mb, args.bucket_plan),
                                 global_batch=world * batch, parallelism=f"dp{world}",
                                 l2="activations (>15 GB per step) far exceed the 126 MB L2; no flush needed",
                                 conv_tflop_per_step_per_gpu=round(conv_flops_per_step(batch) / 1e12, 2),

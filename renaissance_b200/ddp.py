@@ -4,8 +4,9 @@ The reference reduces two fixed region ranges with one in-place FP32 ncclAllRedu
 each and scales by 1/world afterwards (src/backend/ops/range/allreduce_op.cpp:37-105,
 buckets at src/graph/compiler.cpp:1836-1847); only the first is overlapped with
 compute.  Here the flat float gradient buffer is laid out in the order in which
-backward completes its parameters and is cut into buckets (25 MB unless the caller
-says otherwise; the VGG16-BN driver uses 50 MB); a bucket's half gradients are
+backward completes its parameters and is cut into buckets (equal ones of 25 MB unless
+the caller says otherwise; the VGG16-BN driver ends them at tensor ends, 50 MB or more
+each); a bucket's half gradients are
 cast half -> float (the reference's RANGE_CAST_FP16_TO_FP32) and the bucket is handed
 to NCCL as soon as backward has passed its end, so the collective runs under the
 remaining backward kernels.  The wire format stays FP32 and the reduction is NCCL's

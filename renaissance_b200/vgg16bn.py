@@ -10,8 +10,8 @@ reference's ``DeepLearningTask::run_train_epoch_gpu`` plays
               FC 25088-4096-4096-1000 with ReLU + dropout, softmax-CE
     backward: softmax-CE, FC, 13 x CBR_AMP_BWD (first layer without dgrad; max-pool backward fused into
               the BN stage of the pooled blocks)
-    gradients: FC weights in float from their GEMM, conv weights half -> float per ~50 MB bucket in backward
-              order, NCCL all-reduce
+    gradients: FC weights in float from their GEMM, conv weights half -> float per bucket (>= 50 MB, ending at
+              tensor ends) in backward order, NCCL all-reduce
               per bucket overlapped with the rest of backward, non-finite check,
               SGD with momentum on float master weights + half working copy
 
@@ -139,7 +139,7 @@ class Vgg16BnTrainer:
         self.g16 = torch.zeros(self.half_numel - self.half_begin, dtype=torch.float16, device=d)
         self._init_params(seed)
 
-        # ---- ~50 MB buckets over the flat float gradient buffer, all-reduced as backward passes them
+        # ---- buckets over the flat float gradient buffer, all-reduced as backward passes them
         self.buckets = GradientBuckets(
             self.g16, self.g32, self.half_numel, bucket_bytes=bucket_mb * 1024 * 1024, group=process_group,
             cast=lambda src, dst, factor: ops.cast_f16_to_f32(src, dst, factor=factor),
