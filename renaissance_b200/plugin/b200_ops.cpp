@@ -324,7 +324,8 @@ void launch_fc_amp_bwd_b200(const GraphNode& node, const MemoryPlan& mp, const D
 // sum over the ranks with NCCL on the UPDATE stream, over each (start region, end region) byte span of the node,
 // followed for the mean flavours by the 1/world scale (trb200_scale_f32 = tr_scale_fp32_kernel).  The collective
 // stays NCCL's; how many spans a step has, and therefore how much of it overlaps with backward, is the graph
-// builder's choice (the reference cuts two, compiler.cpp:1836-1847; 25-50 MB spans in backward order overlap almost fully).
+// builder's choice (the reference cuts two, compiler.cpp:1836-1847; spans of 50 MB or more that end at tensor ends, in backward
+// order, overlap almost fully).
 void launch_allreduce_b200(const GraphNode& node, const MemoryPlan& mp, const DeviceContext& ctx,
                            MultiStreamCaptureState& state) {
     cudaStream_t s = static_cast<cudaStream_t>(ctx.stream(StreamKind::UPDATE));
